@@ -1,0 +1,198 @@
+/*
+ * lmoe.h -- C ABI of liblmoe.so: the LatentMoE feed-forward hot path on NVIDIA B200 (sm_100a).
+ *
+ * The reference (Orolol/swamla) has no native boundary for this path: its layer is Python
+ * (models/moe.py: LatentMoELayer) calling two Triton entry points (models/moe_triton.py).  This
+ * header is the boundary a host binds instead; each entry point names the reference lines it
+ * replaces.  Conventions shared by all entry points:
+ *
+ *   - plain pointers and sizes only; every data pointer is a DEVICE pointer of the current
+ *     device, 16-byte aligned; `stream` is a cudaStream_t passed as void*;
+ *   - the caller owns every buffer (inputs, outputs, workspace); the library never allocates or
+ *     frees device memory and keeps nothing between calls;
+ *   - all calls are stream-ordered and never synchronise;
+ *   - return value: 0 = OK; <0 = argument / shape / alignment error found on the host before any
+ *     launch (see lmoe_status_string); >0 = a cudaError_t from a launch;
+ *   - `status` is one device int32 the kernels write when a bounded wait inside a kernel gives up
+ *     (0 = no anomaly); the host may read it lazily;
+ *   - bf16 = 16-bit brain float; "rows are padded": routed rows are laid out expert by expert,
+ *     each expert's segment rounded up to a multiple of LMOE_ROW_PAD rows, pad rows zero.
+ *
+ * Shapes (names follow the reference ctor, models/moe.py:625-700):
+ *   T tokens, D = n_embd, L = latent_dim, E = routed experts as built (n_experts*latent_ratio),
+ *   K = activated experts as built, F = routed expert hidden dim, Fs = shared expert hidden dim.
+ */
+#ifndef LMOE_H_
+#define LMOE_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define LMOE_VERSION 1
+#define LMOE_ROW_PAD 128
+#define LMOE_MAX_EXPERTS 256
+#define LMOE_MAX_TOPK 32
+
+/* error codes (<0) */
+#define LMOE_OK 0
+#define LMOE_ERR_ARG (-1)        /* null pointer / bad enum */
+#define LMOE_ERR_SHAPE (-2)      /* unsupported dimension */
+#define LMOE_ERR_ALIGN (-3)      /* pointer or leading dimension not 16-byte aligned */
+#define LMOE_ERR_WORKSPACE (-4)  /* workspace too small */
+#define LMOE_ERR_DRIVER (-5)     /* tensor-map encode entry point unavailable / failed */
+
+/* element types */
+#define LMOE_BF16 0
+#define LMOE_F32 1
+#define LMOE_E4M3 2
+
+typedef struct lmoe_shape {
+  int32_t T, D, L, E, K, F, Fs;
+  int32_t n_shared;
+} lmoe_shape;
+
+/* Routing tables produced by lmoe_route_permute, all int32, caller-allocated.
+ *   counts[E], offsets[E+1], perm[T*K]   canonical (unpadded) result, = models/moe_triton.py:36-78
+ *   pad_offsets[E+1]                      start row of each expert in the padded layout
+ *   pos[T*K]                              flat index t*K+k -> padded row
+ *   row_src[lmoe_padded_rows]             padded row -> flat index, -1 for pad rows
+ *   tile_expert[lmoe_padded_rows/128]     expert owning each 128-row tile
+ *   n_tiles[1]                            number of 128-row tiles in use
+ */
+typedef struct lmoe_route {
+  int32_t* counts;
+  int32_t* offsets;
+  int32_t* perm;
+  int32_t* pad_offsets;
+  int32_t* pos;
+  int32_t* row_src;
+  int32_t* tile_expert;
+  int32_t* n_tiles;
+} lmoe_route;
+
+/* ---- misc ---- */
+int lmoe_version(void);
+const char* lmoe_status_string(int code);
+/* Upper bound of padded routed rows for a shape: roundup(T*K,128) + E*128. */
+int64_t lmoe_padded_rows(const lmoe_shape* s);
+/* Bytes of scratch lmoe_route_permute needs (block histograms). */
+size_t lmoe_route_workspace_bytes(const lmoe_shape* s);
+
+/* ---- generic dense GEMM on tcgen05 (building block; also the unit-test hook) ----
+ * C[M,N] = A[M,K] * B[N,K]^T with fp32 accumulation in tensor memory.
+ *   a_mn = 0: A stored [M,K] row-major (lda = row stride);  a_mn = 1: A stored [K,M] row-major.
+ *   b_mn = 0: B stored [N,K] row-major (an nn.Linear weight); b_mn = 1: B stored [K,N] row-major.
+ *   c_type: LMOE_BF16 or LMOE_F32.  split_k > 1 requires c_type = LMOE_F32 and ADDS into C.
+ * Replaces the cuBLAS calls behind nn.Linear on this path (models/moe.py:63,69,217,722,728). */
+int lmoe_gemm_bf16(int M, int N, int K, const void* A, int64_t lda, int a_mn, const void* B, int64_t ldb, int b_mn,
+                   void* C, int64_t ldc, int c_type, int split_k, int32_t* status, void* stream);
+
+/* ---- forward ---- */
+
+/* Gate logits (fp32) and latent down-projection (bf16) from one read of x.
+ * x[T,D] bf16, w_gate[E,D] bf16, w_down[L,D] bf16 -> logits[T,E] f32, x_latent[T,L] bf16.
+ * Replaces models/moe.py:217 (router.gate) and models/moe.py:722 (down_proj). */
+int lmoe_xproj_fwd(const lmoe_shape* s, const void* x, const void* w_gate, const void* w_down, float* logits,
+                   void* x_latent, int32_t* status, void* stream);
+
+/* Sigmoid affinity + bias, canonical top-K (higher score first, lower expert index on ties),
+ * normalised gating weights, per-row logsumexp and the z-loss.
+ * logits[T,E] f32, expert_bias[E] f32 -> sel[T,K] i32, weights[T,K] f32, lse[T] f32,
+ * z_loss[1] f32 = z_coef * mean(lse^2).  z_partial: scratch of ceil(T/8) floats.
+ * Replaces models/moe.py:220-233 (AuxLossFreeRouter.forward). */
+int lmoe_gate_topk_fwd(const lmoe_shape* s, const float* logits, const float* expert_bias, float z_coef, int32_t* sel,
+                       float* weights, float* lse, float* z_partial, float* z_loss, void* stream);
+
+/* Histogram, exclusive scan and stable permutation of the flat expert ids; also the padded
+ * layout tables.  Deterministic (no global atomics).  Replaces models/moe_triton.py:12-78. */
+int lmoe_route_permute(const lmoe_shape* s, const int32_t* sel, const lmoe_route* r, void* workspace,
+                       size_t workspace_bytes, void* stream);
+
+/* Routed experts: gather x_latent rows into the padded layout, grouped gate_up GEMM with SwiGLU
+ * epilogue, grouped down GEMM.
+ * x_latent[T,L] bf16, w_gate_up[E,L,2F] bf16, w_down[E,F,L] bf16 ->
+ * x_sorted[P,L], h1[P,2F], hidden[P,F], y_sorted[P,L] (all bf16, P = lmoe_padded_rows).
+ * Replaces models/moe.py:762-766 (expand + gather), 814 (moe_gemm #1), 822-823 (SwiGLU),
+ * 828 (moe_gemm #2) and models/moe_triton.py:85-242. */
+int lmoe_experts_fwd(const lmoe_shape* s, const void* x_latent, const void* w_gate_up, const void* w_down,
+                     const lmoe_route* r, void* x_sorted, void* h1, void* hidden, void* y_sorted, int32_t* status,
+                     void* stream);
+
+/* Shared expert, first half: h1_s = x * w_gate_up_s^T, hidden_s = silu(gate) * up.
+ * x[T,D], w_gate_up_s[2Fs,D] -> h1_s[T,2Fs], hidden_s[T,Fs] (bf16).
+ * Replaces models/moe.py:63-67 (SwiGLUExpert.forward). */
+int lmoe_shared_gateup_fwd(const lmoe_shape* s, const void* x, const void* w_gate_up_s, void* h1_s, void* hidden_s,
+                           int32_t* status, void* stream);
+
+/* Weighted combine, latent up-projection, shared down-projection and the final add:
+ *   routed[t] = sum_k weights[t,k] * y_sorted[pos[t*K+k]]
+ *   y = hidden_s * w_down_s^T + routed * w_up^T
+ * -> routed[T,L] bf16, y[T,D] bf16.
+ * Replaces models/moe.py:837, 778-782 (scatter + sum), 728 (up_proj), 69 (shared down_proj), 731. */
+int lmoe_combine_out_fwd(const lmoe_shape* s, const void* y_sorted, const lmoe_route* r, const float* weights,
+                         const void* hidden_s, const void* w_down_s, const void* w_up, void* routed, void* y,
+                         int32_t* status, void* stream);
+
+/* ---- backward (adjoints of the lines cited above; the reference defines them only through
+ *      autograd, and not at all for its grouped GEMM) ---- */
+
+/* dgrad of the output stage: d_routed[T,L] = dy * w_up, d_hidden_s[T,Fs] = dy * w_down_s. */
+int lmoe_combine_out_bwd_dgrad(const lmoe_shape* s, const void* dy, const void* w_up, const void* w_down_s,
+                               void* d_routed, void* d_hidden_s, int32_t* status, void* stream);
+/* wgrad of the output stage (ADDS into fp32): d_w_up[D,L] += dy^T routed, d_w_down_s[D,Fs] += dy^T hidden_s. */
+int lmoe_combine_out_bwd_wgrad(const lmoe_shape* s, const void* dy, const void* routed, const void* hidden_s,
+                               float* d_w_up, float* d_w_down_s, int32_t* status, void* stream);
+/* Adjoint of the weighted combine, in the padded layout:
+ *   d_y_sorted[row] = weights[t,k] * d_routed[t];  d_weights[t,k] = <d_routed[t], y_sorted[row]>. */
+int lmoe_combine_bwd(const lmoe_shape* s, const void* d_routed, const void* y_sorted, const float* weights,
+                     const lmoe_route* r, void* d_y_sorted, float* d_weights, void* stream);
+/* SwiGLU adjoint: h1[R,2H] (gate | up), d_hidden[R,H] -> d_h1[R,2H]; rows = R.  If n_rows_dev is
+ * non-null the row count is read on the device as 128 * n_rows_dev[0] (padded routed rows). */
+int lmoe_swiglu_bwd(int64_t rows, int H, const void* h1, const void* d_hidden, void* d_h1, const int32_t* n_tiles_dev,
+                    void* stream);
+/* Routed dgrads: d_hidden = d_y_sorted * w_down[e]^T, d_h1 = swiglu'(h1, d_hidden),
+ * d_x_sorted = d_h1 * w_gate_up[e]^T.  All in the padded layout. */
+int lmoe_experts_bwd_dgrad(const lmoe_shape* s, const void* d_y_sorted, const void* h1, const void* w_gate_up,
+                           const void* w_down, const lmoe_route* r, void* d_hidden, void* d_h1, void* d_x_sorted,
+                           int32_t* status, void* stream);
+/* Routed wgrads (overwrite, bf16): d_w_gate_up[e] = x_sorted[rows_e]^T d_h1[rows_e],
+ * d_w_down[e] = hidden[rows_e]^T d_y_sorted[rows_e]. */
+int lmoe_experts_bwd_wgrad(const lmoe_shape* s, const void* x_sorted, const void* d_h1, const void* hidden,
+                           const void* d_y_sorted, const lmoe_route* r, void* d_w_gate_up, void* d_w_down,
+                           int32_t* status, void* stream);
+/* Adjoint of the gather: d_x_latent[t] = sum_k d_x_sorted[pos[t*K+k]]. */
+int lmoe_unpermute_sum_bwd(const lmoe_shape* s, const void* d_x_sorted, const lmoe_route* r, void* d_x_latent,
+                           void* stream);
+/* Router adjoint: gating-weight gradient through the normalisation and the sigmoid, plus the
+ * z-loss term d_z * z_coef * 2 * lse * softmax / T (d_z: device float or NULL) -> d_logits[T,E] bf16. */
+int lmoe_gate_topk_bwd(const lmoe_shape* s, const float* logits, const int32_t* sel, const float* weights,
+                       const float* d_weights, const float* lse, const float* d_z, float z_coef, void* d_logits,
+                       void* stream);
+/* Shared expert dgrad chain is lmoe_swiglu_bwd on (h1_s, d_hidden_s); its wgrad (ADDS, fp32):
+ * d_w_gate_up_s[2Fs,D] += d_h1_s^T x. */
+int lmoe_shared_gateup_bwd_wgrad(const lmoe_shape* s, const void* d_h1_s, const void* x, float* d_w_gate_up_s,
+                                 int32_t* status, void* stream);
+/* dx[T,D] = d_h1_s * w_gate_up_s + d_x_latent * w_down + d_logits * w_gate (one GEMM, three K segments);
+ * wgrads (ADD, fp32): d_w_down[L,D] += d_x_latent^T x, d_w_gate[E,D] += d_logits^T x. */
+int lmoe_xproj_bwd(const lmoe_shape* s, const void* d_h1_s, const void* d_x_latent, const void* d_logits,
+                   const void* w_gate_up_s, const void* w_down, const void* w_gate, const void* x, void* dx,
+                   float* d_w_down, float* d_w_gate, int32_t* status, void* stream);
+
+/* ---- router bias update (after backward) ----
+ * load = histogram(sel) (= counts); bias -= gamma * sign(load - T*K/E); history = .99 history + .01 load.
+ * Replaces models/moe.py:254-275. */
+int lmoe_router_bias_update(const lmoe_shape* s, const int32_t* counts, float gamma, float* expert_bias,
+                            float* load_history, void* stream);
+
+/* ---- small utilities ---- */
+int lmoe_cast_f32_to_bf16(const float* src, void* dst, int64_t n, void* stream);
+int lmoe_cast_bf16_to_f32(const void* src, float* dst, int64_t n, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* LMOE_H_ */

@@ -1,0 +1,224 @@
+// Host launcher of the tcgen05 GEMM: tensor-map encoding, template dispatch, grid sizing.
+#include <cuda.h>
+#include <cuda_runtime.h>
+
+#include <mutex>
+
+#include "../../include/lmoe.h"
+#include "gemm.cuh"
+#include "gemm_host.h"
+
+namespace lmoe {
+
+// ---------------------------------------------------------------- driver entry point
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  static std::once_flag once;
+  std::call_once(once, [] {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+        q == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeTiledFn>(p);
+  });
+  return fn;
+}
+
+int num_sms() {
+  static int n = 0;
+  if (n == 0) {
+    int dev = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev);
+    if (n <= 0) n = 148;
+  }
+  return n;
+}
+
+// 2-D map over a row-major [outer, inner] tensor of 16-bit elements, 128-byte swizzle.
+static int encode_2d(CUtensorMap* map, const void* base, long long inner, long long outer, long long ld_elems,
+                     int box_inner, int box_outer) {
+  EncodeTiledFn fn = encode_fn();
+  if (!fn) return LMOE_ERR_DRIVER;
+  if ((reinterpret_cast<uintptr_t>(base) & 15) != 0 || ((ld_elems * 2) & 15) != 0) return LMOE_ERR_ALIGN;
+  if (inner <= 0 || outer <= 0 || box_inner * 2 > 128 || box_outer > 256) return LMOE_ERR_SHAPE;
+  cuuint64_t dims[2] = {static_cast<cuuint64_t>(inner), static_cast<cuuint64_t>(outer)};
+  cuuint64_t strides[1] = {static_cast<cuuint64_t>(ld_elems) * 2};
+  cuuint32_t box[2] = {static_cast<cuuint32_t>(box_inner), static_cast<cuuint32_t>(box_outer)};
+  cuuint32_t estr[2] = {1, 1};
+  CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, estr,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? 0 : LMOE_ERR_DRIVER;
+}
+
+// ---------------------------------------------------------------- dispatch
+template <bool A_MN, bool B_MN, int BN, int EPI, int GRP>
+static int launch_inst(const GemmParams& p, int grid, cudaStream_t stream) {
+  auto kfn = gemm_kernel<A_MN, B_MN, BN, EPI, GRP>;
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(kfn, cudaFuncAttributeMaxDynamicSharedMemorySize, GemmSmem<BN>::kTotal);
+    if (e != cudaSuccess) return static_cast<int>(e);
+    configured = true;
+  }
+  kfn<<<grid, kGemmThreads, GemmSmem<BN>::kTotal, stream>>>(p);
+  cudaError_t e = cudaGetLastError();
+  return e == cudaSuccess ? 0 : static_cast<int>(e);
+}
+
+#define LMOE_KEY(am, bm, bn256, epi, grp) ((am) | ((bm) << 1) | ((bn256) << 2) | ((epi) << 3) | ((grp) << 6))
+#define LMOE_CASE(am, bm, bn, epi, grp)          \
+  case LMOE_KEY(am, bm, (bn == 256), epi, grp):  \
+    return launch_inst<(am != 0), (bm != 0), bn, epi, grp>(p, grid, stream);
+#define LMOE_CASE_BN(am, bm, epi, grp) LMOE_CASE(am, bm, 128, epi, grp) LMOE_CASE(am, bm, 256, epi, grp)
+#define LMOE_CASE_MAJORS(epi, grp) \
+  LMOE_CASE_BN(0, 0, epi, grp) LMOE_CASE_BN(0, 1, epi, grp) LMOE_CASE_BN(1, 0, epi, grp) LMOE_CASE_BN(1, 1, epi, grp)
+
+static int dispatch(const GemmCall& c, int bn, const GemmParams& p, int grid, cudaStream_t stream) {
+  switch (LMOE_KEY(c.a_mn, c.b_mn, (bn == 256), c.epi, c.grp)) {
+    // dense
+    LMOE_CASE_MAJORS(EPI_BF16, GRP_NONE)
+    LMOE_CASE_MAJORS(EPI_F32, GRP_NONE)
+    LMOE_CASE_MAJORS(EPI_F32_ATOMIC, GRP_NONE)
+    LMOE_CASE_BN(0, 0, EPI_SWIGLU, GRP_NONE)
+    // grouped over rows (routed forward and dgrads)
+    LMOE_CASE_BN(0, 1, EPI_SWIGLU, GRP_M)
+    LMOE_CASE_BN(0, 1, EPI_BF16, GRP_M)
+    LMOE_CASE_BN(0, 0, EPI_BF16, GRP_M)
+    // grouped over the contraction (routed wgrads)
+    LMOE_CASE_BN(1, 1, EPI_BF16, GRP_K)
+    default:
+      return LMOE_ERR_ARG;
+  }
+}
+
+int launch_gemm(const GemmCall& c) {
+  if (c.nseg < 1 || c.nseg > 3 || !c.C || c.M <= 0 || c.N <= 0) return LMOE_ERR_ARG;
+  if (c.split_k > 1 && (c.epi != EPI_F32_ATOMIC || c.nseg != 1 || c.grp != GRP_NONE)) return LMOE_ERR_ARG;
+  const bool swiglu = (c.epi == EPI_SWIGLU);
+  if ((c.N & 7) != 0) return LMOE_ERR_SHAPE;
+  const int elem_c = (c.epi == EPI_F32 || c.epi == EPI_F32_ATOMIC) ? 4 : 2;
+  if ((reinterpret_cast<uintptr_t>(c.C) & 15) != 0 || ((c.ldc * elem_c) & 15) != 0) return LMOE_ERR_ALIGN;
+  if (swiglu && (!c.C2 || (reinterpret_cast<uintptr_t>(c.C2) & 15) != 0 || ((c.ldc2 * 2) & 15) != 0))
+    return LMOE_ERR_ALIGN;
+
+  GemmParams p;
+  memset(&p, 0, sizeof(p));
+  // ---- tile geometry ----
+  const int sms = num_sms();
+  const long long rows_total = (c.grp == GRP_M) ? c.padded_rows : c.M;
+  const int m_tiles = static_cast<int>((rows_total + kBM - 1) / kBM);
+  int bn = c.bn;
+  if (bn == 0) {
+    // N per tile: BN for plain epilogues, BN/2 output columns for SwiGLU (gate + up accumulators)
+    const int n_eff = swiglu ? 2 * c.N : c.N;
+    const long long tiles256 = static_cast<long long>(m_tiles) * ((n_eff + 255) / 256) * (c.grp == GRP_K ? c.groups : 1) *
+                               (c.split_k > 1 ? c.split_k : 1);
+    bn = (n_eff >= 256 && tiles256 >= sms) ? 256 : 128;
+  }
+  if (bn != 128 && bn != 256) return LMOE_ERR_ARG;
+  const int n_per_tile = swiglu ? bn / 2 : bn;
+  const int n_tiles = (c.N + n_per_tile - 1) / n_per_tile;
+
+  // ---- tensor maps ----
+  for (int s = 0; s < c.nseg; ++s) {
+    if (!c.A[s] || !c.B[s]) return LMOE_ERR_ARG;
+    int rc;
+    if (c.grp == GRP_K) {
+      // both operands are [padded rows, extent] row-major and contract over rows
+      if (!c.a_mn || !c.b_mn) return LMOE_ERR_ARG;
+      rc = encode_2d(&p.tmA[s], c.A[s], c.M, c.padded_rows, c.lda[s], 64, 64);
+      if (rc) return rc;
+      rc = encode_2d(&p.tmB[s], c.B[s], c.N, c.padded_rows, c.ldb[s], 64, 64);
+      if (rc) return rc;
+      p.seg_kiters[s] = 0;
+      continue;
+    }
+    const int K = c.Kseg[s];
+    if (K <= 0) return LMOE_ERR_SHAPE;
+    p.seg_kiters[s] = (K + kBK - 1) / kBK;
+    // A
+    if (!c.a_mn)
+      rc = encode_2d(&p.tmA[s], c.A[s], K, rows_total, c.lda[s], 64, kBM);
+    else
+      rc = encode_2d(&p.tmA[s], c.A[s], c.M, K, c.lda[s], 64, 64);
+    if (rc) return rc;
+    // B
+    const int n_b_total = swiglu ? 2 * c.N : c.N;  // columns (or rows) of B addressed by this GEMM
+    if (c.grp == GRP_M) {
+      if ((K % kBK) != 0 || c.groups <= 0 || c.b_group_rows <= 0) return LMOE_ERR_SHAPE;
+      const long long outer = static_cast<long long>(c.groups) * c.b_group_rows;
+      if (!c.b_mn)
+        rc = encode_2d(&p.tmB[s], c.B[s], K, outer, c.ldb[s], 64, swiglu ? bn / 2 : bn);
+      else
+        rc = encode_2d(&p.tmB[s], c.B[s], n_b_total, outer, c.ldb[s], 64, 64);
+    } else {
+      if (!c.b_mn)
+        rc = encode_2d(&p.tmB[s], c.B[s], K, n_b_total, c.ldb[s], 64, swiglu ? bn / 2 : bn);
+      else
+        rc = encode_2d(&p.tmB[s], c.B[s], n_b_total, K, c.ldb[s], 64, 64);
+    }
+    if (rc) return rc;
+  }
+
+  p.nseg = c.nseg;
+  p.M = c.M;
+  p.N = c.N;
+  p.m_tiles = m_tiles;
+  p.n_tiles = n_tiles;
+  p.groups = c.groups;
+  p.split_k = c.split_k > 1 ? c.split_k : 1;
+  p.C = c.C;
+  p.ldc = c.ldc;
+  p.c_group_stride = c.c_group_stride;
+  p.C2 = c.C2;
+  p.ldc2 = c.ldc2;
+  p.half = c.N;
+  p.tile_expert = c.tile_expert;
+  p.n_m_tiles = c.n_m_tiles;
+  p.b_group_rows = c.b_group_rows;
+  p.pad_offsets = c.pad_offsets;
+  p.status = c.status;
+  if (c.grp == GRP_M && (!c.tile_expert || !c.n_m_tiles)) return LMOE_ERR_ARG;
+  if (c.grp == GRP_K && (!c.pad_offsets || c.groups <= 0)) return LMOE_ERR_ARG;
+
+  long long total = static_cast<long long>(m_tiles) * n_tiles;
+  if (c.grp == GRP_NONE) total *= p.split_k;
+  if (c.grp == GRP_K) total *= c.groups;
+  const int grid = static_cast<int>(total < sms ? total : sms);
+  return dispatch(c, bn, p, grid, c.stream);
+}
+
+}  // namespace lmoe
+
+// ---------------------------------------------------------------- C ABI
+extern "C" int lmoe_gemm_bf16(int M, int N, int K, const void* A, int64_t lda, int a_mn, const void* B, int64_t ldb,
+                              int b_mn, void* C, int64_t ldc, int c_type, int split_k, int32_t* status, void* stream) {
+  using namespace lmoe;
+  if (!A || !B || !C || M <= 0 || N <= 0 || K <= 0) return LMOE_ERR_ARG;
+  if (c_type != LMOE_BF16 && c_type != LMOE_F32) return LMOE_ERR_ARG;
+  if (split_k > 1 && c_type != LMOE_F32) return LMOE_ERR_ARG;
+  GemmCall c;
+  c.a_mn = a_mn ? 1 : 0;
+  c.b_mn = b_mn ? 1 : 0;
+  c.epi = (split_k > 1) ? EPI_F32_ATOMIC : (c_type == LMOE_F32 ? EPI_F32 : EPI_BF16);
+  c.grp = GRP_NONE;
+  c.A[0] = A;
+  c.lda[0] = lda;
+  c.B[0] = B;
+  c.ldb[0] = ldb;
+  c.Kseg[0] = K;
+  c.M = M;
+  c.N = N;
+  c.C = C;
+  c.ldc = ldc;
+  c.split_k = split_k;
+  c.status = status;
+  c.stream = static_cast<cudaStream_t>(stream);
+  return launch_gemm(c);
+}

@@ -1,0 +1,46 @@
+// Host-side description of one launch of the tcgen05 GEMM kernel (internal to the library).
+#pragma once
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+namespace lmoe {
+
+struct GemmCall {
+  // operand layout
+  int a_mn = 0, b_mn = 0;  // 0 = K-major, 1 = MN-major
+  int epi = 0;             // EPI_*
+  int grp = 0;             // GRP_*
+  int bn = 0;              // 0 = choose; else 128 or 256
+  // up to three K segments accumulated into the same output tile
+  int nseg = 1;
+  const void* A[3] = {nullptr, nullptr, nullptr};
+  long long lda[3] = {0, 0, 0};  // elements
+  const void* B[3] = {nullptr, nullptr, nullptr};
+  long long ldb[3] = {0, 0, 0};
+  int Kseg[3] = {0, 0, 0};  // contraction extent per segment (GRP_K: unused)
+  // output
+  int M = 0, N = 0;  // per group for GRP_K; for EPI_SWIGLU N = width of one half
+  void* C = nullptr;
+  long long ldc = 0;
+  long long c_group_stride = 0;
+  void* C2 = nullptr;
+  long long ldc2 = 0;
+  int split_k = 1;
+  // grouping
+  long long padded_rows = 0;         // GRP_M / GRP_K: rows of the padded routed layout (upper bound)
+  int groups = 0;                    // number of experts
+  int b_group_rows = 0;              // GRP_M: rows of stacked B per expert
+  long long b_inner = 0;             // GRP_M: inner extent of stacked B (K for K-major, N_total for MN-major)
+  const int* tile_expert = nullptr;  // GRP_M
+  const int* n_m_tiles = nullptr;    // GRP_M
+  const int* pad_offsets = nullptr;  // GRP_K
+  int* status = nullptr;
+  cudaStream_t stream = nullptr;
+};
+
+// Returns 0, a negative LMOE_ERR_* code, or a positive cudaError_t.
+int launch_gemm(const GemmCall& c);
+
+int num_sms();
+
+}  // namespace lmoe

@@ -1,0 +1,310 @@
+// Stage-level C-ABI entry points of the LatentMoE path, assembled from the tcgen05 GEMM launcher
+// and the row kernels.  Host code only: argument checks, GEMM descriptions, launches.
+#include <cuda_runtime.h>
+
+#include "../../include/lmoe.h"
+#include "gemm.cuh"
+#include "gemm_host.h"
+#include "rowops.h"
+
+using namespace lmoe;
+
+namespace {
+
+int check_dims(const lmoe_shape* s) {
+  if (!s) return LMOE_ERR_ARG;
+  if (s->T <= 0 || s->D <= 0 || s->L <= 0 || s->E <= 0 || s->K <= 0 || s->F <= 0 || s->Fs <= 0) return LMOE_ERR_SHAPE;
+  if (s->E > LMOE_MAX_EXPERTS || s->K > LMOE_MAX_TOPK || s->K > s->E) return LMOE_ERR_SHAPE;
+  // L and F are contraction extents of grouped GEMMs (whole 64-element k-blocks per expert);
+  // every extent is a multiple of 8 so that rows stay 16-byte aligned.
+  if ((s->L % 64) != 0 || (s->F % 64) != 0 || (s->D % 8) != 0 || (s->Fs % 8) != 0 || (s->E % 8) != 0)
+    return LMOE_ERR_SHAPE;
+  if (s->n_shared != 1) return LMOE_ERR_SHAPE;
+  return 0;
+}
+
+GemmCall dense(const void* A, long long lda, int a_mn, const void* B, long long ldb, int b_mn, int M, int N, int K,
+               void* C, long long ldc, int epi, int* status, void* stream) {
+  GemmCall c;
+  c.a_mn = a_mn;
+  c.b_mn = b_mn;
+  c.epi = epi;
+  c.grp = GRP_NONE;
+  c.A[0] = A;
+  c.lda[0] = lda;
+  c.B[0] = B;
+  c.ldb[0] = ldb;
+  c.Kseg[0] = K;
+  c.M = M;
+  c.N = N;
+  c.C = C;
+  c.ldc = ldc;
+  c.status = status;
+  c.stream = static_cast<cudaStream_t>(stream);
+  return c;
+}
+
+// Split factor for a weight gradient that contracts over `K` rows into m x n outputs.
+int wgrad_split(int M, int N, int K) {
+  const long long tiles = static_cast<long long>((M + 127) / 128) * ((N + 127) / 128);
+  const int kiters = (K + kBK - 1) / kBK;
+  long long split = (2ll * num_sms() + tiles - 1) / tiles;
+  if (split > kiters / 4) split = kiters / 4;  // at least 4 k-blocks per split
+  if (split < 1) split = 1;
+  return static_cast<int>(split);
+}
+
+int wgrad(const void* Aact, long long lda, int M, const void* Bact, long long ldb, int N, int K, float* dW,
+          int* status, void* stream) {
+  // dW[M,N] += Aact[K,M]^T * Bact[K,N]: both operands MN-major, contraction over rows.
+  GemmCall c = dense(Aact, lda, 1, Bact, ldb, 1, M, N, K, dW, N, EPI_F32_ATOMIC, status, stream);
+  c.split_k = wgrad_split(M, N, K);
+  if (c.split_k == 1) c.split_k = 1;
+  return launch_gemm(c);
+}
+
+}  // namespace
+
+extern "C" int lmoe_version(void) { return LMOE_VERSION; }
+
+extern "C" const char* lmoe_status_string(int code) {
+  switch (code) {
+    case LMOE_OK: return "ok";
+    case LMOE_ERR_ARG: return "invalid argument (null pointer or bad enum)";
+    case LMOE_ERR_SHAPE: return "unsupported shape";
+    case LMOE_ERR_ALIGN: return "pointer or leading dimension not 16-byte aligned";
+    case LMOE_ERR_WORKSPACE: return "workspace too small";
+    case LMOE_ERR_DRIVER: return "tensor-map encoding failed or driver entry point missing";
+    case kStatusProducerTimeout: return "device: TMA producer wait timed out";
+    case kStatusMmaTimeout: return "device: MMA issuer wait timed out";
+    case kStatusEpilogueTimeout: return "device: epilogue wait timed out";
+    default: return code > 0 ? cudaGetErrorString(static_cast<cudaError_t>(code)) : "unknown error";
+  }
+}
+
+// ------------------------------------------------------------------ forward
+extern "C" int lmoe_xproj_fwd(const lmoe_shape* s, const void* x, const void* w_gate, const void* w_down, float* logits,
+                              void* x_latent, int32_t* status, void* stream) {
+  if (int rc = check_dims(s)) return rc;
+  if (!x || !w_gate || !w_down || !logits || !x_latent) return LMOE_ERR_ARG;
+  GemmCall g = dense(x, s->D, 0, w_gate, s->D, 0, s->T, s->E, s->D, logits, s->E, EPI_F32, status, stream);
+  if (int rc = launch_gemm(g)) return rc;
+  GemmCall d = dense(x, s->D, 0, w_down, s->D, 0, s->T, s->L, s->D, x_latent, s->L, EPI_BF16, status, stream);
+  return launch_gemm(d);
+}
+
+extern "C" int lmoe_shared_gateup_fwd(const lmoe_shape* s, const void* x, const void* w_gate_up_s, void* h1_s,
+                                      void* hidden_s, int32_t* status, void* stream) {
+  if (int rc = check_dims(s)) return rc;
+  if (!x || !w_gate_up_s || !h1_s || !hidden_s) return LMOE_ERR_ARG;
+  GemmCall c = dense(x, s->D, 0, w_gate_up_s, s->D, 0, s->T, s->Fs, s->D, h1_s, 2ll * s->Fs, EPI_SWIGLU, status, stream);
+  c.C2 = hidden_s;
+  c.ldc2 = s->Fs;
+  return launch_gemm(c);
+}
+
+extern "C" int lmoe_experts_fwd(const lmoe_shape* s, const void* x_latent, const void* w_gate_up, const void* w_down,
+                                const lmoe_route* r, void* x_sorted, void* h1, void* hidden, void* y_sorted,
+                                int32_t* status, void* stream) {
+  if (int rc = check_dims(s)) return rc;
+  if (!x_latent || !w_gate_up || !w_down || !r || !x_sorted || !h1 || !hidden || !y_sorted) return LMOE_ERR_ARG;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const long long P = lmoe_padded_rows(s);
+  if (int rc = gather_rows(x_latent, r, s->K, s->L, P, x_sorted, st)) return rc;
+  // h1 = x_sorted * Wgu[e]  (Wgu stacked [E*L, 2F], N contiguous), hidden = silu(gate) * up
+  GemmCall a;
+  a.a_mn = 0;
+  a.b_mn = 1;
+  a.epi = EPI_SWIGLU;
+  a.grp = GRP_M;
+  a.A[0] = x_sorted;
+  a.lda[0] = s->L;
+  a.B[0] = w_gate_up;
+  a.ldb[0] = 2ll * s->F;
+  a.Kseg[0] = s->L;
+  a.M = static_cast<int>(P);
+  a.N = s->F;
+  a.C = h1;
+  a.ldc = 2ll * s->F;
+  a.C2 = hidden;
+  a.ldc2 = s->F;
+  a.padded_rows = P;
+  a.groups = s->E;
+  a.b_group_rows = s->L;
+  a.tile_expert = r->tile_expert;
+  a.n_m_tiles = r->n_tiles;
+  a.status = status;
+  a.stream = st;
+  if (int rc = launch_gemm(a)) return rc;
+  // y_sorted = hidden * Wd[e]  (Wd stacked [E*F, L], N contiguous)
+  GemmCall b = a;
+  b.epi = EPI_BF16;
+  b.A[0] = hidden;
+  b.lda[0] = s->F;
+  b.B[0] = w_down;
+  b.ldb[0] = s->L;
+  b.Kseg[0] = s->F;
+  b.N = s->L;
+  b.C = y_sorted;
+  b.ldc = s->L;
+  b.C2 = nullptr;
+  b.b_group_rows = s->F;
+  return launch_gemm(b);
+}
+
+extern "C" int lmoe_combine_out_fwd(const lmoe_shape* s, const void* y_sorted, const lmoe_route* r, const float* weights,
+                                    const void* hidden_s, const void* w_down_s, const void* w_up, void* routed, void* y,
+                                    int32_t* status, void* stream) {
+  if (int rc = check_dims(s)) return rc;
+  if (!y_sorted || !r || !weights || !hidden_s || !w_down_s || !w_up || !routed || !y) return LMOE_ERR_ARG;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (int rc = combine_rows(y_sorted, r->pos, weights, s->T, s->K, s->L, routed, st)) return rc;
+  // y = hidden_s * Wd_s^T + routed * Wup^T : two K segments into one accumulator
+  GemmCall c = dense(hidden_s, s->Fs, 0, w_down_s, s->Fs, 0, s->T, s->D, s->Fs, y, s->D, EPI_BF16, status, stream);
+  c.nseg = 2;
+  c.A[1] = routed;
+  c.lda[1] = s->L;
+  c.B[1] = w_up;
+  c.ldb[1] = s->L;
+  c.Kseg[1] = s->L;
+  return launch_gemm(c);
+}
+
+// ------------------------------------------------------------------ backward
+extern "C" int lmoe_combine_out_bwd_dgrad(const lmoe_shape* s, const void* dy, const void* w_up, const void* w_down_s,
+                                          void* d_routed, void* d_hidden_s, int32_t* status, void* stream) {
+  if (int rc = check_dims(s)) return rc;
+  if (!dy || !w_up || !w_down_s || !d_routed || !d_hidden_s) return LMOE_ERR_ARG;
+  // d_routed[T,L] = dy[T,D] * Wup[D,L]      (B stored [K=D, N=L]: MN-major)
+  GemmCall a = dense(dy, s->D, 0, w_up, s->L, 1, s->T, s->L, s->D, d_routed, s->L, EPI_BF16, status, stream);
+  if (int rc = launch_gemm(a)) return rc;
+  // d_hidden_s[T,Fs] = dy[T,D] * Wd_s[D,Fs]
+  GemmCall b = dense(dy, s->D, 0, w_down_s, s->Fs, 1, s->T, s->Fs, s->D, d_hidden_s, s->Fs, EPI_BF16, status, stream);
+  return launch_gemm(b);
+}
+
+extern "C" int lmoe_combine_out_bwd_wgrad(const lmoe_shape* s, const void* dy, const void* routed, const void* hidden_s,
+                                          float* d_w_up, float* d_w_down_s, int32_t* status, void* stream) {
+  if (int rc = check_dims(s)) return rc;
+  if (!dy || !routed || !hidden_s || !d_w_up || !d_w_down_s) return LMOE_ERR_ARG;
+  if (int rc = wgrad(dy, s->D, s->D, routed, s->L, s->L, s->T, d_w_up, status, stream)) return rc;
+  return wgrad(dy, s->D, s->D, hidden_s, s->Fs, s->Fs, s->T, d_w_down_s, status, stream);
+}
+
+extern "C" int lmoe_experts_bwd_dgrad(const lmoe_shape* s, const void* d_y_sorted, const void* h1, const void* w_gate_up,
+                                      const void* w_down, const lmoe_route* r, void* d_hidden, void* d_h1,
+                                      void* d_x_sorted, int32_t* status, void* stream) {
+  if (int rc = check_dims(s)) return rc;
+  if (!d_y_sorted || !h1 || !w_gate_up || !w_down || !r || !d_hidden || !d_h1 || !d_x_sorted) return LMOE_ERR_ARG;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const long long P = lmoe_padded_rows(s);
+  // d_hidden[P,F] = d_y_sorted[P,L] * Wd[e]^T : Wd[e] is [F,L] = [N,K] row-major -> K-major B
+  GemmCall a;
+  a.a_mn = 0;
+  a.b_mn = 0;
+  a.epi = EPI_BF16;
+  a.grp = GRP_M;
+  a.A[0] = d_y_sorted;
+  a.lda[0] = s->L;
+  a.B[0] = w_down;
+  a.ldb[0] = s->L;
+  a.Kseg[0] = s->L;
+  a.M = static_cast<int>(P);
+  a.N = s->F;
+  a.C = d_hidden;
+  a.ldc = s->F;
+  a.padded_rows = P;
+  a.groups = s->E;
+  a.b_group_rows = s->F;
+  a.tile_expert = r->tile_expert;
+  a.n_m_tiles = r->n_tiles;
+  a.status = status;
+  a.stream = st;
+  if (int rc = launch_gemm(a)) return rc;
+  if (int rc = lmoe_swiglu_bwd(P, s->F, h1, d_hidden, d_h1, r->n_tiles, stream)) return rc;
+  // d_x_sorted[P,L] = d_h1[P,2F] * Wgu[e]^T : Wgu[e] is [L,2F] = [N,K] row-major -> K-major B
+  GemmCall b = a;
+  b.A[0] = d_h1;
+  b.lda[0] = 2ll * s->F;
+  b.B[0] = w_gate_up;
+  b.ldb[0] = 2ll * s->F;
+  b.Kseg[0] = 2 * s->F;
+  b.N = s->L;
+  b.C = d_x_sorted;
+  b.ldc = s->L;
+  b.b_group_rows = s->L;
+  return launch_gemm(b);
+}
+
+extern "C" int lmoe_experts_bwd_wgrad(const lmoe_shape* s, const void* x_sorted, const void* d_h1, const void* hidden,
+                                      const void* d_y_sorted, const lmoe_route* r, void* d_w_gate_up, void* d_w_down,
+                                      int32_t* status, void* stream) {
+  if (int rc = check_dims(s)) return rc;
+  if (!x_sorted || !d_h1 || !hidden || !d_y_sorted || !r || !d_w_gate_up || !d_w_down) return LMOE_ERR_ARG;
+  const long long P = lmoe_padded_rows(s);
+  // d_Wgu[e][L,2F] = x_sorted[rows_e]^T * d_h1[rows_e]
+  GemmCall a;
+  a.a_mn = 1;
+  a.b_mn = 1;
+  a.epi = EPI_BF16;
+  a.grp = GRP_K;
+  a.A[0] = x_sorted;
+  a.lda[0] = s->L;
+  a.B[0] = d_h1;
+  a.ldb[0] = 2ll * s->F;
+  a.M = s->L;
+  a.N = 2 * s->F;
+  a.C = d_w_gate_up;
+  a.ldc = 2ll * s->F;
+  a.c_group_stride = static_cast<long long>(s->L) * 2 * s->F;
+  a.padded_rows = P;
+  a.groups = s->E;
+  a.pad_offsets = r->pad_offsets;
+  a.status = status;
+  a.stream = static_cast<cudaStream_t>(stream);
+  if (int rc = launch_gemm(a)) return rc;
+  // d_Wd[e][F,L] = hidden[rows_e]^T * d_y_sorted[rows_e]
+  GemmCall b = a;
+  b.A[0] = hidden;
+  b.lda[0] = s->F;
+  b.B[0] = d_y_sorted;
+  b.ldb[0] = s->L;
+  b.M = s->F;
+  b.N = s->L;
+  b.C = d_w_down;
+  b.ldc = s->L;
+  b.c_group_stride = static_cast<long long>(s->F) * s->L;
+  return launch_gemm(b);
+}
+
+extern "C" int lmoe_shared_gateup_bwd_wgrad(const lmoe_shape* s, const void* d_h1_s, const void* x, float* d_w_gate_up_s,
+                                            int32_t* status, void* stream) {
+  if (int rc = check_dims(s)) return rc;
+  if (!d_h1_s || !x || !d_w_gate_up_s) return LMOE_ERR_ARG;
+  return wgrad(d_h1_s, 2ll * s->Fs, 2 * s->Fs, x, s->D, s->D, s->T, d_w_gate_up_s, status, stream);
+}
+
+extern "C" int lmoe_xproj_bwd(const lmoe_shape* s, const void* d_h1_s, const void* d_x_latent, const void* d_logits,
+                              const void* w_gate_up_s, const void* w_down, const void* w_gate, const void* x, void* dx,
+                              float* d_w_down, float* d_w_gate, int32_t* status, void* stream) {
+  if (int rc = check_dims(s)) return rc;
+  if (!d_h1_s || !d_x_latent || !d_logits || !w_gate_up_s || !w_down || !w_gate || !x || !dx || !d_w_down || !d_w_gate)
+    return LMOE_ERR_ARG;
+  // dx = d_h1_s[T,2Fs] * Wgu_s[2Fs,D] + d_x_latent[T,L] * Wdown[L,D] + d_logits[T,E] * Wg[E,D]
+  GemmCall c = dense(d_h1_s, 2ll * s->Fs, 0, w_gate_up_s, s->D, 1, s->T, s->D, 2 * s->Fs, dx, s->D, EPI_BF16, status,
+                     stream);
+  c.nseg = 3;
+  c.A[1] = d_x_latent;
+  c.lda[1] = s->L;
+  c.B[1] = w_down;
+  c.ldb[1] = s->D;
+  c.Kseg[1] = s->L;
+  c.A[2] = d_logits;
+  c.lda[2] = s->E;
+  c.B[2] = w_gate;
+  c.ldb[2] = s->D;
+  c.Kseg[2] = s->E;
+  if (int rc = launch_gemm(c)) return rc;
+  if (int rc = wgrad(d_x_latent, s->L, s->L, x, s->D, s->D, s->T, d_w_down, status, stream)) return rc;
+  return wgrad(d_logits, s->E, s->E, x, s->D, s->D, s->T, d_w_gate, status, stream);
+}

@@ -1,0 +1,336 @@
+// Router kernels: warp-level top-k with z-loss, and the deterministic histogram / scan / stable
+// permutation that lays the (token, slot) pairs out expert by expert.  All HBM-bound integer work.
+#include <cuda_runtime.h>
+#include <math_constants.h>
+#include <stdint.h>
+
+#include "../../include/lmoe.h"
+
+namespace lmoe {
+
+constexpr int kTopkWarpsPerBlock = 8;
+constexpr int kMaxPerLane = LMOE_MAX_EXPERTS / 32;  // 8 scores per lane at E = 256
+
+__device__ __forceinline__ float sigmoid_f(float x) { return 1.0f / (1.0f + expf(-x)); }
+
+// "better" = higher score, then lower expert index: the canonical tie rule.
+__device__ __forceinline__ bool better(float sa, int ia, float sb, int ib) { return sa > sb || (sa == sb && ia < ib); }
+
+// One warp per token row.  Lane l holds experts l, l+32, ...
+__global__ void __launch_bounds__(kTopkWarpsPerBlock * 32)
+gate_topk_kernel(const float* __restrict__ logits, const float* __restrict__ bias, int T, int E, int K,
+                 int* __restrict__ sel, float* __restrict__ weights, float* __restrict__ lse_out,
+                 float* __restrict__ z_partial) {
+  __shared__ float s_lse2[kTopkWarpsPerBlock];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int t = blockIdx.x * kTopkWarpsPerBlock + warp;
+  float lse2 = 0.f;
+  if (t < T) {
+    float aff[kMaxPerLane], score[kMaxPerLane];
+    const float* row = logits + static_cast<long long>(t) * E;
+    float mx = -CUDART_INF_F;
+#pragma unroll
+    for (int j = 0; j < kMaxPerLane; ++j) {
+      const int e = lane + 32 * j;
+      if (e < E) {
+        const float x = row[e];
+        mx = fmaxf(mx, x);
+        aff[j] = sigmoid_f(x);
+        score[j] = aff[j] + bias[e];
+      } else {
+        aff[j] = 0.f;
+        score[j] = -CUDART_INF_F;
+      }
+    }
+    // logsumexp over the row
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+    float se = 0.f;
+#pragma unroll
+    for (int j = 0; j < kMaxPerLane; ++j) {
+      const int e = lane + 32 * j;
+      if (e < E) se += expf(row[e] - mx);
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) se += __shfl_xor_sync(0xffffffffu, se, o);
+    const float lse = mx + logf(se);
+    lse2 = lse * lse;
+    if (lane == 0) lse_out[t] = lse;
+
+    // K rounds of warp arg-max
+    float my_aff = 0.f;  // lane k keeps the affinity of the k-th winner
+    int my_idx = 0;
+    float aff_sum = 0.f;
+    for (int k = 0; k < K; ++k) {
+      float bs = -CUDART_INF_F;
+      int bi = 0x7fffffff;
+      float ba = 0.f;
+#pragma unroll
+      for (int j = 0; j < kMaxPerLane; ++j) {
+        const int e = lane + 32 * j;
+        if (e < E && better(score[j], e, bs, bi)) {
+          bs = score[j];
+          bi = e;
+          ba = aff[j];
+        }
+      }
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) {
+        const float os = __shfl_xor_sync(0xffffffffu, bs, o);
+        const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+        const float oa = __shfl_xor_sync(0xffffffffu, ba, o);
+        if (better(os, oi, bs, bi)) {
+          bs = os;
+          bi = oi;
+          ba = oa;
+        }
+      }
+      // every lane now agrees on (bs, bi, ba); retire the winner
+      if ((bi & 31) == lane) {
+#pragma unroll
+        for (int j = 0; j < kMaxPerLane; ++j)
+          if (j == (bi >> 5)) score[j] = -CUDART_INF_F;
+      }
+      if (lane == k) {
+        my_aff = ba;
+        my_idx = bi;
+      }
+      aff_sum += ba;  // same order on every lane: slot 0, 1, ...
+    }
+    if (lane < K) {
+      sel[static_cast<long long>(t) * K + lane] = my_idx;
+      weights[static_cast<long long>(t) * K + lane] = my_aff / (aff_sum + 1e-9f);
+    }
+  }
+  if (lane == 0) s_lse2[warp] = lse2;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    float s = 0.f;
+    for (int i = 0; i < kTopkWarpsPerBlock; ++i) s += s_lse2[i];
+    z_partial[blockIdx.x] = s;
+  }
+}
+
+// Deterministic final reduction of the z-loss partials (fixed order, one block).
+__global__ void __launch_bounds__(256) zloss_finalize_kernel(const float* __restrict__ partial, int n, float scale,
+                                                             float* __restrict__ z_loss) {
+  __shared__ double s[256];
+  double acc = 0.0;
+  for (int i = threadIdx.x; i < n; i += 256) acc += static_cast<double>(partial[i]);
+  s[threadIdx.x] = acc;
+  __syncthreads();
+  for (int o = 128; o > 0; o >>= 1) {
+    if (threadIdx.x < o) s[threadIdx.x] += s[threadIdx.x + o];
+    __syncthreads();
+  }
+  if (threadIdx.x == 0) z_loss[0] = static_cast<float>(s[0] * static_cast<double>(scale));
+}
+
+// ----------------------------------------------------------------------------- routing tables
+// The flat (token, slot) list is cut into chunks of kChunk entries, one warp per chunk.
+constexpr int kChunk = 512;
+constexpr int kRouteWarps = 8;
+
+// Pass 1: per-chunk histogram -> chunk_hist[chunk][E].
+__global__ void __launch_bounds__(kRouteWarps * 32)
+route_hist_kernel(const int* __restrict__ sel, int n, int E, int* __restrict__ chunk_hist) {
+  __shared__ int hist[kRouteWarps][LMOE_MAX_EXPERTS];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int chunk = blockIdx.x * kRouteWarps + warp;
+  for (int e = lane; e < E; e += 32) hist[warp][e] = 0;
+  __syncwarp();
+  const long long base = static_cast<long long>(chunk) * kChunk;
+  if (base < n) {
+    for (int s = 0; s < kChunk; s += 32) {
+      const long long i = base + s + lane;
+      const bool valid = i < n;
+      const int e = valid ? sel[i] : -1;
+      const unsigned peers = __match_any_sync(0xffffffffu, e);
+      if (valid && (__ffs(peers) - 1) == lane) hist[warp][e] += __popc(peers);  // one writer per distinct expert
+      __syncwarp();
+    }
+    for (int e = lane; e < E; e += 32) chunk_hist[static_cast<long long>(chunk) * E + e] = hist[warp][e];
+  }
+}
+
+// Pass 2: one block per expert: exclusive scan of that expert's counts over the chunks (in place),
+// total -> counts[e].
+__global__ void __launch_bounds__(256) route_scan_chunks_kernel(int* __restrict__ chunk_hist, int n_chunks, int E,
+                                                                int* __restrict__ counts) {
+  __shared__ int warp_sums[8];
+  __shared__ int carry_s;
+  const int e = blockIdx.x;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  if (threadIdx.x == 0) carry_s = 0;
+  __syncthreads();
+  for (int c0 = 0; c0 < n_chunks; c0 += 256) {
+    const int c = c0 + threadIdx.x;
+    const int v = (c < n_chunks) ? chunk_hist[static_cast<long long>(c) * E + e] : 0;
+    int incl = v;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+      const int y = __shfl_up_sync(0xffffffffu, incl, o);
+      if (lane >= o) incl += y;
+    }
+    if (lane == 31) warp_sums[warp] = incl;
+    __syncthreads();
+    int warp_off = 0;
+    for (int w = 0; w < warp; ++w) warp_off += warp_sums[w];
+    const int carry = carry_s;
+    if (c < n_chunks) chunk_hist[static_cast<long long>(c) * E + e] = carry + warp_off + incl - v;
+    __syncthreads();
+    if (threadIdx.x == 255) carry_s = carry + warp_off + incl;
+    __syncthreads();
+  }
+  if (threadIdx.x == 0) counts[e] = carry_s;
+}
+
+// Pass 3: one block: offsets (canonical) and padded offsets over experts, tile -> expert table,
+// number of tiles in use, and -1 markers for the pad rows of every expert.
+__global__ void __launch_bounds__(LMOE_MAX_EXPERTS)
+route_offsets_kernel(const int* __restrict__ counts, int E, int* __restrict__ offsets, int* __restrict__ pad_offsets,
+                     int* __restrict__ tile_expert, int* __restrict__ n_tiles, int* __restrict__ row_src) {
+  __shared__ int s_cnt[LMOE_MAX_EXPERTS], s_off[LMOE_MAX_EXPERTS + 1], s_poff[LMOE_MAX_EXPERTS + 1];
+  const int e = threadIdx.x;
+  if (e < E) s_cnt[e] = counts[e];
+  __syncthreads();
+  if (e == 0) {
+    int a = 0, b = 0;
+    for (int i = 0; i < E; ++i) {
+      s_off[i] = a;
+      s_poff[i] = b;
+      a += s_cnt[i];
+      b += (s_cnt[i] + LMOE_ROW_PAD - 1) / LMOE_ROW_PAD * LMOE_ROW_PAD;
+    }
+    s_off[E] = a;
+    s_poff[E] = b;
+    n_tiles[0] = b / LMOE_ROW_PAD;
+  }
+  __syncthreads();
+  if (e < E) {
+    offsets[e] = s_off[e];
+    pad_offsets[e] = s_poff[e];
+    for (int t = s_poff[e] / LMOE_ROW_PAD; t < s_poff[e + 1] / LMOE_ROW_PAD; ++t) tile_expert[t] = e;
+    for (int r = s_poff[e] + s_cnt[e]; r < s_poff[e + 1]; ++r) row_src[r] = -1;
+  }
+  if (e == 0) {
+    offsets[E] = s_off[E];
+    pad_offsets[E] = s_poff[E];
+  }
+}
+
+// Pass 4: stable scatter.  Walks each chunk in index order again; rank inside the warp step by
+// match_any + popc, running per-expert cursors in shared memory.
+__global__ void __launch_bounds__(kRouteWarps * 32)
+route_scatter_kernel(const int* __restrict__ sel, int n, int E, const int* __restrict__ chunk_base,
+                     const int* __restrict__ offsets, const int* __restrict__ pad_offsets, int* __restrict__ perm,
+                     int* __restrict__ pos, int* __restrict__ row_src) {
+  __shared__ int cursor[kRouteWarps][LMOE_MAX_EXPERTS];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int chunk = blockIdx.x * kRouteWarps + warp;
+  const long long base = static_cast<long long>(chunk) * kChunk;
+  if (base >= n) return;
+  for (int e = lane; e < E; e += 32) cursor[warp][e] = chunk_base[static_cast<long long>(chunk) * E + e];
+  __syncwarp();
+  for (int s = 0; s < kChunk; s += 32) {
+    const long long i = base + s + lane;
+    const bool valid = i < n;
+    const int e = valid ? sel[i] : -1;
+    const unsigned peers = __match_any_sync(0xffffffffu, e);
+    int rank = 0;
+    if (valid) {
+      rank = cursor[warp][e] + __popc(peers & ((1u << lane) - 1u));
+      perm[offsets[e] + rank] = static_cast<int>(i);
+      const int prow = pad_offsets[e] + rank;
+      pos[i] = prow;
+      row_src[prow] = static_cast<int>(i);
+    }
+    __syncwarp();
+    if (valid && (__ffs(peers) - 1) == lane) cursor[warp][e] += __popc(peers);
+    __syncwarp();
+  }
+}
+
+// Router bias update from the routing histogram.
+__global__ void bias_update_kernel(const int* __restrict__ counts, int E, float expected, float gamma,
+                                   float* __restrict__ bias, float* __restrict__ history) {
+  const int e = blockIdx.x * blockDim.x + threadIdx.x;
+  if (e >= E) return;
+  const float load = static_cast<float>(counts[e]);
+  const float d = load - expected;
+  const float sg = (d > 0.f) ? 1.f : ((d < 0.f) ? -1.f : 0.f);
+  bias[e] -= gamma * sg;
+  history[e] = 0.99f * history[e] + 0.01f * load;
+}
+
+static inline int check_shape(const lmoe_shape* s) {
+  if (!s) return LMOE_ERR_ARG;
+  if (s->T <= 0 || s->E <= 0 || s->E > LMOE_MAX_EXPERTS || s->K <= 0 || s->K > LMOE_MAX_TOPK || s->K > s->E)
+    return LMOE_ERR_SHAPE;
+  if (static_cast<long long>(s->T) * s->K >= (1ll << 31)) return LMOE_ERR_SHAPE;
+  return 0;
+}
+
+}  // namespace lmoe
+
+using namespace lmoe;
+
+extern "C" int lmoe_gate_topk_fwd(const lmoe_shape* s, const float* logits, const float* expert_bias, float z_coef,
+                                  int32_t* sel, float* weights, float* lse, float* z_partial, float* z_loss,
+                                  void* stream) {
+  if (int rc = check_shape(s)) return rc;
+  if (!logits || !expert_bias || !sel || !weights || !lse || !z_partial || !z_loss) return LMOE_ERR_ARG;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const int blocks = (s->T + kTopkWarpsPerBlock - 1) / kTopkWarpsPerBlock;
+  gate_topk_kernel<<<blocks, kTopkWarpsPerBlock * 32, 0, st>>>(logits, expert_bias, s->T, s->E, s->K, sel, weights, lse,
+                                                              z_partial);
+  zloss_finalize_kernel<<<1, 256, 0, st>>>(z_partial, blocks, z_coef / static_cast<float>(s->T), z_loss);
+  cudaError_t e = cudaGetLastError();
+  return e == cudaSuccess ? 0 : static_cast<int>(e);
+}
+
+extern "C" size_t lmoe_route_workspace_bytes(const lmoe_shape* s) {
+  if (check_shape(s)) return 0;
+  const long long n = static_cast<long long>(s->T) * s->K;
+  const long long chunks = (n + kChunk - 1) / kChunk;
+  return static_cast<size_t>(chunks) * s->E * sizeof(int);
+}
+
+extern "C" int64_t lmoe_padded_rows(const lmoe_shape* s) {
+  if (check_shape(s)) return 0;
+  const long long n = static_cast<long long>(s->T) * s->K;
+  return (n + LMOE_ROW_PAD - 1) / LMOE_ROW_PAD * LMOE_ROW_PAD + static_cast<long long>(s->E) * LMOE_ROW_PAD;
+}
+
+extern "C" int lmoe_route_permute(const lmoe_shape* s, const int32_t* sel, const lmoe_route* r, void* workspace,
+                                  size_t workspace_bytes, void* stream) {
+  if (int rc = check_shape(s)) return rc;
+  if (!sel || !r || !workspace || !r->counts || !r->offsets || !r->perm || !r->pad_offsets || !r->pos || !r->row_src ||
+      !r->tile_expert || !r->n_tiles)
+    return LMOE_ERR_ARG;
+  if (workspace_bytes < lmoe_route_workspace_bytes(s)) return LMOE_ERR_WORKSPACE;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const int n = s->T * s->K;
+  const int chunks = (n + kChunk - 1) / kChunk;
+  const int blocks = (chunks + kRouteWarps - 1) / kRouteWarps;
+  int* chunk_hist = static_cast<int*>(workspace);
+  route_hist_kernel<<<blocks, kRouteWarps * 32, 0, st>>>(sel, n, s->E, chunk_hist);
+  route_scan_chunks_kernel<<<s->E, 256, 0, st>>>(chunk_hist, chunks, s->E, r->counts);
+  route_offsets_kernel<<<1, LMOE_MAX_EXPERTS, 0, st>>>(r->counts, s->E, r->offsets, r->pad_offsets, r->tile_expert,
+                                                      r->n_tiles, r->row_src);
+  route_scatter_kernel<<<blocks, kRouteWarps * 32, 0, st>>>(sel, n, s->E, chunk_hist, r->offsets, r->pad_offsets,
+                                                           r->perm, r->pos, r->row_src);
+  cudaError_t e = cudaGetLastError();
+  return e == cudaSuccess ? 0 : static_cast<int>(e);
+}
+
+extern "C" int lmoe_router_bias_update(const lmoe_shape* s, const int32_t* counts, float gamma, float* expert_bias,
+                                       float* load_history, void* stream) {
+  if (int rc = check_shape(s)) return rc;
+  if (!counts || !expert_bias || !load_history) return LMOE_ERR_ARG;
+  const float expected = static_cast<float>(s->T) * static_cast<float>(s->K) / static_cast<float>(s->E);
+  bias_update_kernel<<<(s->E + 127) / 128, 128, 0, static_cast<cudaStream_t>(stream)>>>(counts, s->E, expected, gamma,
+                                                                                        expert_bias, load_history);
+  cudaError_t e = cudaGetLastError();
+  return e == cudaSuccess ? 0 : static_cast<int>(e);
+}

@@ -1,0 +1,276 @@
+// HBM-bound row kernels of the LatentMoE path: gather into the padded expert layout, weighted
+// combine and its adjoint, SwiGLU adjoint, router adjoint, dtype casts.  One warp per row, 16-byte
+// vector accesses, fp32 arithmetic.
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "../../include/lmoe.h"
+#include "rowops.h"
+
+namespace lmoe {
+
+constexpr int kRowWarps = 8;
+
+__device__ __forceinline__ void unpack8(const uint4& v, float (&f)[8]) {
+  const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&v);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const float2 x = __bfloat1622float2(h[i]);
+    f[2 * i] = x.x;
+    f[2 * i + 1] = x.y;
+  }
+}
+__device__ __forceinline__ uint4 pack8(const float (&f)[8]) {
+  uint4 v;
+  __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&v);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) h[i] = __floats2bfloat162_rn(f[2 * i], f[2 * i + 1]);
+  return v;
+}
+
+// x_sorted[row] = x_latent[row_src[row] / K]  (zeros for pad rows); rows < 128 * n_tiles[0].
+__global__ void __launch_bounds__(kRowWarps * 32)
+gather_rows_kernel(const uint4* __restrict__ src, const int* __restrict__ row_src, const int* __restrict__ n_tiles, int K,
+                   int vec_per_row, uint4* __restrict__ dst, long long max_rows) {
+  const int lane = threadIdx.x & 31;
+  const long long rows = min(static_cast<long long>(n_tiles[0]) * LMOE_ROW_PAD, max_rows);
+  for (long long row = static_cast<long long>(blockIdx.x) * kRowWarps + (threadIdx.x >> 5); row < rows;
+       row += static_cast<long long>(gridDim.x) * kRowWarps) {
+    const int flat = row_src[row];
+    const uint4 zero = make_uint4(0, 0, 0, 0);
+    const uint4* s = (flat >= 0) ? src + static_cast<long long>(flat / K) * vec_per_row : nullptr;
+    uint4* d = dst + row * vec_per_row;
+    for (int v = lane; v < vec_per_row; v += 32) d[v] = s ? s[v] : zero;
+  }
+}
+
+// out[t] = sum_k w[t,k] * y[pos[t*K+k]]   (w == nullptr: plain sum).  Slot order k = 0..K-1, fp32.
+__global__ void __launch_bounds__(kRowWarps * 32)
+combine_kernel(const uint4* __restrict__ y, const int* __restrict__ pos, const float* __restrict__ w, int T, int K,
+               int vec_per_row, uint4* __restrict__ out) {
+  const int lane = threadIdx.x & 31;
+  for (long long t = static_cast<long long>(blockIdx.x) * kRowWarps + (threadIdx.x >> 5); t < T;
+       t += static_cast<long long>(gridDim.x) * kRowWarps) {
+    for (int v = lane; v < vec_per_row; v += 32) {
+      float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+      for (int k = 0; k < K; ++k) {
+        const long long i = t * K + k;
+        const float wk = w ? w[i] : 1.0f;
+        float f[8];
+        unpack8(y[static_cast<long long>(pos[i]) * vec_per_row + v], f);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) acc[j] = fmaf(wk, f[j], acc[j]);
+      }
+      out[t * vec_per_row + v] = pack8(acc);
+    }
+  }
+}
+
+// Adjoint of the weighted combine over padded rows:
+//   d_y[row] = w[flat] * d_routed[t],  d_w[flat] = <d_routed[t], y[row]>,  pad rows -> 0.
+__global__ void __launch_bounds__(kRowWarps * 32)
+combine_bwd_kernel(const uint4* __restrict__ d_routed, const uint4* __restrict__ y, const float* __restrict__ w,
+                   const int* __restrict__ row_src, const int* __restrict__ n_tiles, int K, int vec_per_row,
+                   uint4* __restrict__ d_y, float* __restrict__ d_w, long long max_rows) {
+  const int lane = threadIdx.x & 31;
+  const long long rows = min(static_cast<long long>(n_tiles[0]) * LMOE_ROW_PAD, max_rows);
+  for (long long row = static_cast<long long>(blockIdx.x) * kRowWarps + (threadIdx.x >> 5); row < rows;
+       row += static_cast<long long>(gridDim.x) * kRowWarps) {
+    const int flat = row_src[row];
+    uint4* d = d_y + row * vec_per_row;
+    if (flat < 0) {
+      for (int v = lane; v < vec_per_row; v += 32) d[v] = make_uint4(0, 0, 0, 0);
+      continue;
+    }
+    const long long t = flat / K;
+    const float wk = w[flat];
+    float dot = 0.f;
+    for (int v = lane; v < vec_per_row; v += 32) {
+      float g[8], yy[8], o[8];
+      unpack8(d_routed[t * vec_per_row + v], g);
+      unpack8(y[row * vec_per_row + v], yy);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        dot = fmaf(g[j], yy[j], dot);
+        o[j] = wk * g[j];
+      }
+      d[v] = pack8(o);
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) dot += __shfl_xor_sync(0xffffffffu, dot, o);
+    if (lane == 0) d_w[flat] = dot;
+  }
+}
+
+// d_h1 = swiglu'(h1, d_hidden): gate g = h1[:, :H], up u = h1[:, H:];
+//   d_u = d_h * silu(g);  d_g = d_h * u * sig(g) * (1 + g * (1 - sig(g))).
+__global__ void __launch_bounds__(256)
+swiglu_bwd_kernel(const uint4* __restrict__ h1, const uint4* __restrict__ d_hidden, uint4* __restrict__ d_h1,
+                  long long rows_host, const int* __restrict__ n_tiles, int vec_per_half) {
+  long long rows = rows_host;
+  if (n_tiles) rows = min(rows, static_cast<long long>(n_tiles[0]) * LMOE_ROW_PAD);
+  const long long total = rows * vec_per_half;
+  for (long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; i < total;
+       i += static_cast<long long>(gridDim.x) * blockDim.x) {
+    const long long r = i / vec_per_half;
+    const int v = static_cast<int>(i - r * vec_per_half);
+    float g[8], u[8], dh[8], dg[8], du[8];
+    unpack8(h1[r * 2 * vec_per_half + v], g);
+    unpack8(h1[r * 2 * vec_per_half + vec_per_half + v], u);
+    unpack8(d_hidden[r * vec_per_half + v], dh);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      const float sg = 1.0f / (1.0f + __expf(-g[j]));
+      du[j] = dh[j] * g[j] * sg;
+      dg[j] = dh[j] * u[j] * sg * (1.0f + g[j] * (1.0f - sg));
+    }
+    d_h1[r * 2 * vec_per_half + v] = pack8(dg);
+    d_h1[r * 2 * vec_per_half + vec_per_half + v] = pack8(du);
+  }
+}
+
+// Router adjoint, one warp per token: dense d_logits row (bf16).
+//   selected k: a = sig(logit), S = sum_j a_j + 1e-9, w = a / S,
+//               d_a = (d_w_k - sum_j d_w_j w_j) / S,  d_logit = d_a * a (1 - a)
+//   all e:      + d_z * z_coef * 2 * lse * softmax(logits)_e / T
+__global__ void __launch_bounds__(kRowWarps * 32)
+gate_bwd_kernel(const float* __restrict__ logits, const int* __restrict__ sel, const float* __restrict__ w,
+                const float* __restrict__ d_w, const float* __restrict__ lse, const float* __restrict__ d_z,
+                float z_scale, int T, int E, int K, __nv_bfloat16* __restrict__ d_logits) {
+  __shared__ float rowbuf[kRowWarps][LMOE_MAX_EXPERTS];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const float dz = d_z ? d_z[0] * z_scale : 0.f;
+  for (long long t = static_cast<long long>(blockIdx.x) * kRowWarps + warp; t < T;
+       t += static_cast<long long>(gridDim.x) * kRowWarps) {
+    const float* row = logits + t * E;
+    const float l = lse[t];
+    for (int e = lane; e < E; e += 32) rowbuf[warp][e] = (dz != 0.f) ? dz * 2.0f * l * expf(row[e] - l) : 0.f;
+    __syncwarp();
+    // per-slot quantities on lanes < K
+    float a = 0.f, wk = 0.f, dwk = 0.f;
+    int e_sel = 0;
+    if (lane < K) {
+      e_sel = sel[t * K + lane];
+      a = 1.0f / (1.0f + expf(-row[e_sel]));
+      wk = w[t * K + lane];
+      dwk = d_w[t * K + lane];
+    }
+    float asum = a, dot = dwk * wk;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      asum += __shfl_xor_sync(0xffffffffu, asum, o);
+      dot += __shfl_xor_sync(0xffffffffu, dot, o);
+    }
+    if (lane < K) {
+      const float S = asum + 1e-9f;
+      const float da = (dwk - dot) / S;
+      rowbuf[warp][e_sel] += da * a * (1.0f - a);  // experts are distinct within a row
+    }
+    __syncwarp();
+    for (int e = lane; e < E; e += 32) d_logits[t * E + e] = __float2bfloat16_rn(rowbuf[warp][e]);
+    __syncwarp();
+  }
+}
+
+__global__ void cast_f32_bf16_kernel(const float4* __restrict__ src, uint2* __restrict__ dst, long long n4,
+                                     const float* __restrict__ src_tail, __nv_bfloat16* __restrict__ dst_tail, int tail) {
+  for (long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; i < n4;
+       i += static_cast<long long>(gridDim.x) * blockDim.x) {
+    const float4 v = src[i];
+    __nv_bfloat162 a = __floats2bfloat162_rn(v.x, v.y), b = __floats2bfloat162_rn(v.z, v.w);
+    dst[i] = make_uint2(*reinterpret_cast<uint32_t*>(&a), *reinterpret_cast<uint32_t*>(&b));
+  }
+  if (blockIdx.x == 0 && static_cast<int>(threadIdx.x) < tail) dst_tail[threadIdx.x] = __float2bfloat16_rn(src_tail[threadIdx.x]);
+}
+__global__ void cast_bf16_f32_kernel(const __nv_bfloat16* __restrict__ src, float* __restrict__ dst, long long n) {
+  for (long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; i < n;
+       i += static_cast<long long>(gridDim.x) * blockDim.x)
+    dst[i] = __bfloat162float(src[i]);
+}
+
+static inline int grid_for(long long work_items, int per_block) {
+  long long b = (work_items + per_block - 1) / per_block;
+  const long long cap = 148ll * 16;
+  if (b > cap) b = cap;
+  if (b < 1) b = 1;
+  return static_cast<int>(b);
+}
+static inline int last_error() {
+  cudaError_t e = cudaGetLastError();
+  return e == cudaSuccess ? 0 : static_cast<int>(e);
+}
+
+int gather_rows(const void* x_latent, const lmoe_route* r, int K, int L, long long padded_rows, void* x_sorted,
+                cudaStream_t st) {
+  if ((L & 7) != 0) return LMOE_ERR_SHAPE;
+  gather_rows_kernel<<<grid_for(padded_rows, kRowWarps), kRowWarps * 32, 0, st>>>(
+      static_cast<const uint4*>(x_latent), r->row_src, r->n_tiles, K, L / 8, static_cast<uint4*>(x_sorted), padded_rows);
+  return last_error();
+}
+
+int combine_rows(const void* y_sorted, const int* pos, const float* w, int T, int K, int L, void* out, cudaStream_t st) {
+  if ((L & 7) != 0) return LMOE_ERR_SHAPE;
+  combine_kernel<<<grid_for(T, kRowWarps), kRowWarps * 32, 0, st>>>(static_cast<const uint4*>(y_sorted), pos, w, T, K,
+                                                                    L / 8, static_cast<uint4*>(out));
+  return last_error();
+}
+
+}  // namespace lmoe
+
+using namespace lmoe;
+
+extern "C" int lmoe_combine_bwd(const lmoe_shape* s, const void* d_routed, const void* y_sorted, const float* weights,
+                                const lmoe_route* r, void* d_y_sorted, float* d_weights, void* stream) {
+  if (!s || !d_routed || !y_sorted || !weights || !r || !d_y_sorted || !d_weights) return LMOE_ERR_ARG;
+  if ((s->L & 7) != 0) return LMOE_ERR_SHAPE;
+  const long long P = lmoe_padded_rows(s);
+  combine_bwd_kernel<<<grid_for(P, kRowWarps), kRowWarps * 32, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const uint4*>(d_routed), static_cast<const uint4*>(y_sorted), weights, r->row_src, r->n_tiles, s->K,
+      s->L / 8, static_cast<uint4*>(d_y_sorted), d_weights, P);
+  return last_error();
+}
+
+extern "C" int lmoe_swiglu_bwd(int64_t rows, int H, const void* h1, const void* d_hidden, void* d_h1,
+                               const int32_t* n_tiles_dev, void* stream) {
+  if (!h1 || !d_hidden || !d_h1 || rows <= 0 || H <= 0) return LMOE_ERR_ARG;
+  if ((H & 7) != 0) return LMOE_ERR_SHAPE;
+  swiglu_bwd_kernel<<<grid_for(rows * (H / 8), 256), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const uint4*>(h1), static_cast<const uint4*>(d_hidden), static_cast<uint4*>(d_h1), rows, n_tiles_dev,
+      H / 8);
+  return last_error();
+}
+
+extern "C" int lmoe_unpermute_sum_bwd(const lmoe_shape* s, const void* d_x_sorted, const lmoe_route* r, void* d_x_latent,
+                                      void* stream) {
+  if (!s || !d_x_sorted || !r || !d_x_latent) return LMOE_ERR_ARG;
+  return combine_rows(d_x_sorted, r->pos, nullptr, s->T, s->K, s->L, d_x_latent, static_cast<cudaStream_t>(stream));
+}
+
+extern "C" int lmoe_gate_topk_bwd(const lmoe_shape* s, const float* logits, const int32_t* sel, const float* weights,
+                                  const float* d_weights, const float* lse, const float* d_z, float z_coef,
+                                  void* d_logits, void* stream) {
+  if (!s || !logits || !sel || !weights || !d_weights || !lse || !d_logits) return LMOE_ERR_ARG;
+  if (s->E > LMOE_MAX_EXPERTS || s->K > 32) return LMOE_ERR_SHAPE;
+  gate_bwd_kernel<<<grid_for(s->T, kRowWarps), kRowWarps * 32, 0, static_cast<cudaStream_t>(stream)>>>(
+      logits, sel, weights, d_weights, lse, d_z, z_coef / static_cast<float>(s->T), s->T, s->E, s->K,
+      static_cast<__nv_bfloat16*>(d_logits));
+  return last_error();
+}
+
+extern "C" int lmoe_cast_f32_to_bf16(const float* src, void* dst, int64_t n, void* stream) {
+  if (!src || !dst || n <= 0) return LMOE_ERR_ARG;
+  const long long n4 = n / 4;
+  const int tail = static_cast<int>(n - n4 * 4);
+  cast_f32_bf16_kernel<<<grid_for(n4 > 0 ? n4 : 1, 256), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      reinterpret_cast<const float4*>(src), static_cast<uint2*>(dst), n4, src + n4 * 4,
+      static_cast<__nv_bfloat16*>(dst) + n4 * 4, tail);
+  return last_error();
+}
+
+extern "C" int lmoe_cast_bf16_to_f32(const void* src, float* dst, int64_t n, void* stream) {
+  if (!src || !dst || n <= 0) return LMOE_ERR_ARG;
+  cast_bf16_f32_kernel<<<grid_for(n, 256), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const __nv_bfloat16*>(src), dst, n);
+  return last_error();
+}

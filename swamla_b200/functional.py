@@ -1,0 +1,223 @@
+"""Autograd binding of the LatentMoE path: forward and backward assembled from the C-ABI
+entry points of ``liblmoe.so``.  PyTorch only provides device memory and the stream.
+
+Forward follows ``models/moe.py:702-734`` of the reference (``LatentMoELayer.forward``); the
+backward is the adjoint of each cited line (the reference defines it only through autograd and
+not at all for its grouped GEMM, ``models/moe_triton.py:200-242``).
+"""
+from __future__ import annotations
+
+from typing import Optional
+
+import torch
+
+from . import _cabi
+from ._cabi import Route, Shape, ptr
+
+BF = torch.bfloat16
+
+
+def _stream() -> int:
+    return torch.cuda.current_stream().cuda_stream
+
+
+def _as_bf16(t: torch.Tensor) -> torch.Tensor:
+    """bf16 copy of a float tensor through the library's cast kernel (no-op for bf16)."""
+    if t.dtype == BF:
+        return t.contiguous()
+    if t.dtype != torch.float32:
+        t = t.float()
+    t = t.contiguous()
+    out = torch.empty(t.shape, dtype=BF, device=t.device)
+    _cabi.call("lmoe_cast_f32_to_bf16", ptr(t), ptr(out), t.numel(), _stream())
+    return out
+
+
+def _to_dtype(t32: torch.Tensor, dtype: torch.dtype) -> torch.Tensor:
+    if dtype == torch.float32:
+        return t32
+    if dtype == BF:
+        out = torch.empty(t32.shape, dtype=BF, device=t32.device)
+        _cabi.call("lmoe_cast_f32_to_bf16", ptr(t32), ptr(out), t32.numel(), _stream())
+        return out
+    return t32.to(dtype)
+
+
+class RouteTables:
+    """Device buffers behind an ``lmoe_route`` struct."""
+
+    def __init__(self, shape: Shape, device):
+        T, K, E = shape.T, shape.K, shape.E
+        self.padded_rows = int(_cabi.load().lmoe_padded_rows(shape))
+        i32 = dict(dtype=torch.int32, device=device)
+        # one allocation, sliced; every slice starts 16-byte aligned
+        sizes = dict(counts=E, offsets=E + 1, pad_offsets=E + 1, n_tiles=1, tile_expert=self.padded_rows // 128,
+                     perm=T * K, pos=T * K, row_src=self.padded_rows)
+        total = sum((n + 3) // 4 * 4 for n in sizes.values())
+        self.storage = torch.empty(total, **i32)
+        off = 0
+        for name, n in sizes.items():
+            setattr(self, name, self.storage[off:off + n])
+            off += (n + 3) // 4 * 4
+        self.struct = Route(**{k: ptr(getattr(self, k)) for k in sizes})
+
+
+def make_shape(T, D, L, E, K, F, Fs, n_shared=1) -> Shape:
+    return Shape(T=T, D=D, L=L, E=E, K=K, F=F, Fs=Fs, n_shared=n_shared)
+
+
+def check_status(status: torch.Tensor) -> None:
+    """Reads the device status word (synchronises); raises if a kernel wait gave up."""
+    code = int(status.item())
+    if code != 0:
+        raise _cabi.LmoeError(f"device status {code}: {_cabi.status_string(code)}")
+
+
+class LatentMoEFunction(torch.autograd.Function):
+    """y, aux_loss, sel = f(x, w_gate, w_down, w_up, w_gate_up_s, w_down_s, w_gate_up, w_down_e, expert_bias)."""
+
+    @staticmethod
+    def forward(ctx, x, w_gate, w_down, w_up, w_gate_up_s, w_down_s, w_gate_up, w_down_e, expert_bias, top_k: int,
+                z_coef: float):
+        if not x.is_cuda:
+            raise _cabi.LmoeError("the LatentMoE path runs on a CUDA device only (no CPU fallback)")
+        lib = _cabi.load()
+        dev = x.device
+        T, D = x.shape
+        E, L, F2 = w_gate_up.shape
+        F = F2 // 2
+        Fs = w_down_s.shape[1]
+        shape = make_shape(T, D, L, E, top_k, F, Fs)
+        st = _stream()
+
+        xb = _as_bf16(x)
+        wg, wdn, wup = _as_bf16(w_gate), _as_bf16(w_down), _as_bf16(w_up)
+        wgus, wds = _as_bf16(w_gate_up_s), _as_bf16(w_down_s)
+        wgu, wde = _as_bf16(w_gate_up), _as_bf16(w_down_e)
+        bias = expert_bias.to(torch.float32).contiguous()
+
+        status = torch.zeros(1, dtype=torch.int32, device=dev)
+        bf = dict(dtype=BF, device=dev)
+        f32 = dict(dtype=torch.float32, device=dev)
+
+        # router + latent down-projection
+        logits = torch.empty(T, E, **f32)
+        x_latent = torch.empty(T, L, **bf)
+        _cabi.call("lmoe_xproj_fwd", shape, ptr(xb), ptr(wg), ptr(wdn), ptr(logits), ptr(x_latent), ptr(status), st)
+        sel = torch.empty(T, top_k, dtype=torch.int32, device=dev)
+        weights = torch.empty(T, top_k, **f32)
+        lse = torch.empty(T, **f32)
+        z_partial = torch.empty((T + 7) // 8, **f32)
+        z_loss = torch.empty(1, **f32)
+        _cabi.call("lmoe_gate_topk_fwd", shape, ptr(logits), ptr(bias), float(z_coef), ptr(sel), ptr(weights), ptr(lse),
+                   ptr(z_partial), ptr(z_loss), st)
+        route = RouteTables(shape, dev)
+        ws = torch.empty(max(16, lib.lmoe_route_workspace_bytes(shape)), dtype=torch.uint8, device=dev)
+        _cabi.call("lmoe_route_permute", shape, ptr(sel), route.struct, ptr(ws), ws.numel(), st)
+
+        # routed experts in the padded layout
+        P = route.padded_rows
+        x_sorted = torch.empty(P, L, **bf)
+        h1 = torch.empty(P, 2 * F, **bf)
+        hidden = torch.empty(P, F, **bf)
+        y_sorted = torch.empty(P, L, **bf)
+        _cabi.call("lmoe_experts_fwd", shape, ptr(x_latent), ptr(wgu), ptr(wde), route.struct, ptr(x_sorted), ptr(h1),
+                   ptr(hidden), ptr(y_sorted), ptr(status), st)
+
+        # shared expert and output
+        h1_s = torch.empty(T, 2 * Fs, **bf)
+        hidden_s = torch.empty(T, Fs, **bf)
+        _cabi.call("lmoe_shared_gateup_fwd", shape, ptr(xb), ptr(wgus), ptr(h1_s), ptr(hidden_s), ptr(status), st)
+        routed = torch.empty(T, L, **bf)
+        y = torch.empty(T, D, **bf)
+        _cabi.call("lmoe_combine_out_fwd", shape, ptr(y_sorted), route.struct, ptr(weights), ptr(hidden_s), ptr(wds),
+                   ptr(wup), ptr(routed), ptr(y), ptr(status), st)
+
+        ctx.shape = shape
+        ctx.route = route
+        ctx.z_coef = float(z_coef)
+        ctx.status = status
+        ctx.dtypes = [t.dtype for t in (x, w_gate, w_down, w_up, w_gate_up_s, w_down_s, w_gate_up, w_down_e)]
+        ctx.save_for_backward(xb, wg, wdn, wup, wgus, wds, wgu, wde, logits, sel, weights, lse, x_sorted, h1, hidden,
+                              y_sorted, routed, h1_s, hidden_s)
+        ctx.mark_non_differentiable(sel, route.counts)
+        out = y if x.dtype == BF else y.to(x.dtype)
+        return out, z_loss.reshape(()), sel, route.counts
+
+    @staticmethod
+    def backward(ctx, dy, d_z, _d_sel, _d_counts):
+        (xb, wg, wdn, wup, wgus, wds, wgu, wde, logits, sel, weights, lse, x_sorted, h1, hidden, y_sorted, routed, h1_s,
+         hidden_s) = ctx.saved_tensors
+        shape, route, status = ctx.shape, ctx.route, ctx.status
+        T, D, L, E, K, F, Fs = shape.T, shape.D, shape.L, shape.E, shape.K, shape.F, shape.Fs
+        P = route.padded_rows
+        dev = xb.device
+        st = _stream()
+        bf = dict(dtype=BF, device=dev)
+        f32 = dict(dtype=torch.float32, device=dev)
+        if dy is None:
+            dy = torch.zeros(T, D, **bf)
+        dyb = _as_bf16(dy.reshape(T, D))
+
+        # output stage
+        d_routed = torch.empty(T, L, **bf)
+        d_hidden_s = torch.empty(T, Fs, **bf)
+        _cabi.call("lmoe_combine_out_bwd_dgrad", shape, ptr(dyb), ptr(wup), ptr(wds), ptr(d_routed), ptr(d_hidden_s),
+                   ptr(status), st)
+        d_w_up = torch.zeros(D, L, **f32)
+        d_w_down_s = torch.zeros(D, Fs, **f32)
+        _cabi.call("lmoe_combine_out_bwd_wgrad", shape, ptr(dyb), ptr(routed), ptr(hidden_s), ptr(d_w_up),
+                   ptr(d_w_down_s), ptr(status), st)
+        d_h1_s = torch.empty(T, 2 * Fs, **bf)
+        _cabi.call("lmoe_swiglu_bwd", T, Fs, ptr(h1_s), ptr(d_hidden_s), ptr(d_h1_s), None, st)
+
+        # routed experts
+        d_y_sorted = torch.empty(P, L, **bf)
+        d_weights = torch.empty(T, K, **f32)
+        _cabi.call("lmoe_combine_bwd", shape, ptr(d_routed), ptr(y_sorted), ptr(weights), route.struct, ptr(d_y_sorted),
+                   ptr(d_weights), st)
+        d_hidden = torch.empty(P, F, **bf)
+        d_h1 = torch.empty(P, 2 * F, **bf)
+        d_x_sorted = torch.empty(P, L, **bf)
+        _cabi.call("lmoe_experts_bwd_dgrad", shape, ptr(d_y_sorted), ptr(h1), ptr(wgu), ptr(wde), route.struct,
+                   ptr(d_hidden), ptr(d_h1), ptr(d_x_sorted), ptr(status), st)
+        d_w_gate_up = torch.empty(E, L, 2 * F, **bf)
+        d_w_down_e = torch.empty(E, F, L, **bf)
+        _cabi.call("lmoe_experts_bwd_wgrad", shape, ptr(x_sorted), ptr(d_h1), ptr(hidden), ptr(d_y_sorted),
+                   route.struct, ptr(d_w_gate_up), ptr(d_w_down_e), ptr(status), st)
+        d_x_latent = torch.empty(T, L, **bf)
+        _cabi.call("lmoe_unpermute_sum_bwd", shape, ptr(d_x_sorted), route.struct, ptr(d_x_latent), st)
+
+        # router
+        d_logits = torch.empty(T, E, **bf)
+        dz = None
+        if d_z is not None:
+            dz = d_z.to(torch.float32).reshape(1).contiguous()
+        _cabi.call("lmoe_gate_topk_bwd", shape, ptr(logits), ptr(sel), ptr(weights), ptr(d_weights), ptr(lse), ptr(dz),
+                   ctx.z_coef, ptr(d_logits), st)
+
+        # x side
+        d_w_gate_up_s = torch.zeros(2 * Fs, D, **f32)
+        _cabi.call("lmoe_shared_gateup_bwd_wgrad", shape, ptr(d_h1_s), ptr(xb), ptr(d_w_gate_up_s), ptr(status), st)
+        dx = torch.empty(T, D, **bf)
+        d_w_down = torch.zeros(L, D, **f32)
+        d_w_gate = torch.zeros(E, D, **f32)
+        _cabi.call("lmoe_xproj_bwd", shape, ptr(d_h1_s), ptr(d_x_latent), ptr(d_logits), ptr(wgus), ptr(wdn), ptr(wg),
+                   ptr(xb), ptr(dx), ptr(d_w_down), ptr(d_w_gate), ptr(status), st)
+
+        dt = ctx.dtypes
+        grads = (
+            dx if dt[0] == BF else dx.to(dt[0]),
+            _to_dtype(d_w_gate, dt[1]), _to_dtype(d_w_down, dt[2]), _to_dtype(d_w_up, dt[3]),
+            _to_dtype(d_w_gate_up_s, dt[4]), _to_dtype(d_w_down_s, dt[5]),
+            d_w_gate_up if dt[6] == BF else d_w_gate_up.to(dt[6]),
+            d_w_down_e if dt[7] == BF else d_w_down_e.to(dt[7]),
+        )
+        return grads + (None, None, None)
+
+
+def latent_moe(x2d: torch.Tensor, w_gate, w_down, w_up, w_gate_up_s, w_down_s, w_gate_up, w_down_e, expert_bias,
+               top_k: int, z_coef: float):
+    """Functional form on a [T, D] activation.  Returns (y [T,D], aux_loss scalar, sel [T,K] int32, counts [E] int32)."""
+    return LatentMoEFunction.apply(x2d, w_gate, w_down, w_up, w_gate_up_s, w_down_s, w_gate_up, w_down_e, expert_bias,
+                                   int(top_k), float(z_coef))
