@@ -1,0 +1,330 @@
+#!/usr/bin/env python
+"""Benchmark of the LatentMoE feed-forward path: forward+backward tokens/s.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--workload cfgX]
+
+One step = one forward+backward of the layer over one batch of synthetic tokens.  Rank 0 prints ONE
+JSON line.  ``value`` is timed with CUDA events with inputs resident in HBM; ``e2e`` is the same step
+driven through the nn.Module with pinned HOST buffers (H2D of x and dy, D2H of y and the aux loss
+inside the timed region, copies pipelined on side streams).  ``--impl reference`` times the CPU oracle
+(the reference layer's algorithm in fp32 torch) on the host cores on a bounded sample of the workload.
+"""
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+import torch  # noqa: E402
+
+from swamla_b200 import workloads as inputs  # noqa: E402
+
+METRIC = "LatentMoE fwd+bwd tokens/s"
+CPU_SAMPLE_TOKENS = 1024
+
+
+def peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        d = json.load(open(path))
+        return dict(bf16_tflops=d["bf16_tflops"], bf16_tflops_sustained=d.get("bf16_tflops_sustained"),
+                    hbm_gbs=d["hbm_gbs"], source="measured")
+    return dict(bf16_tflops=1590.0, bf16_tflops_sustained=1400.0, hbm_gbs=6650.0, source="fallback")
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons of one GPU with nvidia-smi while the timed region runs."""
+    Q = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+         "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int):
+        self.index, self.rows, self.proc, self.thread = index, [], None, None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.Q}",
+                                          "--format=csv,noheader,nounits", "-lms", "100"],
+                                         stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+        except OSError:
+            self.proc = None
+            return
+        self.thread = threading.Thread(target=self._read, daemon=True)
+        self.thread.start()
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.rows.append([c.strip() for c in line.split(",")])
+
+    def stop(self) -> dict:
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        self.thread.join(timeout=2)
+        sm, mx, reasons = [], None, set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for r in self.rows:
+            if len(r) < 7:
+                continue
+            try:
+                sm.append(float(r[0]))
+                mx = float(r[1])
+            except ValueError:
+                continue
+            for n, v in zip(names, r[3:7]):
+                if v.lower().startswith("active"):
+                    reasons.add(n)
+        sm.sort()
+        return {"sm_mhz": sm[len(sm) // 2] if sm else None, "sm_max_mhz": mx, "samples": len(sm),
+                "reasons": sorted(reasons)}
+
+
+def build_layer(w, seed, device):
+    from swamla_b200.layer import LatentMoELayer
+    params, buffers, x, dy = inputs.make_inputs(w, seed=seed)
+    layer = LatentMoELayer(w.config())
+    layer.load_state_dict({**params, **buffers}, strict=True)
+    layer = layer.to(device).to(torch.bfloat16).train()
+    return layer, x.to(torch.bfloat16), dy.to(torch.bfloat16)
+
+
+def step(layer, x, dy):
+    """One fwd+bwd through the public module API; gradients accumulate into .grad as in training."""
+    y = layer(x)
+    y.backward(dy)
+    return y
+
+
+def zero_grads(layer, x):
+    for p in layer.parameters():
+        p.grad = None
+    x.grad = None
+
+
+def cpu_baseline(w, threads):
+    """Oracle fwd+bwd in fp32 on the host cores over a bounded sample of the workload."""
+    from oracle import latent_moe_ref as R
+    torch.set_num_threads(threads)
+    params, buffers, x, dy = inputs.make_inputs(w, seed=0, tokens=CPU_SAMPLE_TOKENS)
+    best = None
+    for i in range(3):
+        t0 = time.perf_counter()
+        R.layer_forward_backward(params, buffers, x, dy, w.K, z_loss_coef=w.router_z_loss_coef)
+        dt = time.perf_counter() - t0
+        if i > 0:
+            best = dt if best is None else min(best, dt)
+    return CPU_SAMPLE_TOKENS / best, best
+
+
+def run_reference(args, w):
+    """--impl reference: the CPU oracle (a port of the reference layer; the reference itself is Python/Triton
+    with no CPU path) timed on all host cores; each step = fwd+bwd over CPU_SAMPLE_TOKENS tokens."""
+    from oracle import latent_moe_ref as R
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    threads = os.cpu_count() or 1
+    torch.set_num_threads(threads)
+    params, buffers, x, dy = inputs.make_inputs(w, seed=0, tokens=CPU_SAMPLE_TOKENS)
+    for _ in range(max(1, min(args.warmup, 2))):
+        R.layer_forward_backward(params, buffers, x, dy, w.K, z_loss_coef=w.router_z_loss_coef)
+    steps = max(1, min(args.steps, 5))
+    t0 = time.perf_counter()
+    for _ in range(steps):
+        R.layer_forward_backward(params, buffers, x, dy, w.K, z_loss_coef=w.router_z_loss_coef)
+    dt = (time.perf_counter() - t0) / steps
+    value = CPU_SAMPLE_TOKENS / dt
+    sample = f"{CPU_SAMPLE_TOKENS} tokens of {w.name} per step, fp32 torch CPU, {steps} steps"
+    print(json.dumps({
+        "impl": "reference", "metric": METRIC, "value": value, "unit": "tokens/s", "n_gpus": args.gpus,
+        "steps": steps, "warmup": args.warmup, "ms_per_step": dt * 1e3, "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": workload_config(w, args.gpus, "cpu"),
+        "cpu_baseline": {"value": value, "unit": "tokens/s", "cores": threads, "kind": "port", "sample": sample},
+        "e2e": {"value": value, "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+    }))
+
+
+def workload_config(w, n_gpus, parallelism):
+    return {
+        "workload": f"{w.name}: LatentMoE FFN fwd+bwd, x[{w.batch},{w.seq},{w.D}] {w.dtype} per GPU, "
+                    f"E={w.E} top-{w.K} latent={w.L} F={w.F} Fs={w.Fs} n_shared={w.n_shared_experts}",
+        "tokens_per_step_per_gpu": w.T, "parallelism": parallelism,
+        "l2": "per-step working set (~1.5 GB of activations at cfg2) exceeds the 126 MB L2; no explicit flush",
+    }
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=30)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--workload", default=None)
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-e2e", action="store_true")
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 3)
+
+    wname = args.workload or ("cfg2" if args.gpus == 1 else "cfg5")
+    w = inputs.WORKLOADS[wname]
+    if args.impl == "reference":
+        run_reference(args, w)
+        return
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    dist = None
+    if world > 1:
+        import torch.distributed as dist
+        dist.init_process_group("nccl", device_id=dev)
+
+    from swamla_b200 import _cabi
+    lib = _cabi.load()
+    layer, x_host, dy_host = build_layer(w, seed=rank, device=dev)
+    x = x_host.to(dev).requires_grad_(True)
+    dy = dy_host.to(dev)
+
+    def barrier():
+        if dist is not None:
+            dist.barrier()
+
+    # ---------------- device-resident timing ----------------
+    for _ in range(args.warmup):
+        zero_grads(layer, x)
+        step(layer, x, dy)
+    torch.cuda.synchronize()
+    sampler = ClockSampler(local_rank)
+    if rank == 0:
+        sampler.start()
+        time.sleep(0.3)
+    barrier()
+    torch.cuda.synchronize()
+    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    launches0 = lib.lmoe_launch_count()
+    ev0.record()
+    for _ in range(args.steps):
+        zero_grads(layer, x)
+        step(layer, x, dy)
+    ev1.record()
+    torch.cuda.synchronize()
+    barrier()
+    launches = lib.lmoe_launch_count() - launches0
+    ms_total = ev0.elapsed_time(ev1)
+    clocks = sampler.stop() if rank == 0 else None
+    t = torch.tensor([ms_total], device=dev)
+    if dist is not None:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    ms_total = t.item()
+    ms_per_step = ms_total / args.steps
+    tokens_per_s = w.T * world / (ms_per_step * 1e-3)
+
+    # ---------------- end to end with host buffers ----------------
+    e2e = None
+    if not args.no_e2e:
+        xh, dyh = x_host.pin_memory(), dy_host.pin_memory()
+        yh = [torch.empty_like(x_host).pin_memory() for _ in range(2)]
+        auxh = torch.empty(2, dtype=torch.float32).pin_memory()
+        xd = [torch.empty_like(x) for _ in range(2)]
+        dyd = [torch.empty_like(dy) for _ in range(2)]
+        s_h2d, s_d2h = torch.cuda.Stream(), torch.cuda.Stream()
+        main_s = torch.cuda.current_stream()
+
+        def e2e_loop(n):
+            done = [None, None]      # compute finished with buffer b
+            copied = [None, None]    # D2H finished with buffer b
+            for i in range(n):
+                b = i & 1
+                with torch.cuda.stream(s_h2d):
+                    if done[b] is not None:
+                        s_h2d.wait_event(done[b])
+                    xd[b].copy_(xh, non_blocking=True)
+                    dyd[b].copy_(dyh, non_blocking=True)
+                    ready = torch.cuda.Event()
+                    ready.record(s_h2d)
+                main_s.wait_event(ready)
+                zero_grads(layer, x)
+                xin = xd[b].detach().requires_grad_(True)
+                y = layer(xin)
+                y.backward(dyd[b])
+                aux = layer.get_aux_loss().detach()
+                done[b] = torch.cuda.Event()
+                done[b].record(main_s)
+                with torch.cuda.stream(s_d2h):
+                    s_d2h.wait_event(done[b])
+                    if copied[b] is not None:
+                        s_d2h.wait_event(copied[b])
+                    yh[b].copy_(y.detach(), non_blocking=True)
+                    auxh[b:b + 1].copy_(aux.reshape(1), non_blocking=True)
+                    y.record_stream(s_d2h)
+                    copied[b] = torch.cuda.Event()
+                    copied[b].record(s_d2h)
+            torch.cuda.synchronize()
+
+        e2e_loop(args.warmup)
+        barrier()
+        torch.cuda.synchronize()
+        t0 = time.perf_counter()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        e2e_loop(args.steps)
+        e1.record()
+        torch.cuda.synchronize()
+        wall = (time.perf_counter() - t0) * 1e3
+        ms_e2e = max(e0.elapsed_time(e1), wall)   # the D2H stream may finish after the main stream's event
+        barrier()
+        t = torch.tensor([ms_e2e], device=dev)
+        if dist is not None:
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms_e2e = t.item() / args.steps
+        e2e = {"value": w.T * world / (ms_e2e * 1e-3), "unit": "tokens/s",
+               "h2d_bytes_per_step": 2 * x_host.numel() * 2, "d2h_bytes_per_step": x_host.numel() * 2 + 4,
+               "ms_per_step": ms_e2e}
+
+    if rank != 0:
+        if dist is not None:
+            dist.destroy_process_group()
+        return
+
+    pk = peaks()
+    flops_step = 3 * w.flops_fwd_per_token() * w.T        # per GPU
+    achieved = flops_step / (ms_per_step * 1e-3) / 1e12
+    roofline = {"bound": "tensor", "achieved": achieved, "peak": pk["bf16_tflops"], "unit": "TFLOP/s",
+                "frac": achieved / pk["bf16_tflops"], "traffic": None,
+                "peak_source": f"{pk['source']} cuBLAS bf16 burst (sustained {pk['bf16_tflops_sustained']})",
+                "scope": "whole fwd+bwd step per GPU: 3 x GEMM FLOPs of the forward (router, down, routed, up, shared)",
+                "flops_per_token_fwd_bwd": 3 * w.flops_fwd_per_token()}
+    out = {
+        "metric": METRIC, "value": tokens_per_s, "unit": "tokens/s", "n_gpus": world, "steps": args.steps,
+        "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+        "config": workload_config(w, world, "single GPU" if world == 1 else f"replicas x{world}"),
+        "clocks": clocks, "gpu_launches": int(launches), "roofline": roofline,
+    }
+    if e2e is not None:
+        out["e2e"] = e2e
+    if world == 1 and not args.no_cpu_baseline:
+        threads = os.cpu_count() or 1
+        v, secs = cpu_baseline(w, threads)
+        out["cpu_baseline"] = {"value": v, "unit": "tokens/s", "cores": threads, "kind": "port",
+                               "sample": f"{CPU_SAMPLE_TOKENS} tokens of {w.name}, fwd+bwd, fp32 torch CPU, "
+                                         f"best of 2 after 1 warm-up ({secs:.2f} s)"}
+    print(json.dumps(out))
+    if dist is not None:
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

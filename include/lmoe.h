@@ -77,6 +77,8 @@ typedef struct lmoe_route {
 /* ---- misc ---- */
 int lmoe_version(void);
 const char* lmoe_status_string(int code);
+/* Number of kernels this library has launched in this process so far (all entry points). */
+int64_t lmoe_launch_count(void);
 /* Upper bound of padded routed rows for a shape: roundup(T*K,128) + E*128. */
 int64_t lmoe_padded_rows(const lmoe_shape* s);
 /* Bytes of scratch lmoe_route_permute needs (block histograms). */

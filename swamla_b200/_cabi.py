@@ -38,6 +38,7 @@ RP = POINTER(Route)
 SIGNATURES = {
     "lmoe_version": (c_int, []),
     "lmoe_status_string": (c_char_p, [c_int]),
+    "lmoe_launch_count": (c_int64, []),
     "lmoe_padded_rows": (c_int64, [SP]),
     "lmoe_route_workspace_bytes": (c_size_t, [SP]),
     "lmoe_gemm_bf16": (c_int, [c_int, c_int, c_int, P, c_int64, c_int, P, c_int64, c_int, P, c_int64, c_int, c_int, P, P]),

@@ -5,10 +5,13 @@
 #include <mutex>
 
 #include "../../include/lmoe.h"
+#include "counters.h"
 #include "gemm.cuh"
 #include "gemm_host.h"
 
 namespace lmoe {
+
+std::atomic<long long> g_launch_count{0};
 
 // ---------------------------------------------------------------- driver entry point
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
@@ -67,6 +70,7 @@ static int launch_inst(const GemmParams& p, int grid, cudaStream_t stream) {
     configured = true;
   }
   kfn<<<grid, kGemmThreads, GemmSmem<BN>::kTotal, stream>>>(p);
+  count_launch();
   cudaError_t e = cudaGetLastError();
   return e == cudaSuccess ? 0 : static_cast<int>(e);
 }

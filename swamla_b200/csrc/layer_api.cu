@@ -3,6 +3,7 @@
 #include <cuda_runtime.h>
 
 #include "../../include/lmoe.h"
+#include "counters.h"
 #include "gemm.cuh"
 #include "gemm_host.h"
 #include "rowops.h"
@@ -66,6 +67,7 @@ int wgrad(const void* Aact, long long lda, int M, const void* Bact, long long ld
 }  // namespace
 
 extern "C" int lmoe_version(void) { return LMOE_VERSION; }
+extern "C" int64_t lmoe_launch_count(void) { return g_launch_count.load(std::memory_order_relaxed); }
 
 extern "C" const char* lmoe_status_string(int code) {
   switch (code) {

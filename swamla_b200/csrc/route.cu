@@ -5,6 +5,7 @@
 #include <stdint.h>
 
 #include "../../include/lmoe.h"
+#include "counters.h"
 
 namespace lmoe {
 
@@ -284,6 +285,7 @@ extern "C" int lmoe_gate_topk_fwd(const lmoe_shape* s, const float* logits, cons
   const int blocks = (s->T + kTopkWarpsPerBlock - 1) / kTopkWarpsPerBlock;
   gate_topk_kernel<<<blocks, kTopkWarpsPerBlock * 32, 0, st>>>(logits, expert_bias, s->T, s->E, s->K, sel, weights, lse,
                                                               z_partial);
+  count_launch(2);
   zloss_finalize_kernel<<<1, 256, 0, st>>>(z_partial, blocks, z_coef / static_cast<float>(s->T), z_loss);
   cudaError_t e = cudaGetLastError();
   return e == cudaSuccess ? 0 : static_cast<int>(e);
@@ -314,6 +316,7 @@ extern "C" int lmoe_route_permute(const lmoe_shape* s, const int32_t* sel, const
   const int chunks = (n + kChunk - 1) / kChunk;
   const int blocks = (chunks + kRouteWarps - 1) / kRouteWarps;
   int* chunk_hist = static_cast<int*>(workspace);
+  count_launch(4);
   route_hist_kernel<<<blocks, kRouteWarps * 32, 0, st>>>(sel, n, s->E, chunk_hist);
   route_scan_chunks_kernel<<<s->E, 256, 0, st>>>(chunk_hist, chunks, s->E, r->counts);
   route_offsets_kernel<<<1, LMOE_MAX_EXPERTS, 0, st>>>(r->counts, s->E, r->offsets, r->pad_offsets, r->tile_expert,
@@ -329,6 +332,7 @@ extern "C" int lmoe_router_bias_update(const lmoe_shape* s, const int32_t* count
   if (int rc = check_shape(s)) return rc;
   if (!counts || !expert_bias || !load_history) return LMOE_ERR_ARG;
   const float expected = static_cast<float>(s->T) * static_cast<float>(s->K) / static_cast<float>(s->E);
+  count_launch();
   bias_update_kernel<<<(s->E + 127) / 128, 128, 0, static_cast<cudaStream_t>(stream)>>>(counts, s->E, expected, gamma,
                                                                                         expert_bias, load_history);
   cudaError_t e = cudaGetLastError();

@@ -6,6 +6,7 @@
 #include <stdint.h>
 
 #include "../../include/lmoe.h"
+#include "counters.h"
 #include "rowops.h"
 
 namespace lmoe {
@@ -197,6 +198,7 @@ static inline int grid_for(long long work_items, int per_block) {
   return static_cast<int>(b);
 }
 static inline int last_error() {
+  count_launch();  // called once after every launch in this file
   cudaError_t e = cudaGetLastError();
   return e == cudaSuccess ? 0 : static_cast<int>(e);
 }

@@ -16,6 +16,12 @@ from ._cabi import Route, Shape, ptr
 
 BF = torch.bfloat16
 
+# When set to a dict, the next forward/backward stores its intermediates there (parity tests).
+DEBUG_SINK: Optional[dict] = None
+# Test hook: an int [T, K] tensor that replaces the top-k selection of the next forward, so that the
+# float path can be compared with a reference run whose near-tie selections differ.
+DEBUG_FORCE_SEL: Optional[torch.Tensor] = None
+
 
 def _stream() -> int:
     return torch.cuda.current_stream().cuda_stream
@@ -111,6 +117,10 @@ class LatentMoEFunction(torch.autograd.Function):
         z_loss = torch.empty(1, **f32)
         _cabi.call("lmoe_gate_topk_fwd", shape, ptr(logits), ptr(bias), float(z_coef), ptr(sel), ptr(weights), ptr(lse),
                    ptr(z_partial), ptr(z_loss), st)
+        if DEBUG_FORCE_SEL is not None:
+            sel = DEBUG_FORCE_SEL.to(device=dev, dtype=torch.int32).contiguous()
+            aff = torch.sigmoid(logits).gather(1, sel.long())
+            weights = (aff / (aff.sum(-1, keepdim=True) + 1e-9)).contiguous()
         route = RouteTables(shape, dev)
         ws = torch.empty(max(16, lib.lmoe_route_workspace_bytes(shape)), dtype=torch.uint8, device=dev)
         _cabi.call("lmoe_route_permute", shape, ptr(sel), route.struct, ptr(ws), ws.numel(), st)
@@ -141,6 +151,10 @@ class LatentMoEFunction(torch.autograd.Function):
         ctx.save_for_backward(xb, wg, wdn, wup, wgus, wds, wgu, wde, logits, sel, weights, lse, x_sorted, h1, hidden,
                               y_sorted, routed, h1_s, hidden_s)
         ctx.mark_non_differentiable(sel, route.counts)
+        if DEBUG_SINK is not None:
+            DEBUG_SINK.update(logits=logits, x_latent=x_latent, sel=sel, weights=weights, lse=lse, route=route,
+                              x_sorted=x_sorted, h1=h1, hidden=hidden, y_sorted=y_sorted, h1_s=h1_s, hidden_s=hidden_s,
+                              routed=routed, status=status)
         out = y if x.dtype == BF else y.to(x.dtype)
         return out, z_loss.reshape(()), sel, route.counts
 
@@ -205,6 +219,10 @@ class LatentMoEFunction(torch.autograd.Function):
         _cabi.call("lmoe_xproj_bwd", shape, ptr(d_h1_s), ptr(d_x_latent), ptr(d_logits), ptr(wgus), ptr(wdn), ptr(wg),
                    ptr(xb), ptr(dx), ptr(d_w_down), ptr(d_w_gate), ptr(status), st)
 
+        if DEBUG_SINK is not None:
+            DEBUG_SINK.update(d_routed=d_routed, d_hidden_s=d_hidden_s, d_h1_s=d_h1_s, d_y_sorted=d_y_sorted,
+                              d_weights=d_weights, d_hidden=d_hidden, d_h1=d_h1, d_x_sorted=d_x_sorted,
+                              d_x_latent=d_x_latent, d_logits=d_logits)
         dt = ctx.dtypes
         grads = (
             dx if dt[0] == BF else dx.to(dt[0]),

@@ -1,0 +1,184 @@
+"""Drop-in ``LatentMoELayer`` for Orolol/swamla (``models/moe.py:603-866``).
+
+Same constructor (one ``config`` object read with ``getattr``), same ``forward(x)`` signature,
+attributes, buffers and ``state_dict`` keys as the reference module, so it replaces it behind
+``create_moe_layer`` without touching ``swa_mla_model.py``.  The computation runs in bf16 on the
+hand-written sm_100a kernels of ``liblmoe.so``; there is no CPU or PyTorch fallback.
+"""
+from __future__ import annotations
+
+import torch
+import torch.nn as nn
+
+from . import _cabi
+from .functional import latent_moe, make_shape, _stream
+
+
+class SwiGLUExpert(nn.Module):
+    """Parameter container of the shared expert (``models/moe.py:32-69``): ``gate_up_proj`` [2*d_ff, d_model]
+    (gate = first half) and ``down_proj`` [d_model, d_ff].  The math runs inside the fused layer kernels."""
+
+    def __init__(self, d_model: int, d_ff: int, bias: bool = False):
+        super().__init__()
+        if bias:
+            raise NotImplementedError("config.bias=True is not supported on this path (no preset uses it)")
+        self.gate_up_proj = nn.Linear(d_model, 2 * d_ff, bias=False)
+        self.down_proj = nn.Linear(d_ff, d_model, bias=False)
+        nn.init.normal_(self.gate_up_proj.weight, mean=0.0, std=0.02)   # moe.py:48-49
+        nn.init.normal_(self.down_proj.weight, mean=0.0, std=0.02)
+
+
+class LatentBatchedExperts(nn.Module):
+    """Routed expert weights in the reference layout (``models/moe.py:562-600``):
+    ``gate_up_weight`` [E, latent, 2*d_ff] and ``down_weight`` [E, d_ff, latent]."""
+
+    def __init__(self, n_experts: int, latent_dim: int, d_ff: int, bias: bool = False):
+        super().__init__()
+        if bias:
+            raise NotImplementedError("config.bias=True is not supported on this path (no preset uses it)")
+        self.n_experts, self.latent_dim, self.d_ff = n_experts, latent_dim, d_ff
+        self.gate_up_weight = nn.Parameter(torch.empty(n_experts, latent_dim, 2 * d_ff))
+        self.down_weight = nn.Parameter(torch.empty(n_experts, d_ff, latent_dim))
+        self.register_parameter("gate_up_bias", None)
+        self.register_parameter("down_bias", None)
+        nn.init.normal_(self.gate_up_weight, mean=0.0, std=0.02)         # moe.py:599-600
+        nn.init.normal_(self.down_weight, mean=0.0, std=0.02)
+
+
+class AuxLossFreeRouter(nn.Module):
+    """Router state (``models/moe.py:156-291``): the gate weight, the selection bias and the load
+    statistics.  Top-k runs inside the layer kernels; the bias update reuses the routing histogram."""
+
+    def __init__(self, d_model: int, n_experts: int, top_k: int, bias_update_gamma: float = 0.001,
+                 z_loss_coef: float = 0.001):
+        super().__init__()
+        self.n_experts, self.top_k = n_experts, top_k
+        self.gamma, self.z_loss_coef = bias_update_gamma, z_loss_coef
+        self.gate = nn.Linear(d_model, n_experts, bias=False)
+        self.register_buffer("expert_bias", torch.zeros(n_experts))
+        self.register_buffer("load_history", torch.zeros(n_experts))
+        self.register_buffer("update_count", torch.tensor(0))
+        nn.init.normal_(self.gate.weight, mean=0.0, std=0.01)            # moe.py:194
+        self._last_selected_experts = None   # int32 [T, K] of the last training forward
+        self._last_counts = None             # int32 [E] routing histogram of the same forward
+        self._last_num_tokens = None
+
+    def update_bias_from_last_forward(self):
+        """``models/moe.py:244-275``: bias -= gamma * sign(load - T*K/E), after backward."""
+        if self._last_counts is None:
+            return
+        counts, T = self._last_counts, self._last_num_tokens
+        shape = make_shape(T, 8, 64, self.n_experts, self.top_k, 64, 8)
+        if self.expert_bias.dtype != torch.float32 or self.load_history.dtype != torch.float32:
+            # inference-style casts of the buffers: update in fp32, store back
+            bias, hist = self.expert_bias.float(), self.load_history.float()
+            _cabi.call("lmoe_router_bias_update", shape, counts.data_ptr(), float(self.gamma), bias.data_ptr(),
+                       hist.data_ptr(), _stream())
+            self.expert_bias.copy_(bias)
+            self.load_history.copy_(hist)
+        else:
+            _cabi.call("lmoe_router_bias_update", shape, counts.data_ptr(), float(self.gamma),
+                       self.expert_bias.data_ptr(), self.load_history.data_ptr(), _stream())
+        self.update_count += 1
+        self._last_selected_experts = None
+        self._last_counts = None
+        self._last_num_tokens = None
+
+    def get_load_balance_stats(self) -> dict:
+        """``models/moe.py:277-291``."""
+        if self.update_count == 0:
+            return {"load_mean": 0, "load_std": 0, "load_ratio": 1}
+        load = self.load_history.float() / (self.update_count.float() + 1e-9)
+        load_normalized = load / (load.sum() + 1e-9)
+        return {
+            "load_mean": load_normalized.mean().item(),
+            "load_std": load_normalized.std().item(),
+            "load_min": load_normalized.min().item(),
+            "load_max": load_normalized.max().item(),
+            "load_ratio": (load_normalized.max() / (load_normalized.min() + 1e-9)).item(),
+        }
+
+
+class LatentMoELayer(nn.Module):
+    """LatentMoE feed-forward layer; see the module docstring.  ``models/moe.py:603-866``."""
+
+    def __init__(self, config):
+        super().__init__()
+        self.config = config
+        d_model = config.n_embd
+        latent_ratio = getattr(config, "latent_ratio", 4)
+        latent_dim = getattr(config, "latent_dim", None)
+        if latent_dim is None:
+            latent_dim = d_model // latent_ratio
+        base_n_experts = getattr(config, "n_experts", 32)
+        base_n_activated = getattr(config, "n_activated", 3)
+        latent_n_experts = getattr(config, "latent_n_experts", None)
+        latent_n_activated = getattr(config, "latent_n_activated", None)
+        # base values are scaled by latent_ratio unless explicit latent counts are given (moe.py:639-646)
+        n_experts = latent_n_experts if latent_n_experts is not None else base_n_experts * latent_ratio
+        n_activated = latent_n_activated if latent_n_activated is not None else base_n_activated * latent_ratio
+        n_shared = getattr(config, "n_shared_experts", 1)
+        expert_dim = getattr(config, "expert_dim", d_model)
+        bias = getattr(config, "bias", False)
+        z_loss_coef = getattr(config, "router_z_loss_coef", 0.001)
+        if bias:
+            raise NotImplementedError("config.bias=True is not supported on this path (no preset uses it)")
+        if n_shared != 1:
+            raise NotImplementedError("this path implements n_shared_experts == 1 (every preset uses 1)")
+
+        self.n_experts = n_experts
+        self.n_shared = n_shared
+        self.n_activated = n_activated
+        self.d_model = d_model
+        self.latent_dim = latent_dim
+        self.expert_dim = expert_dim
+        self.latent_ratio = d_model // latent_dim
+
+        self.down_proj = nn.Linear(d_model, latent_dim, bias=False)
+        self.up_proj = nn.Linear(latent_dim, d_model, bias=False)
+        nn.init.normal_(self.down_proj.weight, mean=0.0, std=0.02)        # moe.py:666-667
+        nn.init.normal_(self.up_proj.weight, mean=0.0, std=0.02)
+        self.shared_experts = nn.ModuleList([SwiGLUExpert(d_model, expert_dim, bias=False) for _ in range(n_shared)])
+        preserve = getattr(config, "latent_preserve_expert_dim", False)
+        latent_expert_dim = expert_dim if preserve else expert_dim // latent_ratio   # moe.py:680-685
+        self.latent_expert_dim = latent_expert_dim
+        self.experts = LatentBatchedExperts(n_experts, latent_dim, latent_expert_dim, bias=False)
+        self.router = AuxLossFreeRouter(d_model=d_model, n_experts=n_experts, top_k=n_activated, z_loss_coef=z_loss_coef)
+        self.dropout = nn.Dropout(getattr(config, "dropout", 0.0))
+        self.aux_loss = torch.tensor(0.0)
+
+        if latent_dim % 64 or latent_expert_dim % 64 or d_model % 8 or expert_dim % 8 or n_experts % 8:
+            raise ValueError("kernel constraints: latent_dim and routed expert dim multiples of 64; "
+                             "n_embd, expert_dim and the expert count multiples of 8")
+        if n_experts > 256 or n_activated > 32:
+            raise ValueError("kernel constraints: at most 256 routed experts and top-32")
+
+    def forward(self, x: torch.Tensor) -> torch.Tensor:
+        batch_size, seq_len, d_model = x.shape
+        x_flat = x.reshape(-1, d_model)
+        shared = self.shared_experts[0]
+        y, z_loss, sel, counts = latent_moe(
+            x_flat, self.router.gate.weight, self.down_proj.weight, self.up_proj.weight,
+            shared.gate_up_proj.weight, shared.down_proj.weight,
+            self.experts.gate_up_weight, self.experts.down_weight,
+            self.router.expert_bias, self.n_activated, self.router.z_loss_coef)
+        self.aux_loss = z_loss                                            # moe.py:719
+        if self.training:                                                 # moe.py:237-240
+            self.router._last_selected_experts = sel
+            self.router._last_counts = counts
+            self.router._last_num_tokens = x_flat.shape[0]
+        y = self.dropout(y)                                               # moe.py:732
+        return y.view(batch_size, seq_len, d_model)
+
+    def get_aux_loss(self) -> torch.Tensor:
+        return self.aux_loss
+
+    def get_load_balance_stats(self) -> dict:
+        return self.router.get_load_balance_stats()
+
+
+def create_moe_layer(config, use_latent: bool = False):
+    """``models/moe.py:869-882``.  Only the latent branch is provided by this package."""
+    if use_latent or getattr(config, "use_latent_moe", False):
+        return LatentMoELayer(config)
+    raise NotImplementedError("the non-latent MoELayer is outside this package; use the reference's")
