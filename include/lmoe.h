@@ -88,14 +88,19 @@ size_t lmoe_route_workspace_bytes(const lmoe_shape* s);
  * C[M,N] = A[M,K] * B[N,K]^T with fp32 accumulation in tensor memory.
  *   a_mn = 0: A stored [M,K] row-major (lda = row stride);  a_mn = 1: A stored [K,M] row-major.
  *   b_mn = 0: B stored [N,K] row-major (an nn.Linear weight); b_mn = 1: B stored [K,N] row-major.
- *   c_type: LMOE_BF16 or LMOE_F32.  split_k > 1 requires c_type = LMOE_F32 and ADDS into C.
+ *   c_type: LMOE_BF16 or LMOE_F32.  split_k > 1 divides the contraction among split_k tiles whose fp32
+ *   partial results go to `workspace` (lmoe_gemm_workspace_bytes) and are then summed in a fixed order.
  * Replaces the cuBLAS calls behind nn.Linear on this path (models/moe.py:63,69,217,722,728). */
+size_t lmoe_gemm_workspace_bytes(int M, int N, int split_k);
 int lmoe_gemm_bf16(int M, int N, int K, const void* A, int64_t lda, int a_mn, const void* B, int64_t ldb, int b_mn,
-                   void* C, int64_t ldc, int c_type, int split_k, int32_t* status, void* stream);
+                   void* C, int64_t ldc, int c_type, int split_k, void* workspace, size_t workspace_bytes,
+                   int32_t* status, void* stream);
 
-/* ---- forward ---- */
+/* ---- forward ----
+ * Two activations are kept side by side in one buffer so that their weight gradients become one GEMM:
+ *   act_cat[T, L+Fs] bf16: columns [0,L) = routed (combined expert output), [L,L+Fs) = hidden_s. */
 
-/* Gate logits (fp32) and latent down-projection (bf16) from one read of x.
+/* Gate logits (fp32) and latent down-projection (bf16).
  * x[T,D] bf16, w_gate[E,D] bf16, w_down[L,D] bf16 -> logits[T,E] f32, x_latent[T,L] bf16.
  * Replaces models/moe.py:217 (router.gate) and models/moe.py:722 (down_proj). */
 int lmoe_xproj_fwd(const lmoe_shape* s, const void* x, const void* w_gate, const void* w_down, float* logits,
@@ -125,37 +130,41 @@ int lmoe_experts_fwd(const lmoe_shape* s, const void* x_latent, const void* w_ga
                      void* stream);
 
 /* Shared expert, first half: h1_s = x * w_gate_up_s^T, hidden_s = silu(gate) * up.
- * x[T,D], w_gate_up_s[2Fs,D] -> h1_s[T,2Fs], hidden_s[T,Fs] (bf16).
+ * x[T,D], w_gate_up_s[2Fs,D] -> h1_s[T,2Fs] bf16, hidden_s = act_cat[:, L:].
  * Replaces models/moe.py:63-67 (SwiGLUExpert.forward). */
-int lmoe_shared_gateup_fwd(const lmoe_shape* s, const void* x, const void* w_gate_up_s, void* h1_s, void* hidden_s,
+int lmoe_shared_gateup_fwd(const lmoe_shape* s, const void* x, const void* w_gate_up_s, void* h1_s, void* act_cat,
                            int32_t* status, void* stream);
 
 /* Weighted combine, latent up-projection, shared down-projection and the final add:
- *   routed[t] = sum_k weights[t,k] * y_sorted[pos[t*K+k]]
- *   y = hidden_s * w_down_s^T + routed * w_up^T
- * -> routed[T,L] bf16, y[T,D] bf16.
+ *   routed[t] = sum_k weights[t,k] * y_sorted[pos[t*K+k]]   -> act_cat[:, :L]
+ *   y = hidden_s * w_down_s^T + routed * w_up^T             -> y[T,D] bf16
  * Replaces models/moe.py:837, 778-782 (scatter + sum), 728 (up_proj), 69 (shared down_proj), 731. */
 int lmoe_combine_out_fwd(const lmoe_shape* s, const void* y_sorted, const lmoe_route* r, const float* weights,
-                         const void* hidden_s, const void* w_down_s, const void* w_up, void* routed, void* y,
-                         int32_t* status, void* stream);
+                         void* act_cat, const void* w_down_s, const void* w_up, void* y, int32_t* status, void* stream);
 
 /* ---- backward (adjoints of the lines cited above; the reference defines them only through
- *      autograd, and not at all for its grouped GEMM) ---- */
+ *      autograd, and not at all for its grouped GEMM) ----
+ * The three gradients that flow back into x-side GEMMs are kept side by side:
+ *   dgrad_cat[T, 2Fs+L+E] bf16: columns [0,2Fs) = d_h1_s, [2Fs,2Fs+L) = d_x_latent, then d_logits.
+ * Weight gradients of the dense linears are written (not accumulated) as `grad_type` (LMOE_F32 for
+ * fp32 master weights, LMOE_BF16); split-K partials go to `workspace` (lmoe_wgrad_workspace_bytes). */
+size_t lmoe_wgrad_workspace_bytes(const lmoe_shape* s);
 
 /* dgrad of the output stage: d_routed[T,L] = dy * w_up, d_hidden_s[T,Fs] = dy * w_down_s. */
 int lmoe_combine_out_bwd_dgrad(const lmoe_shape* s, const void* dy, const void* w_up, const void* w_down_s,
                                void* d_routed, void* d_hidden_s, int32_t* status, void* stream);
-/* wgrad of the output stage (ADDS into fp32): d_w_up[D,L] += dy^T routed, d_w_down_s[D,Fs] += dy^T hidden_s. */
-int lmoe_combine_out_bwd_wgrad(const lmoe_shape* s, const void* dy, const void* routed, const void* hidden_s,
-                               float* d_w_up, float* d_w_down_s, int32_t* status, void* stream);
+/* wgrad of the output stage, one GEMM dy^T * act_cat: d_w_up[D,L] = dy^T routed, d_w_down_s[D,Fs] = dy^T hidden_s. */
+int lmoe_combine_out_bwd_wgrad(const lmoe_shape* s, const void* dy, const void* act_cat, void* d_w_up,
+                               void* d_w_down_s, int grad_type, void* workspace, size_t workspace_bytes,
+                               int32_t* status, void* stream);
 /* Adjoint of the weighted combine, in the padded layout:
  *   d_y_sorted[row] = weights[t,k] * d_routed[t];  d_weights[t,k] = <d_routed[t], y_sorted[row]>. */
 int lmoe_combine_bwd(const lmoe_shape* s, const void* d_routed, const void* y_sorted, const float* weights,
                      const lmoe_route* r, void* d_y_sorted, float* d_weights, void* stream);
-/* SwiGLU adjoint: h1[R,2H] (gate | up), d_hidden[R,H] -> d_h1[R,2H]; rows = R.  If n_rows_dev is
- * non-null the row count is read on the device as 128 * n_rows_dev[0] (padded routed rows). */
-int lmoe_swiglu_bwd(int64_t rows, int H, const void* h1, const void* d_hidden, void* d_h1, const int32_t* n_tiles_dev,
-                    void* stream);
+/* SwiGLU adjoint: h1[R,2H] (gate | up), d_hidden[R,H] -> d_h1[R,2H] with row stride ld_d_h1 elements.
+ * If n_tiles_dev is non-null the row count is read on the device as 128 * n_tiles_dev[0]. */
+int lmoe_swiglu_bwd(int64_t rows, int H, const void* h1, const void* d_hidden, void* d_h1, int64_t ld_d_h1,
+                    const int32_t* n_tiles_dev, void* stream);
 /* Routed dgrads: d_hidden = d_y_sorted * w_down[e]^T, d_h1 = swiglu'(h1, d_hidden),
  * d_x_sorted = d_h1 * w_gate_up[e]^T.  All in the padded layout. */
 int lmoe_experts_bwd_dgrad(const lmoe_shape* s, const void* d_y_sorted, const void* h1, const void* w_gate_up,
@@ -166,23 +175,20 @@ int lmoe_experts_bwd_dgrad(const lmoe_shape* s, const void* d_y_sorted, const vo
 int lmoe_experts_bwd_wgrad(const lmoe_shape* s, const void* x_sorted, const void* d_h1, const void* hidden,
                            const void* d_y_sorted, const lmoe_route* r, void* d_w_gate_up, void* d_w_down,
                            int32_t* status, void* stream);
-/* Adjoint of the gather: d_x_latent[t] = sum_k d_x_sorted[pos[t*K+k]]. */
-int lmoe_unpermute_sum_bwd(const lmoe_shape* s, const void* d_x_sorted, const lmoe_route* r, void* d_x_latent,
+/* Adjoint of the gather: d_x_latent[t] = sum_k d_x_sorted[pos[t*K+k]]  -> dgrad_cat[:, 2Fs:2Fs+L]. */
+int lmoe_unpermute_sum_bwd(const lmoe_shape* s, const void* d_x_sorted, const lmoe_route* r, void* dgrad_cat,
                            void* stream);
 /* Router adjoint: gating-weight gradient through the normalisation and the sigmoid, plus the
- * z-loss term d_z * z_coef * 2 * lse * softmax / T (d_z: device float or NULL) -> d_logits[T,E] bf16. */
+ * z-loss term d_z * z_coef * 2 * lse * softmax / T (d_z: device float or NULL) -> dgrad_cat[:, 2Fs+L:]. */
 int lmoe_gate_topk_bwd(const lmoe_shape* s, const float* logits, const int32_t* sel, const float* weights,
-                       const float* d_weights, const float* lse, const float* d_z, float z_coef, void* d_logits,
+                       const float* d_weights, const float* lse, const float* d_z, float z_coef, void* dgrad_cat,
                        void* stream);
-/* Shared expert dgrad chain is lmoe_swiglu_bwd on (h1_s, d_hidden_s); its wgrad (ADDS, fp32):
- * d_w_gate_up_s[2Fs,D] += d_h1_s^T x. */
-int lmoe_shared_gateup_bwd_wgrad(const lmoe_shape* s, const void* d_h1_s, const void* x, float* d_w_gate_up_s,
-                                 int32_t* status, void* stream);
-/* dx[T,D] = d_h1_s * w_gate_up_s + d_x_latent * w_down + d_logits * w_gate (one GEMM, three K segments);
- * wgrads (ADD, fp32): d_w_down[L,D] += d_x_latent^T x, d_w_gate[E,D] += d_logits^T x. */
-int lmoe_xproj_bwd(const lmoe_shape* s, const void* d_h1_s, const void* d_x_latent, const void* d_logits,
-                   const void* w_gate_up_s, const void* w_down, const void* w_gate, const void* x, void* dx,
-                   float* d_w_down, float* d_w_gate, int32_t* status, void* stream);
+/* x-side backward.  dx[T,D] = d_h1_s * w_gate_up_s + d_x_latent * w_down + d_logits * w_gate (one GEMM,
+ * three K segments read from dgrad_cat); weight gradients from one GEMM dgrad_cat^T * x:
+ * d_w_gate_up_s[2Fs,D], d_w_down[L,D], d_w_gate[E,D]. */
+int lmoe_xside_bwd(const lmoe_shape* s, const void* dgrad_cat, const void* w_gate_up_s, const void* w_down,
+                   const void* w_gate, const void* x, void* dx, void* d_w_gate_up_s, void* d_w_down, void* d_w_gate,
+                   int grad_type, void* workspace, size_t workspace_bytes, int32_t* status, void* stream);
 
 /* ---- router bias update (after backward) ----
  * load = histogram(sel) (= counts); bias -= gamma * sign(load - T*K/E); history = .99 history + .01 load.

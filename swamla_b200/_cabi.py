@@ -41,23 +41,25 @@ SIGNATURES = {
     "lmoe_launch_count": (c_int64, []),
     "lmoe_padded_rows": (c_int64, [SP]),
     "lmoe_route_workspace_bytes": (c_size_t, [SP]),
-    "lmoe_gemm_bf16": (c_int, [c_int, c_int, c_int, P, c_int64, c_int, P, c_int64, c_int, P, c_int64, c_int, c_int, P, P]),
+    "lmoe_gemm_workspace_bytes": (c_size_t, [c_int, c_int, c_int]),
+    "lmoe_gemm_bf16": (c_int, [c_int, c_int, c_int, P, c_int64, c_int, P, c_int64, c_int, P, c_int64, c_int, c_int, P,
+                               c_size_t, P, P]),
+    "lmoe_wgrad_workspace_bytes": (c_size_t, [SP]),
     "lmoe_xproj_fwd": (c_int, [SP, P, P, P, P, P, P, P]),
     "lmoe_gate_topk_fwd": (c_int, [SP, P, P, c_float, P, P, P, P, P, P]),
     "lmoe_route_permute": (c_int, [SP, P, RP, P, c_size_t, P]),
     "lmoe_experts_fwd": (c_int, [SP, P, P, P, RP, P, P, P, P, P, P]),
     "lmoe_shared_gateup_fwd": (c_int, [SP, P, P, P, P, P, P]),
-    "lmoe_combine_out_fwd": (c_int, [SP, P, RP, P, P, P, P, P, P, P, P]),
+    "lmoe_combine_out_fwd": (c_int, [SP, P, RP, P, P, P, P, P, P, P]),
     "lmoe_combine_out_bwd_dgrad": (c_int, [SP, P, P, P, P, P, P, P]),
-    "lmoe_combine_out_bwd_wgrad": (c_int, [SP, P, P, P, P, P, P, P]),
+    "lmoe_combine_out_bwd_wgrad": (c_int, [SP, P, P, P, P, c_int, P, c_size_t, P, P]),
     "lmoe_combine_bwd": (c_int, [SP, P, P, P, RP, P, P, P]),
-    "lmoe_swiglu_bwd": (c_int, [c_int64, c_int, P, P, P, P, P]),
+    "lmoe_swiglu_bwd": (c_int, [c_int64, c_int, P, P, P, c_int64, P, P]),
     "lmoe_experts_bwd_dgrad": (c_int, [SP, P, P, P, P, RP, P, P, P, P, P]),
     "lmoe_experts_bwd_wgrad": (c_int, [SP, P, P, P, P, RP, P, P, P, P]),
     "lmoe_unpermute_sum_bwd": (c_int, [SP, P, RP, P, P]),
     "lmoe_gate_topk_bwd": (c_int, [SP, P, P, P, P, P, P, c_float, P, P]),
-    "lmoe_shared_gateup_bwd_wgrad": (c_int, [SP, P, P, P, P, P]),
-    "lmoe_xproj_bwd": (c_int, [SP, P, P, P, P, P, P, P, P, P, P, P, P]),
+    "lmoe_xside_bwd": (c_int, [SP, P, P, P, P, P, P, P, P, P, c_int, P, c_size_t, P, P]),
     "lmoe_router_bias_update": (c_int, [SP, P, c_float, P, P, P]),
     "lmoe_cast_f32_to_bf16": (c_int, [P, P, c_int64, P]),
     "lmoe_cast_bf16_to_f32": (c_int, [P, P, c_int64, P]),

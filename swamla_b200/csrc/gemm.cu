@@ -2,6 +2,7 @@
 #include <cuda.h>
 #include <cuda_runtime.h>
 
+#include <cstring>
 #include <mutex>
 
 #include "../../include/lmoe.h"
@@ -42,7 +43,7 @@ int num_sms() {
   return n;
 }
 
-// 2-D map over a row-major [outer, inner] tensor of 16-bit elements, 128-byte swizzle.
+// Operand map: 2-D over a row-major [outer, inner] tensor of 16-bit elements, 128-byte swizzle.
 static int encode_2d(CUtensorMap* map, const void* base, long long inner, long long outer, long long ld_elems,
                      int box_inner, int box_outer) {
   EncodeTiledFn fn = encode_fn();
@@ -59,17 +60,42 @@ static int encode_2d(CUtensorMap* map, const void* base, long long inner, long l
   return r == CUDA_SUCCESS ? 0 : LMOE_ERR_DRIVER;
 }
 
+// Output map: 3-D {cols, rows, planes}; one 128 x 32 slab per store.  bf16: 64-byte rows in shared
+// memory (SWIZZLE_64B); fp32: 128-byte rows (SWIZZLE_128B).
+static int encode_out(CUtensorMap* map, void* base, bool f32, long long cols, long long rows, long long planes,
+                      long long ld_elems, long long plane_elems) {
+  EncodeTiledFn fn = encode_fn();
+  if (!fn) return LMOE_ERR_DRIVER;
+  const int es = f32 ? 4 : 2;
+  if (planes <= 1) {
+    planes = 1;
+    plane_elems = rows * ld_elems;
+  }
+  if ((reinterpret_cast<uintptr_t>(base) & 15) != 0 || ((ld_elems * es) & 15) != 0 || ((plane_elems * es) & 15) != 0)
+    return LMOE_ERR_ALIGN;
+  if (cols <= 0 || rows <= 0) return LMOE_ERR_SHAPE;
+  cuuint64_t dims[3] = {static_cast<cuuint64_t>(cols), static_cast<cuuint64_t>(rows), static_cast<cuuint64_t>(planes)};
+  cuuint64_t strides[2] = {static_cast<cuuint64_t>(ld_elems) * es, static_cast<cuuint64_t>(plane_elems) * es};
+  cuuint32_t box[3] = {static_cast<cuuint32_t>(kSlabCols), static_cast<cuuint32_t>(kBM), 1};
+  cuuint32_t estr[3] = {1, 1, 1};
+  CUresult r = fn(map, f32 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, base, dims, strides,
+                  box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, f32 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_64B,
+                  CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? 0 : LMOE_ERR_DRIVER;
+}
+
 // ---------------------------------------------------------------- dispatch
 template <bool A_MN, bool B_MN, int BN, int EPI, int GRP>
 static int launch_inst(const GemmParams& p, int grid, cudaStream_t stream) {
   auto kfn = gemm_kernel<A_MN, B_MN, BN, EPI, GRP>;
+  constexpr int smem = GemmSmem<BN, EPI>::kTotal;
   static bool configured = false;
   if (!configured) {
-    cudaError_t e = cudaFuncSetAttribute(kfn, cudaFuncAttributeMaxDynamicSharedMemorySize, GemmSmem<BN>::kTotal);
+    cudaError_t e = cudaFuncSetAttribute(kfn, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
     if (e != cudaSuccess) return static_cast<int>(e);
     configured = true;
   }
-  kfn<<<grid, kGemmThreads, GemmSmem<BN>::kTotal, stream>>>(p);
+  kfn<<<grid, kGemmThreads, smem, stream>>>(p);
   count_launch();
   cudaError_t e = cudaGetLastError();
   return e == cudaSuccess ? 0 : static_cast<int>(e);
@@ -88,7 +114,6 @@ static int dispatch(const GemmCall& c, int bn, const GemmParams& p, int grid, cu
     // dense
     LMOE_CASE_MAJORS(EPI_BF16, GRP_NONE)
     LMOE_CASE_MAJORS(EPI_F32, GRP_NONE)
-    LMOE_CASE_MAJORS(EPI_F32_ATOMIC, GRP_NONE)
     LMOE_CASE_BN(0, 0, EPI_SWIGLU, GRP_NONE)
     // grouped over rows (routed forward and dgrads)
     LMOE_CASE_BN(0, 1, EPI_SWIGLU, GRP_M)
@@ -103,13 +128,10 @@ static int dispatch(const GemmCall& c, int bn, const GemmParams& p, int grid, cu
 
 int launch_gemm(const GemmCall& c) {
   if (c.nseg < 1 || c.nseg > 3 || !c.C || c.M <= 0 || c.N <= 0) return LMOE_ERR_ARG;
-  if (c.split_k > 1 && (c.epi != EPI_F32_ATOMIC || c.nseg != 1 || c.grp != GRP_NONE)) return LMOE_ERR_ARG;
+  if (c.split_k > 1 && (c.epi != EPI_F32 || c.nseg != 1 || c.grp != GRP_NONE)) return LMOE_ERR_ARG;
   const bool swiglu = (c.epi == EPI_SWIGLU);
   if ((c.N & 7) != 0) return LMOE_ERR_SHAPE;
-  const int elem_c = (c.epi == EPI_F32 || c.epi == EPI_F32_ATOMIC) ? 4 : 2;
-  if ((reinterpret_cast<uintptr_t>(c.C) & 15) != 0 || ((c.ldc * elem_c) & 15) != 0) return LMOE_ERR_ALIGN;
-  if (swiglu && (!c.C2 || (reinterpret_cast<uintptr_t>(c.C2) & 15) != 0 || ((c.ldc2 * 2) & 15) != 0))
-    return LMOE_ERR_ALIGN;
+  if (swiglu && ((c.N % kSlabCols) != 0 || !c.C2)) return LMOE_ERR_SHAPE;
 
   GemmParams p;
   memset(&p, 0, sizeof(p));
@@ -117,19 +139,20 @@ int launch_gemm(const GemmCall& c) {
   const int sms = num_sms();
   const long long rows_total = (c.grp == GRP_M) ? c.padded_rows : c.M;
   const int m_tiles = static_cast<int>((rows_total + kBM - 1) / kBM);
+  const int split = c.split_k > 1 ? c.split_k : 1;
   int bn = c.bn;
   if (bn == 0) {
     // N per tile: BN for plain epilogues, BN/2 output columns for SwiGLU (gate + up accumulators)
     const int n_eff = swiglu ? 2 * c.N : c.N;
-    const long long tiles256 = static_cast<long long>(m_tiles) * ((n_eff + 255) / 256) * (c.grp == GRP_K ? c.groups : 1) *
-                               (c.split_k > 1 ? c.split_k : 1);
+    const long long tiles256 =
+        static_cast<long long>(m_tiles) * ((n_eff + 255) / 256) * (c.grp == GRP_K ? c.groups : 1) * split;
     bn = (n_eff >= 256 && tiles256 >= sms) ? 256 : 128;
   }
   if (bn != 128 && bn != 256) return LMOE_ERR_ARG;
   const int n_per_tile = swiglu ? bn / 2 : bn;
   const int n_tiles = (c.N + n_per_tile - 1) / n_per_tile;
 
-  // ---- tensor maps ----
+  // ---- operand maps ----
   for (int s = 0; s < c.nseg; ++s) {
     if (!c.A[s] || !c.B[s]) return LMOE_ERR_ARG;
     int rc;
@@ -170,18 +193,34 @@ int launch_gemm(const GemmCall& c) {
     if (rc) return rc;
   }
 
+  // ---- output maps ----
+  {
+    const bool f32 = (c.epi == EPI_F32);
+    const long long cols = swiglu ? 2ll * c.N : c.N;
+    long long planes = 1, plane_elems = 0;
+    if (c.grp == GRP_K) {
+      planes = c.groups;
+      plane_elems = c.c_group_stride;
+    } else if (split > 1) {
+      planes = split;
+      plane_elems = c.c_group_stride;
+      if (plane_elems < static_cast<long long>(c.M) * c.ldc) return LMOE_ERR_ARG;
+    }
+    int rc = encode_out(&p.tmC, c.C, f32, cols, rows_total, planes, c.ldc, plane_elems);
+    if (rc) return rc;
+    if (swiglu) {
+      rc = encode_out(&p.tmC2, c.C2, false, c.N, rows_total, 1, c.ldc2, 0);
+      if (rc) return rc;
+    }
+  }
+
   p.nseg = c.nseg;
   p.M = c.M;
   p.N = c.N;
   p.m_tiles = m_tiles;
   p.n_tiles = n_tiles;
   p.groups = c.groups;
-  p.split_k = c.split_k > 1 ? c.split_k : 1;
-  p.C = c.C;
-  p.ldc = c.ldc;
-  p.c_group_stride = c.c_group_stride;
-  p.C2 = c.C2;
-  p.ldc2 = c.ldc2;
+  p.split_k = split;
   p.half = c.N;
   p.tile_expert = c.tile_expert;
   p.n_m_tiles = c.n_m_tiles;
@@ -192,25 +231,73 @@ int launch_gemm(const GemmCall& c) {
   if (c.grp == GRP_K && (!c.pad_offsets || c.groups <= 0)) return LMOE_ERR_ARG;
 
   long long total = static_cast<long long>(m_tiles) * n_tiles;
-  if (c.grp == GRP_NONE) total *= p.split_k;
+  if (c.grp == GRP_NONE) total *= split;
   if (c.grp == GRP_K) total *= c.groups;
   const int grid = static_cast<int>(total < sms ? total : sms);
   return dispatch(c, bn, p, grid, c.stream);
 }
 
+// ---------------------------------------------------------------- split-K reduction
+// out[r, c] = sum_s ws[s, r, c] for a row range of the workspace, written as fp32 or bf16 with its own
+// leading dimension.  Fixed summation order: deterministic.
+__global__ void __launch_bounds__(256)
+splitk_reduce_kernel(const float* __restrict__ ws, int planes, long long plane_elems, int ws_ld, int row0, int col0,
+                     int rows, int cols, void* __restrict__ out, long long out_ld, int out_f32) {
+  const int vec_per_row = cols / 4;
+  const long long total = static_cast<long long>(rows) * vec_per_row;
+  for (long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; i < total;
+       i += static_cast<long long>(gridDim.x) * blockDim.x) {
+    const int r = static_cast<int>(i / vec_per_row);
+    const int c = static_cast<int>(i - static_cast<long long>(r) * vec_per_row) * 4;
+    const float* src = ws + static_cast<long long>(row0 + r) * ws_ld + col0 + c;
+    float4 acc = *reinterpret_cast<const float4*>(src);
+    for (int s = 1; s < planes; ++s) {
+      const float4 v = *reinterpret_cast<const float4*>(src + s * plane_elems);
+      acc.x += v.x;
+      acc.y += v.y;
+      acc.z += v.z;
+      acc.w += v.w;
+    }
+    if (out_f32) {
+      *reinterpret_cast<float4*>(static_cast<float*>(out) + r * out_ld + c) = acc;
+    } else {
+      __nv_bfloat162 a = __floats2bfloat162_rn(acc.x, acc.y), b = __floats2bfloat162_rn(acc.z, acc.w);
+      *reinterpret_cast<uint2*>(static_cast<__nv_bfloat16*>(out) + r * out_ld + c) =
+          make_uint2(*reinterpret_cast<uint32_t*>(&a), *reinterpret_cast<uint32_t*>(&b));
+    }
+  }
+}
+
+int splitk_reduce(const float* ws, int planes, long long plane_elems, int ws_ld, int row0, int col0, int rows, int cols,
+                  void* out, long long out_ld, int out_f32, cudaStream_t stream) {
+  if ((cols & 3) != 0 || (col0 & 3) != 0 || (ws_ld & 3) != 0 || (out_ld & 3) != 0) return LMOE_ERR_SHAPE;
+  const long long total = static_cast<long long>(rows) * (cols / 4);
+  long long blocks = (total + 255) / 256;
+  if (blocks > 148 * 8) blocks = 148 * 8;
+  splitk_reduce_kernel<<<static_cast<int>(blocks), 256, 0, stream>>>(ws, planes, plane_elems, ws_ld, row0, col0, rows,
+                                                                    cols, out, out_ld, out_f32);
+  count_launch();
+  cudaError_t e = cudaGetLastError();
+  return e == cudaSuccess ? 0 : static_cast<int>(e);
+}
+
 }  // namespace lmoe
 
 // ---------------------------------------------------------------- C ABI
+extern "C" size_t lmoe_gemm_workspace_bytes(int M, int N, int split_k) {
+  if (split_k <= 1 || M <= 0 || N <= 0) return 0;
+  return static_cast<size_t>(split_k) * M * N * sizeof(float);
+}
+
 extern "C" int lmoe_gemm_bf16(int M, int N, int K, const void* A, int64_t lda, int a_mn, const void* B, int64_t ldb,
-                              int b_mn, void* C, int64_t ldc, int c_type, int split_k, int32_t* status, void* stream) {
+                              int b_mn, void* C, int64_t ldc, int c_type, int split_k, void* workspace,
+                              size_t workspace_bytes, int32_t* status, void* stream) {
   using namespace lmoe;
   if (!A || !B || !C || M <= 0 || N <= 0 || K <= 0) return LMOE_ERR_ARG;
   if (c_type != LMOE_BF16 && c_type != LMOE_F32) return LMOE_ERR_ARG;
-  if (split_k > 1 && c_type != LMOE_F32) return LMOE_ERR_ARG;
   GemmCall c;
   c.a_mn = a_mn ? 1 : 0;
   c.b_mn = b_mn ? 1 : 0;
-  c.epi = (split_k > 1) ? EPI_F32_ATOMIC : (c_type == LMOE_F32 ? EPI_F32 : EPI_BF16);
   c.grp = GRP_NONE;
   c.A[0] = A;
   c.lda[0] = lda;
@@ -219,10 +306,22 @@ extern "C" int lmoe_gemm_bf16(int M, int N, int K, const void* A, int64_t lda, i
   c.Kseg[0] = K;
   c.M = M;
   c.N = N;
-  c.C = C;
-  c.ldc = ldc;
-  c.split_k = split_k;
   c.status = status;
   c.stream = static_cast<cudaStream_t>(stream);
+  if (split_k > 1) {
+    if (!workspace || workspace_bytes < lmoe_gemm_workspace_bytes(M, N, split_k)) return LMOE_ERR_WORKSPACE;
+    if ((N & 3) != 0) return LMOE_ERR_SHAPE;
+    c.epi = EPI_F32;
+    c.C = workspace;
+    c.ldc = N;
+    c.c_group_stride = static_cast<long long>(M) * N;
+    c.split_k = split_k;
+    if (int rc = launch_gemm(c)) return rc;
+    return splitk_reduce(static_cast<const float*>(workspace), split_k, c.c_group_stride, N, 0, 0, M, N, C, ldc,
+                         c_type == LMOE_F32, c.stream);
+  }
+  c.epi = (c_type == LMOE_F32) ? EPI_F32 : EPI_BF16;
+  c.C = C;
+  c.ldc = ldc;
   return launch_gemm(c);
 }

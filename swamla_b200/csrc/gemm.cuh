@@ -1,13 +1,18 @@
 // Persistent, warp-specialised tcgen05 GEMM for sm_100a.
 //
-//   C[M,N] (+)= A[M,K] * B[N,K]^T      bf16 (or e4m3) operands, fp32 accumulation in tensor memory
+//   C[M,N] = A[M,K] * B[N,K]^T      bf16 operands, fp32 accumulation in tensor memory
 //
 // One CTA per SM walks a static tile schedule.  Roles:
 //   warp 0      TMA producer: fills a ring of shared-memory stages (A tile 128 x 64, B tile BN x 64)
 //   warp 1      MMA issuer: one thread issues tcgen05.mma (M=128, N=BN, K=16) and commits to mbarriers;
 //               also owns the tensor-memory allocation (two accumulators of BN columns)
-//   warps 2..5  epilogue: tcgen05.ld the finished accumulator (each warp owns 32 lanes = 32 rows),
-//               apply the epilogue and store; overlaps the next tile's main loop
+//   warps 2..9  epilogue, two groups of four warps: tcgen05.ld the finished accumulator (a warp owns the 32
+//               lanes = rows of its quadrant), convert, write 32-column slabs into a swizzled shared-memory
+//               staging buffer and hand it to a TMA store.  Group 0 takes the even slabs, group 1 the odd
+//               ones, each with its own buffer, named barrier and issuing thread, so one group's store
+//               drains while the other computes and every scheduler has two warps to hide latency with.
+//               The accumulator is released as soon as its last slab is in registers, so the next tile's
+//               main loop overlaps the stores
 //
 // Operand major-ness (template): K-major = the contraction index is contiguous in memory
 // (activations [rows,K], nn.Linear weights [N,K]); MN-major = the row/column index is contiguous
@@ -20,17 +25,22 @@
 //
 // K segments: up to three (A_i, B_i) pairs are accumulated into one tile, which fuses sums of
 // products such as hidden_s*Wd_s^T + routed*Wup^T without a concatenated copy.
+// Split-K (dense only): the k-blocks are divided among `split_k` tiles; slice s writes its partial
+// result to plane s of a [split_k, M, N] fp32 workspace (third coordinate of the output map) and a
+// separate deterministic kernel reduces the planes.
 #pragma once
 #include "common/ptx.cuh"
 
 namespace lmoe {
 
-enum : int { EPI_BF16 = 0, EPI_F32 = 1, EPI_F32_ATOMIC = 2, EPI_SWIGLU = 3, EPI_SWIGLU_BWD = 4 };
+enum : int { EPI_BF16 = 0, EPI_F32 = 1, EPI_SWIGLU = 2 };
 enum : int { GRP_NONE = 0, GRP_M = 1, GRP_K = 2 };
 
 constexpr int kBM = 128;
 constexpr int kBK = 64;  // 16-bit elements per k-block (one 128-byte swizzle row)
-constexpr int kGemmThreads = 192;
+constexpr int kGemmThreads = 320;
+constexpr int kEpiGroupThreads = 128;
+constexpr int kSlabCols = 32;  // output columns per epilogue slab
 
 // status codes written by a wait that gave up
 constexpr int kStatusProducerTimeout = 101;
@@ -40,40 +50,90 @@ constexpr int kStatusEpilogueTimeout = 103;
 struct alignas(64) GemmParams {
   CUtensorMap tmA[3];
   CUtensorMap tmB[3];
+  CUtensorMap tmC;   // 3-D {N, M, planes}: main output (h1 for SwiGLU)
+  CUtensorMap tmC2;  // SwiGLU: hidden output
   int seg_kiters[3];
   int nseg;
-  int M, N;              // output extent (per group for GRP_K)
+  int M, N;              // output extent (per group for GRP_K); SwiGLU: N = width of one half
   int m_tiles, n_tiles;  // tile counts (per group for GRP_K; upper bound for GRP_M)
   int groups;            // GRP_K: number of experts
-  int split_k;           // GRP_NONE: k-blocks are divided among split_k tiles which ADD into C
-  void* C;
-  long long ldc;
-  long long c_group_stride;  // GRP_K: elements between consecutive experts' outputs
-  void* C2;                  // EPI_SWIGLU: hidden output;  EPI_SWIGLU_BWD: h1 input
-  long long ldc2;
-  int half;                  // EPI_SWIGLU*: width of the gate half (F or Fs)
-  const int* tile_expert;    // GRP_M
-  const int* n_m_tiles;      // GRP_M: device scalar, number of 128-row tiles in use
-  int b_group_rows;          // GRP_M: rows of the stacked B tensor per expert
-  const int* pad_offsets;    // GRP_K
+  int split_k;           // GRP_NONE: number of k-slices (each writes its own output plane)
+  int half;              // SwiGLU: width of the gate half (F or Fs)
+  const int* tile_expert;  // GRP_M
+  const int* n_m_tiles;    // GRP_M: device scalar, number of 128-row tiles in use
+  int b_group_rows;        // GRP_M: rows of the stacked B tensor per expert
+  const int* pad_offsets;  // GRP_K
   int* status;
 };
 
-template <int BN>
+template <int BN, int EPI>
 struct GemmSmem {
   static constexpr int kABytes = kBM * kBK * 2;
   static constexpr int kBBytes = BN * kBK * 2;
   static constexpr int kStageBytes = kABytes + kBBytes;
-  static constexpr int kStages = (BN == 256) ? 4 : 6;
+  // one slab = 128 rows x 32 columns: 8 KB in bf16 (64-byte rows), 16 KB in fp32 (128-byte rows)
+  static constexpr int kSlabBytes = (EPI == EPI_F32) ? 16384 : 8192;
+  static constexpr int kStreams = (EPI == EPI_SWIGLU) ? 3 : 1;  // gate, up, hidden
+  static constexpr int kStagingBytes = 2 * kStreams * kSlabBytes;  // one buffer per epilogue group
   static constexpr int kBarrierBytes = 256;
-  static constexpr int kTotal = kStages * kStageBytes + kBarrierBytes + 1024;  // +1024: manual alignment
+  static constexpr int kBudget = 232448 - 1024 - kBarrierBytes - kStagingBytes;
+  static constexpr int kStagesMax = kBudget / kStageBytes;
+  static constexpr int kStages = kStagesMax > 6 ? 6 : kStagesMax;
+  static constexpr int kTotal = kStages * kStageBytes + kStagingBytes + kBarrierBytes + 1024;  // +1024: alignment
+  static_assert(kStages >= 3, "pipeline too shallow");
 };
 
-__device__ __forceinline__ float silu_f(float g) { return g / (1.0f + __expf(-g)); }
+// silu(g) = g * sigmoid(g) with the approximate exp2 / reciprocal units (error far below bf16 rounding).
+__device__ __forceinline__ float silu_f(float g) { return __fdividef(g, 1.0f + __expf(-g)); }
+
+// Named barrier over the 128 threads of one epilogue group (barrier id 1 or 2).
+__device__ __forceinline__ void epi_bar_sync(int id) { asm volatile("bar.sync %0, 128;" ::"r"(id) : "memory"); }
+// AND-reduction of a predicate over the 128 threads of one epilogue group.
+__device__ __forceinline__ bool epi_bar_all(int id, bool pred) {
+  uint32_t out;
+  asm volatile(
+      "{\n"
+      ".reg .pred p, q;\n"
+      "setp.ne.u32 p, %2, 0;\n"
+      "bar.red.and.pred q, %1, 128, p;\n"
+      "selp.u32 %0, 1, 0, q;\n"
+      "}\n"
+      : "=r"(out)
+      : "r"(id), "r"(static_cast<uint32_t>(pred))
+      : "memory");
+  return out != 0;
+}
+
+// 3-D tiled store; c0 = innermost (column) coordinate.
+__device__ __forceinline__ void tma_store_3d(const CUtensorMap* map, const void* smem_src, int c0, int c1, int c2) {
+  asm volatile("cp.async.bulk.tensor.3d.global.shared::cta.tile.bulk_group [%0, {%2, %3, %4}], [%1];" ::"l"(
+                   reinterpret_cast<uint64_t>(map)),
+               "r"(smem_u32(smem_src)), "r"(c0), "r"(c1), "r"(c2)
+               : "memory");
+}
+__device__ __forceinline__ void tma_store_wait_read_all() { asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory"); }
+
+// One 128 x 32 bf16 slab row (64 bytes) into a 64-byte-swizzled staging buffer: the 16-byte chunk j of
+// row r lands at chunk j ^ ((r >> 1) & 3), which is what a SWIZZLE_64B tensor map expects.
+__device__ __forceinline__ void stage_row_bf16(uint8_t* buf, int r, const uint32_t (&p)[16]) {
+  const int sw = (r >> 1) & 3;
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    *reinterpret_cast<uint4*>(buf + r * 64 + ((j ^ sw) << 4)) = make_uint4(p[4 * j], p[4 * j + 1], p[4 * j + 2], p[4 * j + 3]);
+  }
+}
+// One 128 x 32 fp32 slab row (128 bytes), 128-byte swizzle: chunk j of row r lands at chunk j ^ (r & 7).
+__device__ __forceinline__ void stage_row_f32(uint8_t* buf, int r, const float (&v)[32]) {
+  const int sw = r & 7;
+#pragma unroll
+  for (int j = 0; j < 8; ++j) {
+    *reinterpret_cast<float4*>(buf + r * 128 + ((j ^ sw) << 4)) = make_float4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
+  }
+}
 
 template <bool A_MN, bool B_MN, int BN, int EPI, int GRP>
 __global__ void __launch_bounds__(kGemmThreads, 1) gemm_kernel(const __grid_constant__ GemmParams p) {
-  using S = GemmSmem<BN>;
+  using S = GemmSmem<BN, EPI>;
   constexpr int STAGES = S::kStages;
   constexpr uint32_t TMEM_COLS = 2 * BN;
   static_assert(BN == 128 || BN == 256, "BN");
@@ -81,7 +141,8 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_kernel(const __grid_cons
 
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-  uint64_t* bar_full = reinterpret_cast<uint64_t*>(smem + STAGES * S::kStageBytes);
+  uint8_t* staging = smem + STAGES * S::kStageBytes;  // 1024-aligned: stage sizes are multiples of 1024
+  uint64_t* bar_full = reinterpret_cast<uint64_t*>(staging + S::kStagingBytes);
   uint64_t* bar_empty = bar_full + STAGES;
   uint64_t* bar_tfull = bar_empty + STAGES;
   uint64_t* bar_tempty = bar_tfull + 2;
@@ -98,7 +159,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_kernel(const __grid_cons
     }
     for (int i = 0; i < 2; ++i) {
       mbar_init(&bar_tfull[i], 1);
-      mbar_init(&bar_tempty[i], 4);
+      mbar_init(&bar_tempty[i], 8);
     }
     *abort_flag = 0;
     fence_mbar_init();
@@ -106,6 +167,8 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_kernel(const __grid_cons
       tma_prefetch_desc(&p.tmA[i]);
       tma_prefetch_desc(&p.tmB[i]);
     }
+    tma_prefetch_desc(&p.tmC);
+    if (kSwiglu) tma_prefetch_desc(&p.tmC2);
   }
   if (warp == 1) {
     tmem_alloc(tmem_slot, TMEM_COLS);
@@ -125,7 +188,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_kernel(const __grid_cons
   if (GRP == GRP_K) total_tiles = tiles_mn * p.groups;
 
   struct Tile {
-    int m0, nt, grp, kb, ke, krow0;
+    int m0, nt, plane, grp, kb, ke, krow0;
   };
   auto decode = [&](int id) {
     Tile t;
@@ -133,6 +196,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_kernel(const __grid_cons
     const int rem = id - outer * tiles_mn;
     t.m0 = (rem / p.n_tiles) * kBM;
     t.nt = rem % p.n_tiles;
+    t.plane = 0;
     t.grp = 0;
     t.kb = 0;
     t.ke = p.seg_kiters[0];
@@ -142,11 +206,13 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_kernel(const __grid_cons
         const int per = (p.seg_kiters[0] + p.split_k - 1) / p.split_k;
         t.kb = min(outer * per, p.seg_kiters[0]);
         t.ke = min(t.kb + per, p.seg_kiters[0]);
+        t.plane = outer;
       }
     } else if (GRP == GRP_M) {
       t.grp = p.tile_expert[t.m0 / kBM];
     } else {
       t.grp = outer;
+      t.plane = outer;
       const int r0 = p.pad_offsets[outer], r1 = p.pad_offsets[outer + 1];
       t.krow0 = r0;
       t.ke = (r1 - r0) / kBK;
@@ -266,113 +332,105 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_kernel(const __grid_cons
     }
   } else {
     // ============================= epilogue =============================
-    const int q = warp & 3;  // TMEM lane quadrant this warp may access
-    const int row_in_tile = q * 32 + lane;
+    const int q = warp & 3;             // TMEM lane quadrant this warp may access
+    const int group = (warp - 2) >> 2;  // 0: even slabs, 1: odd slabs
+    const int bar_id = 1 + group;
+    const int r = q * 32 + lane;        // row of the tile owned by this thread
+    const bool issuer = (((warp - 2) & 3) == 0) && lane == 0;
+    uint8_t* sbuf = staging + group * (S::kStreams * S::kSlabBytes);
     int acc = 0;
     uint32_t acc_phase = 0;
-    for (int id = blockIdx.x; id < total_tiles; id += gridDim.x) {
+    bool ok = true;
+    for (int id = blockIdx.x; id < total_tiles && ok; id += gridDim.x) {
       const Tile t = decode(id);
       const int nk = tile_kiters(t);
-      if (nk == 0 && EPI == EPI_F32_ATOMIC) continue;  // nothing to add
       if (nk > 0) {
-        if (!mbar_wait(&bar_tfull[acc], acc_phase, abort_flag, p.status, kStatusEpilogueTimeout)) break;
+        if (!mbar_wait(&bar_tfull[acc], acc_phase, abort_flag, p.status, kStatusEpilogueTimeout)) ok = false;
         tc_fence_after();
       }
-      const long long grow = t.m0 + row_in_tile;
-      const bool row_ok = (GRP == GRP_M) ? true : (grow < p.M);
+      // All threads of the group must agree before entering the (unbounded) named barriers below:
+      // a barrier-wide AND, which every thread reaches on every tile whatever its wait returned.
+      ok = epi_bar_all(bar_id, ok);
+      if (!ok) break;
       const uint32_t taddr = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + acc * BN;
-
-      if (EPI == EPI_SWIGLU) {
-        // accumulator columns [0,BN/2) = gate, [BN/2,BN) = up, for output columns nh..nh+BN/2
-        const int nh = t.nt * (BN / 2);
-        __nv_bfloat16* h1 = reinterpret_cast<__nv_bfloat16*>(p.C) + grow * p.ldc;
-        __nv_bfloat16* hid = reinterpret_cast<__nv_bfloat16*>(p.C2) + grow * p.ldc2;
-#pragma unroll 1
-        for (int c = 0; c < BN / 64; ++c) {
-          float g[32], u[32];
-          if (nk > 0) {
-            tmem_ld32(taddr + c * 32, g);
-            tmem_ld32(taddr + BN / 2 + c * 32, u);
-            tmem_ld_wait();
-          } else {
-#pragma unroll
-            for (int j = 0; j < 32; ++j) g[j] = u[j] = 0.f;
-          }
-          const int col = nh + c * 32;
-          if (row_ok && col < p.half) {
-            uint32_t pg[16], pu[16], ph[16];
-#pragma unroll
-            for (int j = 0; j < 16; ++j) {
-              // the saved gate/up are bf16; hidden is formed from the rounded values
-              const float g0 = bf16_round(g[2 * j]), g1 = bf16_round(g[2 * j + 1]);
-              const float u0 = bf16_round(u[2 * j]), u1 = bf16_round(u[2 * j + 1]);
-              pg[j] = pack_bf16x2(g0, g1);
-              pu[j] = pack_bf16x2(u0, u1);
-              ph[j] = pack_bf16x2(silu_f(g0) * u0, silu_f(g1) * u1);
-            }
-            uint4* dg = reinterpret_cast<uint4*>(h1 + col);
-            uint4* du = reinterpret_cast<uint4*>(h1 + p.half + col);
-            uint4* dh = reinterpret_cast<uint4*>(hid + col);
-#pragma unroll
-            for (int j = 0; j < 4; ++j) {
-              if (col + j * 8 < p.half) {
-                dg[j] = make_uint4(pg[4 * j], pg[4 * j + 1], pg[4 * j + 2], pg[4 * j + 3]);
-                du[j] = make_uint4(pu[4 * j], pu[4 * j + 1], pu[4 * j + 2], pu[4 * j + 3]);
-                dh[j] = make_uint4(ph[4 * j], ph[4 * j + 1], ph[4 * j + 2], ph[4 * j + 3]);
-              }
-            }
-          }
-        }
-      } else {
-        const int n0 = t.nt * BN;
-        const long long cbase = (GRP == GRP_K ? static_cast<long long>(t.grp) * p.c_group_stride : 0) + grow * p.ldc;
-#pragma unroll 1
-        for (int c = 0; c < BN / 32; ++c) {
-          float v[32];
-          if (nk > 0) {
-            tmem_ld32(taddr + c * 32, v);
-            tmem_ld_wait();
-          } else {
-#pragma unroll
-            for (int j = 0; j < 32; ++j) v[j] = 0.f;
-          }
-          const int col = n0 + c * 32;
-          if (row_ok && col < p.N) {
-            if (EPI == EPI_BF16) {
-              __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(p.C) + cbase + col;
-#pragma unroll
-              for (int j = 0; j < 4; ++j) {
-                if (col + j * 8 < p.N) {
-                  reinterpret_cast<uint4*>(dst)[j] =
-                      make_uint4(pack_bf16x2(v[8 * j], v[8 * j + 1]), pack_bf16x2(v[8 * j + 2], v[8 * j + 3]),
-                                 pack_bf16x2(v[8 * j + 4], v[8 * j + 5]), pack_bf16x2(v[8 * j + 6], v[8 * j + 7]));
-                }
-              }
-            } else if (EPI == EPI_F32) {
-              float* dst = reinterpret_cast<float*>(p.C) + cbase + col;
-#pragma unroll
-              for (int j = 0; j < 8; ++j) {
-                if (col + j * 4 < p.N)
-                  reinterpret_cast<float4*>(dst)[j] = make_float4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
-              }
-            } else if (EPI == EPI_F32_ATOMIC) {
-              float* dst = reinterpret_cast<float*>(p.C) + cbase + col;
-#pragma unroll
-              for (int j = 0; j < 32; ++j) {
-                if (col + j < p.N) atomicAdd(dst + j, v[j]);
-              }
-            }
-          }
-        }
-      }
-      if (nk > 0) {
+      const int n_per_tile = kSwiglu ? BN / 2 : BN;
+      const int n0 = t.nt * n_per_tile;
+      const int n_lim = kSwiglu ? p.half : p.N;
+      int slabs = (n_lim - n0 + kSlabCols - 1) / kSlabCols;
+      if (slabs > n_per_tile / kSlabCols) slabs = n_per_tile / kSlabCols;
+      // this group's slabs: group, group + 2, ...; the accumulator is released after the last one is loaded
+      const int last = ((slabs - 1 - group) >= 0) ? group + ((slabs - 1 - group) & ~1) : -1;
+      if (nk > 0 && last < 0) {
         tc_fence_before();
         __syncwarp();
         if (lane == 0) mbar_arrive(&bar_tempty[acc]);
+      }
+
+#pragma unroll 1
+      for (int c = group; c < slabs; c += 2) {
+        float v[32], u[32];
+        if (nk > 0) {
+          tmem_ld32(taddr + c * 32, v);
+          if (kSwiglu) tmem_ld32(taddr + BN / 2 + c * 32, u);
+          tmem_ld_wait();
+          if (c == last) {
+            // last slab of this warp is in registers: hand the accumulator back to the MMA warp
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&bar_tempty[acc]);
+          }
+        } else {
+#pragma unroll
+          for (int j = 0; j < 32; ++j) v[j] = u[j] = 0.f;
+        }
+        uint32_t pk[16], pu[16], ph[16];
+        if (EPI == EPI_BF16) {
+#pragma unroll
+          for (int j = 0; j < 16; ++j) pk[j] = pack_bf16x2(v[2 * j], v[2 * j + 1]);
+        } else if (EPI == EPI_SWIGLU) {
+#pragma unroll
+          for (int j = 0; j < 16; ++j) {
+            // gate/up are saved as bf16; hidden is formed from the rounded values (one packed convert
+            // per pair, unpacked again with shifts)
+            pk[j] = pack_bf16x2(v[2 * j], v[2 * j + 1]);
+            pu[j] = pack_bf16x2(u[2 * j], u[2 * j + 1]);
+            const float g0 = __uint_as_float(pk[j] << 16), g1 = __uint_as_float(pk[j] & 0xffff0000u);
+            const float u0 = __uint_as_float(pu[j] << 16), u1 = __uint_as_float(pu[j] & 0xffff0000u);
+            ph[j] = pack_bf16x2(silu_f(g0) * u0, silu_f(g1) * u1);
+          }
+        }
+        // the group's staging buffer was last read by the store of its previous slab
+        if (issuer) tma_store_wait_read_all();
+        epi_bar_sync(bar_id);
+        if (EPI == EPI_F32) {
+          stage_row_f32(sbuf, r, v);
+        } else if (EPI == EPI_BF16) {
+          stage_row_bf16(sbuf, r, pk);
+        } else {
+          stage_row_bf16(sbuf, r, pk);
+          stage_row_bf16(sbuf + S::kSlabBytes, r, pu);
+          stage_row_bf16(sbuf + 2 * S::kSlabBytes, r, ph);
+        }
+        fence_proxy_async_smem();
+        epi_bar_sync(bar_id);
+        if (issuer) {
+          const int col = n0 + c * kSlabCols;
+          if (kSwiglu) {
+            tma_store_3d(&p.tmC, sbuf, col, t.m0, 0);
+            tma_store_3d(&p.tmC, sbuf + S::kSlabBytes, p.half + col, t.m0, 0);
+            tma_store_3d(&p.tmC2, sbuf + 2 * S::kSlabBytes, col, t.m0, 0);
+          } else {
+            tma_store_3d(&p.tmC, sbuf, col, t.m0, t.plane);
+          }
+          tma_store_commit();
+        }
+      }
+      if (nk > 0) {
         acc ^= 1;
         if (acc == 0) acc_phase ^= 1;
       }
     }
+    if (issuer) tma_store_wait0();  // staging memory must outlive the last reads
   }
 
   // ---- teardown: every role falls through to here, also after an abort ----

@@ -22,10 +22,10 @@ struct GemmCall {
   int M = 0, N = 0;  // per group for GRP_K; for EPI_SWIGLU N = width of one half
   void* C = nullptr;
   long long ldc = 0;
-  long long c_group_stride = 0;
+  long long c_group_stride = 0;  // GRP_K: elements between experts' outputs; split-K: elements between planes
   void* C2 = nullptr;
   long long ldc2 = 0;
-  int split_k = 1;
+  int split_k = 1;               // >1 (GRP_NONE, EPI_F32): C is a [split_k, M, N] workspace of partial sums
   // grouping
   long long padded_rows = 0;         // GRP_M / GRP_K: rows of the padded routed layout (upper bound)
   int groups = 0;                    // number of experts
@@ -42,5 +42,9 @@ struct GemmCall {
 int launch_gemm(const GemmCall& c);
 
 int num_sms();
+
+// out[rows, cols] = sum over `planes` of ws[plane][row0 + r][col0 + c]; fp32 or bf16 output.
+int splitk_reduce(const float* ws, int planes, long long plane_elems, int ws_ld, int row0, int col0, int rows, int cols,
+                  void* out, long long out_ld, int out_f32, cudaStream_t stream);
 
 }  // namespace lmoe

@@ -1,5 +1,6 @@
 // Stage-level C-ABI entry points of the LatentMoE path, assembled from the tcgen05 GEMM launcher
 // and the row kernels.  Host code only: argument checks, GEMM descriptions, launches.
+#include <cuda_bf16.h>
 #include <cuda_runtime.h>
 
 #include "../../include/lmoe.h"
@@ -12,13 +13,15 @@ using namespace lmoe;
 
 namespace {
 
+typedef __nv_bfloat16 bf16;
+
 int check_dims(const lmoe_shape* s) {
   if (!s) return LMOE_ERR_ARG;
   if (s->T <= 0 || s->D <= 0 || s->L <= 0 || s->E <= 0 || s->K <= 0 || s->F <= 0 || s->Fs <= 0) return LMOE_ERR_SHAPE;
   if (s->E > LMOE_MAX_EXPERTS || s->K > LMOE_MAX_TOPK || s->K > s->E) return LMOE_ERR_SHAPE;
-  // L and F are contraction extents of grouped GEMMs (whole 64-element k-blocks per expert);
-  // every extent is a multiple of 8 so that rows stay 16-byte aligned.
-  if ((s->L % 64) != 0 || (s->F % 64) != 0 || (s->D % 8) != 0 || (s->Fs % 8) != 0 || (s->E % 8) != 0)
+  // L and F are contraction extents of grouped GEMMs (whole 64-element k-blocks per expert); Fs is cut
+  // into 32-column slabs by the SwiGLU epilogue; every extent is a multiple of 8 so rows stay 16-byte aligned.
+  if ((s->L % 64) != 0 || (s->F % 64) != 0 || (s->D % 8) != 0 || (s->Fs % 32) != 0 || (s->E % 8) != 0)
     return LMOE_ERR_SHAPE;
   if (s->n_shared != 1) return LMOE_ERR_SHAPE;
   return 0;
@@ -45,22 +48,25 @@ GemmCall dense(const void* A, long long lda, int a_mn, const void* B, long long 
   return c;
 }
 
-// Split factor for a weight gradient that contracts over `K` rows into m x n outputs.
+// Number of k-slices for a weight gradient with an M x N output contracting over K rows:
+// enough tiles for one wave, at least 8 k-blocks per slice.
 int wgrad_split(int M, int N, int K) {
-  const long long tiles = static_cast<long long>((M + 127) / 128) * ((N + 127) / 128);
+  const long long tiles = static_cast<long long>((M + 127) / 128) * ((N + 255) / 256);
   const int kiters = (K + kBK - 1) / kBK;
-  long long split = (2ll * num_sms() + tiles - 1) / tiles;
-  if (split > kiters / 4) split = kiters / 4;  // at least 4 k-blocks per split
+  long long split = (num_sms() + tiles / 2) / tiles;  // round to nearest
+  if (split > kiters / 8) split = kiters / 8;
+  if (split > 16) split = 16;
   if (split < 1) split = 1;
   return static_cast<int>(split);
 }
 
-int wgrad(const void* Aact, long long lda, int M, const void* Bact, long long ldb, int N, int K, float* dW,
-          int* status, void* stream) {
-  // dW[M,N] += Aact[K,M]^T * Bact[K,N]: both operands MN-major, contraction over rows.
-  GemmCall c = dense(Aact, lda, 1, Bact, ldb, 1, M, N, K, dW, N, EPI_F32_ATOMIC, status, stream);
-  c.split_k = wgrad_split(M, N, K);
-  if (c.split_k == 1) c.split_k = 1;
+// dW[M,N] (fp32 planes in `ws`) = Aact[K,M]^T * Bact[K,N]: both operands MN-major, contraction over rows.
+int wgrad_gemm(const void* Aact, long long lda, int M, const void* Bact, long long ldb, int N, int K, float* ws,
+               int split, int* status, void* stream) {
+  GemmCall c = dense(Aact, lda, 1, Bact, ldb, 1, M, N, K, ws, N, EPI_F32, status, stream);
+  c.split_k = split;
+  c.c_group_stride = static_cast<long long>(M) * N;
+  c.bn = 256;
   return launch_gemm(c);
 }
 
@@ -84,6 +90,16 @@ extern "C" const char* lmoe_status_string(int code) {
   }
 }
 
+extern "C" size_t lmoe_wgrad_workspace_bytes(const lmoe_shape* s) {
+  if (check_dims(s)) return 0;
+  // the two dense weight-gradient GEMMs run one after the other and share the workspace
+  const int Mx = 2 * s->Fs + s->L + s->E;
+  const size_t a = static_cast<size_t>(wgrad_split(Mx, s->D, s->T)) * Mx * s->D;
+  const int Ny = s->L + s->Fs;
+  const size_t b = static_cast<size_t>(wgrad_split(s->D, Ny, s->T)) * s->D * Ny;
+  return (a > b ? a : b) * sizeof(float);
+}
+
 // ------------------------------------------------------------------ forward
 extern "C" int lmoe_xproj_fwd(const lmoe_shape* s, const void* x, const void* w_gate, const void* w_down, float* logits,
                               void* x_latent, int32_t* status, void* stream) {
@@ -96,12 +112,12 @@ extern "C" int lmoe_xproj_fwd(const lmoe_shape* s, const void* x, const void* w_
 }
 
 extern "C" int lmoe_shared_gateup_fwd(const lmoe_shape* s, const void* x, const void* w_gate_up_s, void* h1_s,
-                                      void* hidden_s, int32_t* status, void* stream) {
+                                      void* act_cat, int32_t* status, void* stream) {
   if (int rc = check_dims(s)) return rc;
-  if (!x || !w_gate_up_s || !h1_s || !hidden_s) return LMOE_ERR_ARG;
+  if (!x || !w_gate_up_s || !h1_s || !act_cat) return LMOE_ERR_ARG;
   GemmCall c = dense(x, s->D, 0, w_gate_up_s, s->D, 0, s->T, s->Fs, s->D, h1_s, 2ll * s->Fs, EPI_SWIGLU, status, stream);
-  c.C2 = hidden_s;
-  c.ldc2 = s->Fs;
+  c.C2 = static_cast<bf16*>(act_cat) + s->L;  // hidden_s = act_cat[:, L:]
+  c.ldc2 = s->L + s->Fs;
   return launch_gemm(c);
 }
 
@@ -155,17 +171,20 @@ extern "C" int lmoe_experts_fwd(const lmoe_shape* s, const void* x_latent, const
 }
 
 extern "C" int lmoe_combine_out_fwd(const lmoe_shape* s, const void* y_sorted, const lmoe_route* r, const float* weights,
-                                    const void* hidden_s, const void* w_down_s, const void* w_up, void* routed, void* y,
-                                    int32_t* status, void* stream) {
+                                    void* act_cat, const void* w_down_s, const void* w_up, void* y, int32_t* status,
+                                    void* stream) {
   if (int rc = check_dims(s)) return rc;
-  if (!y_sorted || !r || !weights || !hidden_s || !w_down_s || !w_up || !routed || !y) return LMOE_ERR_ARG;
+  if (!y_sorted || !r || !weights || !act_cat || !w_down_s || !w_up || !y) return LMOE_ERR_ARG;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
-  if (int rc = combine_rows(y_sorted, r->pos, weights, s->T, s->K, s->L, routed, st)) return rc;
+  const long long ld = s->L + s->Fs;
+  bf16* routed = static_cast<bf16*>(act_cat);
+  bf16* hidden_s = routed + s->L;
+  if (int rc = combine_rows(y_sorted, r->pos, weights, s->T, s->K, s->L, routed, ld, st)) return rc;
   // y = hidden_s * Wd_s^T + routed * Wup^T : two K segments into one accumulator
-  GemmCall c = dense(hidden_s, s->Fs, 0, w_down_s, s->Fs, 0, s->T, s->D, s->Fs, y, s->D, EPI_BF16, status, stream);
+  GemmCall c = dense(hidden_s, ld, 0, w_down_s, s->Fs, 0, s->T, s->D, s->Fs, y, s->D, EPI_BF16, status, stream);
   c.nseg = 2;
   c.A[1] = routed;
-  c.lda[1] = s->L;
+  c.lda[1] = ld;
   c.B[1] = w_up;
   c.ldb[1] = s->L;
   c.Kseg[1] = s->L;
@@ -185,12 +204,22 @@ extern "C" int lmoe_combine_out_bwd_dgrad(const lmoe_shape* s, const void* dy, c
   return launch_gemm(b);
 }
 
-extern "C" int lmoe_combine_out_bwd_wgrad(const lmoe_shape* s, const void* dy, const void* routed, const void* hidden_s,
-                                          float* d_w_up, float* d_w_down_s, int32_t* status, void* stream) {
+extern "C" int lmoe_combine_out_bwd_wgrad(const lmoe_shape* s, const void* dy, const void* act_cat, void* d_w_up,
+                                          void* d_w_down_s, int grad_type, void* workspace, size_t workspace_bytes,
+                                          int32_t* status, void* stream) {
   if (int rc = check_dims(s)) return rc;
-  if (!dy || !routed || !hidden_s || !d_w_up || !d_w_down_s) return LMOE_ERR_ARG;
-  if (int rc = wgrad(dy, s->D, s->D, routed, s->L, s->L, s->T, d_w_up, status, stream)) return rc;
-  return wgrad(dy, s->D, s->D, hidden_s, s->Fs, s->Fs, s->T, d_w_down_s, status, stream);
+  if (!dy || !act_cat || !d_w_up || !d_w_down_s || !workspace) return LMOE_ERR_ARG;
+  if (grad_type != LMOE_F32 && grad_type != LMOE_BF16) return LMOE_ERR_ARG;
+  if (workspace_bytes < lmoe_wgrad_workspace_bytes(s)) return LMOE_ERR_WORKSPACE;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  // [d_w_up | d_w_down_s][D, L+Fs] = dy[T,D]^T * act_cat[T, L+Fs]
+  const int N = s->L + s->Fs;
+  const int split = wgrad_split(s->D, N, s->T);
+  float* ws = static_cast<float*>(workspace);
+  if (int rc = wgrad_gemm(dy, s->D, s->D, act_cat, N, N, s->T, ws, split, status, stream)) return rc;
+  const long long plane = static_cast<long long>(s->D) * N;
+  if (int rc = splitk_reduce(ws, split, plane, N, 0, 0, s->D, s->L, d_w_up, s->L, grad_type == LMOE_F32, st)) return rc;
+  return splitk_reduce(ws, split, plane, N, 0, s->L, s->D, s->Fs, d_w_down_s, s->Fs, grad_type == LMOE_F32, st);
 }
 
 extern "C" int lmoe_experts_bwd_dgrad(const lmoe_shape* s, const void* d_y_sorted, const void* h1, const void* w_gate_up,
@@ -223,7 +252,7 @@ extern "C" int lmoe_experts_bwd_dgrad(const lmoe_shape* s, const void* d_y_sorte
   a.status = status;
   a.stream = st;
   if (int rc = launch_gemm(a)) return rc;
-  if (int rc = lmoe_swiglu_bwd(P, s->F, h1, d_hidden, d_h1, r->n_tiles, stream)) return rc;
+  if (int rc = lmoe_swiglu_bwd(P, s->F, h1, d_hidden, d_h1, 2ll * s->F, r->n_tiles, stream)) return rc;
   // d_x_sorted[P,L] = d_h1[P,2F] * Wgu[e]^T : Wgu[e] is [L,2F] = [N,K] row-major -> K-major B
   GemmCall b = a;
   b.A[0] = d_h1;
@@ -279,34 +308,44 @@ extern "C" int lmoe_experts_bwd_wgrad(const lmoe_shape* s, const void* x_sorted,
   return launch_gemm(b);
 }
 
-extern "C" int lmoe_shared_gateup_bwd_wgrad(const lmoe_shape* s, const void* d_h1_s, const void* x, float* d_w_gate_up_s,
-                                            int32_t* status, void* stream) {
+extern "C" int lmoe_xside_bwd(const lmoe_shape* s, const void* dgrad_cat, const void* w_gate_up_s, const void* w_down,
+                              const void* w_gate, const void* x, void* dx, void* d_w_gate_up_s, void* d_w_down,
+                              void* d_w_gate, int grad_type, void* workspace, size_t workspace_bytes, int32_t* status,
+                              void* stream) {
   if (int rc = check_dims(s)) return rc;
-  if (!d_h1_s || !x || !d_w_gate_up_s) return LMOE_ERR_ARG;
-  return wgrad(d_h1_s, 2ll * s->Fs, 2 * s->Fs, x, s->D, s->D, s->T, d_w_gate_up_s, status, stream);
-}
-
-extern "C" int lmoe_xproj_bwd(const lmoe_shape* s, const void* d_h1_s, const void* d_x_latent, const void* d_logits,
-                              const void* w_gate_up_s, const void* w_down, const void* w_gate, const void* x, void* dx,
-                              float* d_w_down, float* d_w_gate, int32_t* status, void* stream) {
-  if (int rc = check_dims(s)) return rc;
-  if (!d_h1_s || !d_x_latent || !d_logits || !w_gate_up_s || !w_down || !w_gate || !x || !dx || !d_w_down || !d_w_gate)
+  if (!dgrad_cat || !w_gate_up_s || !w_down || !w_gate || !x || !dx || !d_w_gate_up_s || !d_w_down || !d_w_gate ||
+      !workspace)
     return LMOE_ERR_ARG;
+  if (grad_type != LMOE_F32 && grad_type != LMOE_BF16) return LMOE_ERR_ARG;
+  if (workspace_bytes < lmoe_wgrad_workspace_bytes(s)) return LMOE_ERR_WORKSPACE;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const int Fs2 = 2 * s->Fs;
+  const long long ld = static_cast<long long>(Fs2) + s->L + s->E;
+  const bf16* d_h1_s = static_cast<const bf16*>(dgrad_cat);
+  const bf16* d_x_latent = d_h1_s + Fs2;
+  const bf16* d_logits = d_x_latent + s->L;
   // dx = d_h1_s[T,2Fs] * Wgu_s[2Fs,D] + d_x_latent[T,L] * Wdown[L,D] + d_logits[T,E] * Wg[E,D]
-  GemmCall c = dense(d_h1_s, 2ll * s->Fs, 0, w_gate_up_s, s->D, 1, s->T, s->D, 2 * s->Fs, dx, s->D, EPI_BF16, status,
-                     stream);
+  GemmCall c = dense(d_h1_s, ld, 0, w_gate_up_s, s->D, 1, s->T, s->D, Fs2, dx, s->D, EPI_BF16, status, stream);
   c.nseg = 3;
   c.A[1] = d_x_latent;
-  c.lda[1] = s->L;
+  c.lda[1] = ld;
   c.B[1] = w_down;
   c.ldb[1] = s->D;
   c.Kseg[1] = s->L;
   c.A[2] = d_logits;
-  c.lda[2] = s->E;
+  c.lda[2] = ld;
   c.B[2] = w_gate;
   c.ldb[2] = s->D;
   c.Kseg[2] = s->E;
   if (int rc = launch_gemm(c)) return rc;
-  if (int rc = wgrad(d_x_latent, s->L, s->L, x, s->D, s->D, s->T, d_w_down, status, stream)) return rc;
-  return wgrad(d_logits, s->E, s->E, x, s->D, s->D, s->T, d_w_gate, status, stream);
+  // [d_Wgu_s ; d_Wdown ; d_Wg][2Fs+L+E, D] = dgrad_cat[T, 2Fs+L+E]^T * x[T,D]
+  const int M = static_cast<int>(ld);
+  const int split = wgrad_split(M, s->D, s->T);
+  float* ws = static_cast<float*>(workspace);
+  if (int rc = wgrad_gemm(dgrad_cat, ld, M, x, s->D, s->D, s->T, ws, split, status, stream)) return rc;
+  const long long plane = static_cast<long long>(M) * s->D;
+  const int f32 = grad_type == LMOE_F32;
+  if (int rc = splitk_reduce(ws, split, plane, s->D, 0, 0, Fs2, s->D, d_w_gate_up_s, s->D, f32, st)) return rc;
+  if (int rc = splitk_reduce(ws, split, plane, s->D, Fs2, 0, s->L, s->D, d_w_down, s->D, f32, st)) return rc;
+  return splitk_reduce(ws, split, plane, s->D, Fs2 + s->L, 0, s->E, s->D, d_w_gate, s->D, f32, st);
 }

@@ -14,8 +14,6 @@ constexpr int kMaxPerLane = LMOE_MAX_EXPERTS / 32;  // 8 scores per lane at E = 
 
 __device__ __forceinline__ float sigmoid_f(float x) { return 1.0f / (1.0f + expf(-x)); }
 
-// "better" = higher score, then lower expert index: the canonical tie rule.
-__device__ __forceinline__ bool better(float sa, int ia, float sb, int ib) { return sa > sb || (sa == sb && ia < ib); }
 
 // One warp per token row.  Lane l holds experts l, l+32, ...
 __global__ void __launch_bounds__(kTopkWarpsPerBlock * 32)
@@ -58,39 +56,41 @@ gate_topk_kernel(const float* __restrict__ logits, const float* __restrict__ bia
     lse2 = lse * lse;
     if (lane == 0) lse_out[t] = lse;
 
-    // K rounds of warp arg-max
+    // Order-preserving 32-bit keys: key(a) > key(b) <=> a > b (with -0 folded onto +0), so that the
+    // warp-wide maximum is one redux instruction.  Ties go to the lower expert index through a
+    // second redux (minimum index among the lanes that hold the maximum).
+    unsigned key[kMaxPerLane];
+#pragma unroll
+    for (int j = 0; j < kMaxPerLane; ++j) {
+      const unsigned u = __float_as_uint(score[j] + 0.0f);
+      key[j] = (lane + 32 * j < E) ? ((u & 0x80000000u) ? ~u : (u | 0x80000000u)) : 0u;
+    }
     float my_aff = 0.f;  // lane k keeps the affinity of the k-th winner
     int my_idx = 0;
     float aff_sum = 0.f;
     for (int k = 0; k < K; ++k) {
-      float bs = -CUDART_INF_F;
-      int bi = 0x7fffffff;
-      float ba = 0.f;
+      unsigned bk = 0u;
+      int bj = 0;
 #pragma unroll
       for (int j = 0; j < kMaxPerLane; ++j) {
-        const int e = lane + 32 * j;
-        if (e < E && better(score[j], e, bs, bi)) {
-          bs = score[j];
-          bi = e;
-          ba = aff[j];
+        if (key[j] > bk) {  // strict: the lowest j (lowest expert index) wins a tie inside the lane
+          bk = key[j];
+          bj = j;
         }
       }
+      const unsigned wmax = __reduce_max_sync(0xffffffffu, bk);
+      const unsigned cand = (bk == wmax) ? static_cast<unsigned>(lane + 32 * bj) : 0xffffffffu;
+      const int bi = static_cast<int>(__reduce_min_sync(0xffffffffu, cand));
+      const int wl = bi & 31;
+      float la = 0.f;
 #pragma unroll
-      for (int o = 16; o > 0; o >>= 1) {
-        const float os = __shfl_xor_sync(0xffffffffu, bs, o);
-        const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
-        const float oa = __shfl_xor_sync(0xffffffffu, ba, o);
-        if (better(os, oi, bs, bi)) {
-          bs = os;
-          bi = oi;
-          ba = oa;
-        }
-      }
-      // every lane now agrees on (bs, bi, ba); retire the winner
-      if ((bi & 31) == lane) {
+      for (int j = 0; j < kMaxPerLane; ++j)
+        if (j == bj) la = aff[j];
+      const float ba = __shfl_sync(0xffffffffu, la, wl);
+      if (lane == wl) {
 #pragma unroll
         for (int j = 0; j < kMaxPerLane; ++j)
-          if (j == (bi >> 5)) score[j] = -CUDART_INF_F;
+          if (j == (bi >> 5)) key[j] = 0u;  // retire the winner (every live key has its top bit pattern > 0)
       }
       if (lane == k) {
         my_aff = ba;
@@ -186,48 +186,68 @@ __global__ void __launch_bounds__(256) route_scan_chunks_kernel(int* __restrict_
   if (threadIdx.x == 0) counts[e] = carry_s;
 }
 
-// Pass 3: one block: offsets (canonical) and padded offsets over experts, tile -> expert table,
-// number of tiles in use, and -1 markers for the pad rows of every expert.
-__global__ void __launch_bounds__(LMOE_MAX_EXPERTS)
-route_offsets_kernel(const int* __restrict__ counts, int E, int* __restrict__ offsets, int* __restrict__ pad_offsets,
-                     int* __restrict__ tile_expert, int* __restrict__ n_tiles, int* __restrict__ row_src) {
-  __shared__ int s_cnt[LMOE_MAX_EXPERTS], s_off[LMOE_MAX_EXPERTS + 1], s_poff[LMOE_MAX_EXPERTS + 1];
-  const int e = threadIdx.x;
-  if (e < E) s_cnt[e] = counts[e];
-  __syncthreads();
-  if (e == 0) {
-    int a = 0, b = 0;
-    for (int i = 0; i < E; ++i) {
-      s_off[i] = a;
-      s_poff[i] = b;
-      a += s_cnt[i];
-      b += (s_cnt[i] + LMOE_ROW_PAD - 1) / LMOE_ROW_PAD * LMOE_ROW_PAD;
-    }
-    s_off[E] = a;
-    s_poff[E] = b;
-    n_tiles[0] = b / LMOE_ROW_PAD;
-  }
-  __syncthreads();
-  if (e < E) {
-    offsets[e] = s_off[e];
-    pad_offsets[e] = s_poff[e];
-    for (int t = s_poff[e] / LMOE_ROW_PAD; t < s_poff[e + 1] / LMOE_ROW_PAD; ++t) tile_expert[t] = e;
-    for (int r = s_poff[e] + s_cnt[e]; r < s_poff[e + 1]; ++r) row_src[r] = -1;
-  }
-  if (e == 0) {
-    offsets[E] = s_off[E];
-    pad_offsets[E] = s_poff[E];
-  }
-}
-
-// Pass 4: stable scatter.  Walks each chunk in index order again; rank inside the warp step by
-// match_any + popc, running per-expert cursors in shared memory.
+// Pass 3: stable scatter.  Every block first scans the per-expert counts in shared memory (canonical
+// and padded offsets); block b also publishes the tables of experts b, b + gridDim.x, ... (offsets,
+// tile -> expert entries, -1 markers of the pad rows).  Then each warp walks its chunk in index order
+// again: rank inside the warp step by match_any + popc, running per-expert cursors in shared memory.
 __global__ void __launch_bounds__(kRouteWarps * 32)
 route_scatter_kernel(const int* __restrict__ sel, int n, int E, const int* __restrict__ chunk_base,
-                     const int* __restrict__ offsets, const int* __restrict__ pad_offsets, int* __restrict__ perm,
+                     const int* __restrict__ counts, int* __restrict__ offsets, int* __restrict__ pad_offsets,
+                     int* __restrict__ tile_expert, int* __restrict__ n_tiles, int* __restrict__ perm,
                      int* __restrict__ pos, int* __restrict__ row_src) {
   __shared__ int cursor[kRouteWarps][LMOE_MAX_EXPERTS];
+  __shared__ int s_off[LMOE_MAX_EXPERTS + 1], s_poff[LMOE_MAX_EXPERTS + 1], s_cnt[LMOE_MAX_EXPERTS];
+  __shared__ int s_wsum[2][kRouteWarps];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int tid = threadIdx.x;  // blockDim.x == LMOE_MAX_EXPERTS == 256
+  {
+    const int c = (tid < E) ? counts[tid] : 0;
+    const int pc = (c + LMOE_ROW_PAD - 1) / LMOE_ROW_PAD * LMOE_ROW_PAD;
+    int ic = c, ip = pc;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+      const int a = __shfl_up_sync(0xffffffffu, ic, o), b = __shfl_up_sync(0xffffffffu, ip, o);
+      if (lane >= o) {
+        ic += a;
+        ip += b;
+      }
+    }
+    if (lane == 31) {
+      s_wsum[0][warp] = ic;
+      s_wsum[1][warp] = ip;
+    }
+    __syncthreads();
+    int wc = 0, wp = 0;
+    for (int w = 0; w < warp; ++w) {
+      wc += s_wsum[0][w];
+      wp += s_wsum[1][w];
+    }
+    if (tid < E) {
+      s_cnt[tid] = c;
+      s_off[tid] = wc + ic - c;
+      s_poff[tid] = wp + ip - pc;
+      if (tid == E - 1) {
+        s_off[E] = wc + ic;
+        s_poff[E] = wp + ip;
+      }
+    }
+    __syncthreads();
+  }
+  // publish the tables of the experts this block is responsible for
+  for (int e = blockIdx.x; e < E; e += gridDim.x) {
+    if (tid == 0) {
+      offsets[e] = s_off[e];
+      pad_offsets[e] = s_poff[e];
+    }
+    for (int t = s_poff[e] / LMOE_ROW_PAD + tid; t < s_poff[e + 1] / LMOE_ROW_PAD; t += blockDim.x) tile_expert[t] = e;
+    for (int r = s_poff[e] + s_cnt[e] + tid; r < s_poff[e + 1]; r += blockDim.x) row_src[r] = -1;
+  }
+  if (blockIdx.x == 0 && tid == 0) {
+    offsets[E] = s_off[E];
+    pad_offsets[E] = s_poff[E];
+    n_tiles[0] = s_poff[E] / LMOE_ROW_PAD;
+  }
+
   const int chunk = blockIdx.x * kRouteWarps + warp;
   const long long base = static_cast<long long>(chunk) * kChunk;
   if (base >= n) return;
@@ -238,11 +258,10 @@ route_scatter_kernel(const int* __restrict__ sel, int n, int E, const int* __res
     const bool valid = i < n;
     const int e = valid ? sel[i] : -1;
     const unsigned peers = __match_any_sync(0xffffffffu, e);
-    int rank = 0;
     if (valid) {
-      rank = cursor[warp][e] + __popc(peers & ((1u << lane) - 1u));
-      perm[offsets[e] + rank] = static_cast<int>(i);
-      const int prow = pad_offsets[e] + rank;
+      const int rank = cursor[warp][e] + __popc(peers & ((1u << lane) - 1u));
+      perm[s_off[e] + rank] = static_cast<int>(i);
+      const int prow = s_poff[e] + rank;
       pos[i] = prow;
       row_src[prow] = static_cast<int>(i);
     }
@@ -316,13 +335,12 @@ extern "C" int lmoe_route_permute(const lmoe_shape* s, const int32_t* sel, const
   const int chunks = (n + kChunk - 1) / kChunk;
   const int blocks = (chunks + kRouteWarps - 1) / kRouteWarps;
   int* chunk_hist = static_cast<int*>(workspace);
-  count_launch(4);
+  count_launch(3);
   route_hist_kernel<<<blocks, kRouteWarps * 32, 0, st>>>(sel, n, s->E, chunk_hist);
   route_scan_chunks_kernel<<<s->E, 256, 0, st>>>(chunk_hist, chunks, s->E, r->counts);
-  route_offsets_kernel<<<1, LMOE_MAX_EXPERTS, 0, st>>>(r->counts, s->E, r->offsets, r->pad_offsets, r->tile_expert,
-                                                      r->n_tiles, r->row_src);
-  route_scatter_kernel<<<blocks, kRouteWarps * 32, 0, st>>>(sel, n, s->E, chunk_hist, r->offsets, r->pad_offsets,
-                                                           r->perm, r->pos, r->row_src);
+  route_scatter_kernel<<<blocks, kRouteWarps * 32, 0, st>>>(sel, n, s->E, chunk_hist, r->counts, r->offsets,
+                                                           r->pad_offsets, r->tile_expert, r->n_tiles, r->perm, r->pos,
+                                                           r->row_src);
   cudaError_t e = cudaGetLastError();
   return e == cudaSuccess ? 0 : static_cast<int>(e);
 }

@@ -49,7 +49,7 @@ gather_rows_kernel(const uint4* __restrict__ src, const int* __restrict__ row_sr
 // out[t] = sum_k w[t,k] * y[pos[t*K+k]]   (w == nullptr: plain sum).  Slot order k = 0..K-1, fp32.
 __global__ void __launch_bounds__(kRowWarps * 32)
 combine_kernel(const uint4* __restrict__ y, const int* __restrict__ pos, const float* __restrict__ w, int T, int K,
-               int vec_per_row, uint4* __restrict__ out) {
+               int vec_per_row, uint4* __restrict__ out, long long out_ld_vec) {
   const int lane = threadIdx.x & 31;
   for (long long t = static_cast<long long>(blockIdx.x) * kRowWarps + (threadIdx.x >> 5); t < T;
        t += static_cast<long long>(gridDim.x) * kRowWarps) {
@@ -63,7 +63,7 @@ combine_kernel(const uint4* __restrict__ y, const int* __restrict__ pos, const f
 #pragma unroll
         for (int j = 0; j < 8; ++j) acc[j] = fmaf(wk, f[j], acc[j]);
       }
-      out[t * vec_per_row + v] = pack8(acc);
+      out[t * out_ld_vec + v] = pack8(acc);
     }
   }
 }
@@ -108,7 +108,7 @@ combine_bwd_kernel(const uint4* __restrict__ d_routed, const uint4* __restrict__
 //   d_u = d_h * silu(g);  d_g = d_h * u * sig(g) * (1 + g * (1 - sig(g))).
 __global__ void __launch_bounds__(256)
 swiglu_bwd_kernel(const uint4* __restrict__ h1, const uint4* __restrict__ d_hidden, uint4* __restrict__ d_h1,
-                  long long rows_host, const int* __restrict__ n_tiles, int vec_per_half) {
+                  long long rows_host, const int* __restrict__ n_tiles, int vec_per_half, long long out_ld_vec) {
   long long rows = rows_host;
   if (n_tiles) rows = min(rows, static_cast<long long>(n_tiles[0]) * LMOE_ROW_PAD);
   const long long total = rows * vec_per_half;
@@ -126,8 +126,8 @@ swiglu_bwd_kernel(const uint4* __restrict__ h1, const uint4* __restrict__ d_hidd
       du[j] = dh[j] * g[j] * sg;
       dg[j] = dh[j] * u[j] * sg * (1.0f + g[j] * (1.0f - sg));
     }
-    d_h1[r * 2 * vec_per_half + v] = pack8(dg);
-    d_h1[r * 2 * vec_per_half + vec_per_half + v] = pack8(du);
+    d_h1[r * out_ld_vec + v] = pack8(dg);
+    d_h1[r * out_ld_vec + vec_per_half + v] = pack8(du);
   }
 }
 
@@ -138,7 +138,7 @@ swiglu_bwd_kernel(const uint4* __restrict__ h1, const uint4* __restrict__ d_hidd
 __global__ void __launch_bounds__(kRowWarps * 32)
 gate_bwd_kernel(const float* __restrict__ logits, const int* __restrict__ sel, const float* __restrict__ w,
                 const float* __restrict__ d_w, const float* __restrict__ lse, const float* __restrict__ d_z,
-                float z_scale, int T, int E, int K, __nv_bfloat16* __restrict__ d_logits) {
+                float z_scale, int T, int E, int K, __nv_bfloat16* __restrict__ d_logits, long long out_ld) {
   __shared__ float rowbuf[kRowWarps][LMOE_MAX_EXPERTS];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const float dz = d_z ? d_z[0] * z_scale : 0.f;
@@ -169,7 +169,7 @@ gate_bwd_kernel(const float* __restrict__ logits, const int* __restrict__ sel, c
       rowbuf[warp][e_sel] += da * a * (1.0f - a);  // experts are distinct within a row
     }
     __syncwarp();
-    for (int e = lane; e < E; e += 32) d_logits[t * E + e] = __float2bfloat16_rn(rowbuf[warp][e]);
+    for (int e = lane; e < E; e += 32) d_logits[t * out_ld + e] = __float2bfloat16_rn(rowbuf[warp][e]);
     __syncwarp();
   }
 }
@@ -211,10 +211,11 @@ int gather_rows(const void* x_latent, const lmoe_route* r, int K, int L, long lo
   return last_error();
 }
 
-int combine_rows(const void* y_sorted, const int* pos, const float* w, int T, int K, int L, void* out, cudaStream_t st) {
-  if ((L & 7) != 0) return LMOE_ERR_SHAPE;
+int combine_rows(const void* y_sorted, const int* pos, const float* w, int T, int K, int L, void* out, long long out_ld,
+                 cudaStream_t st) {
+  if ((L & 7) != 0 || (out_ld & 7) != 0) return LMOE_ERR_SHAPE;
   combine_kernel<<<grid_for(T, kRowWarps), kRowWarps * 32, 0, st>>>(static_cast<const uint4*>(y_sorted), pos, w, T, K,
-                                                                    L / 8, static_cast<uint4*>(out));
+                                                                    L / 8, static_cast<uint4*>(out), out_ld / 8);
   return last_error();
 }
 
@@ -233,30 +234,33 @@ extern "C" int lmoe_combine_bwd(const lmoe_shape* s, const void* d_routed, const
   return last_error();
 }
 
-extern "C" int lmoe_swiglu_bwd(int64_t rows, int H, const void* h1, const void* d_hidden, void* d_h1,
+extern "C" int lmoe_swiglu_bwd(int64_t rows, int H, const void* h1, const void* d_hidden, void* d_h1, int64_t ld_d_h1,
                                const int32_t* n_tiles_dev, void* stream) {
   if (!h1 || !d_hidden || !d_h1 || rows <= 0 || H <= 0) return LMOE_ERR_ARG;
-  if ((H & 7) != 0) return LMOE_ERR_SHAPE;
+  if ((H & 7) != 0 || (ld_d_h1 & 7) != 0 || ld_d_h1 < 2 * H) return LMOE_ERR_SHAPE;
   swiglu_bwd_kernel<<<grid_for(rows * (H / 8), 256), 256, 0, static_cast<cudaStream_t>(stream)>>>(
       static_cast<const uint4*>(h1), static_cast<const uint4*>(d_hidden), static_cast<uint4*>(d_h1), rows, n_tiles_dev,
-      H / 8);
+      H / 8, ld_d_h1 / 8);
   return last_error();
 }
 
-extern "C" int lmoe_unpermute_sum_bwd(const lmoe_shape* s, const void* d_x_sorted, const lmoe_route* r, void* d_x_latent,
+extern "C" int lmoe_unpermute_sum_bwd(const lmoe_shape* s, const void* d_x_sorted, const lmoe_route* r, void* dgrad_cat,
                                       void* stream) {
-  if (!s || !d_x_sorted || !r || !d_x_latent) return LMOE_ERR_ARG;
-  return combine_rows(d_x_sorted, r->pos, nullptr, s->T, s->K, s->L, d_x_latent, static_cast<cudaStream_t>(stream));
+  if (!s || !d_x_sorted || !r || !dgrad_cat) return LMOE_ERR_ARG;
+  const long long ld = 2ll * s->Fs + s->L + s->E;
+  __nv_bfloat16* out = static_cast<__nv_bfloat16*>(dgrad_cat) + 2ll * s->Fs;
+  return combine_rows(d_x_sorted, r->pos, nullptr, s->T, s->K, s->L, out, ld, static_cast<cudaStream_t>(stream));
 }
 
 extern "C" int lmoe_gate_topk_bwd(const lmoe_shape* s, const float* logits, const int32_t* sel, const float* weights,
                                   const float* d_weights, const float* lse, const float* d_z, float z_coef,
-                                  void* d_logits, void* stream) {
-  if (!s || !logits || !sel || !weights || !d_weights || !lse || !d_logits) return LMOE_ERR_ARG;
+                                  void* dgrad_cat, void* stream) {
+  if (!s || !logits || !sel || !weights || !d_weights || !lse || !dgrad_cat) return LMOE_ERR_ARG;
   if (s->E > LMOE_MAX_EXPERTS || s->K > 32) return LMOE_ERR_SHAPE;
+  const long long ld = 2ll * s->Fs + s->L + s->E;
+  __nv_bfloat16* d_logits = static_cast<__nv_bfloat16*>(dgrad_cat) + 2ll * s->Fs + s->L;
   gate_bwd_kernel<<<grid_for(s->T, kRowWarps), kRowWarps * 32, 0, static_cast<cudaStream_t>(stream)>>>(
-      logits, sel, weights, d_weights, lse, d_z, z_coef / static_cast<float>(s->T), s->T, s->E, s->K,
-      static_cast<__nv_bfloat16*>(d_logits));
+      logits, sel, weights, d_weights, lse, d_z, z_coef / static_cast<float>(s->T), s->T, s->E, s->K, d_logits, ld);
   return last_error();
 }
 

@@ -39,16 +39,6 @@ def _as_bf16(t: torch.Tensor) -> torch.Tensor:
     return out
 
 
-def _to_dtype(t32: torch.Tensor, dtype: torch.dtype) -> torch.Tensor:
-    if dtype == torch.float32:
-        return t32
-    if dtype == BF:
-        out = torch.empty(t32.shape, dtype=BF, device=t32.device)
-        _cabi.call("lmoe_cast_f32_to_bf16", ptr(t32), ptr(out), t32.numel(), _stream())
-        return out
-    return t32.to(dtype)
-
-
 class RouteTables:
     """Device buffers behind an ``lmoe_route`` struct."""
 
@@ -134,14 +124,14 @@ class LatentMoEFunction(torch.autograd.Function):
         _cabi.call("lmoe_experts_fwd", shape, ptr(x_latent), ptr(wgu), ptr(wde), route.struct, ptr(x_sorted), ptr(h1),
                    ptr(hidden), ptr(y_sorted), ptr(status), st)
 
-        # shared expert and output
+        # shared expert and output; routed and hidden_s live side by side in act_cat[T, L+Fs]
         h1_s = torch.empty(T, 2 * Fs, **bf)
-        hidden_s = torch.empty(T, Fs, **bf)
-        _cabi.call("lmoe_shared_gateup_fwd", shape, ptr(xb), ptr(wgus), ptr(h1_s), ptr(hidden_s), ptr(status), st)
-        routed = torch.empty(T, L, **bf)
+        act_cat = torch.empty(T, L + Fs, **bf)
+        _cabi.call("lmoe_shared_gateup_fwd", shape, ptr(xb), ptr(wgus), ptr(h1_s), ptr(act_cat), ptr(status), st)
         y = torch.empty(T, D, **bf)
-        _cabi.call("lmoe_combine_out_fwd", shape, ptr(y_sorted), route.struct, ptr(weights), ptr(hidden_s), ptr(wds),
-                   ptr(wup), ptr(routed), ptr(y), ptr(status), st)
+        _cabi.call("lmoe_combine_out_fwd", shape, ptr(y_sorted), route.struct, ptr(weights), ptr(act_cat), ptr(wds),
+                   ptr(wup), ptr(y), ptr(status), st)
+        routed, hidden_s = act_cat[:, :L], act_cat[:, L:]
 
         ctx.shape = shape
         ctx.route = route
@@ -149,7 +139,7 @@ class LatentMoEFunction(torch.autograd.Function):
         ctx.status = status
         ctx.dtypes = [t.dtype for t in (x, w_gate, w_down, w_up, w_gate_up_s, w_down_s, w_gate_up, w_down_e)]
         ctx.save_for_backward(xb, wg, wdn, wup, wgus, wds, wgu, wde, logits, sel, weights, lse, x_sorted, h1, hidden,
-                              y_sorted, routed, h1_s, hidden_s)
+                              y_sorted, act_cat, h1_s)
         ctx.mark_non_differentiable(sel, route.counts)
         if DEBUG_SINK is not None:
             DEBUG_SINK.update(logits=logits, x_latent=x_latent, sel=sel, weights=weights, lse=lse, route=route,
@@ -160,30 +150,39 @@ class LatentMoEFunction(torch.autograd.Function):
 
     @staticmethod
     def backward(ctx, dy, d_z, _d_sel, _d_counts):
-        (xb, wg, wdn, wup, wgus, wds, wgu, wde, logits, sel, weights, lse, x_sorted, h1, hidden, y_sorted, routed, h1_s,
-         hidden_s) = ctx.saved_tensors
+        (xb, wg, wdn, wup, wgus, wds, wgu, wde, logits, sel, weights, lse, x_sorted, h1, hidden, y_sorted, act_cat,
+         h1_s) = ctx.saved_tensors
         shape, route, status = ctx.shape, ctx.route, ctx.status
         T, D, L, E, K, F, Fs = shape.T, shape.D, shape.L, shape.E, shape.K, shape.F, shape.Fs
         P = route.padded_rows
         dev = xb.device
         st = _stream()
+        lib = _cabi.load()
         bf = dict(dtype=BF, device=dev)
         f32 = dict(dtype=torch.float32, device=dev)
         if dy is None:
             dy = torch.zeros(T, D, **bf)
         dyb = _as_bf16(dy.reshape(T, D))
+        dt = ctx.dtypes
+        # dense linears share one gradient dtype (fp32 master weights or bf16 module)
+        lin_dtype = torch.float32 if any(d == torch.float32 for d in dt[1:6]) else BF
+        gtype = _cabi.F32 if lin_dtype == torch.float32 else _cabi.BF16
+        lin = dict(dtype=lin_dtype, device=dev)
+        ws = torch.empty(max(16, lib.lmoe_wgrad_workspace_bytes(shape)), dtype=torch.uint8, device=dev)
 
         # output stage
         d_routed = torch.empty(T, L, **bf)
         d_hidden_s = torch.empty(T, Fs, **bf)
         _cabi.call("lmoe_combine_out_bwd_dgrad", shape, ptr(dyb), ptr(wup), ptr(wds), ptr(d_routed), ptr(d_hidden_s),
                    ptr(status), st)
-        d_w_up = torch.zeros(D, L, **f32)
-        d_w_down_s = torch.zeros(D, Fs, **f32)
-        _cabi.call("lmoe_combine_out_bwd_wgrad", shape, ptr(dyb), ptr(routed), ptr(hidden_s), ptr(d_w_up),
-                   ptr(d_w_down_s), ptr(status), st)
-        d_h1_s = torch.empty(T, 2 * Fs, **bf)
-        _cabi.call("lmoe_swiglu_bwd", T, Fs, ptr(h1_s), ptr(d_hidden_s), ptr(d_h1_s), None, st)
+        d_w_up = torch.empty(D, L, **lin)
+        d_w_down_s = torch.empty(D, Fs, **lin)
+        _cabi.call("lmoe_combine_out_bwd_wgrad", shape, ptr(dyb), ptr(act_cat), ptr(d_w_up), ptr(d_w_down_s), gtype,
+                   ptr(ws), ws.numel(), ptr(status), st)
+        # the three x-side gradients live side by side in dgrad_cat[T, 2Fs+L+E]
+        dgrad_cat = torch.empty(T, 2 * Fs + L + E, **bf)
+        d_h1_s, d_x_latent, d_logits = dgrad_cat[:, :2 * Fs], dgrad_cat[:, 2 * Fs:2 * Fs + L], dgrad_cat[:, 2 * Fs + L:]
+        _cabi.call("lmoe_swiglu_bwd", T, Fs, ptr(h1_s), ptr(d_hidden_s), ptr(dgrad_cat), 2 * Fs + L + E, None, st)
 
         # routed experts
         d_y_sorted = torch.empty(P, L, **bf)
@@ -199,37 +198,34 @@ class LatentMoEFunction(torch.autograd.Function):
         d_w_down_e = torch.empty(E, F, L, **bf)
         _cabi.call("lmoe_experts_bwd_wgrad", shape, ptr(x_sorted), ptr(d_h1), ptr(hidden), ptr(d_y_sorted),
                    route.struct, ptr(d_w_gate_up), ptr(d_w_down_e), ptr(status), st)
-        d_x_latent = torch.empty(T, L, **bf)
-        _cabi.call("lmoe_unpermute_sum_bwd", shape, ptr(d_x_sorted), route.struct, ptr(d_x_latent), st)
+        _cabi.call("lmoe_unpermute_sum_bwd", shape, ptr(d_x_sorted), route.struct, ptr(dgrad_cat), st)
 
         # router
-        d_logits = torch.empty(T, E, **bf)
         dz = None
         if d_z is not None:
             dz = d_z.to(torch.float32).reshape(1).contiguous()
         _cabi.call("lmoe_gate_topk_bwd", shape, ptr(logits), ptr(sel), ptr(weights), ptr(d_weights), ptr(lse), ptr(dz),
-                   ctx.z_coef, ptr(d_logits), st)
+                   ctx.z_coef, ptr(dgrad_cat), st)
 
-        # x side
-        d_w_gate_up_s = torch.zeros(2 * Fs, D, **f32)
-        _cabi.call("lmoe_shared_gateup_bwd_wgrad", shape, ptr(d_h1_s), ptr(xb), ptr(d_w_gate_up_s), ptr(status), st)
+        # x side: dx and the three weight gradients that contract with x
         dx = torch.empty(T, D, **bf)
-        d_w_down = torch.zeros(L, D, **f32)
-        d_w_gate = torch.zeros(E, D, **f32)
-        _cabi.call("lmoe_xproj_bwd", shape, ptr(d_h1_s), ptr(d_x_latent), ptr(d_logits), ptr(wgus), ptr(wdn), ptr(wg),
-                   ptr(xb), ptr(dx), ptr(d_w_down), ptr(d_w_gate), ptr(status), st)
+        d_w_gate_up_s = torch.empty(2 * Fs, D, **lin)
+        d_w_down = torch.empty(L, D, **lin)
+        d_w_gate = torch.empty(E, D, **lin)
+        _cabi.call("lmoe_xside_bwd", shape, ptr(dgrad_cat), ptr(wgus), ptr(wdn), ptr(wg), ptr(xb), ptr(dx),
+                   ptr(d_w_gate_up_s), ptr(d_w_down), ptr(d_w_gate), gtype, ptr(ws), ws.numel(), ptr(status), st)
 
         if DEBUG_SINK is not None:
             DEBUG_SINK.update(d_routed=d_routed, d_hidden_s=d_hidden_s, d_h1_s=d_h1_s, d_y_sorted=d_y_sorted,
                               d_weights=d_weights, d_hidden=d_hidden, d_h1=d_h1, d_x_sorted=d_x_sorted,
                               d_x_latent=d_x_latent, d_logits=d_logits)
-        dt = ctx.dtypes
+        def as_param(g, d):
+            return g if g.dtype == d else g.to(d)
+
         grads = (
-            dx if dt[0] == BF else dx.to(dt[0]),
-            _to_dtype(d_w_gate, dt[1]), _to_dtype(d_w_down, dt[2]), _to_dtype(d_w_up, dt[3]),
-            _to_dtype(d_w_gate_up_s, dt[4]), _to_dtype(d_w_down_s, dt[5]),
-            d_w_gate_up if dt[6] == BF else d_w_gate_up.to(dt[6]),
-            d_w_down_e if dt[7] == BF else d_w_down_e.to(dt[7]),
+            as_param(dx, dt[0]), as_param(d_w_gate, dt[1]), as_param(d_w_down, dt[2]), as_param(d_w_up, dt[3]),
+            as_param(d_w_gate_up_s, dt[4]), as_param(d_w_down_s, dt[5]), as_param(d_w_gate_up, dt[6]),
+            as_param(d_w_down_e, dt[7]),
         )
         return grads + (None, None, None)
 

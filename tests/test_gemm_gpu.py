@@ -18,9 +18,11 @@ def _run(M, N, K, a_mn, b_mn, c_f32, split_k=1, seed=0):
     ldb = N if b_mn else K
     C = torch.zeros(M, N, dtype=torch.float32 if c_f32 else torch.bfloat16, device=dev)
     status = torch.zeros(1, dtype=torch.int32, device=dev)
+    ws_bytes = _cabi.load().lmoe_gemm_workspace_bytes(M, N, split_k)
+    ws = torch.empty(max(16, ws_bytes), dtype=torch.uint8, device=dev)
     _cabi.call("lmoe_gemm_bf16", M, N, K, A_dev.data_ptr(), lda, int(a_mn), B_dev.data_ptr(), ldb, int(b_mn),
-               C.data_ptr(), N, _cabi.F32 if c_f32 else _cabi.BF16, split_k, status.data_ptr(),
-               torch.cuda.current_stream().cuda_stream)
+               C.data_ptr(), N, _cabi.F32 if c_f32 else _cabi.BF16, split_k, ws.data_ptr(), ws_bytes,
+               status.data_ptr(), torch.cuda.current_stream().cuda_stream)
     torch.cuda.synchronize()
     assert status.item() == 0, _cabi.status_string(status.item())
     # bf16 operands, fp32 accumulation: error is accumulation order (+ bf16 rounding of C)
@@ -46,8 +48,9 @@ def test_gemm_wide_tiles_f32_out(a_mn, b_mn):
 
 
 @pytest.mark.parametrize("split_k", [2, 5])
-def test_gemm_split_k_adds(split_k):
+def test_gemm_split_k(split_k):
     _run(256, 128, 64 * 37, 1, 1, c_f32=True, split_k=split_k)
+    _run(384, 320, 64 * 9 + 8, 1, 1, c_f32=False, split_k=split_k)
 
 
 def test_gemm_ragged_rows_and_small_k():
@@ -60,6 +63,8 @@ def test_gemm_rejects_bad_arguments():
     lib = _cabi.load()
     x = torch.zeros(128, 128, dtype=torch.bfloat16, device="cuda:0")
     st = torch.cuda.current_stream().cuda_stream
-    assert lib.lmoe_gemm_bf16(128, 128, 128, None, 128, 0, x.data_ptr(), 128, 0, x.data_ptr(), 128, 0, 1, None, st) == -1
-    assert lib.lmoe_gemm_bf16(128, 100, 128, x.data_ptr(), 128, 0, x.data_ptr(), 128, 0, x.data_ptr(), 100, 0, 1, None, st) == -2
-    assert lib.lmoe_gemm_bf16(128, 128, 128, x.data_ptr() + 2, 128, 0, x.data_ptr(), 128, 0, x.data_ptr(), 128, 0, 1, None, st) == -3
+    p = x.data_ptr()
+    assert lib.lmoe_gemm_bf16(128, 128, 128, None, 128, 0, p, 128, 0, p, 128, 0, 1, None, 0, None, st) == -1
+    assert lib.lmoe_gemm_bf16(128, 100, 128, p, 128, 0, p, 128, 0, p, 100, 0, 1, None, 0, None, st) == -2
+    assert lib.lmoe_gemm_bf16(128, 128, 128, p + 2, 128, 0, p, 128, 0, p, 128, 0, 1, None, 0, None, st) == -3
+    assert lib.lmoe_gemm_bf16(128, 128, 128, p, 128, 0, p, 128, 0, p, 128, 1, 4, None, 0, None, st) == -4

@@ -42,7 +42,7 @@ def assert_matches_bf16_model(name, test, model):
     differences of its inputs: 4 ulp there and for what is computed from it."""
     ulps = 4 if any(s in name for s in ("d_logits", "router.gate")) else 2
     rep = R.closeness(test.detach().float().cpu(), model, ulps * BF16_ULP)
-    assert rep["rel_fro"] <= 2.5e-3 and rep["max_ratio"] <= 1.0, f"{name} vs bf16 pipeline model: {rep}"
+    assert rep["rel_fro"] <= 2.5e-3 and rep["max_ratio"] <= 1.5 and rep["frac_out"] <= 1e-5, f"{name} vs bf16 pipeline model: {rep}"
 
 
 @pytest.mark.parametrize("name", ["tiny", "tiny_ragged", "cfg1"])
