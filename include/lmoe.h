@@ -44,6 +44,7 @@ extern "C" {
 #define LMOE_ERR_ALIGN (-3)      /* pointer or leading dimension not 16-byte aligned */
 #define LMOE_ERR_WORKSPACE (-4)  /* workspace too small */
 #define LMOE_ERR_DRIVER (-5)     /* tensor-map encode entry point unavailable / failed */
+#define LMOE_ERR_TOO_LARGE (-6)  /* problem exceeds the fixed scratch of a no-allocation entry point */
 
 /* element types */
 #define LMOE_BF16 0
@@ -118,6 +119,26 @@ int lmoe_gate_topk_fwd(const lmoe_shape* s, const float* logits, const float* ex
  * layout tables.  Deterministic (no global atomics).  Replaces models/moe_triton.py:12-78. */
 int lmoe_route_permute(const lmoe_shape* s, const int32_t* sel, const lmoe_route* r, void* workspace,
                        size_t workspace_bytes, void* stream);
+
+/* Same result as lmoe_route_permute, for hosts that have no device memory to give as workspace.
+ * (No counterpart in the reference: this entry point exists only on this boundary.)
+ * Who needs it: a caller that cannot obtain device memory at the moment of the call -- a plugin whose
+ * host interface hands it input and output buffers and nothing else, a serving process whose memory
+ * pool already owns the whole GPU so that a fresh cudaMalloc fails, or a code path (an error handler,
+ * a callback) where allocating is forbidden.  Such a caller passes only `sel` and the output tables;
+ * the chunk histograms go to a fixed array of LMOE_STATIC_ROUTE_SCRATCH_BYTES that is part of the
+ * library image on every GPU that loads it (held until the process exits).
+ *   - Nothing is allocated or freed, here or in any library routine this calls.
+ *   - Limit: lmoe_route_workspace_bytes(s) must not exceed LMOE_STATIC_ROUTE_SCRATCH_BYTES, i.e.
+ *     ceil(T*K/512) * E <= 1,048,576 (for E = 128: T*K up to 4,194,304); beyond that the call launches
+ *     nothing and returns LMOE_ERR_TOO_LARGE.
+ *   - The first call on each device looks up the array's device address (with that device current);
+ *     make that first call before any stream capture begins.
+ *   - All calls on a device share the one array.  Nothing in it needs clearing between calls (each call
+ *     writes every word before reading it), but two calls that overlap on the GPU -- different streams,
+ *     or different host threads without ordering between them -- race on it and corrupt each other. */
+#define LMOE_STATIC_ROUTE_SCRATCH_BYTES (4u << 20)
+int lmoe_route_permute_static(const lmoe_shape* s, const int32_t* sel, const lmoe_route* r, void* stream);
 
 /* Routed experts: gather x_latent rows into the padded layout, grouped gate_up GEMM with SwiGLU
  * epilogue, grouped down GEMM.

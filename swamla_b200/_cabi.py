@@ -48,6 +48,7 @@ SIGNATURES = {
     "lmoe_xproj_fwd": (c_int, [SP, P, P, P, P, P, P, P]),
     "lmoe_gate_topk_fwd": (c_int, [SP, P, P, c_float, P, P, P, P, P, P]),
     "lmoe_route_permute": (c_int, [SP, P, RP, P, c_size_t, P]),
+    "lmoe_route_permute_static": (c_int, [SP, P, RP, P]),
     "lmoe_experts_fwd": (c_int, [SP, P, P, P, RP, P, P, P, P, P, P]),
     "lmoe_shared_gateup_fwd": (c_int, [SP, P, P, P, P, P, P]),
     "lmoe_combine_out_fwd": (c_int, [SP, P, RP, P, P, P, P, P, P, P]),

@@ -83,6 +83,7 @@ extern "C" const char* lmoe_status_string(int code) {
     case LMOE_ERR_ALIGN: return "pointer or leading dimension not 16-byte aligned";
     case LMOE_ERR_WORKSPACE: return "workspace too small";
     case LMOE_ERR_DRIVER: return "tensor-map encoding failed or driver entry point missing";
+    case LMOE_ERR_TOO_LARGE: return "problem exceeds the fixed scratch capacity of a no-allocation entry point";
     case kStatusProducerTimeout: return "device: TMA producer wait timed out";
     case kStatusMmaTimeout: return "device: MMA issuer wait timed out";
     case kStatusEpilogueTimeout: return "device: epilogue wait timed out";

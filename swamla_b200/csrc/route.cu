@@ -4,6 +4,8 @@
 #include <math_constants.h>
 #include <stdint.h>
 
+#include <mutex>
+
 #include "../../include/lmoe.h"
 #include "counters.h"
 
@@ -335,6 +337,62 @@ extern "C" int lmoe_route_permute(const lmoe_shape* s, const int32_t* sel, const
   const int chunks = (n + kChunk - 1) / kChunk;
   const int blocks = (chunks + kRouteWarps - 1) / kRouteWarps;
   int* chunk_hist = static_cast<int*>(workspace);
+  count_launch(3);
+  route_hist_kernel<<<blocks, kRouteWarps * 32, 0, st>>>(sel, n, s->E, chunk_hist);
+  route_scan_chunks_kernel<<<s->E, 256, 0, st>>>(chunk_hist, chunks, s->E, r->counts);
+  route_scatter_kernel<<<blocks, kRouteWarps * 32, 0, st>>>(sel, n, s->E, chunk_hist, r->counts, r->offsets,
+                                                           r->pad_offsets, r->tile_expert, r->n_tiles, r->perm, r->pos,
+                                                           r->row_src);
+  cudaError_t e = cudaGetLastError();
+  return e == cudaSuccess ? 0 : static_cast<int>(e);
+}
+
+// ----------------------------------------------------------------------------- no-allocation variant
+// Scratch of lmoe_route_permute_static: the per-chunk histograms live in this file-scope device array
+// instead of a caller-provided workspace.  Every GPU that loads the library holds these 4 MiB until
+// the process exits.  Host code must not hand `g_route_scratch` itself to a kernel (in host code the
+// name is only a handle): the device address is looked up once per device with cudaGetSymbolAddress.
+constexpr size_t kStaticRouteScratchInts = LMOE_STATIC_ROUTE_SCRATCH_BYTES / sizeof(int);
+static __device__ __align__(256) int g_route_scratch[kStaticRouteScratchInts];
+
+namespace {
+constexpr int kMaxDevices = 64;
+std::mutex g_static_scratch_mutex;
+int* g_static_scratch_ptr[kMaxDevices] = {nullptr};
+
+// Device address of the scratch array on the CURRENT device; resolved on the first call per device.
+int static_route_scratch(int** out) {
+  int dev = -1;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return static_cast<int>(e);
+  if (dev < 0 || dev >= kMaxDevices) return LMOE_ERR_ARG;
+  std::lock_guard<std::mutex> lock(g_static_scratch_mutex);
+  if (!g_static_scratch_ptr[dev]) {
+    void* p = nullptr;
+    e = cudaGetSymbolAddress(&p, g_route_scratch);
+    if (e != cudaSuccess) return static_cast<int>(e);
+    if (!p) return LMOE_ERR_DRIVER;
+    g_static_scratch_ptr[dev] = static_cast<int*>(p);
+  }
+  *out = g_static_scratch_ptr[dev];
+  return 0;
+}
+}  // namespace
+
+extern "C" int lmoe_route_permute_static(const lmoe_shape* s, const int32_t* sel, const lmoe_route* r, void* stream) {
+  if (int rc = check_shape(s)) return rc;
+  if (!sel || !r || !r->counts || !r->offsets || !r->perm || !r->pad_offsets || !r->pos || !r->row_src ||
+      !r->tile_expert || !r->n_tiles)
+    return LMOE_ERR_ARG;
+  if (lmoe_route_workspace_bytes(s) > LMOE_STATIC_ROUTE_SCRATCH_BYTES) return LMOE_ERR_TOO_LARGE;
+  int* chunk_hist = nullptr;
+  if (int rc = static_route_scratch(&chunk_hist)) return rc;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const int n = s->T * s->K;
+  const int chunks = (n + kChunk - 1) / kChunk;
+  const int blocks = (chunks + kRouteWarps - 1) / kRouteWarps;
+  // Nothing in the scratch has to start at zero: pass 1 writes every word that passes 2 and 3 read,
+  // so what an earlier call left behind is never observed.
   count_launch(3);
   route_hist_kernel<<<blocks, kRouteWarps * 32, 0, st>>>(sel, n, s->E, chunk_hist);
   route_scan_chunks_kernel<<<s->E, 256, 0, st>>>(chunk_hist, chunks, s->E, r->counts);
