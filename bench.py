@@ -88,13 +88,44 @@ class ClockSampler:
                 "reasons": sorted(reasons)}
 
 
-def build_layer(w, seed, device):
+def build_layer(w, rank, device, ep_group=None):
+    """The layer with seed-0 parameters (identical on every rank) and this rank's own tokens (seed = rank).
+    With `ep_group` the routed experts are sharded: this rank keeps experts [rank*E/G, (rank+1)*E/G)."""
     from swamla_b200.layer import LatentMoELayer
-    params, buffers, x, dy = inputs.make_inputs(w, seed=seed)
-    layer = LatentMoELayer(w.config())
-    layer.load_state_dict({**params, **buffers}, strict=True)
+    params, buffers, x, dy = inputs.make_inputs(w, seed=0)
+    if rank != 0:
+        g = torch.Generator("cpu").manual_seed(1000 + rank)
+        x = torch.randn(x.shape, generator=g)
+        dy = torch.randn(dy.shape, generator=g)
+    cfg = w.config()
+    state = {**params, **buffers}
+    if ep_group is not None:
+        import torch.distributed as dist
+        cfg.ep_group = ep_group
+        G = dist.get_world_size(ep_group)
+        El = w.E // G
+        for k in ("experts.gate_up_weight", "experts.down_weight"):
+            state[k] = state[k][rank * El:(rank + 1) * El].clone()
+    layer = LatentMoELayer(cfg)
+    layer.load_state_dict(state, strict=True)
     layer = layer.to(device).to(torch.bfloat16).train()
     return layer, x.to(torch.bfloat16), dy.to(torch.bfloat16)
+
+
+def time_steps(layer, x, dy, steps, warmup):
+    """ms per fwd+bwd step on this rank alone (CUDA events on the current stream)."""
+    for _ in range(warmup):
+        zero_grads(layer, x)
+        step(layer, x, dy)
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(steps):
+        zero_grads(layer, x)
+        step(layer, x, dy)
+    e1.record()
+    torch.cuda.synchronize()
+    return e0.elapsed_time(e1) / steps
 
 
 def step(layer, x, dy):
@@ -193,7 +224,17 @@ def main():
 
     from swamla_b200 import _cabi
     lib = _cabi.load()
-    layer, x_host, dy_host = build_layer(w, seed=rank, device=dev)
+    same_workload_1gpu = None
+    if world > 1 and rank == 0:
+        # the same per-GPU workload on ONE GPU with all experts local: the denominator of the
+        # expert-parallel scaling efficiency (measured here because N=1 defaults to another workload)
+        l1, xh1, dyh1 = build_layer(w, 0, dev)
+        x1 = xh1.to(dev).requires_grad_(True)
+        ms1 = time_steps(l1, x1, dyh1.to(dev), max(3, args.steps // 2), args.warmup)
+        same_workload_1gpu = w.T / (ms1 * 1e-3)
+        del l1, x1, xh1, dyh1
+        torch.cuda.empty_cache()
+    layer, x_host, dy_host = build_layer(w, rank, dev, ep_group=dist.group.WORLD if world > 1 else None)
     x = x_host.to(dev).requires_grad_(True)
     dy = dy_host.to(dev)
 
@@ -310,11 +351,15 @@ def main():
         "metric": METRIC, "value": tokens_per_s, "unit": "tokens/s", "n_gpus": world, "steps": args.steps,
         "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak",
         "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
-        "config": workload_config(w, world, "single GPU" if world == 1 else f"replicas x{world}"),
+        "config": workload_config(w, world, "single GPU" if world == 1 else
+                                  f"ep{world}: experts sharded {w.E // world} per GPU, tokens data-parallel, "
+                                  "dispatch/combine all-to-all (NCCL) of latent rows"),
         "clocks": clocks, "gpu_launches": int(launches), "roofline": roofline,
     }
     if e2e is not None:
         out["e2e"] = e2e
+    if same_workload_1gpu is not None:
+        out["tokens_per_s_1gpu_same_workload"] = same_workload_1gpu
     if world == 1 and not args.no_cpu_baseline:
         threads = os.cpu_count() or 1
         v, secs = cpu_baseline(w, threads)

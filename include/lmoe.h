@@ -211,6 +211,45 @@ int lmoe_xside_bwd(const lmoe_shape* s, const void* dgrad_cat, const void* w_gat
                    const void* w_gate, const void* x, void* dx, void* d_w_gate_up_s, void* d_w_down, void* d_w_gate,
                    int grad_type, void* workspace, size_t workspace_bytes, int32_t* status, void* stream);
 
+/* ---- building blocks on explicit row counts (used by the expert-parallel host code) ----
+ * The routed-expert stages again, but on a caller-chosen padded row count P (multiple of 128) and expert
+ * count E (the local shard), with the tile tables given directly.  lmoe_experts_* above are these plus the
+ * single-GPU gather.  Same reference lines: models/moe.py:814-828 and their adjoints. */
+int lmoe_grouped_fwd(int64_t P, int E, int L, int F, const void* x_sorted, const void* w_gate_up, const void* w_down,
+                     const int32_t* tile_expert, const int32_t* n_tiles, void* h1, void* hidden, void* y_sorted,
+                     int32_t* status, void* stream);
+int lmoe_grouped_bwd_dgrad(int64_t P, int E, int L, int F, const void* d_y_sorted, const void* h1, const void* w_gate_up,
+                           const void* w_down, const int32_t* tile_expert, const int32_t* n_tiles, void* d_hidden,
+                           void* d_h1, void* d_x_sorted, int32_t* status, void* stream);
+int lmoe_grouped_bwd_wgrad(int64_t P, int E, int L, int F, const void* x_sorted, const void* d_h1, const void* hidden,
+                           const void* d_y_sorted, const int32_t* pad_offsets, void* d_w_gate_up, void* d_w_down,
+                           int32_t* status, void* stream);
+/* dst[r] = src[index[r] / div] for r < rows (zeros where index[r] < 0); rows of L bf16.  If n_tiles_dev is
+ * non-null only the first 128 * n_tiles_dev[0] rows are written.  (models/moe.py:762-766 as a primitive.) */
+int lmoe_gather_rows(const void* src, const int32_t* index, int div, int64_t rows, int L, const int32_t* n_tiles_dev,
+                     void* dst, void* stream);
+/* out[t] = sum_k weights[t,k] * rows_in[index[t*K+k]] (weights NULL: plain sum), fp32 accumulation in slot
+ * order; out has row stride ld_out elements.  (models/moe.py:837,778-782 as a primitive.) */
+int lmoe_combine_rows(const void* rows_in, const int32_t* index, const float* weights, int T, int K, int L, void* out,
+                      int64_t ld_out, void* stream);
+/* Adjoint of lmoe_combine_rows over `rows` rows: flat = row_to_flat[r] (t = flat / K);
+ * d_y_rows[r] = weights[flat] * d_routed[t], d_weights[flat] = <d_routed[t], y_rows[r]>; zeros where flat < 0. */
+int lmoe_combine_bwd_rows(const void* d_routed, const void* y_rows, const float* weights, const int32_t* row_to_flat,
+                          int64_t rows, int K, int L, const int32_t* n_tiles_dev, void* d_y_rows, float* d_weights,
+                          void* stream);
+/* inv[perm[i]] = i. */
+int lmoe_invert_perm(const int32_t* perm, int64_t n, int32_t* inv, void* stream);
+
+/* ---- expert parallelism (no counterpart in the reference, which has data parallelism only;
+ *      design note aidocs/moe.md:940-997) ----
+ * Rank g of G owns experts [g*E/G, (g+1)*E/G).  counts_all[G][E] = rows every source rank routes to every
+ * expert (an all-gather of the `counts` tables).  The receive buffer of the dispatch all-to-all is ordered by
+ * source rank, then local expert.  Outputs, for this rank's shard:
+ *   recv_pos[n_recv]  receive index -> padded local row       row_src[P_local]  padded row -> receive index | -1
+ *   pad_offsets[E/G+1], tile_expert[P_local/128], n_tiles[1]   with P_local >= roundup(n_recv,128) + 128*E/G */
+int lmoe_ep_plan(const int32_t* counts_all, int G, int E, int rank, int32_t* recv_pos, int32_t* row_src,
+                 int32_t* pad_offsets, int32_t* tile_expert, int32_t* n_tiles, void* stream);
+
 /* ---- router bias update (after backward) ----
  * load = histogram(sel) (= counts); bias -= gamma * sign(load - T*K/E); history = .99 history + .01 load.
  * Replaces models/moe.py:254-275. */

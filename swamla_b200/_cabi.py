@@ -61,6 +61,14 @@ SIGNATURES = {
     "lmoe_unpermute_sum_bwd": (c_int, [SP, P, RP, P, P]),
     "lmoe_gate_topk_bwd": (c_int, [SP, P, P, P, P, P, P, c_float, P, P]),
     "lmoe_xside_bwd": (c_int, [SP, P, P, P, P, P, P, P, P, P, c_int, P, c_size_t, P, P]),
+    "lmoe_grouped_fwd": (c_int, [c_int64, c_int, c_int, c_int, P, P, P, P, P, P, P, P, P, P]),
+    "lmoe_grouped_bwd_dgrad": (c_int, [c_int64, c_int, c_int, c_int, P, P, P, P, P, P, P, P, P, P, P]),
+    "lmoe_grouped_bwd_wgrad": (c_int, [c_int64, c_int, c_int, c_int, P, P, P, P, P, P, P, P, P]),
+    "lmoe_gather_rows": (c_int, [P, P, c_int, c_int64, c_int, P, P, P]),
+    "lmoe_combine_rows": (c_int, [P, P, P, c_int, c_int, c_int, P, c_int64, P]),
+    "lmoe_combine_bwd_rows": (c_int, [P, P, P, P, c_int64, c_int, c_int, P, P, P, P]),
+    "lmoe_invert_perm": (c_int, [P, c_int64, P, P]),
+    "lmoe_ep_plan": (c_int, [P, c_int, c_int, c_int, P, P, P, P, P, P]),
     "lmoe_router_bias_update": (c_int, [SP, P, c_float, P, P, P]),
     "lmoe_cast_f32_to_bf16": (c_int, [P, P, c_int64, P]),
     "lmoe_cast_bf16_to_f32": (c_int, [P, P, c_int64, P]),

@@ -122,14 +122,11 @@ extern "C" int lmoe_shared_gateup_fwd(const lmoe_shape* s, const void* x, const 
   return launch_gemm(c);
 }
 
-extern "C" int lmoe_experts_fwd(const lmoe_shape* s, const void* x_latent, const void* w_gate_up, const void* w_down,
-                                const lmoe_route* r, void* x_sorted, void* h1, void* hidden, void* y_sorted,
-                                int32_t* status, void* stream) {
-  if (int rc = check_dims(s)) return rc;
-  if (!x_latent || !w_gate_up || !w_down || !r || !x_sorted || !h1 || !hidden || !y_sorted) return LMOE_ERR_ARG;
-  cudaStream_t st = static_cast<cudaStream_t>(stream);
-  const long long P = lmoe_padded_rows(s);
-  if (int rc = gather_rows(x_latent, r, s->K, s->L, P, x_sorted, st)) return rc;
+extern "C" int lmoe_grouped_fwd(int64_t P, int E, int L, int F, const void* x_sorted, const void* w_gate_up,
+                                const void* w_down, const int32_t* tile_expert, const int32_t* n_tiles, void* h1,
+                                void* hidden, void* y_sorted, int32_t* status, void* stream) {
+  if (!x_sorted || !w_gate_up || !w_down || !tile_expert || !n_tiles || !h1 || !hidden || !y_sorted) return LMOE_ERR_ARG;
+  if (P <= 0 || (P % LMOE_ROW_PAD) != 0 || E <= 0 || (L % 64) != 0 || (F % 64) != 0) return LMOE_ERR_SHAPE;
   // h1 = x_sorted * Wgu[e]  (Wgu stacked [E*L, 2F], N contiguous), hidden = silu(gate) * up
   GemmCall a;
   a.a_mn = 0;
@@ -137,38 +134,49 @@ extern "C" int lmoe_experts_fwd(const lmoe_shape* s, const void* x_latent, const
   a.epi = EPI_SWIGLU;
   a.grp = GRP_M;
   a.A[0] = x_sorted;
-  a.lda[0] = s->L;
+  a.lda[0] = L;
   a.B[0] = w_gate_up;
-  a.ldb[0] = 2ll * s->F;
-  a.Kseg[0] = s->L;
+  a.ldb[0] = 2ll * F;
+  a.Kseg[0] = L;
   a.M = static_cast<int>(P);
-  a.N = s->F;
+  a.N = F;
   a.C = h1;
-  a.ldc = 2ll * s->F;
+  a.ldc = 2ll * F;
   a.C2 = hidden;
-  a.ldc2 = s->F;
+  a.ldc2 = F;
   a.padded_rows = P;
-  a.groups = s->E;
-  a.b_group_rows = s->L;
-  a.tile_expert = r->tile_expert;
-  a.n_m_tiles = r->n_tiles;
+  a.groups = E;
+  a.b_group_rows = L;
+  a.tile_expert = tile_expert;
+  a.n_m_tiles = n_tiles;
   a.status = status;
-  a.stream = st;
+  a.stream = static_cast<cudaStream_t>(stream);
   if (int rc = launch_gemm(a)) return rc;
   // y_sorted = hidden * Wd[e]  (Wd stacked [E*F, L], N contiguous)
   GemmCall b = a;
   b.epi = EPI_BF16;
   b.A[0] = hidden;
-  b.lda[0] = s->F;
+  b.lda[0] = F;
   b.B[0] = w_down;
-  b.ldb[0] = s->L;
-  b.Kseg[0] = s->F;
-  b.N = s->L;
+  b.ldb[0] = L;
+  b.Kseg[0] = F;
+  b.N = L;
   b.C = y_sorted;
-  b.ldc = s->L;
+  b.ldc = L;
   b.C2 = nullptr;
-  b.b_group_rows = s->F;
+  b.b_group_rows = F;
   return launch_gemm(b);
+}
+
+extern "C" int lmoe_experts_fwd(const lmoe_shape* s, const void* x_latent, const void* w_gate_up, const void* w_down,
+                                const lmoe_route* r, void* x_sorted, void* h1, void* hidden, void* y_sorted,
+                                int32_t* status, void* stream) {
+  if (int rc = check_dims(s)) return rc;
+  if (!x_latent || !w_gate_up || !w_down || !r || !x_sorted || !h1 || !hidden || !y_sorted) return LMOE_ERR_ARG;
+  const long long P = lmoe_padded_rows(s);
+  if (int rc = gather_rows(x_latent, r, s->K, s->L, P, x_sorted, static_cast<cudaStream_t>(stream))) return rc;
+  return lmoe_grouped_fwd(P, s->E, s->L, s->F, x_sorted, w_gate_up, w_down, r->tile_expert, r->n_tiles, h1, hidden,
+                          y_sorted, status, stream);
 }
 
 extern "C" int lmoe_combine_out_fwd(const lmoe_shape* s, const void* y_sorted, const lmoe_route* r, const float* weights,
@@ -223,13 +231,13 @@ extern "C" int lmoe_combine_out_bwd_wgrad(const lmoe_shape* s, const void* dy, c
   return splitk_reduce(ws, split, plane, N, 0, s->L, s->D, s->Fs, d_w_down_s, s->Fs, grad_type == LMOE_F32, st);
 }
 
-extern "C" int lmoe_experts_bwd_dgrad(const lmoe_shape* s, const void* d_y_sorted, const void* h1, const void* w_gate_up,
-                                      const void* w_down, const lmoe_route* r, void* d_hidden, void* d_h1,
-                                      void* d_x_sorted, int32_t* status, void* stream) {
-  if (int rc = check_dims(s)) return rc;
-  if (!d_y_sorted || !h1 || !w_gate_up || !w_down || !r || !d_hidden || !d_h1 || !d_x_sorted) return LMOE_ERR_ARG;
-  cudaStream_t st = static_cast<cudaStream_t>(stream);
-  const long long P = lmoe_padded_rows(s);
+extern "C" int lmoe_grouped_bwd_dgrad(int64_t P, int E, int L, int F, const void* d_y_sorted, const void* h1,
+                                      const void* w_gate_up, const void* w_down, const int32_t* tile_expert,
+                                      const int32_t* n_tiles, void* d_hidden, void* d_h1, void* d_x_sorted,
+                                      int32_t* status, void* stream) {
+  if (!d_y_sorted || !h1 || !w_gate_up || !w_down || !tile_expert || !n_tiles || !d_hidden || !d_h1 || !d_x_sorted)
+    return LMOE_ERR_ARG;
+  if (P <= 0 || (P % LMOE_ROW_PAD) != 0 || E <= 0 || (L % 64) != 0 || (F % 64) != 0) return LMOE_ERR_SHAPE;
   // d_hidden[P,F] = d_y_sorted[P,L] * Wd[e]^T : Wd[e] is [F,L] = [N,K] row-major -> K-major B
   GemmCall a;
   a.a_mn = 0;
@@ -237,43 +245,51 @@ extern "C" int lmoe_experts_bwd_dgrad(const lmoe_shape* s, const void* d_y_sorte
   a.epi = EPI_BF16;
   a.grp = GRP_M;
   a.A[0] = d_y_sorted;
-  a.lda[0] = s->L;
+  a.lda[0] = L;
   a.B[0] = w_down;
-  a.ldb[0] = s->L;
-  a.Kseg[0] = s->L;
+  a.ldb[0] = L;
+  a.Kseg[0] = L;
   a.M = static_cast<int>(P);
-  a.N = s->F;
+  a.N = F;
   a.C = d_hidden;
-  a.ldc = s->F;
+  a.ldc = F;
   a.padded_rows = P;
-  a.groups = s->E;
-  a.b_group_rows = s->F;
-  a.tile_expert = r->tile_expert;
-  a.n_m_tiles = r->n_tiles;
+  a.groups = E;
+  a.b_group_rows = F;
+  a.tile_expert = tile_expert;
+  a.n_m_tiles = n_tiles;
   a.status = status;
-  a.stream = st;
+  a.stream = static_cast<cudaStream_t>(stream);
   if (int rc = launch_gemm(a)) return rc;
-  if (int rc = lmoe_swiglu_bwd(P, s->F, h1, d_hidden, d_h1, 2ll * s->F, r->n_tiles, stream)) return rc;
+  if (int rc = lmoe_swiglu_bwd(P, F, h1, d_hidden, d_h1, 2ll * F, n_tiles, stream)) return rc;
   // d_x_sorted[P,L] = d_h1[P,2F] * Wgu[e]^T : Wgu[e] is [L,2F] = [N,K] row-major -> K-major B
   GemmCall b = a;
   b.A[0] = d_h1;
-  b.lda[0] = 2ll * s->F;
+  b.lda[0] = 2ll * F;
   b.B[0] = w_gate_up;
-  b.ldb[0] = 2ll * s->F;
-  b.Kseg[0] = 2 * s->F;
-  b.N = s->L;
+  b.ldb[0] = 2ll * F;
+  b.Kseg[0] = 2 * F;
+  b.N = L;
   b.C = d_x_sorted;
-  b.ldc = s->L;
-  b.b_group_rows = s->L;
+  b.ldc = L;
+  b.b_group_rows = L;
   return launch_gemm(b);
 }
 
-extern "C" int lmoe_experts_bwd_wgrad(const lmoe_shape* s, const void* x_sorted, const void* d_h1, const void* hidden,
-                                      const void* d_y_sorted, const lmoe_route* r, void* d_w_gate_up, void* d_w_down,
-                                      int32_t* status, void* stream) {
+extern "C" int lmoe_experts_bwd_dgrad(const lmoe_shape* s, const void* d_y_sorted, const void* h1, const void* w_gate_up,
+                                      const void* w_down, const lmoe_route* r, void* d_hidden, void* d_h1,
+                                      void* d_x_sorted, int32_t* status, void* stream) {
   if (int rc = check_dims(s)) return rc;
-  if (!x_sorted || !d_h1 || !hidden || !d_y_sorted || !r || !d_w_gate_up || !d_w_down) return LMOE_ERR_ARG;
-  const long long P = lmoe_padded_rows(s);
+  if (!r) return LMOE_ERR_ARG;
+  return lmoe_grouped_bwd_dgrad(lmoe_padded_rows(s), s->E, s->L, s->F, d_y_sorted, h1, w_gate_up, w_down,
+                                r->tile_expert, r->n_tiles, d_hidden, d_h1, d_x_sorted, status, stream);
+}
+
+extern "C" int lmoe_grouped_bwd_wgrad(int64_t P, int E, int L, int F, const void* x_sorted, const void* d_h1,
+                                      const void* hidden, const void* d_y_sorted, const int32_t* pad_offsets,
+                                      void* d_w_gate_up, void* d_w_down, int32_t* status, void* stream) {
+  if (!x_sorted || !d_h1 || !hidden || !d_y_sorted || !pad_offsets || !d_w_gate_up || !d_w_down) return LMOE_ERR_ARG;
+  if (P <= 0 || (P % LMOE_ROW_PAD) != 0 || E <= 0 || (L % 64) != 0 || (F % 64) != 0) return LMOE_ERR_SHAPE;
   // d_Wgu[e][L,2F] = x_sorted[rows_e]^T * d_h1[rows_e]
   GemmCall a;
   a.a_mn = 1;
@@ -281,32 +297,41 @@ extern "C" int lmoe_experts_bwd_wgrad(const lmoe_shape* s, const void* x_sorted,
   a.epi = EPI_BF16;
   a.grp = GRP_K;
   a.A[0] = x_sorted;
-  a.lda[0] = s->L;
+  a.lda[0] = L;
   a.B[0] = d_h1;
-  a.ldb[0] = 2ll * s->F;
-  a.M = s->L;
-  a.N = 2 * s->F;
+  a.ldb[0] = 2ll * F;
+  a.M = L;
+  a.N = 2 * F;
   a.C = d_w_gate_up;
-  a.ldc = 2ll * s->F;
-  a.c_group_stride = static_cast<long long>(s->L) * 2 * s->F;
+  a.ldc = 2ll * F;
+  a.c_group_stride = static_cast<long long>(L) * 2 * F;
   a.padded_rows = P;
-  a.groups = s->E;
-  a.pad_offsets = r->pad_offsets;
+  a.groups = E;
+  a.pad_offsets = pad_offsets;
   a.status = status;
   a.stream = static_cast<cudaStream_t>(stream);
   if (int rc = launch_gemm(a)) return rc;
   // d_Wd[e][F,L] = hidden[rows_e]^T * d_y_sorted[rows_e]
   GemmCall b = a;
   b.A[0] = hidden;
-  b.lda[0] = s->F;
+  b.lda[0] = F;
   b.B[0] = d_y_sorted;
-  b.ldb[0] = s->L;
-  b.M = s->F;
-  b.N = s->L;
+  b.ldb[0] = L;
+  b.M = F;
+  b.N = L;
   b.C = d_w_down;
-  b.ldc = s->L;
-  b.c_group_stride = static_cast<long long>(s->F) * s->L;
+  b.ldc = L;
+  b.c_group_stride = static_cast<long long>(F) * L;
   return launch_gemm(b);
+}
+
+extern "C" int lmoe_experts_bwd_wgrad(const lmoe_shape* s, const void* x_sorted, const void* d_h1, const void* hidden,
+                                      const void* d_y_sorted, const lmoe_route* r, void* d_w_gate_up, void* d_w_down,
+                                      int32_t* status, void* stream) {
+  if (int rc = check_dims(s)) return rc;
+  if (!r) return LMOE_ERR_ARG;
+  return lmoe_grouped_bwd_wgrad(lmoe_padded_rows(s), s->E, s->L, s->F, x_sorted, d_h1, hidden, d_y_sorted,
+                                r->pad_offsets, d_w_gate_up, d_w_down, status, stream);
 }
 
 extern "C" int lmoe_xside_bwd(const lmoe_shape* s, const void* dgrad_cat, const void* w_gate_up_s, const void* w_down,

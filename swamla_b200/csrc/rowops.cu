@@ -35,7 +35,7 @@ __global__ void __launch_bounds__(kRowWarps * 32)
 gather_rows_kernel(const uint4* __restrict__ src, const int* __restrict__ row_src, const int* __restrict__ n_tiles, int K,
                    int vec_per_row, uint4* __restrict__ dst, long long max_rows) {
   const int lane = threadIdx.x & 31;
-  const long long rows = min(static_cast<long long>(n_tiles[0]) * LMOE_ROW_PAD, max_rows);
+  const long long rows = n_tiles ? min(static_cast<long long>(n_tiles[0]) * LMOE_ROW_PAD, max_rows) : max_rows;
   for (long long row = static_cast<long long>(blockIdx.x) * kRowWarps + (threadIdx.x >> 5); row < rows;
        row += static_cast<long long>(gridDim.x) * kRowWarps) {
     const int flat = row_src[row];
@@ -75,7 +75,7 @@ combine_bwd_kernel(const uint4* __restrict__ d_routed, const uint4* __restrict__
                    const int* __restrict__ row_src, const int* __restrict__ n_tiles, int K, int vec_per_row,
                    uint4* __restrict__ d_y, float* __restrict__ d_w, long long max_rows) {
   const int lane = threadIdx.x & 31;
-  const long long rows = min(static_cast<long long>(n_tiles[0]) * LMOE_ROW_PAD, max_rows);
+  const long long rows = n_tiles ? min(static_cast<long long>(n_tiles[0]) * LMOE_ROW_PAD, max_rows) : max_rows;
   for (long long row = static_cast<long long>(blockIdx.x) * kRowWarps + (threadIdx.x >> 5); row < rows;
        row += static_cast<long long>(gridDim.x) * kRowWarps) {
     const int flat = row_src[row];
@@ -261,6 +261,44 @@ extern "C" int lmoe_gate_topk_bwd(const lmoe_shape* s, const float* logits, cons
   __nv_bfloat16* d_logits = static_cast<__nv_bfloat16*>(dgrad_cat) + 2ll * s->Fs + s->L;
   gate_bwd_kernel<<<grid_for(s->T, kRowWarps), kRowWarps * 32, 0, static_cast<cudaStream_t>(stream)>>>(
       logits, sel, weights, d_weights, lse, d_z, z_coef / static_cast<float>(s->T), s->T, s->E, s->K, d_logits, ld);
+  return last_error();
+}
+
+// ---- generic row primitives (used by the expert-parallel host code, which works on explicit row counts) ----
+__global__ void invert_perm_kernel(const int* __restrict__ perm, int n, int* __restrict__ inv) {
+  for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < n; i += gridDim.x * blockDim.x) inv[perm[i]] = i;
+}
+
+extern "C" int lmoe_invert_perm(const int32_t* perm, int64_t n, int32_t* inv, void* stream) {
+  if (!perm || !inv || n <= 0 || n >= (1ll << 31)) return LMOE_ERR_ARG;
+  invert_perm_kernel<<<grid_for(n, 256), 256, 0, static_cast<cudaStream_t>(stream)>>>(perm, static_cast<int>(n), inv);
+  return last_error();
+}
+
+extern "C" int lmoe_gather_rows(const void* src, const int32_t* index, int div, int64_t rows, int L,
+                                const int32_t* n_tiles_dev, void* dst, void* stream) {
+  if (!src || !index || !dst || rows <= 0 || div <= 0) return LMOE_ERR_ARG;
+  if ((L & 7) != 0) return LMOE_ERR_SHAPE;
+  gather_rows_kernel<<<grid_for(rows, kRowWarps), kRowWarps * 32, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const uint4*>(src), index, n_tiles_dev, div, L / 8, static_cast<uint4*>(dst), rows);
+  return last_error();
+}
+
+extern "C" int lmoe_combine_rows(const void* rows_in, const int32_t* index, const float* weights, int T, int K, int L,
+                                 void* out, int64_t ld_out, void* stream) {
+  if (!rows_in || !index || !out || T <= 0 || K <= 0) return LMOE_ERR_ARG;
+  return combine_rows(rows_in, index, weights, T, K, L, out, ld_out, static_cast<cudaStream_t>(stream));
+}
+
+extern "C" int lmoe_combine_bwd_rows(const void* d_routed, const void* y_rows, const float* weights,
+                                     const int32_t* row_to_flat, int64_t rows, int K, int L, const int32_t* n_tiles_dev,
+                                     void* d_y_rows, float* d_weights, void* stream) {
+  if (!d_routed || !y_rows || !weights || !row_to_flat || !d_y_rows || !d_weights || rows <= 0 || K <= 0)
+    return LMOE_ERR_ARG;
+  if ((L & 7) != 0) return LMOE_ERR_SHAPE;
+  combine_bwd_kernel<<<grid_for(rows, kRowWarps), kRowWarps * 32, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const uint4*>(d_routed), static_cast<const uint4*>(y_rows), weights, row_to_flat, n_tiles_dev, K,
+      L / 8, static_cast<uint4*>(d_y_rows), d_weights, rows);
   return last_error();
 }
 

@@ -1,0 +1,226 @@
+"""Expert-parallel LatentMoE: the routed experts sharded over the ranks of a process group.
+
+The reference has data parallelism only (``train.py:944-949``); expert parallelism is the sharding its
+design note sketches (``aidocs/moe.md:940-997``).  Partition: every rank keeps its own tokens end to end
+(router, latent projections, shared expert, combine) and owns the contiguous expert block
+``[rank*E/G, (rank+1)*E/G)`` of ``experts.gate_up_weight`` / ``experts.down_weight``.  One exchange step each way:
+
+  forward   dispatch all-to-all of latent rows (canonical expert order is also destination-rank order,
+            so the send buffer is the expert-sorted row list) -> local grouped experts -> combine all-to-all
+  backward  the same two exchanges with gradients
+
+Tokens travel in latent space (L = D/4 elements per row).  Row counts are exchanged with one all-gather of
+the per-expert histogram; the split sizes NCCL needs are read on the host once per forward (the only host
+synchronisation), after the shared-expert GEMM has been queued so the GPU stays busy meanwhile.
+Gradients of the replicated parameters are local sums (averaging them across ranks is the data-parallel
+wrapper's job, as in the reference); gradients of the expert shard are complete on the owning rank.
+"""
+from __future__ import annotations
+
+from typing import List, Tuple
+
+import torch
+import torch.distributed as dist
+
+from . import _cabi
+from ._cabi import Route, ptr
+from .functional import BF, RouteTables, _as_bf16, _stream, make_shape
+
+
+def splits_from_counts(counts_all: torch.Tensor, rank: int) -> Tuple[List[int], List[int]]:
+    """counts_all[G, E] (rows every source routes to every expert) -> (send_splits, recv_splits) of ``rank``:
+    rows it sends to each destination rank and rows it receives from each source rank."""
+    G, E = counts_all.shape
+    El = E // G
+    per_dest = counts_all.view(G, G, El).sum(-1)          # [source, destination]
+    return per_dest[rank].tolist(), per_dest[:, rank].tolist()
+
+
+def _a2a(rows_in: torch.Tensor, out_rows: int, in_splits, out_splits, group) -> torch.Tensor:
+    out = torch.empty(out_rows, rows_in.shape[1], dtype=rows_in.dtype, device=rows_in.device)
+    dist.all_to_all_single(out, rows_in, output_split_sizes=out_splits, input_split_sizes=in_splits, group=group)
+    return out
+
+
+class ExpertParallelLatentMoE(torch.autograd.Function):
+    """Same signature as ``functional.LatentMoEFunction`` with the expert weights being the local shard."""
+
+    @staticmethod
+    def forward(ctx, x, w_gate, w_down, w_up, w_gate_up_s, w_down_s, w_gate_up_loc, w_down_e_loc, expert_bias,
+                top_k: int, z_coef: float, group):
+        if not x.is_cuda:
+            raise _cabi.LmoeError("the LatentMoE path runs on a CUDA device only (no CPU fallback)")
+        lib = _cabi.load()
+        G, rank = dist.get_world_size(group), dist.get_rank(group)
+        dev = x.device
+        T, D = x.shape
+        El, L, F2 = w_gate_up_loc.shape
+        E, F, Fs, K = El * G, F2 // 2, w_down_s.shape[1], top_k
+        shape = make_shape(T, D, L, E, K, F, Fs)
+        st = _stream()
+        bf = dict(dtype=BF, device=dev)
+        f32 = dict(dtype=torch.float32, device=dev)
+        i32 = dict(dtype=torch.int32, device=dev)
+
+        xb = _as_bf16(x)
+        wg, wdn, wup = _as_bf16(w_gate), _as_bf16(w_down), _as_bf16(w_up)
+        wgus, wds = _as_bf16(w_gate_up_s), _as_bf16(w_down_s)
+        wgu, wde = _as_bf16(w_gate_up_loc), _as_bf16(w_down_e_loc)
+        bias = expert_bias.to(torch.float32).contiguous()
+        status = torch.zeros(1, **i32)
+
+        # local router over the GLOBAL expert set
+        logits = torch.empty(T, E, **f32)
+        x_latent = torch.empty(T, L, **bf)
+        _cabi.call("lmoe_xproj_fwd", shape, ptr(xb), ptr(wg), ptr(wdn), ptr(logits), ptr(x_latent), ptr(status), st)
+        sel = torch.empty(T, K, **i32)
+        weights = torch.empty(T, K, **f32)
+        lse = torch.empty(T, **f32)
+        z_partial = torch.empty((T + 7) // 8, **f32)
+        z_loss = torch.empty(1, **f32)
+        _cabi.call("lmoe_gate_topk_fwd", shape, ptr(logits), ptr(bias), float(z_coef), ptr(sel), ptr(weights), ptr(lse),
+                   ptr(z_partial), ptr(z_loss), st)
+        route = RouteTables(shape, dev)
+        ws = torch.empty(max(16, lib.lmoe_route_workspace_bytes(shape)), dtype=torch.uint8, device=dev)
+        _cabi.call("lmoe_route_permute", shape, ptr(sel), route.struct, ptr(ws), ws.numel(), st)
+        counts_all = torch.empty(G, E, **i32)
+        dist.all_gather_into_tensor(counts_all, route.counts.contiguous(), group=group)
+
+        # work that needs no routing result goes first: it keeps the GPU busy across the host read below
+        h1_s = torch.empty(T, 2 * Fs, **bf)
+        act_cat = torch.empty(T, L + Fs, **bf)
+        _cabi.call("lmoe_shared_gateup_fwd", shape, ptr(xb), ptr(wgus), ptr(h1_s), ptr(act_cat), ptr(status), st)
+        n_send = T * K
+        send_rows = torch.empty(n_send, L, **bf)      # expert-sorted rows = destination-rank order
+        _cabi.call("lmoe_gather_rows", ptr(x_latent), ptr(route.perm), K, n_send, L, None, ptr(send_rows), st)
+        inv = torch.empty(n_send, **i32)              # flat index t*K+k -> position in send order
+        _cabi.call("lmoe_invert_perm", ptr(route.perm), n_send, ptr(inv), st)
+
+        send_splits, recv_splits = splits_from_counts(counts_all.cpu(), rank)   # the one host sync
+        n_recv = int(sum(recv_splits))
+        recv_rows = _a2a(send_rows, n_recv, send_splits, recv_splits, group)    # dispatch
+
+        # regroup the received rows expert by expert (padded) and run the local experts
+        P = (n_recv + 127) // 128 * 128 + El * 128
+        recv_pos = torch.empty(max(n_recv, 1), **i32)
+        row_src = torch.empty(P, **i32)
+        pad_offsets = torch.empty(El + 1, **i32)
+        tile_expert = torch.empty(P // 128, **i32)
+        n_tiles = torch.empty(1, **i32)
+        _cabi.call("lmoe_ep_plan", ptr(counts_all), G, E, rank, ptr(recv_pos), ptr(row_src), ptr(pad_offsets),
+                   ptr(tile_expert), ptr(n_tiles), st)
+        x_sorted = torch.empty(P, L, **bf)
+        h1 = torch.empty(P, 2 * F, **bf)
+        hidden = torch.empty(P, F, **bf)
+        y_sorted = torch.empty(P, L, **bf)
+        y_recv = torch.empty(n_recv, L, **bf)
+        if n_recv > 0:
+            _cabi.call("lmoe_gather_rows", ptr(recv_rows), ptr(row_src), 1, P, L, ptr(n_tiles), ptr(x_sorted), st)
+            _cabi.call("lmoe_grouped_fwd", P, El, L, F, ptr(x_sorted), ptr(wgu), ptr(wde), ptr(tile_expert), ptr(n_tiles),
+                       ptr(h1), ptr(hidden), ptr(y_sorted), ptr(status), st)
+            _cabi.call("lmoe_gather_rows", ptr(y_sorted), ptr(recv_pos), 1, n_recv, L, None, ptr(y_recv), st)
+        y_back = _a2a(y_recv, n_send, recv_splits, send_splits, group)          # combine
+
+        # weighted combine over the returned rows, up-projection, shared down-projection, add
+        y = torch.empty(T, D, **bf)
+        back_route = Route(counts=ptr(route.counts), offsets=ptr(route.offsets), perm=ptr(route.perm),
+                           pad_offsets=ptr(route.pad_offsets), pos=ptr(inv), row_src=ptr(route.row_src),
+                           tile_expert=ptr(route.tile_expert), n_tiles=ptr(route.n_tiles))
+        _cabi.call("lmoe_combine_out_fwd", shape, ptr(y_back), back_route, ptr(weights), ptr(act_cat), ptr(wds),
+                   ptr(wup), ptr(y), ptr(status), st)
+
+        ctx.shape, ctx.route, ctx.group, ctx.z_coef, ctx.status = shape, route, group, float(z_coef), status
+        ctx.splits = (send_splits, recv_splits, n_recv, P, El)
+        ctx.dtypes = [t.dtype for t in (x, w_gate, w_down, w_up, w_gate_up_s, w_down_s, w_gate_up_loc, w_down_e_loc)]
+        ctx.save_for_backward(xb, wg, wdn, wup, wgus, wds, wgu, wde, logits, sel, weights, lse, inv, y_back, act_cat,
+                              h1_s, x_sorted, h1, hidden, recv_pos, row_src, pad_offsets, tile_expert, n_tiles)
+        global_counts = counts_all.sum(0, dtype=torch.int32)
+        ctx.mark_non_differentiable(sel, global_counts)
+        out = y if x.dtype == BF else y.to(x.dtype)
+        return out, z_loss.reshape(()), sel, global_counts
+
+    @staticmethod
+    def backward(ctx, dy, d_z, _d_sel, _d_counts):
+        (xb, wg, wdn, wup, wgus, wds, wgu, wde, logits, sel, weights, lse, inv, y_back, act_cat, h1_s, x_sorted, h1,
+         hidden, recv_pos, row_src, pad_offsets, tile_expert, n_tiles) = ctx.saved_tensors
+        shape, route, group, status = ctx.shape, ctx.route, ctx.group, ctx.status
+        send_splits, recv_splits, n_recv, P, El = ctx.splits
+        T, D, L, E, K, F, Fs = shape.T, shape.D, shape.L, shape.E, shape.K, shape.F, shape.Fs
+        dev = xb.device
+        st = _stream()
+        lib = _cabi.load()
+        bf = dict(dtype=BF, device=dev)
+        f32 = dict(dtype=torch.float32, device=dev)
+        if dy is None:
+            dy = torch.zeros(T, D, **bf)
+        dyb = _as_bf16(dy.reshape(T, D))
+        dt = ctx.dtypes
+        lin_dtype = torch.float32 if any(d == torch.float32 for d in dt[1:6]) else BF
+        gtype = _cabi.F32 if lin_dtype == torch.float32 else _cabi.BF16
+        lin = dict(dtype=lin_dtype, device=dev)
+        ws = torch.empty(max(16, lib.lmoe_wgrad_workspace_bytes(shape)), dtype=torch.uint8, device=dev)
+        n_send = T * K
+
+        # output stage (local)
+        d_routed = torch.empty(T, L, **bf)
+        d_hidden_s = torch.empty(T, Fs, **bf)
+        _cabi.call("lmoe_combine_out_bwd_dgrad", shape, ptr(dyb), ptr(wup), ptr(wds), ptr(d_routed), ptr(d_hidden_s),
+                   ptr(status), st)
+        # adjoint of the combine in send order, then back to the expert ranks
+        d_y_send = torch.empty(n_send, L, **bf)
+        d_weights = torch.empty(T, K, **f32)
+        _cabi.call("lmoe_combine_bwd_rows", ptr(d_routed), ptr(y_back), ptr(weights), ptr(route.perm), n_send, K, L, None,
+                   ptr(d_y_send), ptr(d_weights), st)
+        d_y_recv = _a2a(d_y_send, n_recv, send_splits, recv_splits, group)
+
+        # local work that overlaps nothing yet but needs no exchange
+        d_w_up = torch.empty(D, L, **lin)
+        d_w_down_s = torch.empty(D, Fs, **lin)
+        _cabi.call("lmoe_combine_out_bwd_wgrad", shape, ptr(dyb), ptr(act_cat), ptr(d_w_up), ptr(d_w_down_s), gtype,
+                   ptr(ws), ws.numel(), ptr(status), st)
+        dgrad_cat = torch.empty(T, 2 * Fs + L + E, **bf)
+        _cabi.call("lmoe_swiglu_bwd", T, Fs, ptr(h1_s), ptr(d_hidden_s), ptr(dgrad_cat), 2 * Fs + L + E, None, st)
+
+        # local experts: dgrads and the shard's weight gradients
+        d_w_gate_up = torch.zeros(El, L, 2 * F, **bf)
+        d_w_down_e = torch.zeros(El, F, L, **bf)
+        d_x_recv = torch.empty(n_recv, L, **bf)
+        if n_recv > 0:
+            d_y_sorted = torch.empty(P, L, **bf)
+            _cabi.call("lmoe_gather_rows", ptr(d_y_recv), ptr(row_src), 1, P, L, ptr(n_tiles), ptr(d_y_sorted), st)
+            d_hidden = torch.empty(P, F, **bf)
+            d_h1 = torch.empty(P, 2 * F, **bf)
+            d_x_sorted = torch.empty(P, L, **bf)
+            _cabi.call("lmoe_grouped_bwd_dgrad", P, El, L, F, ptr(d_y_sorted), ptr(h1), ptr(wgu), ptr(wde),
+                       ptr(tile_expert), ptr(n_tiles), ptr(d_hidden), ptr(d_h1), ptr(d_x_sorted), ptr(status), st)
+            _cabi.call("lmoe_grouped_bwd_wgrad", P, El, L, F, ptr(x_sorted), ptr(d_h1), ptr(hidden), ptr(d_y_sorted),
+                       ptr(pad_offsets), ptr(d_w_gate_up), ptr(d_w_down_e), ptr(status), st)
+            _cabi.call("lmoe_gather_rows", ptr(d_x_sorted), ptr(recv_pos), 1, n_recv, L, None, ptr(d_x_recv), st)
+        d_x_back = _a2a(d_x_recv, n_send, recv_splits, send_splits, group)
+        # adjoint of the gather: d_x_latent[t] = sum_k d_x_back[inv[t*K+k]]  -> dgrad_cat[:, 2Fs:2Fs+L]
+        d_x_latent = dgrad_cat[:, 2 * Fs:]
+        _cabi.call("lmoe_combine_rows", ptr(d_x_back), ptr(inv), None, T, K, L, ptr(d_x_latent), 2 * Fs + L + E, st)
+
+        dz = None if d_z is None else d_z.to(torch.float32).reshape(1).contiguous()
+        _cabi.call("lmoe_gate_topk_bwd", shape, ptr(logits), ptr(sel), ptr(weights), ptr(d_weights), ptr(lse), ptr(dz),
+                   ctx.z_coef, ptr(dgrad_cat), st)
+        dx = torch.empty(T, D, **bf)
+        d_w_gate_up_s = torch.empty(2 * Fs, D, **lin)
+        d_w_down = torch.empty(L, D, **lin)
+        d_w_gate = torch.empty(E, D, **lin)
+        _cabi.call("lmoe_xside_bwd", shape, ptr(dgrad_cat), ptr(wgus), ptr(wdn), ptr(wg), ptr(xb), ptr(dx),
+                   ptr(d_w_gate_up_s), ptr(d_w_down), ptr(d_w_gate), gtype, ptr(ws), ws.numel(), ptr(status), st)
+
+        def as_param(g, d):
+            return g if g.dtype == d else g.to(d)
+
+        return (as_param(dx, dt[0]), as_param(d_w_gate, dt[1]), as_param(d_w_down, dt[2]), as_param(d_w_up, dt[3]),
+                as_param(d_w_gate_up_s, dt[4]), as_param(d_w_down_s, dt[5]), as_param(d_w_gate_up, dt[6]),
+                as_param(d_w_down_e, dt[7]), None, None, None, None)
+
+
+def latent_moe_ep(x2d, w_gate, w_down, w_up, w_gate_up_s, w_down_s, w_gate_up_loc, w_down_e_loc, expert_bias, top_k,
+                  z_coef, group):
+    """Functional form; the expert weights are this rank's shard.  Returns (y, aux_loss, sel, global counts)."""
+    return ExpertParallelLatentMoE.apply(x2d, w_gate, w_down, w_up, w_gate_up_s, w_down_s, w_gate_up_loc, w_down_e_loc,
+                                         expert_bias, int(top_k), float(z_coef), group)

@@ -14,6 +14,13 @@ from . import _cabi
 from .functional import latent_moe, make_shape, _stream
 
 
+def _ep_size(group) -> int:
+    if group is None:
+        return 1
+    import torch.distributed as dist
+    return dist.get_world_size(group)
+
+
 class SwiGLUExpert(nn.Module):
     """Parameter container of the shared expert (``models/moe.py:32-69``): ``gate_up_proj`` [2*d_ff, d_model]
     (gate = first half) and ``down_proj`` [d_model, d_ff].  The math runs inside the fused layer kernels."""
@@ -142,7 +149,13 @@ class LatentMoELayer(nn.Module):
         preserve = getattr(config, "latent_preserve_expert_dim", False)
         latent_expert_dim = expert_dim if preserve else expert_dim // latent_ratio   # moe.py:680-685
         self.latent_expert_dim = latent_expert_dim
-        self.experts = LatentBatchedExperts(n_experts, latent_dim, latent_expert_dim, bias=False)
+        # Optional expert parallelism: `config.ep_group` (a torch.distributed process group) shards the
+        # routed experts; this rank then holds experts [rank*E/G, (rank+1)*E/G) only.  Absent -> all experts.
+        self.ep_group = getattr(config, "ep_group", None)
+        self.ep_size = _ep_size(self.ep_group)
+        if n_experts % self.ep_size:
+            raise ValueError("the expert count must be divisible by the expert-parallel group size")
+        self.experts = LatentBatchedExperts(n_experts // self.ep_size, latent_dim, latent_expert_dim, bias=False)
         self.router = AuxLossFreeRouter(d_model=d_model, n_experts=n_experts, top_k=n_activated, z_loss_coef=z_loss_coef)
         self.dropout = nn.Dropout(getattr(config, "dropout", 0.0))
         self.aux_loss = torch.tensor(0.0)
@@ -157,16 +170,20 @@ class LatentMoELayer(nn.Module):
         batch_size, seq_len, d_model = x.shape
         x_flat = x.reshape(-1, d_model)
         shared = self.shared_experts[0]
-        y, z_loss, sel, counts = latent_moe(
-            x_flat, self.router.gate.weight, self.down_proj.weight, self.up_proj.weight,
-            shared.gate_up_proj.weight, shared.down_proj.weight,
-            self.experts.gate_up_weight, self.experts.down_weight,
-            self.router.expert_bias, self.n_activated, self.router.z_loss_coef)
+        args = (x_flat, self.router.gate.weight, self.down_proj.weight, self.up_proj.weight,
+                shared.gate_up_proj.weight, shared.down_proj.weight,
+                self.experts.gate_up_weight, self.experts.down_weight,
+                self.router.expert_bias, self.n_activated, self.router.z_loss_coef)
+        if self.ep_size > 1:
+            from .ep import latent_moe_ep
+            y, z_loss, sel, counts = latent_moe_ep(*args, self.ep_group)   # counts: load summed over all ranks
+        else:
+            y, z_loss, sel, counts = latent_moe(*args)
         self.aux_loss = z_loss                                            # moe.py:719
         if self.training:                                                 # moe.py:237-240
             self.router._last_selected_experts = sel
             self.router._last_counts = counts
-            self.router._last_num_tokens = x_flat.shape[0]
+            self.router._last_num_tokens = x_flat.shape[0] * self.ep_size
         y = self.dropout(y)                                               # moe.py:732
         return y.view(batch_size, seq_len, d_model)
 

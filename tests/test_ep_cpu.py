@@ -1,0 +1,84 @@
+"""Expert-parallel host logic on CPU: two gloo ranks exchange rows exactly as the GPU path does (same split
+sizes, same receive order, same regroup contract) and must reproduce the single-rank oracle."""
+import os
+import sys
+
+import pytest
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+from conftest import ROOT
+
+
+def _worker(rank, world, port, tmpdir):
+    sys.path.insert(0, ROOT)
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        from oracle import inputs, latent_moe_ref as R, ep_ref
+        from swamla_b200.ep import splits_from_counts
+        w = inputs.WORKLOADS["tiny_ragged"]                         # E = 32, K = 8, L = 64
+        params, buffers, _, _ = inputs.make_inputs(w, seed=0)       # same parameters on every rank
+        g = torch.Generator().manual_seed(100 + rank)
+        x = torch.randn(1, 50 + 13 * rank, w.D, generator=g)        # different token counts per rank
+        E, K, L, El = w.E, w.K, w.L, w.E // world
+        with torch.no_grad():
+            ref = R.layer_forward(params, buffers, x, K)            # all experts local: the expected result
+        # --- what the GPU path does, in torch ---
+        counts_all = [torch.zeros(E, dtype=torch.int32) for _ in range(world)]
+        dist.all_gather(counts_all, ref["counts"].to(torch.int32))
+        counts_all = torch.stack(counts_all)
+        send_splits, recv_splits = splits_from_counts(counts_all, rank)
+        assert sum(send_splits) == x.shape[1] * K
+        send_rows = ref["x_sorted"].contiguous()                    # expert order = destination order
+        recv_rows = torch.empty(sum(recv_splits), L)
+        dist.all_to_all_single(recv_rows, send_rows, recv_splits, send_splits)
+        recv_pos, row_src, pad_offsets, tile_expert, n_tiles = ep_ref.regroup_tables(counts_all, rank)
+        x_sorted = torch.zeros(n_tiles * 128, L)
+        valid = row_src >= 0
+        x_sorted[valid] = recv_rows[row_src[valid]]
+        # local experts over the padded layout
+        lo, hi = rank * El, (rank + 1) * El
+        wgu, wd = params["experts.gate_up_weight"][lo:hi], params["experts.down_weight"][lo:hi]
+        h1 = R.grouped_gemm(x_sorted, wgu, pad_offsets)
+        gate, up = h1.chunk(2, -1)
+        y_sorted = R.grouped_gemm(torch.nn.functional.silu(gate) * up, wd, pad_offsets)
+        y_recv = y_sorted[recv_pos]
+        y_back = torch.empty(sum(send_splits), L)
+        dist.all_to_all_single(y_back, y_recv, send_splits, recv_splits)
+        torch.testing.assert_close(y_back, ref["y_sorted"], rtol=1e-5, atol=1e-6)
+        inv = torch.empty_like(ref["perm"])
+        inv[ref["perm"]] = torch.arange(inv.numel())
+        T = x.shape[1]
+        routed = (ref["weights"].reshape(T, K, 1) * y_back[inv].view(T, K, L)).sum(1)
+        torch.testing.assert_close(routed, ref["routed"], rtol=1e-5, atol=1e-6)
+        # every received row sits in the segment of its expert, sources in rank order
+        assert torch.equal(tile_expert, torch.repeat_interleave(torch.arange(El), (pad_offsets[1:] - pad_offsets[:-1]) // 128))
+        open(os.path.join(tmpdir, f"ok{rank}"), "w").write("ok")
+    finally:
+        dist.destroy_process_group()
+
+
+def test_two_rank_exchange_reproduces_single_rank_oracle(tmp_path):
+    port = 29500 + (os.getpid() % 500)
+    mp.spawn(_worker, args=(2, port, str(tmp_path)), nprocs=2, join=True)
+    assert (tmp_path / "ok0").exists() and (tmp_path / "ok1").exists()
+
+
+def test_splits_from_counts():
+    from swamla_b200.ep import splits_from_counts
+    counts_all = torch.tensor([[1, 2, 3, 4], [5, 6, 7, 8]], dtype=torch.int32)      # G = 2, E = 4
+    assert splits_from_counts(counts_all, 0) == ([3, 7], [3, 11])
+    assert splits_from_counts(counts_all, 1) == ([11, 15], [7, 15])
+
+
+def test_regroup_tables_contract():
+    from oracle import ep_ref
+    counts_all = torch.tensor([[3, 0, 130, 1], [2, 0, 5, 0]], dtype=torch.int32)
+    recv_pos, row_src, pad_offsets, tile_expert, n_tiles = ep_ref.regroup_tables(counts_all, 1)   # experts 2, 3
+    assert pad_offsets.tolist() == [0, 256, 384] and n_tiles == 3 and tile_expert.tolist() == [0, 0, 1]
+    # receive order: (s0,e2) x130, (s0,e3) x1, (s1,e2) x5 ; padded: e2: s0 rows, s1 rows ; e3: s0 row
+    assert recv_pos[:130].tolist() == list(range(130)) and recv_pos[130].item() == 256
+    assert recv_pos[131:].tolist() == list(range(130, 135))
+    assert (row_src[135:256] == -1).all() and row_src[256].item() == 130 and (row_src[257:] == -1).all()
