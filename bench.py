@@ -88,7 +88,7 @@ class ClockSampler:
                 "reasons": sorted(reasons)}
 
 
-def build_layer(w, rank, device, ep_group=None):
+def build_layer(w, rank, device, ep_group=None, ep_mode="p2p"):
     """The layer with seed-0 parameters (identical on every rank) and this rank's own tokens (seed = rank).
     With `ep_group` the routed experts are sharded: this rank keeps experts [rank*E/G, (rank+1)*E/G)."""
     from swamla_b200.layer import LatentMoELayer
@@ -102,6 +102,7 @@ def build_layer(w, rank, device, ep_group=None):
     if ep_group is not None:
         import torch.distributed as dist
         cfg.ep_group = ep_group
+        cfg.ep_mode = ep_mode
         G = dist.get_world_size(ep_group)
         El = w.E // G
         for k in ("experts.gate_up_weight", "experts.down_weight"):
@@ -203,6 +204,7 @@ def main():
     ap.add_argument("--workload", default=None)
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--ep-mode", default="p2p", choices=["p2p", "nccl"])
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
 
@@ -234,7 +236,8 @@ def main():
         same_workload_1gpu = w.T / (ms1 * 1e-3)
         del l1, x1, xh1, dyh1
         torch.cuda.empty_cache()
-    layer, x_host, dy_host = build_layer(w, rank, dev, ep_group=dist.group.WORLD if world > 1 else None)
+    layer, x_host, dy_host = build_layer(w, rank, dev, ep_group=dist.group.WORLD if world > 1 else None,
+                                         ep_mode=args.ep_mode)
     x = x_host.to(dev).requires_grad_(True)
     dy = dy_host.to(dev)
 
@@ -353,7 +356,8 @@ def main():
         "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
         "config": workload_config(w, world, "single GPU" if world == 1 else
                                   f"ep{world}: experts sharded {w.E // world} per GPU, tokens data-parallel, "
-                                  "dispatch/combine all-to-all (NCCL) of latent rows"),
+                                  + ("dispatch/combine by one-sided NVLink stores into symmetric buffers"
+                                     if args.ep_mode == "p2p" else "dispatch/combine all-to-all (NCCL) of latent rows")),
         "clocks": clocks, "gpu_launches": int(launches), "roofline": roofline,
     }
     if e2e is not None:

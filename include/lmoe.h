@@ -250,6 +250,34 @@ int lmoe_invert_perm(const int32_t* perm, int64_t n, int32_t* inv, void* stream)
 int lmoe_ep_plan(const int32_t* counts_all, int G, int E, int rank, int32_t* recv_pos, int32_t* row_src,
                  int32_t* pad_offsets, int32_t* tile_expert, int32_t* n_tiles, void* stream);
 
+/* One-sided variant of the exchange: rows are stored through peer pointers (NVLink) straight into the destination
+ * rank's padded expert layout, so there is no send buffer, no all-to-all and no regroup copy, and nothing is sized
+ * on the host.  `capacity_rows` (multiple of 128) is the static size of every rank's incoming buffer; if a shard
+ * would receive more, `status` is set to 201 and the excess rows are dropped.  The caller orders the phases across
+ * ranks with stream-ordered collectives (dispatch -> barrier -> grouped GEMMs -> return -> barrier).
+ *   lmoe_ep_tables   src_off[G*E], dst_base[E], seg_cum[(E/G)*G], pad_offsets[E/G+1], tile_expert[cap/128], n_tiles[1]
+ *   lmoe_ep_dispatch      row i of this rank's expert-sorted order (perm, sel, offsets from lmoe_route_permute) =
+ *                         src_rows[perm[i]/K]  ->  peer_bufs[owner][dst_base[e] + i - offsets[e]]
+ *   lmoe_ep_dispatch_bwd  same walk with rows weights[flat] * d_routed[t]; also d_weights[flat] = <d_routed[t], y_ret[i]>
+ *   lmoe_ep_zero_pads     zeroes the pad rows of this rank's incoming buffer
+ *   lmoe_ep_return        padded local row p -> peer_ret[source][src_off[source][e] + r]  (inverse walk)
+ * peer_bufs / peer_ret: DEVICE arrays of G device pointers (this rank's own buffer at index `rank`). */
+int lmoe_ep_tables(const int32_t* counts_all, int G, int E, int rank, int64_t capacity_rows, int32_t* src_off,
+                   int32_t* dst_base, int32_t* seg_cum, int32_t* pad_offsets, int32_t* tile_expert, int32_t* n_tiles,
+                   int32_t* status, void* stream);
+int lmoe_ep_zero_pads(void* buf, int L, const int32_t* pad_offsets, const int32_t* seg_cum, const int32_t* counts_all,
+                      int G, int E, int rank, void* stream);
+int lmoe_ep_dispatch(const void* src_rows, const int32_t* perm, const int32_t* sel, const int32_t* offsets,
+                     const int32_t* dst_base, int64_t n_rows, int K, int E, int G, int L, int64_t capacity_rows,
+                     void* const* peer_bufs, int32_t* status, void* stream);
+int lmoe_ep_dispatch_bwd(const void* d_routed, const void* y_ret, const float* weights, const int32_t* perm,
+                         const int32_t* sel, const int32_t* offsets, const int32_t* dst_base, int64_t n_rows, int K,
+                         int E, int G, int L, int64_t capacity_rows, void* const* peer_bufs, float* d_weights,
+                         int32_t* status, void* stream);
+int lmoe_ep_return(const void* rows, const int32_t* tile_expert, const int32_t* n_tiles, const int32_t* pad_offsets,
+                   const int32_t* seg_cum, const int32_t* src_off, const int32_t* counts_all, int G, int E, int rank,
+                   int L, int64_t capacity_rows, void* const* peer_ret, void* stream);
+
 /* ---- router bias update (after backward) ----
  * load = histogram(sel) (= counts); bias -= gamma * sign(load - T*K/E); history = .99 history + .01 load.
  * Replaces models/moe.py:254-275. */

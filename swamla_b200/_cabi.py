@@ -69,6 +69,11 @@ SIGNATURES = {
     "lmoe_combine_bwd_rows": (c_int, [P, P, P, P, c_int64, c_int, c_int, P, P, P, P]),
     "lmoe_invert_perm": (c_int, [P, c_int64, P, P]),
     "lmoe_ep_plan": (c_int, [P, c_int, c_int, c_int, P, P, P, P, P, P]),
+    "lmoe_ep_tables": (c_int, [P, c_int, c_int, c_int, c_int64, P, P, P, P, P, P, P, P]),
+    "lmoe_ep_zero_pads": (c_int, [P, c_int, P, P, P, c_int, c_int, c_int, P]),
+    "lmoe_ep_dispatch": (c_int, [P, P, P, P, P, c_int64, c_int, c_int, c_int, c_int, c_int64, P, P, P]),
+    "lmoe_ep_dispatch_bwd": (c_int, [P, P, P, P, P, P, P, c_int64, c_int, c_int, c_int, c_int, c_int64, P, P, P, P]),
+    "lmoe_ep_return": (c_int, [P, P, P, P, P, P, P, c_int, c_int, c_int, c_int, c_int64, P, P]),
     "lmoe_router_bias_update": (c_int, [SP, P, c_float, P, P, P]),
     "lmoe_cast_f32_to_bf16": (c_int, [P, P, c_int64, P]),
     "lmoe_cast_bf16_to_f32": (c_int, [P, P, c_int64, P]),

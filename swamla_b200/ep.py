@@ -224,3 +224,212 @@ def latent_moe_ep(x2d, w_gate, w_down, w_up, w_gate_up_s, w_down_s, w_gate_up_lo
     """Functional form; the expert weights are this rank's shard.  Returns (y, aux_loss, sel, global counts)."""
     return ExpertParallelLatentMoE.apply(x2d, w_gate, w_down, w_up, w_gate_up_s, w_down_s, w_gate_up_loc, w_down_e_loc,
                                          expert_bias, int(top_k), float(z_coef), group)
+
+
+# ======================================================================================================
+# One-sided exchange over NVLink: rows are stored straight into the destination rank's padded expert
+# layout through peer pointers of symmetric buffers (csrc/ep_p2p.cu).  No send buffer, no all-to-all, no
+# regroup copy and no host synchronisation: sizes stay on the device, capacities are static.
+# ======================================================================================================
+class SymmetricBuffers:
+    """Per-layer symmetric buffers and their peer pointer tables.
+
+    x_in / dy_in  [capacity, L]  rows arriving from all ranks in this rank's padded expert layout (fwd / bwd)
+    y_ret / dx_ret [n_send, L]   result rows coming back, in this rank's expert-sorted (send) order
+    capacity = roundup(capacity_factor * n_send, 128) + 128 * E/G rows; an expert shard that receives more
+    than that raises device status 201 (rows beyond the capacity are dropped).
+    """
+
+    def __init__(self, group, n_send: int, L: int, El: int, capacity_factor: float, device):
+        import torch.distributed._symmetric_memory as symm_mem
+        t = torch.tensor([n_send], dtype=torch.int64, device=device)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX, group=group)       # symmetric allocations: same size everywhere
+        self.n_send_max = int(t.item())
+        self.capacity = (int(capacity_factor * self.n_send_max) + 127) // 128 * 128 + El * 128
+        self.L = L
+        mk = lambda rows: symm_mem.empty(rows, L, dtype=BF, device=device)
+        self.x_in, self.dy_in = mk(self.capacity), mk(self.capacity)
+        self.y_ret, self.dx_ret = mk(self.n_send_max), mk(self.n_send_max)
+        self.handles = [symm_mem.rendezvous(b, group) for b in (self.x_in, self.dy_in, self.y_ret, self.dx_ret)]
+        ptrs = lambda h: torch.tensor(list(h.buffer_ptrs), dtype=torch.int64, device=device)
+        self.peer_x_in, self.peer_dy_in, self.peer_y_ret, self.peer_dx_ret = (ptrs(h) for h in self.handles)
+        self.sync_word = torch.zeros(1, dtype=torch.int32, device=device)
+
+    def barrier(self, group):
+        """Stream-ordered barrier across the ranks: a collective on one word.  Every kernel queued before it on any
+        rank has completed (its peer stores included) before any kernel queued after it starts."""
+        dist.all_reduce(self.sync_word, group=group)
+
+
+class ExpertParallelP2P(torch.autograd.Function):
+    """Expert-parallel forward/backward with one-sided NVLink stores (see the banner above)."""
+
+    @staticmethod
+    def forward(ctx, x, w_gate, w_down, w_up, w_gate_up_s, w_down_s, w_gate_up_loc, w_down_e_loc, expert_bias,
+                top_k: int, z_coef: float, group, bufs: SymmetricBuffers):
+        if not x.is_cuda:
+            raise _cabi.LmoeError("the LatentMoE path runs on a CUDA device only (no CPU fallback)")
+        lib = _cabi.load()
+        G, rank = dist.get_world_size(group), dist.get_rank(group)
+        dev = x.device
+        T, D = x.shape
+        El, L, F2 = w_gate_up_loc.shape
+        E, F, Fs, K = El * G, F2 // 2, w_down_s.shape[1], top_k
+        shape = make_shape(T, D, L, E, K, F, Fs)
+        st = _stream()
+        bf = dict(dtype=BF, device=dev)
+        f32 = dict(dtype=torch.float32, device=dev)
+        i32 = dict(dtype=torch.int32, device=dev)
+        n_send, P = T * K, bufs.capacity
+        if n_send > bufs.n_send_max:
+            raise _cabi.LmoeError("more rows than the symmetric buffers were sized for")
+
+        xb = _as_bf16(x)
+        wg, wdn, wup = _as_bf16(w_gate), _as_bf16(w_down), _as_bf16(w_up)
+        wgus, wds = _as_bf16(w_gate_up_s), _as_bf16(w_down_s)
+        wgu, wde = _as_bf16(w_gate_up_loc), _as_bf16(w_down_e_loc)
+        bias = expert_bias.to(torch.float32).contiguous()
+        status = torch.zeros(1, **i32)
+
+        logits = torch.empty(T, E, **f32)
+        x_latent = torch.empty(T, L, **bf)
+        _cabi.call("lmoe_xproj_fwd", shape, ptr(xb), ptr(wg), ptr(wdn), ptr(logits), ptr(x_latent), ptr(status), st)
+        sel = torch.empty(T, K, **i32)
+        weights = torch.empty(T, K, **f32)
+        lse = torch.empty(T, **f32)
+        z_partial = torch.empty((T + 7) // 8, **f32)
+        z_loss = torch.empty(1, **f32)
+        _cabi.call("lmoe_gate_topk_fwd", shape, ptr(logits), ptr(bias), float(z_coef), ptr(sel), ptr(weights), ptr(lse),
+                   ptr(z_partial), ptr(z_loss), st)
+        route = RouteTables(shape, dev)
+        ws = torch.empty(max(16, lib.lmoe_route_workspace_bytes(shape)), dtype=torch.uint8, device=dev)
+        _cabi.call("lmoe_route_permute", shape, ptr(sel), route.struct, ptr(ws), ws.numel(), st)
+        # the histogram exchange is also the barrier that orders this step's peer stores after every
+        # rank's previous use of its buffers
+        counts_all = torch.empty(G, E, **i32)
+        dist.all_gather_into_tensor(counts_all, route.counts.contiguous(), group=group)
+
+        src_off = torch.empty(G * E, **i32)
+        dst_base = torch.empty(E, **i32)
+        seg_cum = torch.empty(El * G, **i32)
+        pad_offsets = torch.empty(El + 1, **i32)
+        tile_expert = torch.empty(P // 128, **i32)
+        n_tiles = torch.empty(1, **i32)
+        _cabi.call("lmoe_ep_tables", ptr(counts_all), G, E, rank, P, ptr(src_off), ptr(dst_base), ptr(seg_cum),
+                   ptr(pad_offsets), ptr(tile_expert), ptr(n_tiles), ptr(status), st)
+        _cabi.call("lmoe_ep_dispatch", ptr(x_latent), ptr(route.perm), ptr(sel), ptr(route.offsets), ptr(dst_base), n_send,
+                   K, E, G, L, P, ptr(bufs.peer_x_in), ptr(status), st)
+        _cabi.call("lmoe_ep_zero_pads", ptr(bufs.x_in), L, ptr(pad_offsets), ptr(seg_cum), ptr(counts_all), G, E, rank, st)
+        inv = torch.empty(n_send, **i32)
+        _cabi.call("lmoe_invert_perm", ptr(route.perm), n_send, ptr(inv), st)
+        # shared expert: independent of the exchange, queued before the barrier so it overlaps the peers' stores
+        h1_s = torch.empty(T, 2 * Fs, **bf)
+        act_cat = torch.empty(T, L + Fs, **bf)
+        _cabi.call("lmoe_shared_gateup_fwd", shape, ptr(xb), ptr(wgus), ptr(h1_s), ptr(act_cat), ptr(status), st)
+        bufs.barrier(group)                                   # all rows have landed in x_in
+
+        h1 = torch.empty(P, 2 * F, **bf)
+        hidden = torch.empty(P, F, **bf)
+        y_sorted = torch.empty(P, L, **bf)
+        _cabi.call("lmoe_grouped_fwd", P, El, L, F, ptr(bufs.x_in), ptr(wgu), ptr(wde), ptr(tile_expert), ptr(n_tiles),
+                   ptr(h1), ptr(hidden), ptr(y_sorted), ptr(status), st)
+        _cabi.call("lmoe_ep_return", ptr(y_sorted), ptr(tile_expert), ptr(n_tiles), ptr(pad_offsets), ptr(seg_cum),
+                   ptr(src_off), ptr(counts_all), G, E, rank, L, P, ptr(bufs.peer_y_ret), st)
+        bufs.barrier(group)                                   # all results have landed in y_ret
+
+        y = torch.empty(T, D, **bf)
+        back_route = Route(counts=ptr(route.counts), offsets=ptr(route.offsets), perm=ptr(route.perm),
+                           pad_offsets=ptr(route.pad_offsets), pos=ptr(inv), row_src=ptr(route.row_src),
+                           tile_expert=ptr(route.tile_expert), n_tiles=ptr(route.n_tiles))
+        _cabi.call("lmoe_combine_out_fwd", shape, ptr(bufs.y_ret), back_route, ptr(weights), ptr(act_cat), ptr(wds),
+                   ptr(wup), ptr(y), ptr(status), st)
+
+        ctx.shape, ctx.route, ctx.group, ctx.z_coef, ctx.status, ctx.bufs = shape, route, group, float(z_coef), status, bufs
+        ctx.dims = (G, rank, El, P)
+        ctx.dtypes = [t.dtype for t in (x, w_gate, w_down, w_up, w_gate_up_s, w_down_s, w_gate_up_loc, w_down_e_loc)]
+        ctx.save_for_backward(xb, wg, wdn, wup, wgus, wds, wgu, wde, logits, sel, weights, lse, inv, act_cat, h1_s, h1,
+                              hidden, counts_all, src_off, dst_base, seg_cum, pad_offsets, tile_expert, n_tiles)
+        global_counts = counts_all.sum(0, dtype=torch.int32)
+        ctx.mark_non_differentiable(sel, global_counts)
+        out = y if x.dtype == BF else y.to(x.dtype)
+        return out, z_loss.reshape(()), sel, global_counts
+
+    @staticmethod
+    def backward(ctx, dy, d_z, _d_sel, _d_counts):
+        (xb, wg, wdn, wup, wgus, wds, wgu, wde, logits, sel, weights, lse, inv, act_cat, h1_s, h1, hidden, counts_all,
+         src_off, dst_base, seg_cum, pad_offsets, tile_expert, n_tiles) = ctx.saved_tensors
+        shape, route, group, status, bufs = ctx.shape, ctx.route, ctx.group, ctx.status, ctx.bufs
+        G, rank, El, P = ctx.dims
+        T, D, L, E, K, F, Fs = shape.T, shape.D, shape.L, shape.E, shape.K, shape.F, shape.Fs
+        dev = xb.device
+        st = _stream()
+        lib = _cabi.load()
+        bf = dict(dtype=BF, device=dev)
+        f32 = dict(dtype=torch.float32, device=dev)
+        if dy is None:
+            dy = torch.zeros(T, D, **bf)
+        dyb = _as_bf16(dy.reshape(T, D))
+        dt = ctx.dtypes
+        lin_dtype = torch.float32 if any(d == torch.float32 for d in dt[1:6]) else BF
+        gtype = _cabi.F32 if lin_dtype == torch.float32 else _cabi.BF16
+        lin = dict(dtype=lin_dtype, device=dev)
+        ws = torch.empty(max(16, lib.lmoe_wgrad_workspace_bytes(shape)), dtype=torch.uint8, device=dev)
+        n_send = T * K
+
+        d_routed = torch.empty(T, L, **bf)
+        d_hidden_s = torch.empty(T, Fs, **bf)
+        _cabi.call("lmoe_combine_out_bwd_dgrad", shape, ptr(dyb), ptr(wup), ptr(wds), ptr(d_routed), ptr(d_hidden_s),
+                   ptr(status), st)
+        # adjoint of the combine fused into the dispatch: rows w * d_routed go to the expert ranks, the gating
+        # gradients <d_routed, y> are formed from the returned rows kept in y_ret
+        d_weights = torch.empty(T, K, **f32)
+        _cabi.call("lmoe_ep_dispatch_bwd", ptr(d_routed), ptr(bufs.y_ret), ptr(weights), ptr(route.perm), ptr(sel),
+                   ptr(route.offsets), ptr(dst_base), n_send, K, E, G, L, P, ptr(bufs.peer_dy_in), ptr(d_weights),
+                   ptr(status), st)
+        _cabi.call("lmoe_ep_zero_pads", ptr(bufs.dy_in), L, ptr(pad_offsets), ptr(seg_cum), ptr(counts_all), G, E, rank, st)
+        # local work that needs no exchange overlaps the peers' stores
+        d_w_up = torch.empty(D, L, **lin)
+        d_w_down_s = torch.empty(D, Fs, **lin)
+        _cabi.call("lmoe_combine_out_bwd_wgrad", shape, ptr(dyb), ptr(act_cat), ptr(d_w_up), ptr(d_w_down_s), gtype,
+                   ptr(ws), ws.numel(), ptr(status), st)
+        dgrad_cat = torch.empty(T, 2 * Fs + L + E, **bf)
+        _cabi.call("lmoe_swiglu_bwd", T, Fs, ptr(h1_s), ptr(d_hidden_s), ptr(dgrad_cat), 2 * Fs + L + E, None, st)
+        bufs.barrier(group)                                   # all gradient rows have landed in dy_in
+
+        d_hidden = torch.empty(P, F, **bf)
+        d_h1 = torch.empty(P, 2 * F, **bf)
+        d_x_sorted = torch.empty(P, L, **bf)
+        _cabi.call("lmoe_grouped_bwd_dgrad", P, El, L, F, ptr(bufs.dy_in), ptr(h1), ptr(wgu), ptr(wde), ptr(tile_expert),
+                   ptr(n_tiles), ptr(d_hidden), ptr(d_h1), ptr(d_x_sorted), ptr(status), st)
+        _cabi.call("lmoe_ep_return", ptr(d_x_sorted), ptr(tile_expert), ptr(n_tiles), ptr(pad_offsets), ptr(seg_cum),
+                   ptr(src_off), ptr(counts_all), G, E, rank, L, P, ptr(bufs.peer_dx_ret), st)
+        d_w_gate_up = torch.empty(El, L, 2 * F, **bf)
+        d_w_down_e = torch.empty(El, F, L, **bf)
+        _cabi.call("lmoe_grouped_bwd_wgrad", P, El, L, F, ptr(bufs.x_in), ptr(d_h1), ptr(hidden), ptr(bufs.dy_in),
+                   ptr(pad_offsets), ptr(d_w_gate_up), ptr(d_w_down_e), ptr(status), st)
+        bufs.barrier(group)                                   # all rows have landed in dx_ret
+
+        d_x_latent = dgrad_cat[:, 2 * Fs:]
+        _cabi.call("lmoe_combine_rows", ptr(bufs.dx_ret), ptr(inv), None, T, K, L, ptr(d_x_latent), 2 * Fs + L + E, st)
+        dz = None if d_z is None else d_z.to(torch.float32).reshape(1).contiguous()
+        _cabi.call("lmoe_gate_topk_bwd", shape, ptr(logits), ptr(sel), ptr(weights), ptr(d_weights), ptr(lse), ptr(dz),
+                   ctx.z_coef, ptr(dgrad_cat), st)
+        dx = torch.empty(T, D, **bf)
+        d_w_gate_up_s = torch.empty(2 * Fs, D, **lin)
+        d_w_down = torch.empty(L, D, **lin)
+        d_w_gate = torch.empty(E, D, **lin)
+        _cabi.call("lmoe_xside_bwd", shape, ptr(dgrad_cat), ptr(wgus), ptr(wdn), ptr(wg), ptr(xb), ptr(dx),
+                   ptr(d_w_gate_up_s), ptr(d_w_down), ptr(d_w_gate), gtype, ptr(ws), ws.numel(), ptr(status), st)
+
+        def as_param(g, d):
+            return g if g.dtype == d else g.to(d)
+
+        return (as_param(dx, dt[0]), as_param(d_w_gate, dt[1]), as_param(d_w_down, dt[2]), as_param(d_w_up, dt[3]),
+                as_param(d_w_gate_up_s, dt[4]), as_param(d_w_down_s, dt[5]), as_param(d_w_gate_up, dt[6]),
+                as_param(d_w_down_e, dt[7]), None, None, None, None, None)
+
+
+def latent_moe_ep_p2p(x2d, w_gate, w_down, w_up, w_gate_up_s, w_down_s, w_gate_up_loc, w_down_e_loc, expert_bias, top_k,
+                      z_coef, group, bufs: SymmetricBuffers):
+    return ExpertParallelP2P.apply(x2d, w_gate, w_down, w_up, w_gate_up_s, w_down_s, w_gate_up_loc, w_down_e_loc,
+                                   expert_bias, int(top_k), float(z_coef), group, bufs)

@@ -153,6 +153,11 @@ class LatentMoELayer(nn.Module):
         # routed experts; this rank then holds experts [rank*E/G, (rank+1)*E/G) only.  Absent -> all experts.
         self.ep_group = getattr(config, "ep_group", None)
         self.ep_size = _ep_size(self.ep_group)
+        # "p2p": one-sided stores over NVLink into symmetric buffers; "nccl": all-to-all through NCCL
+        self.ep_mode = getattr(config, "ep_mode", "p2p")
+        # incoming-buffer capacity of a shard, as a multiple of this rank's own row count T*K (p2p mode)
+        self.ep_capacity_factor = float(getattr(config, "ep_capacity_factor", 2.0))
+        self._ep_bufs = None
         if n_experts % self.ep_size:
             raise ValueError("the expert count must be divisible by the expert-parallel group size")
         self.experts = LatentBatchedExperts(n_experts // self.ep_size, latent_dim, latent_expert_dim, bias=False)
@@ -174,7 +179,16 @@ class LatentMoELayer(nn.Module):
                 shared.gate_up_proj.weight, shared.down_proj.weight,
                 self.experts.gate_up_weight, self.experts.down_weight,
                 self.router.expert_bias, self.n_activated, self.router.z_loss_coef)
-        if self.ep_size > 1:
+        if self.ep_size > 1 and self.ep_mode == "p2p":
+            # one-sided NVLink stores into the peers' padded expert layout (symmetric buffers owned by the layer;
+            # one forward must be followed by its backward before the next forward reuses them)
+            from .ep import SymmetricBuffers, latent_moe_ep_p2p
+            n_send = x_flat.shape[0] * self.n_activated
+            if self._ep_bufs is None or self._ep_bufs.n_send_max < n_send:
+                self._ep_bufs = SymmetricBuffers(self.ep_group, n_send, self.latent_dim, self.experts.n_experts,
+                                                 self.ep_capacity_factor, x.device)
+            y, z_loss, sel, counts = latent_moe_ep_p2p(*args, self.ep_group, self._ep_bufs)
+        elif self.ep_size > 1:
             from .ep import latent_moe_ep
             y, z_loss, sel, counts = latent_moe_ep(*args, self.ep_group)   # counts: load summed over all ranks
         else:

@@ -37,7 +37,7 @@ def test_ep_plan_kernel_matches_reference_tables(G, E, rank):
     assert torch.equal(d["tile_expert"].cpu().long()[:n_tiles], tile_expert)
 
 
-def _ep_worker(rank, world, port, tmpdir):
+def _ep_worker(rank, world, port, tmpdir, mode):
     sys.path.insert(0, ROOT)
     os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
     import torch.distributed as dist
@@ -58,6 +58,7 @@ def _ep_worker(rank, world, port, tmpdir):
             cfg = w.config()
             if ep:
                 cfg.ep_group = dist.group.WORLD
+                cfg.ep_mode = mode
             layer = LatentMoELayer(cfg)
             state = {**params, **buffers}
             if ep:
@@ -69,9 +70,12 @@ def _ep_worker(rank, world, port, tmpdir):
         single, ep = build(False), build(True)
         outs = []
         for layer in (single, ep):
-            xg = x.to(dev).to(torch.bfloat16).requires_grad_(True)
-            y = layer(xg)
-            (y.float() * dy.to(dev).to(torch.bfloat16).float()).sum().backward()
+            for _ in range(2):                      # twice: the second step reuses the exchange buffers
+                for p_ in layer.parameters():
+                    p_.grad = None
+                xg = x.to(dev).to(torch.bfloat16).requires_grad_(True)
+                y = layer(xg)
+                (y.float() * dy.to(dev).to(torch.bfloat16).float()).sum().backward()
             outs.append((y.detach(), xg.grad, layer))
         torch.cuda.synchronize()
         (y1, dx1, l1), (y2, dx2, l2) = outs
@@ -100,8 +104,9 @@ def _ep_worker(rank, world, port, tmpdir):
 
 
 @pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs 2 GPUs")
-def test_expert_parallel_layer_matches_single_gpu_layer(tmp_path):
+@pytest.mark.parametrize("mode", ["nccl", "p2p"])
+def test_expert_parallel_layer_matches_single_gpu_layer(tmp_path, mode):
     import torch.multiprocessing as mp
-    port = 29600 + (os.getpid() % 300)
-    mp.spawn(_ep_worker, args=(2, port, str(tmp_path)), nprocs=2, join=True)
+    port = 29600 + (os.getpid() % 300) + (7 if mode == "p2p" else 0)
+    mp.spawn(_ep_worker, args=(2, port, str(tmp_path), mode), nprocs=2, join=True)
     assert (tmp_path / "ok0").exists() and (tmp_path / "ok1").exists()
