@@ -254,6 +254,7 @@ class SymmetricBuffers:
         ptrs = lambda h: torch.tensor(list(h.buffer_ptrs), dtype=torch.int64, device=device)
         self.peer_x_in, self.peer_dy_in, self.peer_y_ret, self.peer_dx_ret = (ptrs(h) for h in self.handles)
         self.sync_word = torch.zeros(1, dtype=torch.int32, device=device)
+        self.side = torch.cuda.Stream(device=device)   # the exchange kernels run here, beside independent GEMMs
 
     def barrier(self, group):
         """Stream-ordered barrier across the ranks: a collective on one word.  Every kernel queued before it on any
@@ -317,15 +318,23 @@ class ExpertParallelP2P(torch.autograd.Function):
         n_tiles = torch.empty(1, **i32)
         _cabi.call("lmoe_ep_tables", ptr(counts_all), G, E, rank, P, ptr(src_off), ptr(dst_base), ptr(seg_cum),
                    ptr(pad_offsets), ptr(tile_expert), ptr(n_tiles), ptr(status), st)
+        # the stores over NVLink run on a side stream, beside the shared-expert GEMM (which needs no exchange)
+        main, side = torch.cuda.current_stream(), bufs.side
+        ready = torch.cuda.Event()
+        ready.record(main)
+        side.wait_event(ready)
+        sst = side.cuda_stream
         _cabi.call("lmoe_ep_dispatch", ptr(x_latent), ptr(route.perm), ptr(sel), ptr(route.offsets), ptr(dst_base), n_send,
-                   K, E, G, L, P, ptr(bufs.peer_x_in), ptr(status), st)
-        _cabi.call("lmoe_ep_zero_pads", ptr(bufs.x_in), L, ptr(pad_offsets), ptr(seg_cum), ptr(counts_all), G, E, rank, st)
+                   K, E, G, L, P, ptr(bufs.peer_x_in), ptr(status), sst)
+        _cabi.call("lmoe_ep_zero_pads", ptr(bufs.x_in), L, ptr(pad_offsets), ptr(seg_cum), ptr(counts_all), G, E, rank, sst)
+        sent = torch.cuda.Event()
+        sent.record(side)
         inv = torch.empty(n_send, **i32)
         _cabi.call("lmoe_invert_perm", ptr(route.perm), n_send, ptr(inv), st)
-        # shared expert: independent of the exchange, queued before the barrier so it overlaps the peers' stores
         h1_s = torch.empty(T, 2 * Fs, **bf)
         act_cat = torch.empty(T, L + Fs, **bf)
         _cabi.call("lmoe_shared_gateup_fwd", shape, ptr(xb), ptr(wgus), ptr(h1_s), ptr(act_cat), ptr(status), st)
+        main.wait_event(sent)
         bufs.barrier(group)                                   # all rows have landed in x_in
 
         h1 = torch.empty(P, 2 * F, **bf)
@@ -383,10 +392,17 @@ class ExpertParallelP2P(torch.autograd.Function):
         # adjoint of the combine fused into the dispatch: rows w * d_routed go to the expert ranks, the gating
         # gradients <d_routed, y> are formed from the returned rows kept in y_ret
         d_weights = torch.empty(T, K, **f32)
+        main, side = torch.cuda.current_stream(), bufs.side
+        ready = torch.cuda.Event()
+        ready.record(main)
+        side.wait_event(ready)
+        sst = side.cuda_stream
         _cabi.call("lmoe_ep_dispatch_bwd", ptr(d_routed), ptr(bufs.y_ret), ptr(weights), ptr(route.perm), ptr(sel),
                    ptr(route.offsets), ptr(dst_base), n_send, K, E, G, L, P, ptr(bufs.peer_dy_in), ptr(d_weights),
-                   ptr(status), st)
-        _cabi.call("lmoe_ep_zero_pads", ptr(bufs.dy_in), L, ptr(pad_offsets), ptr(seg_cum), ptr(counts_all), G, E, rank, st)
+                   ptr(status), sst)
+        _cabi.call("lmoe_ep_zero_pads", ptr(bufs.dy_in), L, ptr(pad_offsets), ptr(seg_cum), ptr(counts_all), G, E, rank, sst)
+        sent = torch.cuda.Event()
+        sent.record(side)
         # local work that needs no exchange overlaps the peers' stores
         d_w_up = torch.empty(D, L, **lin)
         d_w_down_s = torch.empty(D, Fs, **lin)
@@ -394,6 +410,7 @@ class ExpertParallelP2P(torch.autograd.Function):
                    ptr(ws), ws.numel(), ptr(status), st)
         dgrad_cat = torch.empty(T, 2 * Fs + L + E, **bf)
         _cabi.call("lmoe_swiglu_bwd", T, Fs, ptr(h1_s), ptr(d_hidden_s), ptr(dgrad_cat), 2 * Fs + L + E, None, st)
+        main.wait_event(sent)
         bufs.barrier(group)                                   # all gradient rows have landed in dy_in
 
         d_hidden = torch.empty(P, F, **bf)
@@ -401,12 +418,19 @@ class ExpertParallelP2P(torch.autograd.Function):
         d_x_sorted = torch.empty(P, L, **bf)
         _cabi.call("lmoe_grouped_bwd_dgrad", P, El, L, F, ptr(bufs.dy_in), ptr(h1), ptr(wgu), ptr(wde), ptr(tile_expert),
                    ptr(n_tiles), ptr(d_hidden), ptr(d_h1), ptr(d_x_sorted), ptr(status), st)
+        ready2 = torch.cuda.Event()
+        ready2.record(main)
+        side.wait_event(ready2)
         _cabi.call("lmoe_ep_return", ptr(d_x_sorted), ptr(tile_expert), ptr(n_tiles), ptr(pad_offsets), ptr(seg_cum),
-                   ptr(src_off), ptr(counts_all), G, E, rank, L, P, ptr(bufs.peer_dx_ret), st)
+                   ptr(src_off), ptr(counts_all), G, E, rank, L, P, ptr(bufs.peer_dx_ret), sst)
+        returned = torch.cuda.Event()
+        returned.record(side)
+        # the shard's weight gradients need no exchange: they run beside the return stores
         d_w_gate_up = torch.empty(El, L, 2 * F, **bf)
         d_w_down_e = torch.empty(El, F, L, **bf)
         _cabi.call("lmoe_grouped_bwd_wgrad", P, El, L, F, ptr(bufs.x_in), ptr(d_h1), ptr(hidden), ptr(bufs.dy_in),
                    ptr(pad_offsets), ptr(d_w_gate_up), ptr(d_w_down_e), ptr(status), st)
+        main.wait_event(returned)
         bufs.barrier(group)                                   # all rows have landed in dx_ret
 
         d_x_latent = dgrad_cat[:, 2 * Fs:]
