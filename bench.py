@@ -98,6 +98,8 @@ def build_layer(w, rank, device, ep_group=None, ep_mode="p2p"):
         x = torch.randn(x.shape, generator=g)
         dy = torch.randn(dy.shape, generator=g)
     cfg = w.config()
+    if w.dtype == "fp8":
+        cfg.moe_fp8 = True          # routed expert GEMMs in e4m3 with per-tensor scaling (BASELINE cfg 4)
     state = {**params, **buffers}
     if ep_group is not None:
         import torch.distributed as dist
@@ -353,7 +355,8 @@ def main():
     out = {
         "metric": METRIC, "value": tokens_per_s, "unit": "tokens/s", "n_gpus": world, "steps": args.steps,
         "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak",
-        "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+        "vs_baseline": None, "dtype": "bf16" if w.dtype != "fp8" else "bf16 (routed expert GEMMs e4m3)",
+        "data": "synthetic",
         "config": workload_config(w, world, "single GPU" if world == 1 else
                                   f"ep{world}: experts sharded {w.E // world} per GPU, tokens data-parallel, "
                                   + ("dispatch/combine by one-sided NVLink stores into symmetric buffers"

@@ -278,6 +278,33 @@ int lmoe_ep_return(const void* rows, const int32_t* tile_expert, const int32_t* 
                    const int32_t* seg_cum, const int32_t* src_off, const int32_t* counts_all, int G, int E, int rank,
                    int L, int64_t capacity_rows, void* const* peer_ret, void* stream);
 
+/* ---- FP8 (e4m3) expert path ----
+ * Per-tensor dynamic scaling, the "tensorwise" recipe named by optimization/fp8_native.py:103-110 (torchao
+ * Float8Linear; the reference applies it to nn.Linear modules only, fp8_native.py:38-66,112-116, never to the
+ * routed experts -- running the expert GEMMs in e4m3 is this boundary's extension of that recipe).
+ *   q = saturate_e4m3(x * 448 / amax(x)),  deq = amax(x) / 448,  result = deq_a * deq_b * (A_q * B_q^T), fp32 accumulate.
+ * A tensor is quantised once and serves forward, dgrad and wgrad GEMMs alike (the scale is per tensor).
+ * Contraction extents of e4m3 GEMMs must be multiples of 128. */
+/* x[rows,row_len] bf16 -> q e4m3 (same shape), amax[1], deq[1].  With n_tiles_dev only the first
+ * 128 * n_tiles_dev[0] rows are read and written (padded routed layout). */
+int lmoe_fp8_quantize(const void* x_bf16, int64_t rows, int row_len, const int32_t* n_tiles_dev, void* q_e4m3,
+                      float* amax, float* deq, void* stream);
+/* C[M,N] bf16 = deq_a * deq_b * A_q[M,K] * B_q[N,K]^T; operand major-ness as in lmoe_gemm_bf16. */
+int lmoe_gemm_fp8(int M, int N, int K, const void* A, int64_t lda, int a_mn, const void* B, int64_t ldb, int b_mn,
+                  const float* deq_a, const float* deq_b, void* C, int64_t ldc, int32_t* status, void* stream);
+/* Routed gate_up with SwiGLU epilogue (models/moe.py:814,822-823): xq[P,L], wq[E,L,2F] -> h1[P,2F], hidden[P,F] bf16. */
+int lmoe_grouped_gateup_fp8(int64_t P, int E, int L, int F, const void* xq, const void* wq, const float* deq_x,
+                            const float* deq_w, const int32_t* tile_expert, const int32_t* n_tiles, void* h1,
+                            void* hidden, int32_t* status, void* stream);
+/* out[P,N] bf16 = aq[P,K] * Bq[e]: Bq stacked [E,K,N] (b_mn = 1: forward down GEMM, models/moe.py:828) or
+ * [E,N,K] (b_mn = 0: the same weights as dgrad operand). */
+int lmoe_grouped_rows_fp8(int64_t P, int E, int K, int N, const void* aq, const void* bq, int b_mn, const float* deq_a,
+                          const float* deq_b, const int32_t* tile_expert, const int32_t* n_tiles, void* out,
+                          int32_t* status, void* stream);
+/* Expert weight gradients: out[e][M,N] bf16 = aq[rows_e, M]^T * bq[rows_e, N]. */
+int lmoe_grouped_wgrad_fp8(int64_t P, int E, int M, int N, const void* aq, const void* bq, const float* deq_a,
+                           const float* deq_b, const int32_t* pad_offsets, void* out, int32_t* status, void* stream);
+
 /* ---- router bias update (after backward) ----
  * load = histogram(sel) (= counts); bias -= gamma * sign(load - T*K/E); history = .99 history + .01 load.
  * Replaces models/moe.py:254-275. */

@@ -23,6 +23,18 @@ def rb(t: torch.Tensor) -> torch.Tensor:
     return t.to(torch.bfloat16).to(torch.float32)
 
 
+def fq(t: torch.Tensor) -> torch.Tensor:
+    """Per-tensor e4m3 fake quantisation ("tensorwise" recipe, ``optimization/fp8_native.py:103-110``; the
+    arithmetic itself is torchao's, which the reference does not vendor -- parity unpinned for this part):
+    scale = 448 / amax, q = clamp(x * scale, +-448) rounded to e4m3, returned de-scaled in fp32."""
+    amax = t.abs().max()
+    if amax == 0:
+        return t.clone()
+    scale = 448.0 / amax
+    q = (t * scale).clamp(-448.0, 448.0).to(torch.float8_e4m3fn).to(torch.float32)
+    return q * (amax / 448.0)
+
+
 def _swiglu_bwd(h1, d_hidden):
     g, u = h1.chunk(2, -1)
     sg = torch.sigmoid(g)
@@ -36,8 +48,10 @@ def _grouped(a, b, offsets, transpose_b=False):
 
 
 def forward_backward(params: Dict[str, torch.Tensor], buffers, x, dy, top_k: int, z_coef: float = 0.001,
-                     aux_grad: float = 0.0, sel_override=None, param_grads_bf16: bool = True):
-    """Returns (forward dict, grads dict) of the bf16 pipeline for bf16-representable inputs."""
+                     aux_grad: float = 0.0, sel_override=None, param_grads_bf16: bool = True, fp8: bool = False):
+    """Returns (forward dict, grads dict) of the bf16 pipeline for bf16-representable inputs.
+    ``fp8``: the six operands of the routed-expert GEMMs are fake-quantised to e4m3 per tensor."""
+    q8 = fq if fp8 else (lambda t: t)
     p = {k: rb(v) for k, v in params.items()}
     B, S, D = x.shape
     x = rb(x).reshape(-1, D)
@@ -60,10 +74,12 @@ def forward_backward(params: Dict[str, torch.Tensor], buffers, x, dy, top_k: int
     counts, offsets, perm = R.route_permute(sel, E)
     tok = perm // K
     x_sorted = x_latent[tok]
-    h1 = rb(_grouped(x_sorted, Wgu, offsets))
+    xs_q, wgu_q, wde_q = q8(x_sorted), q8(Wgu), q8(Wde)
+    h1 = rb(_grouped(xs_q, wgu_q, offsets))
     g, u = h1.chunk(2, -1)
     hidden = rb(F.silu(g) * u)
-    y_sorted = rb(_grouped(hidden, Wde, offsets))
+    hid_q = q8(hidden)
+    y_sorted = rb(_grouped(hid_q, wde_q, offsets))
     w_sorted = w.reshape(-1)[perm]
     inv = torch.empty_like(perm)
     inv[perm] = torch.arange(perm.numel())
@@ -87,9 +103,11 @@ def forward_backward(params: Dict[str, torch.Tensor], buffers, x, dy, top_k: int
     d_w = torch.empty(T * K)
     d_w[perm] = d_w_sorted
     d_w = d_w.view(T, K)
-    d_hidden = rb(_grouped(d_y_sorted, Wde, offsets, transpose_b=True))
+    dy_q = q8(d_y_sorted)
+    d_hidden = rb(_grouped(dy_q, wde_q, offsets, transpose_b=True))
     d_h1 = _swiglu_bwd(h1, d_hidden)
-    d_x_sorted = rb(_grouped(d_h1, Wgu, offsets, transpose_b=True))
+    dh1_q = q8(d_h1)
+    d_x_sorted = rb(_grouped(dh1_q, wgu_q, offsets, transpose_b=True))
     d_x_latent = torch.zeros(T, L)
     for k in range(K):
         d_x_latent = d_x_latent + d_x_sorted[inv[torch.arange(T) * K + k]]
@@ -112,9 +130,9 @@ def forward_backward(params: Dict[str, torch.Tensor], buffers, x, dy, top_k: int
         "up_proj.weight": pg(dy.t() @ routed),
         "shared_experts.0.gate_up_proj.weight": pg(d_h1_s.t() @ x),
         "shared_experts.0.down_proj.weight": pg(dy.t() @ hidden_s),
-        "experts.gate_up_weight": rb(torch.stack([x_sorted[offsets[e]:offsets[e + 1]].t() @ d_h1[offsets[e]:offsets[e + 1]]
+        "experts.gate_up_weight": rb(torch.stack([xs_q[offsets[e]:offsets[e + 1]].t() @ dh1_q[offsets[e]:offsets[e + 1]]
                                                   for e in range(E)])),
-        "experts.down_weight": rb(torch.stack([hidden[offsets[e]:offsets[e + 1]].t() @ d_y_sorted[offsets[e]:offsets[e + 1]]
+        "experts.down_weight": rb(torch.stack([hid_q[offsets[e]:offsets[e + 1]].t() @ dy_q[offsets[e]:offsets[e + 1]]
                                                for e in range(E)])),
     }
     fwd = dict(y=y.view(B, S, D), aux_loss=z, logits=logits, sel=sel, weights=w, counts=counts, offsets=offsets,

@@ -74,6 +74,11 @@ SIGNATURES = {
     "lmoe_ep_dispatch": (c_int, [P, P, P, P, P, c_int64, c_int, c_int, c_int, c_int, c_int64, P, P, P]),
     "lmoe_ep_dispatch_bwd": (c_int, [P, P, P, P, P, P, P, c_int64, c_int, c_int, c_int, c_int, c_int64, P, P, P, P]),
     "lmoe_ep_return": (c_int, [P, P, P, P, P, P, P, c_int, c_int, c_int, c_int, c_int64, P, P]),
+    "lmoe_fp8_quantize": (c_int, [P, c_int64, c_int, P, P, P, P, P]),
+    "lmoe_gemm_fp8": (c_int, [c_int, c_int, c_int, P, c_int64, c_int, P, c_int64, c_int, P, P, P, c_int64, P, P]),
+    "lmoe_grouped_gateup_fp8": (c_int, [c_int64, c_int, c_int, c_int, P, P, P, P, P, P, P, P, P, P]),
+    "lmoe_grouped_rows_fp8": (c_int, [c_int64, c_int, c_int, c_int, P, P, c_int, P, P, P, P, P, P, P]),
+    "lmoe_grouped_wgrad_fp8": (c_int, [c_int64, c_int, c_int, c_int, P, P, P, P, P, P, P, P]),
     "lmoe_router_bias_update": (c_int, [SP, P, c_float, P, P, P]),
     "lmoe_cast_f32_to_bf16": (c_int, [P, P, c_int64, P]),
     "lmoe_cast_bf16_to_f32": (c_int, [P, P, c_int64, P]),

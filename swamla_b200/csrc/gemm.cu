@@ -43,18 +43,20 @@ int num_sms() {
   return n;
 }
 
-// Operand map: 2-D over a row-major [outer, inner] tensor of 16-bit elements, 128-byte swizzle.
+// Operand map: 2-D over a row-major [outer, inner] tensor of 16-bit (esz 2) or 8-bit (esz 1) elements,
+// 128-byte swizzle; the inner box extent is always 128 bytes.
 static int encode_2d(CUtensorMap* map, const void* base, long long inner, long long outer, long long ld_elems,
-                     int box_inner, int box_outer) {
+                     int box_outer, int esz) {
   EncodeTiledFn fn = encode_fn();
   if (!fn) return LMOE_ERR_DRIVER;
-  if ((reinterpret_cast<uintptr_t>(base) & 15) != 0 || ((ld_elems * 2) & 15) != 0) return LMOE_ERR_ALIGN;
-  if (inner <= 0 || outer <= 0 || box_inner * 2 > 128 || box_outer > 256) return LMOE_ERR_SHAPE;
+  if ((reinterpret_cast<uintptr_t>(base) & 15) != 0 || ((ld_elems * esz) & 15) != 0) return LMOE_ERR_ALIGN;
+  if (inner <= 0 || outer <= 0 || box_outer > 256) return LMOE_ERR_SHAPE;
   cuuint64_t dims[2] = {static_cast<cuuint64_t>(inner), static_cast<cuuint64_t>(outer)};
-  cuuint64_t strides[1] = {static_cast<cuuint64_t>(ld_elems) * 2};
-  cuuint32_t box[2] = {static_cast<cuuint32_t>(box_inner), static_cast<cuuint32_t>(box_outer)};
+  cuuint64_t strides[1] = {static_cast<cuuint64_t>(ld_elems) * esz};
+  cuuint32_t box[2] = {static_cast<cuuint32_t>(128 / esz), static_cast<cuuint32_t>(box_outer)};
   cuuint32_t estr[2] = {1, 1};
-  CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, estr,
+  CUresult r = fn(map, esz == 2 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_UINT8, 2,
+                  const_cast<void*>(base), dims, strides, box, estr,
                   CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   return r == CUDA_SUCCESS ? 0 : LMOE_ERR_DRIVER;
@@ -85,9 +87,9 @@ static int encode_out(CUtensorMap* map, void* base, bool f32, long long cols, lo
 }
 
 // ---------------------------------------------------------------- dispatch
-template <bool A_MN, bool B_MN, int BN, int EPI, int GRP>
+template <bool A_MN, bool B_MN, int BN, int EPI, int GRP, int ESZ>
 static int launch_inst(const GemmParams& p, int grid, cudaStream_t stream) {
-  auto kfn = gemm_kernel<A_MN, B_MN, BN, EPI, GRP>;
+  auto kfn = gemm_kernel<A_MN, B_MN, BN, EPI, GRP, ESZ>;
   constexpr int smem = GemmSmem<BN, EPI>::kTotal;
   static bool configured = false;
   if (!configured) {
@@ -101,26 +103,35 @@ static int launch_inst(const GemmParams& p, int grid, cudaStream_t stream) {
   return e == cudaSuccess ? 0 : static_cast<int>(e);
 }
 
-#define LMOE_KEY(am, bm, bn256, epi, grp) ((am) | ((bm) << 1) | ((bn256) << 2) | ((epi) << 3) | ((grp) << 6))
-#define LMOE_CASE(am, bm, bn, epi, grp)          \
-  case LMOE_KEY(am, bm, (bn == 256), epi, grp):  \
-    return launch_inst<(am != 0), (bm != 0), bn, epi, grp>(p, grid, stream);
-#define LMOE_CASE_BN(am, bm, epi, grp) LMOE_CASE(am, bm, 128, epi, grp) LMOE_CASE(am, bm, 256, epi, grp)
-#define LMOE_CASE_MAJORS(epi, grp) \
-  LMOE_CASE_BN(0, 0, epi, grp) LMOE_CASE_BN(0, 1, epi, grp) LMOE_CASE_BN(1, 0, epi, grp) LMOE_CASE_BN(1, 1, epi, grp)
+#define LMOE_KEY(am, bm, bn256, epi, grp, esz) \
+  ((am) | ((bm) << 1) | ((bn256) << 2) | ((epi) << 3) | ((grp) << 6) | (((esz) == 1 ? 1 : 0) << 9))
+#define LMOE_CASE(am, bm, bn, epi, grp, esz)          \
+  case LMOE_KEY(am, bm, (bn == 256), epi, grp, esz):  \
+    return launch_inst<(am != 0), (bm != 0), bn, epi, grp, esz>(p, grid, stream);
+#define LMOE_CASE_BN(am, bm, epi, grp, esz) LMOE_CASE(am, bm, 128, epi, grp, esz) LMOE_CASE(am, bm, 256, epi, grp, esz)
+#define LMOE_CASE_MAJORS(epi, grp, esz)                                                                      \
+  LMOE_CASE_BN(0, 0, epi, grp, esz) LMOE_CASE_BN(0, 1, epi, grp, esz) LMOE_CASE_BN(1, 0, epi, grp, esz) \
+      LMOE_CASE_BN(1, 1, epi, grp, esz)
 
 static int dispatch(const GemmCall& c, int bn, const GemmParams& p, int grid, cudaStream_t stream) {
-  switch (LMOE_KEY(c.a_mn, c.b_mn, (bn == 256), c.epi, c.grp)) {
+  switch (LMOE_KEY(c.a_mn, c.b_mn, (bn == 256), c.epi, c.grp, c.esz)) {
+    // ---- bf16 ----
     // dense
-    LMOE_CASE_MAJORS(EPI_BF16, GRP_NONE)
-    LMOE_CASE_MAJORS(EPI_F32, GRP_NONE)
-    LMOE_CASE_BN(0, 0, EPI_SWIGLU, GRP_NONE)
+    LMOE_CASE_MAJORS(EPI_BF16, GRP_NONE, 2)
+    LMOE_CASE_MAJORS(EPI_F32, GRP_NONE, 2)
+    LMOE_CASE_BN(0, 0, EPI_SWIGLU, GRP_NONE, 2)
     // grouped over rows (routed forward and dgrads)
-    LMOE_CASE_BN(0, 1, EPI_SWIGLU, GRP_M)
-    LMOE_CASE_BN(0, 1, EPI_BF16, GRP_M)
-    LMOE_CASE_BN(0, 0, EPI_BF16, GRP_M)
+    LMOE_CASE_BN(0, 1, EPI_SWIGLU, GRP_M, 2)
+    LMOE_CASE_BN(0, 1, EPI_BF16, GRP_M, 2)
+    LMOE_CASE_BN(0, 0, EPI_BF16, GRP_M, 2)
     // grouped over the contraction (routed wgrads)
-    LMOE_CASE_BN(1, 1, EPI_BF16, GRP_K)
+    LMOE_CASE_BN(1, 1, EPI_BF16, GRP_K, 2)
+    // ---- e4m3 ----
+    LMOE_CASE_MAJORS(EPI_BF16, GRP_NONE, 1)
+    LMOE_CASE(0, 1, 256, EPI_SWIGLU, GRP_M, 1)
+    LMOE_CASE_BN(0, 1, EPI_BF16, GRP_M, 1)
+    LMOE_CASE_BN(0, 0, EPI_BF16, GRP_M, 1)
+    LMOE_CASE_BN(1, 1, EPI_BF16, GRP_K, 1)
     default:
       return LMOE_ERR_ARG;
   }
@@ -130,6 +141,10 @@ int launch_gemm(const GemmCall& c) {
   if (c.nseg < 1 || c.nseg > 3 || !c.C || c.M <= 0 || c.N <= 0) return LMOE_ERR_ARG;
   if (c.split_k > 1 && (c.epi != EPI_F32 || c.nseg != 1 || c.grp != GRP_NONE)) return LMOE_ERR_ARG;
   const bool swiglu = (c.epi == EPI_SWIGLU);
+  if (c.esz != 1 && c.esz != 2) return LMOE_ERR_ARG;
+  const int esz = c.esz;
+  const int bk = kBKBytes / esz;  // elements per k-block
+  const int ch = 128 / esz;       // MN-major chunk width in elements
   if ((c.N & 7) != 0) return LMOE_ERR_SHAPE;
   if (swiglu && ((c.N % kSlabCols) != 0 || !c.C2)) return LMOE_ERR_SHAPE;
 
@@ -147,6 +162,7 @@ int launch_gemm(const GemmCall& c) {
     const long long tiles256 =
         static_cast<long long>(m_tiles) * ((n_eff + 255) / 256) * (c.grp == GRP_K ? c.groups : 1) * split;
     bn = (n_eff >= 256 && tiles256 >= sms) ? 256 : 128;
+    if (esz == 1 && swiglu && c.b_mn) bn = 256;  // gate and up halves must each be a whole 128-wide chunk
   }
   if (bn != 128 && bn != 256) return LMOE_ERR_ARG;
   const int n_per_tile = swiglu ? bn / 2 : bn;
@@ -159,36 +175,36 @@ int launch_gemm(const GemmCall& c) {
     if (c.grp == GRP_K) {
       // both operands are [padded rows, extent] row-major and contract over rows
       if (!c.a_mn || !c.b_mn) return LMOE_ERR_ARG;
-      rc = encode_2d(&p.tmA[s], c.A[s], c.M, c.padded_rows, c.lda[s], 64, 64);
+      rc = encode_2d(&p.tmA[s], c.A[s], c.M, c.padded_rows, c.lda[s], bk, esz);
       if (rc) return rc;
-      rc = encode_2d(&p.tmB[s], c.B[s], c.N, c.padded_rows, c.ldb[s], 64, 64);
+      rc = encode_2d(&p.tmB[s], c.B[s], c.N, c.padded_rows, c.ldb[s], bk, esz);
       if (rc) return rc;
       p.seg_kiters[s] = 0;
       continue;
     }
     const int K = c.Kseg[s];
     if (K <= 0) return LMOE_ERR_SHAPE;
-    p.seg_kiters[s] = (K + kBK - 1) / kBK;
+    p.seg_kiters[s] = (K + bk - 1) / bk;
     // A
     if (!c.a_mn)
-      rc = encode_2d(&p.tmA[s], c.A[s], K, rows_total, c.lda[s], 64, kBM);
+      rc = encode_2d(&p.tmA[s], c.A[s], K, rows_total, c.lda[s], kBM, esz);
     else
-      rc = encode_2d(&p.tmA[s], c.A[s], c.M, K, c.lda[s], 64, 64);
+      rc = encode_2d(&p.tmA[s], c.A[s], c.M, K, c.lda[s], bk, esz);
     if (rc) return rc;
     // B
     const int n_b_total = swiglu ? 2 * c.N : c.N;  // columns (or rows) of B addressed by this GEMM
     if (c.grp == GRP_M) {
-      if ((K % kBK) != 0 || c.groups <= 0 || c.b_group_rows <= 0) return LMOE_ERR_SHAPE;
+      if ((K % bk) != 0 || c.groups <= 0 || c.b_group_rows <= 0) return LMOE_ERR_SHAPE;
       const long long outer = static_cast<long long>(c.groups) * c.b_group_rows;
       if (!c.b_mn)
-        rc = encode_2d(&p.tmB[s], c.B[s], K, outer, c.ldb[s], 64, swiglu ? bn / 2 : bn);
+        rc = encode_2d(&p.tmB[s], c.B[s], K, outer, c.ldb[s], swiglu ? bn / 2 : bn, esz);
       else
-        rc = encode_2d(&p.tmB[s], c.B[s], n_b_total, outer, c.ldb[s], 64, 64);
+        rc = encode_2d(&p.tmB[s], c.B[s], n_b_total, outer, c.ldb[s], bk, esz);
     } else {
       if (!c.b_mn)
-        rc = encode_2d(&p.tmB[s], c.B[s], K, n_b_total, c.ldb[s], 64, swiglu ? bn / 2 : bn);
+        rc = encode_2d(&p.tmB[s], c.B[s], K, n_b_total, c.ldb[s], swiglu ? bn / 2 : bn, esz);
       else
-        rc = encode_2d(&p.tmB[s], c.B[s], n_b_total, K, c.ldb[s], 64, 64);
+        rc = encode_2d(&p.tmB[s], c.B[s], n_b_total, K, c.ldb[s], bk, esz);
     }
     if (rc) return rc;
   }
@@ -226,7 +242,10 @@ int launch_gemm(const GemmCall& c) {
   p.n_m_tiles = c.n_m_tiles;
   p.b_group_rows = c.b_group_rows;
   p.pad_offsets = c.pad_offsets;
+  p.deq_a = c.deq_a;
+  p.deq_b = c.deq_b;
   p.status = c.status;
+  (void)ch;
   if (c.grp == GRP_M && (!c.tile_expert || !c.n_m_tiles)) return LMOE_ERR_ARG;
   if (c.grp == GRP_K && (!c.pad_offsets || c.groups <= 0)) return LMOE_ERR_ARG;
 

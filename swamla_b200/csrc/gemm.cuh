@@ -1,6 +1,7 @@
 // Persistent, warp-specialised tcgen05 GEMM for sm_100a.
 //
-//   C[M,N] = A[M,K] * B[N,K]^T      bf16 operands, fp32 accumulation in tensor memory
+//   C[M,N] = A[M,K] * B[N,K]^T      bf16 (kind::f16) or e4m3 (kind::f8f6f4) operands, fp32 accumulation in
+//                                   tensor memory; e4m3 results are multiplied by two per-tensor de-scale factors
 //
 // One CTA per SM walks a static tile schedule.  Roles:
 //   warp 0      TMA producer: fills a ring of shared-memory stages (A tile 128 x 64, B tile BN x 64)
@@ -37,7 +38,7 @@ enum : int { EPI_BF16 = 0, EPI_F32 = 1, EPI_SWIGLU = 2 };
 enum : int { GRP_NONE = 0, GRP_M = 1, GRP_K = 2 };
 
 constexpr int kBM = 128;
-constexpr int kBK = 64;  // 16-bit elements per k-block (one 128-byte swizzle row)
+constexpr int kBKBytes = 128;  // bytes per k-block row (one 128-byte swizzle row): 64 bf16 or 128 e4m3 elements
 constexpr int kGemmThreads = 320;
 constexpr int kEpiGroupThreads = 128;
 constexpr int kSlabCols = 32;  // output columns per epilogue slab
@@ -63,13 +64,15 @@ struct alignas(64) GemmParams {
   const int* n_m_tiles;    // GRP_M: device scalar, number of 128-row tiles in use
   int b_group_rows;        // GRP_M: rows of the stacked B tensor per expert
   const int* pad_offsets;  // GRP_K
+  const float* deq_a;      // e4m3: per-tensor de-scale factors (amax / 448) of A and B, device scalars
+  const float* deq_b;
   int* status;
 };
 
 template <int BN, int EPI>
 struct GemmSmem {
-  static constexpr int kABytes = kBM * kBK * 2;
-  static constexpr int kBBytes = BN * kBK * 2;
+  static constexpr int kABytes = kBM * kBKBytes;
+  static constexpr int kBBytes = BN * kBKBytes;
   static constexpr int kStageBytes = kABytes + kBBytes;
   // one slab = 128 rows x 32 columns: 8 KB in bf16 (64-byte rows), 16 KB in fp32 (128-byte rows)
   static constexpr int kSlabBytes = (EPI == EPI_F32) ? 16384 : 8192;
@@ -131,13 +134,20 @@ __device__ __forceinline__ void stage_row_f32(uint8_t* buf, int r, const float (
   }
 }
 
-template <bool A_MN, bool B_MN, int BN, int EPI, int GRP>
+// ESZ = operand element size in bytes: 2 (bf16) or 1 (e4m3).
+template <bool A_MN, bool B_MN, int BN, int EPI, int GRP, int ESZ = 2>
 __global__ void __launch_bounds__(kGemmThreads, 1) gemm_kernel(const __grid_constant__ GemmParams p) {
   using S = GemmSmem<BN, EPI>;
   constexpr int STAGES = S::kStages;
   constexpr uint32_t TMEM_COLS = 2 * BN;
   static_assert(BN == 128 || BN == 256, "BN");
+  static_assert(ESZ == 1 || ESZ == 2, "ESZ");
   constexpr bool kSwiglu = (EPI == EPI_SWIGLU);
+  constexpr int BK_E = kBKBytes / ESZ;   // elements per k-block
+  constexpr int CH = 128 / ESZ;          // width (elements) of one MN-major chunk: 128 bytes of row/column index
+  constexpr int CH_BYTES = BK_E * 128;   // one MN-major chunk: BK_E k-rows of 128 bytes
+  constexpr int UK = 32 / ESZ;           // elements per tcgen05.mma along K
+  static_assert(!(kSwiglu && B_MN && (BN / 2) < CH), "gate and up halves must each be whole MN-major chunks");
 
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -215,7 +225,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_kernel(const __grid_cons
       t.plane = outer;
       const int r0 = p.pad_offsets[outer], r1 = p.pad_offsets[outer + 1];
       t.krow0 = r0;
-      t.ke = (r1 - r0) / kBK;
+      t.ke = (r1 - r0) / BK_E;
     }
     return t;
   };
@@ -244,14 +254,14 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_kernel(const __grid_cons
             uint8_t* sa = smem + stage * S::kStageBytes;
             uint8_t* sb = sa + S::kABytes;
             mbar_expect_tx(&bar_full[stage], S::kStageBytes);
-            const int kcoord = t.krow0 + kit * kBK;  // element (K-major) or row (MN-major) coordinate along K
+            const int kcoord = t.krow0 + kit * BK_E;  // element (K-major) or row (MN-major) coordinate along K
             // ---- A ----
             if (!A_MN) {
               tma_load_2d(sa, &p.tmA[s], &bar_full[stage], kcoord, t.m0);
             } else {
 #pragma unroll
-              for (int j = 0; j < kBM / 64; ++j)
-                tma_load_2d(sa + j * 8192, &p.tmA[s], &bar_full[stage], t.m0 + j * 64, kcoord);
+              for (int j = 0; j < kBM / CH; ++j)
+                tma_load_2d(sa + j * CH_BYTES, &p.tmA[s], &bar_full[stage], t.m0 + j * CH, kcoord);
             }
             // ---- B ----
             const int grp_rows = (GRP == GRP_M) ? t.grp * p.b_group_rows : 0;
@@ -265,15 +275,16 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_kernel(const __grid_cons
               }
             } else {
 #pragma unroll
-              for (int j = 0; j < BN / 64; ++j) {
+              for (int j = 0; j < BN / CH; ++j) {
+                constexpr int kHalfChunks = BN / (2 * CH);
                 int ncol;
                 if (kSwiglu) {
                   const int nh = t.nt * (BN / 2);
-                  ncol = (j < BN / 128) ? (nh + j * 64) : (p.half + nh + (j - BN / 128) * 64);
+                  ncol = (j < kHalfChunks) ? (nh + j * CH) : (p.half + nh + (j - kHalfChunks) * CH);
                 } else {
-                  ncol = t.nt * BN + j * 64;
+                  ncol = t.nt * BN + j * CH;
                 }
-                tma_load_2d(sb + j * 8192, &p.tmB[s], &bar_full[stage], ncol, grp_rows + kcoord);
+                tma_load_2d(sb + j * CH_BYTES, &p.tmB[s], &bar_full[stage], ncol, grp_rows + kcoord);
               }
             }
             if (++stage == STAGES) {
@@ -287,11 +298,12 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_kernel(const __grid_cons
   } else if (warp == 1) {
     // ============================ MMA issuer ============================
     if (lane == 0) {
-      constexpr uint32_t idesc = make_idesc(1, 1, A_MN, B_MN, kBM, BN);
-      constexpr uint32_t a_lbo = A_MN ? 8192u : 0u;
-      constexpr uint32_t b_lbo = B_MN ? 8192u : 0u;
-      constexpr uint32_t a_kstep = A_MN ? 2048u : 32u;  // bytes per 16-element k-step
-      constexpr uint32_t b_kstep = B_MN ? 2048u : 32u;
+      constexpr uint32_t fmt = (ESZ == 2) ? 1u : 0u;  // kind::f16: 1 = bf16;  kind::f8f6f4: 0 = e4m3
+      constexpr uint32_t idesc = make_idesc(fmt, fmt, A_MN, B_MN, kBM, BN);
+      constexpr uint32_t a_lbo = A_MN ? static_cast<uint32_t>(CH_BYTES) : 0u;
+      constexpr uint32_t b_lbo = B_MN ? static_cast<uint32_t>(CH_BYTES) : 0u;
+      constexpr uint32_t a_kstep = A_MN ? static_cast<uint32_t>(UK * 128) : 32u;  // bytes per tcgen05.mma along K
+      constexpr uint32_t b_kstep = B_MN ? static_cast<uint32_t>(UK * 128) : 32u;
       int stage = 0;
       uint32_t phase = 0;
       int acc = 0;
@@ -313,10 +325,13 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_kernel(const __grid_cons
           const uint32_t sa = smem_u32(smem + stage * S::kStageBytes);
           const uint32_t sb = sa + S::kABytes;
 #pragma unroll
-          for (int k = 0; k < kBK / 16; ++k) {
+          for (int k = 0; k < BK_E / UK; ++k) {
             const uint64_t da = make_smem_desc_sw128(sa + k * a_kstep, a_lbo, 1024);
             const uint64_t db = make_smem_desc_sw128(sb + k * b_kstep, b_lbo, 1024);
-            umma_f16(d_tmem, da, db, idesc, (it > 0 || k > 0) ? 1u : 0u);
+            if (ESZ == 2)
+              umma_f16(d_tmem, da, db, idesc, (it > 0 || k > 0) ? 1u : 0u);
+            else
+              umma_f8(d_tmem, da, db, idesc, (it > 0 || k > 0) ? 1u : 0u);
           }
           umma_commit(&bar_empty[stage]);  // stage is free once these MMAs have read it
           if (++stage == STAGES) {
@@ -338,6 +353,8 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_kernel(const __grid_cons
     const int r = q * 32 + lane;        // row of the tile owned by this thread
     const bool issuer = (((warp - 2) & 3) == 0) && lane == 0;
     uint8_t* sbuf = staging + group * (S::kStreams * S::kSlabBytes);
+    float deq = 1.0f;
+    if (ESZ == 1) deq = (p.deq_a ? p.deq_a[0] : 1.0f) * (p.deq_b ? p.deq_b[0] : 1.0f);
     int acc = 0;
     uint32_t acc_phase = 0;
     bool ok = true;
@@ -382,6 +399,13 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_kernel(const __grid_cons
         } else {
 #pragma unroll
           for (int j = 0; j < 32; ++j) v[j] = u[j] = 0.f;
+        }
+        if (ESZ == 1) {
+#pragma unroll
+          for (int j = 0; j < 32; ++j) {
+            v[j] *= deq;
+            if (kSwiglu) u[j] *= deq;
+          }
         }
         uint32_t pk[16], pu[16], ph[16];
         if (EPI == EPI_BF16) {

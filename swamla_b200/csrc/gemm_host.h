@@ -11,6 +11,9 @@ struct GemmCall {
   int epi = 0;             // EPI_*
   int grp = 0;             // GRP_*
   int bn = 0;              // 0 = choose; else 128 or 256
+  int esz = 2;             // operand element size: 2 = bf16, 1 = e4m3
+  const float* deq_a = nullptr;  // e4m3: device scalars, result is multiplied by deq_a[0] * deq_b[0]
+  const float* deq_b = nullptr;
   // up to three K segments accumulated into the same output tile
   int nseg = 1;
   const void* A[3] = {nullptr, nullptr, nullptr};

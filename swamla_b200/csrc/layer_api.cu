@@ -52,7 +52,7 @@ GemmCall dense(const void* A, long long lda, int a_mn, const void* B, long long 
 // enough tiles for one wave, at least 8 k-blocks per slice.
 int wgrad_split(int M, int N, int K) {
   const long long tiles = static_cast<long long>((M + 127) / 128) * ((N + 255) / 256);
-  const int kiters = (K + kBK - 1) / kBK;
+  const int kiters = (K + 63) / 64;  // bf16 k-blocks of 64 rows
   long long split = (num_sms() + tiles / 2) / tiles;  // round to nearest
   if (split > kiters / 8) split = kiters / 8;
   if (split > 16) split = 16;

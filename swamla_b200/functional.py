@@ -74,7 +74,7 @@ class LatentMoEFunction(torch.autograd.Function):
 
     @staticmethod
     def forward(ctx, x, w_gate, w_down, w_up, w_gate_up_s, w_down_s, w_gate_up, w_down_e, expert_bias, top_k: int,
-                z_coef: float):
+                z_coef: float, fp8: bool = False):
         if not x.is_cuda:
             raise _cabi.LmoeError("the LatentMoE path runs on a CUDA device only (no CPU fallback)")
         lib = _cabi.load()
@@ -117,12 +117,18 @@ class LatentMoEFunction(torch.autograd.Function):
 
         # routed experts in the padded layout
         P = route.padded_rows
-        x_sorted = torch.empty(P, L, **bf)
-        h1 = torch.empty(P, 2 * F, **bf)
-        hidden = torch.empty(P, F, **bf)
-        y_sorted = torch.empty(P, L, **bf)
-        _cabi.call("lmoe_experts_fwd", shape, ptr(x_latent), ptr(wgu), ptr(wde), route.struct, ptr(x_sorted), ptr(h1),
-                   ptr(hidden), ptr(y_sorted), ptr(status), st)
+        fp8_saved = None
+        if fp8:
+            from . import fp8 as fp8_path
+            x_sorted, hidden, y_sorted, fp8_saved = fp8_path.experts_fwd(shape, route, x_latent, wgu, wde, status, st)
+            h1 = fp8_saved["h1"]
+        else:
+            x_sorted = torch.empty(P, L, **bf)
+            h1 = torch.empty(P, 2 * F, **bf)
+            hidden = torch.empty(P, F, **bf)
+            y_sorted = torch.empty(P, L, **bf)
+            _cabi.call("lmoe_experts_fwd", shape, ptr(x_latent), ptr(wgu), ptr(wde), route.struct, ptr(x_sorted), ptr(h1),
+                       ptr(hidden), ptr(y_sorted), ptr(status), st)
 
         # shared expert and output; routed and hidden_s live side by side in act_cat[T, L+Fs]
         h1_s = torch.empty(T, 2 * Fs, **bf)
@@ -135,11 +141,17 @@ class LatentMoEFunction(torch.autograd.Function):
 
         ctx.shape = shape
         ctx.route = route
+        ctx.fp8_saved = fp8_saved
         ctx.z_coef = float(z_coef)
         ctx.status = status
         ctx.dtypes = [t.dtype for t in (x, w_gate, w_down, w_up, w_gate_up_s, w_down_s, w_gate_up, w_down_e)]
-        ctx.save_for_backward(xb, wg, wdn, wup, wgus, wds, wgu, wde, logits, sel, weights, lse, x_sorted, h1, hidden,
-                              y_sorted, act_cat, h1_s)
+        if fp8:   # the e4m3 copies replace the bf16 operands of the routed GEMMs
+            none = torch.empty(0, **bf)
+            ctx.save_for_backward(xb, wg, wdn, wup, wgus, wds, none, none, logits, sel, weights, lse, none, h1, none,
+                                  y_sorted, act_cat, h1_s)
+        else:
+            ctx.save_for_backward(xb, wg, wdn, wup, wgus, wds, wgu, wde, logits, sel, weights, lse, x_sorted, h1, hidden,
+                                  y_sorted, act_cat, h1_s)
         ctx.mark_non_differentiable(sel, route.counts)
         if DEBUG_SINK is not None:
             DEBUG_SINK.update(logits=logits, x_latent=x_latent, sel=sel, weights=weights, lse=lse, route=route,
@@ -189,15 +201,20 @@ class LatentMoEFunction(torch.autograd.Function):
         d_weights = torch.empty(T, K, **f32)
         _cabi.call("lmoe_combine_bwd", shape, ptr(d_routed), ptr(y_sorted), ptr(weights), route.struct, ptr(d_y_sorted),
                    ptr(d_weights), st)
-        d_hidden = torch.empty(P, F, **bf)
-        d_h1 = torch.empty(P, 2 * F, **bf)
-        d_x_sorted = torch.empty(P, L, **bf)
-        _cabi.call("lmoe_experts_bwd_dgrad", shape, ptr(d_y_sorted), ptr(h1), ptr(wgu), ptr(wde), route.struct,
-                   ptr(d_hidden), ptr(d_h1), ptr(d_x_sorted), ptr(status), st)
-        d_w_gate_up = torch.empty(E, L, 2 * F, **bf)
-        d_w_down_e = torch.empty(E, F, L, **bf)
-        _cabi.call("lmoe_experts_bwd_wgrad", shape, ptr(x_sorted), ptr(d_h1), ptr(hidden), ptr(d_y_sorted),
-                   route.struct, ptr(d_w_gate_up), ptr(d_w_down_e), ptr(status), st)
+        if ctx.fp8_saved is not None:
+            from . import fp8 as fp8_path
+            d_hidden, d_h1, d_x_sorted, d_w_gate_up, d_w_down_e = fp8_path.experts_bwd(shape, route, d_y_sorted,
+                                                                                       ctx.fp8_saved, status, st)
+        else:
+            d_hidden = torch.empty(P, F, **bf)
+            d_h1 = torch.empty(P, 2 * F, **bf)
+            d_x_sorted = torch.empty(P, L, **bf)
+            _cabi.call("lmoe_experts_bwd_dgrad", shape, ptr(d_y_sorted), ptr(h1), ptr(wgu), ptr(wde), route.struct,
+                       ptr(d_hidden), ptr(d_h1), ptr(d_x_sorted), ptr(status), st)
+            d_w_gate_up = torch.empty(E, L, 2 * F, **bf)
+            d_w_down_e = torch.empty(E, F, L, **bf)
+            _cabi.call("lmoe_experts_bwd_wgrad", shape, ptr(x_sorted), ptr(d_h1), ptr(hidden), ptr(d_y_sorted),
+                       route.struct, ptr(d_w_gate_up), ptr(d_w_down_e), ptr(status), st)
         _cabi.call("lmoe_unpermute_sum_bwd", shape, ptr(d_x_sorted), route.struct, ptr(dgrad_cat), st)
 
         # router
@@ -227,11 +244,12 @@ class LatentMoEFunction(torch.autograd.Function):
             as_param(d_w_gate_up_s, dt[4]), as_param(d_w_down_s, dt[5]), as_param(d_w_gate_up, dt[6]),
             as_param(d_w_down_e, dt[7]),
         )
-        return grads + (None, None, None)
+        return grads + (None, None, None, None)
 
 
 def latent_moe(x2d: torch.Tensor, w_gate, w_down, w_up, w_gate_up_s, w_down_s, w_gate_up, w_down_e, expert_bias,
-               top_k: int, z_coef: float):
-    """Functional form on a [T, D] activation.  Returns (y [T,D], aux_loss scalar, sel [T,K] int32, counts [E] int32)."""
+               top_k: int, z_coef: float, fp8: bool = False):
+    """Functional form on a [T, D] activation.  Returns (y [T,D], aux_loss scalar, sel [T,K] int32, counts [E] int32).
+    ``fp8``: run the routed expert GEMMs in e4m3 with per-tensor scaling (latent and routed hidden dims % 128 == 0)."""
     return LatentMoEFunction.apply(x2d, w_gate, w_down, w_up, w_gate_up_s, w_down_s, w_gate_up, w_down_e, expert_bias,
-                                   int(top_k), float(z_coef))
+                                   int(top_k), float(z_coef), bool(fp8))

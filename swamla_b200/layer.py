@@ -162,6 +162,10 @@ class LatentMoELayer(nn.Module):
             raise ValueError("the expert count must be divisible by the expert-parallel group size")
         self.experts = LatentBatchedExperts(n_experts // self.ep_size, latent_dim, latent_expert_dim, bias=False)
         self.router = AuxLossFreeRouter(d_model=d_model, n_experts=n_experts, top_k=n_activated, z_loss_coef=z_loss_coef)
+        # `config.moe_fp8 = True`: routed expert GEMMs in e4m3 with per-tensor dynamic scaling
+        self.fp8_experts = bool(getattr(config, "moe_fp8", False))
+        if self.fp8_experts and (latent_dim % 128 or latent_expert_dim % 128):
+            raise ValueError("moe_fp8 needs latent_dim and the routed expert dim to be multiples of 128")
         self.dropout = nn.Dropout(getattr(config, "dropout", 0.0))
         self.aux_loss = torch.tensor(0.0)
 
@@ -192,7 +196,7 @@ class LatentMoELayer(nn.Module):
             from .ep import latent_moe_ep
             y, z_loss, sel, counts = latent_moe_ep(*args, self.ep_group)   # counts: load summed over all ranks
         else:
-            y, z_loss, sel, counts = latent_moe(*args)
+            y, z_loss, sel, counts = latent_moe(*args, fp8=self.fp8_experts)
         self.aux_loss = z_loss                                            # moe.py:719
         if self.training:                                                 # moe.py:237-240
             self.router._last_selected_experts = sel

@@ -71,6 +71,8 @@ WORKLOADS: Dict[str, Workload] = {
     # small shapes for exhaustive parity (all dims are multiples of 64 so they fit the kernels)
     "tiny": Workload("tiny", n_embd=256, n_experts=4, n_activated=1, expert_dim=256, batch=2, seq=96),
     "tiny_ragged": Workload("tiny_ragged", n_embd=256, n_experts=8, n_activated=2, expert_dim=256, batch=1, seq=131),
+    # e4m3 GEMMs contract over multiples of 128: latent 128, routed hidden 128
+    "tiny_fp8": Workload("tiny_fp8", n_embd=512, n_experts=4, n_activated=1, expert_dim=512, batch=2, seq=160, dtype="fp8"),
     # the five benchmark configurations
     "cfg1": Workload("cfg1", batch=2, seq=512, dtype="fp32"),
     "cfg2": Workload("cfg2", batch=8, seq=2048, dtype="bf16"),
