@@ -171,9 +171,12 @@ int lmoe_combine_out_fwd(const lmoe_shape* s, const void* y_sorted, const lmoe_r
  * fp32 master weights, LMOE_BF16); split-K partials go to `workspace` (lmoe_wgrad_workspace_bytes). */
 size_t lmoe_wgrad_workspace_bytes(const lmoe_shape* s);
 
-/* dgrad of the output stage: d_routed[T,L] = dy * w_up, d_hidden_s[T,Fs] = dy * w_down_s. */
+/* dgrad of the output stage: d_routed[T,L] = dy * w_up, and d_h1_s = swiglu'(h1_s, dy * w_down_s) -> dgrad_cat[:, :2Fs].
+ * d_hidden_s[T,Fs]: scratch for dy * w_down_s; if NULL the SwiGLU adjoint runs in the epilogue of that GEMM instead
+ * and d_hidden_s never reaches memory. */
 int lmoe_combine_out_bwd_dgrad(const lmoe_shape* s, const void* dy, const void* w_up, const void* w_down_s,
-                               void* d_routed, void* d_hidden_s, int32_t* status, void* stream);
+                               const void* h1_s, void* d_routed, void* d_hidden_s, void* dgrad_cat, int32_t* status,
+                               void* stream);
 /* wgrad of the output stage, one GEMM dy^T * act_cat: d_w_up[D,L] = dy^T routed, d_w_down_s[D,Fs] = dy^T hidden_s. */
 int lmoe_combine_out_bwd_wgrad(const lmoe_shape* s, const void* dy, const void* act_cat, void* d_w_up,
                                void* d_w_down_s, int grad_type, void* workspace, size_t workspace_bytes,
@@ -187,7 +190,8 @@ int lmoe_combine_bwd(const lmoe_shape* s, const void* d_routed, const void* y_so
 int lmoe_swiglu_bwd(int64_t rows, int H, const void* h1, const void* d_hidden, void* d_h1, int64_t ld_d_h1,
                     const int32_t* n_tiles_dev, void* stream);
 /* Routed dgrads: d_hidden = d_y_sorted * w_down[e]^T, d_h1 = swiglu'(h1, d_hidden),
- * d_x_sorted = d_h1 * w_gate_up[e]^T.  All in the padded layout. */
+ * d_x_sorted = d_h1 * w_gate_up[e]^T.  All in the padded layout.  d_hidden may be NULL: the SwiGLU adjoint then
+ * runs in the epilogue of the first GEMM and d_hidden is never written (also for lmoe_grouped_bwd_dgrad). */
 int lmoe_experts_bwd_dgrad(const lmoe_shape* s, const void* d_y_sorted, const void* h1, const void* w_gate_up,
                            const void* w_down, const lmoe_route* r, void* d_hidden, void* d_h1, void* d_x_sorted,
                            int32_t* status, void* stream);
@@ -224,6 +228,12 @@ int lmoe_grouped_bwd_dgrad(int64_t P, int E, int L, int F, const void* d_y_sorte
 int lmoe_grouped_bwd_wgrad(int64_t P, int E, int L, int F, const void* x_sorted, const void* d_h1, const void* hidden,
                            const void* d_y_sorted, const int32_t* pad_offsets, void* d_w_gate_up, void* d_w_down,
                            int32_t* status, void* stream);
+/* The single GEMMs behind the three calls above, for hosts that schedule them individually:
+ * out[P,N] = a[P,K] * B[e] with B stacked [E,K,N] (b_mn = 1) or [E,N,K] (b_mn = 0); out[e][M,N] = a[rows_e,M]^T b[rows_e,N]. */
+int lmoe_grouped_rows_bf16(int64_t P, int E, int K, int N, const void* a, const void* b, int b_mn,
+                           const int32_t* tile_expert, const int32_t* n_tiles, void* out, int32_t* status, void* stream);
+int lmoe_grouped_wgrad_bf16(int64_t P, int E, int M, int N, const void* a, const void* b, const int32_t* pad_offsets,
+                            void* out, int32_t* status, void* stream);
 /* dst[r] = src[index[r] / div] for r < rows (zeros where index[r] < 0); rows of L bf16.  If n_tiles_dev is
  * non-null only the first 128 * n_tiles_dev[0] rows are written.  (models/moe.py:762-766 as a primitive.) */
 int lmoe_gather_rows(const void* src, const int32_t* index, int div, int64_t rows, int L, const int32_t* n_tiles_dev,

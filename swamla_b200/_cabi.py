@@ -52,7 +52,7 @@ SIGNATURES = {
     "lmoe_experts_fwd": (c_int, [SP, P, P, P, RP, P, P, P, P, P, P]),
     "lmoe_shared_gateup_fwd": (c_int, [SP, P, P, P, P, P, P]),
     "lmoe_combine_out_fwd": (c_int, [SP, P, RP, P, P, P, P, P, P, P]),
-    "lmoe_combine_out_bwd_dgrad": (c_int, [SP, P, P, P, P, P, P, P]),
+    "lmoe_combine_out_bwd_dgrad": (c_int, [SP, P, P, P, P, P, P, P, P, P]),
     "lmoe_combine_out_bwd_wgrad": (c_int, [SP, P, P, P, P, c_int, P, c_size_t, P, P]),
     "lmoe_combine_bwd": (c_int, [SP, P, P, P, RP, P, P, P]),
     "lmoe_swiglu_bwd": (c_int, [c_int64, c_int, P, P, P, c_int64, P, P]),
@@ -64,6 +64,8 @@ SIGNATURES = {
     "lmoe_grouped_fwd": (c_int, [c_int64, c_int, c_int, c_int, P, P, P, P, P, P, P, P, P, P]),
     "lmoe_grouped_bwd_dgrad": (c_int, [c_int64, c_int, c_int, c_int, P, P, P, P, P, P, P, P, P, P, P]),
     "lmoe_grouped_bwd_wgrad": (c_int, [c_int64, c_int, c_int, c_int, P, P, P, P, P, P, P, P, P]),
+    "lmoe_grouped_rows_bf16": (c_int, [c_int64, c_int, c_int, c_int, P, P, c_int, P, P, P, P, P]),
+    "lmoe_grouped_wgrad_bf16": (c_int, [c_int64, c_int, c_int, c_int, P, P, P, P, P, P]),
     "lmoe_gather_rows": (c_int, [P, P, c_int, c_int64, c_int, P, P, P]),
     "lmoe_combine_rows": (c_int, [P, P, P, c_int, c_int, c_int, P, c_int64, P]),
     "lmoe_combine_bwd_rows": (c_int, [P, P, P, P, c_int64, c_int, c_int, P, P, P, P]),

@@ -95,6 +95,9 @@ static int launch_inst(const GemmParams& p, int grid, cudaStream_t stream) {
   if (!configured) {
     cudaError_t e = cudaFuncSetAttribute(kfn, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
     if (e != cudaSuccess) return static_cast<int>(e);
+    // ask for the largest shared-memory carveout so that what the GEMM leaves unused stays available to small
+    // kernels of other streams running beside it
+    cudaFuncSetAttribute(kfn, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
     configured = true;
   }
   kfn<<<grid, kGemmThreads, smem, stream>>>(p);
@@ -126,6 +129,9 @@ static int dispatch(const GemmCall& c, int bn, const GemmParams& p, int grid, cu
     LMOE_CASE_BN(0, 0, EPI_BF16, GRP_M, 2)
     // grouped over the contraction (routed wgrads)
     LMOE_CASE_BN(1, 1, EPI_BF16, GRP_K, 2)
+    // dgrad with the SwiGLU adjoint in the epilogue (routed and shared)
+    LMOE_CASE_BN(0, 0, EPI_SWIGLU_BWD, GRP_M, 2)
+    LMOE_CASE_BN(0, 1, EPI_SWIGLU_BWD, GRP_NONE, 2)
     // ---- e4m3 ----
     LMOE_CASE_MAJORS(EPI_BF16, GRP_NONE, 1)
     LMOE_CASE(0, 1, 256, EPI_SWIGLU, GRP_M, 1)
@@ -147,6 +153,10 @@ int launch_gemm(const GemmCall& c) {
   const int ch = 128 / esz;       // MN-major chunk width in elements
   if ((c.N & 7) != 0) return LMOE_ERR_SHAPE;
   if (swiglu && ((c.N % kSlabCols) != 0 || !c.C2)) return LMOE_ERR_SHAPE;
+  const bool swiglu_bwd = (c.epi == EPI_SWIGLU_BWD);
+  if (swiglu_bwd && ((c.N % kSlabCols) != 0 || !c.aux || (reinterpret_cast<uintptr_t>(c.aux) & 15) != 0 ||
+                     ((c.ld_aux * 2) & 15) != 0))
+    return LMOE_ERR_SHAPE;
 
   GemmParams p;
   memset(&p, 0, sizeof(p));
@@ -212,7 +222,7 @@ int launch_gemm(const GemmCall& c) {
   // ---- output maps ----
   {
     const bool f32 = (c.epi == EPI_F32);
-    const long long cols = swiglu ? 2ll * c.N : c.N;
+    const long long cols = (swiglu || swiglu_bwd) ? 2ll * c.N : c.N;
     long long planes = 1, plane_elems = 0;
     if (c.grp == GRP_K) {
       planes = c.groups;
@@ -244,6 +254,8 @@ int launch_gemm(const GemmCall& c) {
   p.pad_offsets = c.pad_offsets;
   p.deq_a = c.deq_a;
   p.deq_b = c.deq_b;
+  p.aux = c.aux;
+  p.ld_aux = c.ld_aux;
   p.status = c.status;
   (void)ch;
   if (c.grp == GRP_M && (!c.tile_expert || !c.n_m_tiles)) return LMOE_ERR_ARG;

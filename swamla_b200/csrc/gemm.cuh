@@ -34,7 +34,9 @@
 
 namespace lmoe {
 
-enum : int { EPI_BF16 = 0, EPI_F32 = 1, EPI_SWIGLU = 2 };
+// EPI_SWIGLU_BWD: the accumulator is d_hidden; the epilogue reads the saved gate/up of the same rows and
+// columns (aux = h1) and writes d_h1 = [d_gate | d_up] -- the SwiGLU adjoint without a d_hidden round trip.
+enum : int { EPI_BF16 = 0, EPI_F32 = 1, EPI_SWIGLU = 2, EPI_SWIGLU_BWD = 3 };
 enum : int { GRP_NONE = 0, GRP_M = 1, GRP_K = 2 };
 
 constexpr int kBM = 128;
@@ -66,6 +68,8 @@ struct alignas(64) GemmParams {
   const int* pad_offsets;  // GRP_K
   const float* deq_a;      // e4m3: per-tensor de-scale factors (amax / 448) of A and B, device scalars
   const float* deq_b;
+  const void* aux;         // EPI_SWIGLU_BWD: h1 [rows, 2*N] bf16 (gate | up), row stride ld_aux elements
+  long long ld_aux;
   int* status;
 };
 
@@ -76,7 +80,7 @@ struct GemmSmem {
   static constexpr int kStageBytes = kABytes + kBBytes;
   // one slab = 128 rows x 32 columns: 8 KB in bf16 (64-byte rows), 16 KB in fp32 (128-byte rows)
   static constexpr int kSlabBytes = (EPI == EPI_F32) ? 16384 : 8192;
-  static constexpr int kStreams = (EPI == EPI_SWIGLU) ? 3 : 1;  // gate, up, hidden
+  static constexpr int kStreams = (EPI == EPI_SWIGLU) ? 3 : (EPI == EPI_SWIGLU_BWD ? 2 : 1);  // gate, up, hidden
   static constexpr int kStagingBytes = 2 * kStreams * kSlabBytes;  // one buffer per epilogue group
   static constexpr int kBarrierBytes = 256;
   static constexpr int kBudget = 232448 - 1024 - kBarrierBytes - kStagingBytes;
@@ -386,6 +390,24 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_kernel(const __grid_cons
 #pragma unroll 1
       for (int c = group; c < slabs; c += 2) {
         float v[32], u[32];
+        uint4 hg[4], hu[4];  // EPI_SWIGLU_BWD: saved gate / up of this row, 32 columns each
+        if (EPI == EPI_SWIGLU_BWD) {
+          const long long grow = static_cast<long long>(t.m0) + r;
+          if (GRP == GRP_M || grow < p.M) {
+            const uint4* gp = reinterpret_cast<const uint4*>(static_cast<const __nv_bfloat16*>(p.aux) + grow * p.ld_aux +
+                                                             n0 + c * kSlabCols);
+            const uint4* up = reinterpret_cast<const uint4*>(static_cast<const __nv_bfloat16*>(p.aux) + grow * p.ld_aux +
+                                                             p.N + n0 + c * kSlabCols);
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+              hg[j] = __ldg(gp + j);
+              hu[j] = __ldg(up + j);
+            }
+          } else {
+#pragma unroll
+            for (int j = 0; j < 4; ++j) hg[j] = hu[j] = make_uint4(0, 0, 0, 0);
+          }
+        }
         if (nk > 0) {
           tmem_ld32(taddr + c * 32, v);
           if (kSwiglu) tmem_ld32(taddr + BN / 2 + c * 32, u);
@@ -411,6 +433,27 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_kernel(const __grid_cons
         if (EPI == EPI_BF16) {
 #pragma unroll
           for (int j = 0; j < 16; ++j) pk[j] = pack_bf16x2(v[2 * j], v[2 * j + 1]);
+        } else if (EPI == EPI_SWIGLU_BWD) {
+          const uint32_t* wg = reinterpret_cast<const uint32_t*>(hg);
+          const uint32_t* wu = reinterpret_cast<const uint32_t*>(hu);
+#pragma unroll
+          for (int j = 0; j < 16; ++j) {
+            // d_hidden is rounded to bf16 first (what a stored d_hidden would hold), then
+            //   d_up = dh * g * sig(g),  d_gate = dh * u * sig(g) * (1 + g * (1 - sig(g)))
+            const uint32_t dh2 = pack_bf16x2(v[2 * j], v[2 * j + 1]);
+            float dh[2] = {__uint_as_float(dh2 << 16), __uint_as_float(dh2 & 0xffff0000u)};
+            float g[2] = {__uint_as_float(wg[j] << 16), __uint_as_float(wg[j] & 0xffff0000u)};
+            float uu[2] = {__uint_as_float(wu[j] << 16), __uint_as_float(wu[j] & 0xffff0000u)};
+            float dg[2], du[2];
+#pragma unroll
+            for (int k = 0; k < 2; ++k) {
+              const float sg = __fdividef(1.0f, 1.0f + __expf(-g[k]));
+              du[k] = dh[k] * g[k] * sg;
+              dg[k] = dh[k] * uu[k] * sg * (1.0f + g[k] * (1.0f - sg));
+            }
+            pk[j] = pack_bf16x2(dg[0], dg[1]);
+            pu[j] = pack_bf16x2(du[0], du[1]);
+          }
         } else if (EPI == EPI_SWIGLU) {
 #pragma unroll
           for (int j = 0; j < 16; ++j) {
@@ -430,6 +473,9 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_kernel(const __grid_cons
           stage_row_f32(sbuf, r, v);
         } else if (EPI == EPI_BF16) {
           stage_row_bf16(sbuf, r, pk);
+        } else if (EPI == EPI_SWIGLU_BWD) {
+          stage_row_bf16(sbuf, r, pk);
+          stage_row_bf16(sbuf + S::kSlabBytes, r, pu);
         } else {
           stage_row_bf16(sbuf, r, pk);
           stage_row_bf16(sbuf + S::kSlabBytes, r, pu);
@@ -443,6 +489,9 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_kernel(const __grid_cons
             tma_store_3d(&p.tmC, sbuf, col, t.m0, 0);
             tma_store_3d(&p.tmC, sbuf + S::kSlabBytes, p.half + col, t.m0, 0);
             tma_store_3d(&p.tmC2, sbuf + 2 * S::kSlabBytes, col, t.m0, 0);
+          } else if (EPI == EPI_SWIGLU_BWD) {
+            tma_store_3d(&p.tmC, sbuf, col, t.m0, 0);                        // d_gate
+            tma_store_3d(&p.tmC, sbuf + S::kSlabBytes, p.N + col, t.m0, 0);  // d_up
           } else {
             tma_store_3d(&p.tmC, sbuf, col, t.m0, t.plane);
           }

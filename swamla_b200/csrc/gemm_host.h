@@ -28,6 +28,8 @@ struct GemmCall {
   long long c_group_stride = 0;  // GRP_K: elements between experts' outputs; split-K: elements between planes
   void* C2 = nullptr;
   long long ldc2 = 0;
+  const void* aux = nullptr;     // EPI_SWIGLU_BWD: h1 [rows, 2N] bf16; C is then d_h1 [rows, 2N]
+  long long ld_aux = 0;
   int split_k = 1;               // >1 (GRP_NONE, EPI_F32): C is a [split_k, M, N] workspace of partial sums
   // grouping
   long long padded_rows = 0;         // GRP_M / GRP_K: rows of the padded routed layout (upper bound)

@@ -48,16 +48,25 @@ GemmCall dense(const void* A, long long lda, int a_mn, const void* B, long long 
   return c;
 }
 
-// Number of k-slices for a weight gradient with an M x N output contracting over K rows:
-// enough tiles for one wave, at least 8 k-blocks per slice.
+// Number of k-slices for a weight gradient with an M x N output contracting over K rows, from a cost model in
+// units of one k-block of main loop: waves x (k-blocks per slice + epilogue) + the reduce traffic of the planes.
 int wgrad_split(int M, int N, int K) {
   const long long tiles = static_cast<long long>((M + 127) / 128) * ((N + 255) / 256);
   const int kiters = (K + 63) / 64;  // bf16 k-blocks of 64 rows
-  long long split = (num_sms() + tiles / 2) / tiles;  // round to nearest
-  if (split > kiters / 8) split = kiters / 8;
-  if (split > 16) split = 16;
-  if (split < 1) split = 1;
-  return static_cast<int>(split);
+  const int sms = num_sms();
+  const double kblock_us = 0.40;                                       // 128 x 256 x 64 on one SM
+  const double plane_us = 2.0 * M * N * 4.0 / 6.5e6;                   // write + read of one fp32 plane at HBM rate
+  int best = 1;
+  double best_cost = 1e30;
+  for (int s = 1; s <= 16 && s <= kiters; ++s) {
+    const long long waves = (tiles * s + sms - 1) / sms;
+    const double cost = waves * ((kiters + s - 1) / s + 8.0) * kblock_us + (s > 1 ? s * plane_us : 0.0);
+    if (cost < best_cost - 1e-9) {
+      best_cost = cost;
+      best = s;
+    }
+  }
+  return best;
 }
 
 // dW[M,N] (fp32 planes in `ws`) = Aact[K,M]^T * Bact[K,N]: both operands MN-major, contraction over rows.
@@ -202,14 +211,24 @@ extern "C" int lmoe_combine_out_fwd(const lmoe_shape* s, const void* y_sorted, c
 
 // ------------------------------------------------------------------ backward
 extern "C" int lmoe_combine_out_bwd_dgrad(const lmoe_shape* s, const void* dy, const void* w_up, const void* w_down_s,
-                                          void* d_routed, void* d_hidden_s, int32_t* status, void* stream) {
+                                          const void* h1_s, void* d_routed, void* d_hidden_s, void* dgrad_cat,
+                                          int32_t* status, void* stream) {
   if (int rc = check_dims(s)) return rc;
-  if (!dy || !w_up || !w_down_s || !d_routed || !d_hidden_s) return LMOE_ERR_ARG;
+  if (!dy || !w_up || !w_down_s || !h1_s || !d_routed || !dgrad_cat) return LMOE_ERR_ARG;
   // d_routed[T,L] = dy[T,D] * Wup[D,L]      (B stored [K=D, N=L]: MN-major)
   GemmCall a = dense(dy, s->D, 0, w_up, s->L, 1, s->T, s->L, s->D, d_routed, s->L, EPI_BF16, status, stream);
   if (int rc = launch_gemm(a)) return rc;
-  // d_hidden_s[T,Fs] = dy[T,D] * Wd_s[D,Fs]
-  GemmCall b = dense(dy, s->D, 0, w_down_s, s->Fs, 1, s->T, s->Fs, s->D, d_hidden_s, s->Fs, EPI_BF16, status, stream);
+  const long long ld = 2ll * s->Fs + s->L + s->E;
+  if (d_hidden_s) {
+    // d_hidden_s[T,Fs] = dy * Wd_s, then the SwiGLU adjoint as a separate streaming kernel -> dgrad_cat[:, :2Fs]
+    GemmCall b = dense(dy, s->D, 0, w_down_s, s->Fs, 1, s->T, s->Fs, s->D, d_hidden_s, s->Fs, EPI_BF16, status, stream);
+    if (int rc = launch_gemm(b)) return rc;
+    return lmoe_swiglu_bwd(s->T, s->Fs, h1_s, d_hidden_s, dgrad_cat, ld, nullptr, stream);
+  }
+  // fused: the SwiGLU adjoint in the epilogue of the d_hidden_s GEMM
+  GemmCall b = dense(dy, s->D, 0, w_down_s, s->Fs, 1, s->T, s->Fs, s->D, dgrad_cat, ld, EPI_SWIGLU_BWD, status, stream);
+  b.aux = h1_s;
+  b.ld_aux = 2ll * s->Fs;
   return launch_gemm(b);
 }
 
@@ -231,11 +250,68 @@ extern "C" int lmoe_combine_out_bwd_wgrad(const lmoe_shape* s, const void* dy, c
   return splitk_reduce(ws, split, plane, N, 0, s->L, s->D, s->Fs, d_w_down_s, s->Fs, grad_type == LMOE_F32, st);
 }
 
+// Generic grouped-by-rows bf16 GEMM: out[P,N] = a[P,K] * B[e], B stacked [E,K,N] (b_mn = 1) or [E,N,K] (b_mn = 0).
+extern "C" int lmoe_grouped_rows_bf16(int64_t P, int E, int K, int N, const void* a, const void* b, int b_mn,
+                                      const int32_t* tile_expert, const int32_t* n_tiles, void* out, int32_t* status,
+                                      void* stream) {
+  if (!a || !b || !tile_expert || !n_tiles || !out) return LMOE_ERR_ARG;
+  if (P <= 0 || (P % LMOE_ROW_PAD) != 0 || E <= 0 || (K % 64) != 0 || (N % 8) != 0) return LMOE_ERR_SHAPE;
+  GemmCall c;
+  c.a_mn = 0;
+  c.b_mn = b_mn ? 1 : 0;
+  c.epi = EPI_BF16;
+  c.grp = GRP_M;
+  c.A[0] = a;
+  c.lda[0] = K;
+  c.B[0] = b;
+  c.ldb[0] = b_mn ? N : K;
+  c.Kseg[0] = K;
+  c.M = static_cast<int>(P);
+  c.N = N;
+  c.C = out;
+  c.ldc = N;
+  c.padded_rows = P;
+  c.groups = E;
+  c.b_group_rows = b_mn ? K : N;
+  c.tile_expert = tile_expert;
+  c.n_m_tiles = n_tiles;
+  c.status = status;
+  c.stream = static_cast<cudaStream_t>(stream);
+  return launch_gemm(c);
+}
+
+// Generic grouped-by-contraction bf16 GEMM: out[e][M,N] = a[rows_e, M]^T * b[rows_e, N].
+extern "C" int lmoe_grouped_wgrad_bf16(int64_t P, int E, int M, int N, const void* a, const void* b,
+                                       const int32_t* pad_offsets, void* out, int32_t* status, void* stream) {
+  if (!a || !b || !pad_offsets || !out) return LMOE_ERR_ARG;
+  if (P <= 0 || (P % LMOE_ROW_PAD) != 0 || E <= 0 || (M % 8) != 0 || (N % 8) != 0) return LMOE_ERR_SHAPE;
+  GemmCall c;
+  c.a_mn = 1;
+  c.b_mn = 1;
+  c.epi = EPI_BF16;
+  c.grp = GRP_K;
+  c.A[0] = a;
+  c.lda[0] = M;
+  c.B[0] = b;
+  c.ldb[0] = N;
+  c.M = M;
+  c.N = N;
+  c.C = out;
+  c.ldc = N;
+  c.c_group_stride = static_cast<long long>(M) * N;
+  c.padded_rows = P;
+  c.groups = E;
+  c.pad_offsets = pad_offsets;
+  c.status = status;
+  c.stream = static_cast<cudaStream_t>(stream);
+  return launch_gemm(c);
+}
+
 extern "C" int lmoe_grouped_bwd_dgrad(int64_t P, int E, int L, int F, const void* d_y_sorted, const void* h1,
                                       const void* w_gate_up, const void* w_down, const int32_t* tile_expert,
                                       const int32_t* n_tiles, void* d_hidden, void* d_h1, void* d_x_sorted,
                                       int32_t* status, void* stream) {
-  if (!d_y_sorted || !h1 || !w_gate_up || !w_down || !tile_expert || !n_tiles || !d_hidden || !d_h1 || !d_x_sorted)
+  if (!d_y_sorted || !h1 || !w_gate_up || !w_down || !tile_expert || !n_tiles || !d_h1 || !d_x_sorted)
     return LMOE_ERR_ARG;
   if (P <= 0 || (P % LMOE_ROW_PAD) != 0 || E <= 0 || (L % 64) != 0 || (F % 64) != 0) return LMOE_ERR_SHAPE;
   // d_hidden[P,F] = d_y_sorted[P,L] * Wd[e]^T : Wd[e] is [F,L] = [N,K] row-major -> K-major B
@@ -260,8 +336,19 @@ extern "C" int lmoe_grouped_bwd_dgrad(int64_t P, int E, int L, int F, const void
   a.n_m_tiles = n_tiles;
   a.status = status;
   a.stream = static_cast<cudaStream_t>(stream);
-  if (int rc = launch_gemm(a)) return rc;
-  if (int rc = lmoe_swiglu_bwd(P, F, h1, d_hidden, d_h1, 2ll * F, n_tiles, stream)) return rc;
+  if (d_hidden) {
+    if (int rc = launch_gemm(a)) return rc;
+    if (int rc = lmoe_swiglu_bwd(P, F, h1, d_hidden, d_h1, 2ll * F, n_tiles, stream)) return rc;
+  } else {
+    // fused: the SwiGLU adjoint runs in the epilogue of the d_hidden GEMM, d_hidden never reaches memory
+    GemmCall f = a;
+    f.epi = EPI_SWIGLU_BWD;
+    f.C = d_h1;
+    f.ldc = 2ll * F;
+    f.aux = h1;
+    f.ld_aux = 2ll * F;
+    if (int rc = launch_gemm(f)) return rc;
+  }
   // d_x_sorted[P,L] = d_h1[P,2F] * Wgu[e]^T : Wgu[e] is [L,2F] = [N,K] row-major -> K-major B
   GemmCall b = a;
   b.A[0] = d_h1;

@@ -163,9 +163,10 @@ class ExpertParallelLatentMoE(torch.autograd.Function):
 
         # output stage (local)
         d_routed = torch.empty(T, L, **bf)
+        dgrad_cat = torch.empty(T, 2 * Fs + L + E, **bf)
         d_hidden_s = torch.empty(T, Fs, **bf)
-        _cabi.call("lmoe_combine_out_bwd_dgrad", shape, ptr(dyb), ptr(wup), ptr(wds), ptr(d_routed), ptr(d_hidden_s),
-                   ptr(status), st)
+        _cabi.call("lmoe_combine_out_bwd_dgrad", shape, ptr(dyb), ptr(wup), ptr(wds), ptr(h1_s), ptr(d_routed),
+                   ptr(d_hidden_s), ptr(dgrad_cat), ptr(status), st)
         # adjoint of the combine in send order, then back to the expert ranks
         d_y_send = torch.empty(n_send, L, **bf)
         d_weights = torch.empty(T, K, **f32)
@@ -178,8 +179,6 @@ class ExpertParallelLatentMoE(torch.autograd.Function):
         d_w_down_s = torch.empty(D, Fs, **lin)
         _cabi.call("lmoe_combine_out_bwd_wgrad", shape, ptr(dyb), ptr(act_cat), ptr(d_w_up), ptr(d_w_down_s), gtype,
                    ptr(ws), ws.numel(), ptr(status), st)
-        dgrad_cat = torch.empty(T, 2 * Fs + L + E, **bf)
-        _cabi.call("lmoe_swiglu_bwd", T, Fs, ptr(h1_s), ptr(d_hidden_s), ptr(dgrad_cat), 2 * Fs + L + E, None, st)
 
         # local experts: dgrads and the shard's weight gradients
         d_w_gate_up = torch.zeros(El, L, 2 * F, **bf)
@@ -188,9 +187,9 @@ class ExpertParallelLatentMoE(torch.autograd.Function):
         if n_recv > 0:
             d_y_sorted = torch.empty(P, L, **bf)
             _cabi.call("lmoe_gather_rows", ptr(d_y_recv), ptr(row_src), 1, P, L, ptr(n_tiles), ptr(d_y_sorted), st)
-            d_hidden = torch.empty(P, F, **bf)
             d_h1 = torch.empty(P, 2 * F, **bf)
             d_x_sorted = torch.empty(P, L, **bf)
+            d_hidden = torch.empty(P, F, **bf)
             _cabi.call("lmoe_grouped_bwd_dgrad", P, El, L, F, ptr(d_y_sorted), ptr(h1), ptr(wgu), ptr(wde),
                        ptr(tile_expert), ptr(n_tiles), ptr(d_hidden), ptr(d_h1), ptr(d_x_sorted), ptr(status), st)
             _cabi.call("lmoe_grouped_bwd_wgrad", P, El, L, F, ptr(x_sorted), ptr(d_h1), ptr(hidden), ptr(d_y_sorted),
@@ -386,9 +385,10 @@ class ExpertParallelP2P(torch.autograd.Function):
         n_send = T * K
 
         d_routed = torch.empty(T, L, **bf)
+        dgrad_cat = torch.empty(T, 2 * Fs + L + E, **bf)
         d_hidden_s = torch.empty(T, Fs, **bf)
-        _cabi.call("lmoe_combine_out_bwd_dgrad", shape, ptr(dyb), ptr(wup), ptr(wds), ptr(d_routed), ptr(d_hidden_s),
-                   ptr(status), st)
+        _cabi.call("lmoe_combine_out_bwd_dgrad", shape, ptr(dyb), ptr(wup), ptr(wds), ptr(h1_s), ptr(d_routed),
+                   ptr(d_hidden_s), ptr(dgrad_cat), ptr(status), st)
         # adjoint of the combine fused into the dispatch: rows w * d_routed go to the expert ranks, the gating
         # gradients <d_routed, y> are formed from the returned rows kept in y_ret
         d_weights = torch.empty(T, K, **f32)
@@ -408,14 +408,12 @@ class ExpertParallelP2P(torch.autograd.Function):
         d_w_down_s = torch.empty(D, Fs, **lin)
         _cabi.call("lmoe_combine_out_bwd_wgrad", shape, ptr(dyb), ptr(act_cat), ptr(d_w_up), ptr(d_w_down_s), gtype,
                    ptr(ws), ws.numel(), ptr(status), st)
-        dgrad_cat = torch.empty(T, 2 * Fs + L + E, **bf)
-        _cabi.call("lmoe_swiglu_bwd", T, Fs, ptr(h1_s), ptr(d_hidden_s), ptr(dgrad_cat), 2 * Fs + L + E, None, st)
         main.wait_event(sent)
         bufs.barrier(group)                                   # all gradient rows have landed in dy_in
 
-        d_hidden = torch.empty(P, F, **bf)
         d_h1 = torch.empty(P, 2 * F, **bf)
         d_x_sorted = torch.empty(P, L, **bf)
+        d_hidden = torch.empty(P, F, **bf)
         _cabi.call("lmoe_grouped_bwd_dgrad", P, El, L, F, ptr(bufs.dy_in), ptr(h1), ptr(wgu), ptr(wde), ptr(tile_expert),
                    ptr(n_tiles), ptr(d_hidden), ptr(d_h1), ptr(d_x_sorted), ptr(status), st)
         ready2 = torch.cuda.Event()

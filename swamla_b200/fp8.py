@@ -25,13 +25,12 @@ def quantize(t: torch.Tensor, rows: int, row_len: int, n_tiles, stream):
     return q, scal[1:2]
 
 
-def experts_fwd(shape, route, x_latent, wgu, wde, status, stream):
-    """Gather + e4m3 gate_up (SwiGLU epilogue) + e4m3 down.  Returns what backward needs and y_sorted."""
-    P, E, L, F, K = route.padded_rows, shape.E, shape.L, shape.F, shape.K
-    dev = x_latent.device
+def experts_fwd(shape, route, x_sorted, wgu, wde, status, stream):
+    """e4m3 gate_up (SwiGLU epilogue) + e4m3 down on the gathered rows x_sorted[P, L] (bf16, padded layout).
+    Returns hidden, y_sorted and what backward needs."""
+    P, E, L, F = route.padded_rows, shape.E, shape.L, shape.F
+    dev = x_sorted.device
     bf = dict(dtype=BF, device=dev)
-    x_sorted = torch.empty(P, L, **bf)
-    _cabi.call("lmoe_gather_rows", ptr(x_latent), ptr(route.row_src), K, P, L, ptr(route.n_tiles), ptr(x_sorted), stream)
     xq, dq_x = quantize(x_sorted, P, L, route.n_tiles, stream)
     wguq, dq_wgu = quantize(wgu.reshape(E * L, 2 * F), E * L, 2 * F, None, stream)
     wdq, dq_wd = quantize(wde.reshape(E * F, L), E * F, L, None, stream)
@@ -44,7 +43,7 @@ def experts_fwd(shape, route, x_latent, wgu, wde, status, stream):
     _cabi.call("lmoe_grouped_rows_fp8", P, E, F, L, ptr(hq), ptr(wdq), 1, ptr(dq_h), ptr(dq_wd), ptr(route.tile_expert),
                ptr(route.n_tiles), ptr(y_sorted), ptr(status), stream)
     saved = dict(xq=xq, dq_x=dq_x, wguq=wguq, dq_wgu=dq_wgu, wdq=wdq, dq_wd=dq_wd, hq=hq, dq_h=dq_h, h1=h1)
-    return x_sorted, hidden, y_sorted, saved
+    return hidden, y_sorted, saved
 
 
 def experts_bwd(shape, route, d_y_sorted, s, status, stream):

@@ -21,6 +21,11 @@ DEBUG_SINK: Optional[dict] = None
 # Test hook: an int [T, K] tensor that replaces the top-k selection of the next forward, so that the
 # float path can be compared with a reference run whose near-tie selections differ.
 DEBUG_FORCE_SEL: Optional[torch.Tensor] = None
+# SwiGLU adjoint inside the epilogue of the dgrad GEMMs (no d_hidden round trip) instead of a streaming kernel.
+# Off by default: the epilogue's row-wise reads of the saved gate/up are uncoalesced and the fused kernel measured
+# slower than GEMM + streaming kernel (cfg2: 164 us vs 37 + 90 us for the routed experts).
+import os as _os
+FUSE_SWIGLU_BWD = _os.environ.get("LMOE_FUSE_SWIGLU_BWD", "0") == "1"
 
 
 def _stream() -> int:
@@ -37,6 +42,35 @@ def _as_bf16(t: torch.Tensor) -> torch.Tensor:
     out = torch.empty(t.shape, dtype=BF, device=t.device)
     _cabi.call("lmoe_cast_f32_to_bf16", ptr(t), ptr(out), t.numel(), _stream())
     return out
+
+
+_SIDE_STREAMS = {}
+
+
+class _Fork:
+    """Two-stream scheduling inside one forward/backward: HBM-bound row kernels run on a side stream beside the
+    tensor-bound GEMMs of the main (current) stream.  `to_side()` makes the side stream wait for everything queued
+    on the main stream so far, `to_main()` the reverse.  Every tensor is allocated on the main stream and every
+    side-stream section is joined before the function returns, so the caching allocator never recycles a block
+    that side-stream work still uses."""
+
+    def __init__(self, device):
+        self.main = torch.cuda.current_stream(device)
+        key = (device.index, self.main.cuda_stream)
+        if key not in _SIDE_STREAMS:
+            _SIDE_STREAMS[key] = torch.cuda.Stream(device=device)
+        self.side = _SIDE_STREAMS[key]
+        self.m, self.s = self.main.cuda_stream, self.side.cuda_stream
+
+    def to_side(self):
+        ev = torch.cuda.Event()
+        ev.record(self.main)
+        self.side.wait_event(ev)
+
+    def to_main(self):
+        ev = torch.cuda.Event()
+        ev.record(self.side)
+        self.main.wait_event(ev)
 
 
 class RouteTables:
@@ -97,6 +131,7 @@ class LatentMoEFunction(torch.autograd.Function):
         f32 = dict(dtype=torch.float32, device=dev)
 
         # router + latent down-projection
+        fork = _Fork(dev)
         logits = torch.empty(T, E, **f32)
         x_latent = torch.empty(T, L, **bf)
         _cabi.call("lmoe_xproj_fwd", shape, ptr(xb), ptr(wg), ptr(wdn), ptr(logits), ptr(x_latent), ptr(status), st)
@@ -105,35 +140,44 @@ class LatentMoEFunction(torch.autograd.Function):
         lse = torch.empty(T, **f32)
         z_partial = torch.empty((T + 7) // 8, **f32)
         z_loss = torch.empty(1, **f32)
-        _cabi.call("lmoe_gate_topk_fwd", shape, ptr(logits), ptr(bias), float(z_coef), ptr(sel), ptr(weights), ptr(lse),
-                   ptr(z_partial), ptr(z_loss), st)
-        if DEBUG_FORCE_SEL is not None:
-            sel = DEBUG_FORCE_SEL.to(device=dev, dtype=torch.int32).contiguous()
-            aff = torch.sigmoid(logits).gather(1, sel.long())
-            weights = (aff / (aff.sum(-1, keepdim=True) + 1e-9)).contiguous()
         route = RouteTables(shape, dev)
+        P = route.padded_rows
         ws = torch.empty(max(16, lib.lmoe_route_workspace_bytes(shape)), dtype=torch.uint8, device=dev)
-        _cabi.call("lmoe_route_permute", shape, ptr(sel), route.struct, ptr(ws), ws.numel(), st)
+        x_sorted = torch.empty(P, L, **bf)
+        h1_s = torch.empty(T, 2 * Fs, **bf)
+        act_cat = torch.empty(T, L + Fs, **bf)
+        if DEBUG_FORCE_SEL is not None:
+            forced = DEBUG_FORCE_SEL.to(device=dev, dtype=torch.int32).contiguous()
+            aff = torch.sigmoid(logits).gather(1, forced.long())
+            forced_w = (aff / (aff.sum(-1, keepdim=True) + 1e-9)).contiguous()
+        # side stream: top-k, routing tables, gather (latency- and HBM-bound) beside the shared-expert GEMM
+        fork.to_side()
+        _cabi.call("lmoe_gate_topk_fwd", shape, ptr(logits), ptr(bias), float(z_coef), ptr(sel), ptr(weights), ptr(lse),
+                   ptr(z_partial), ptr(z_loss), fork.s)
+        if DEBUG_FORCE_SEL is not None:
+            fork.to_main()
+            sel, weights = forced, forced_w
+            fork.to_side()
+        _cabi.call("lmoe_route_permute", shape, ptr(sel), route.struct, ptr(ws), ws.numel(), fork.s)
+        _cabi.call("lmoe_gather_rows", ptr(x_latent), ptr(route.row_src), top_k, P, L, ptr(route.n_tiles), ptr(x_sorted),
+                   fork.s)
+        _cabi.call("lmoe_shared_gateup_fwd", shape, ptr(xb), ptr(wgus), ptr(h1_s), ptr(act_cat), ptr(status), st)
+        fork.to_main()
 
         # routed experts in the padded layout
-        P = route.padded_rows
         fp8_saved = None
         if fp8:
             from . import fp8 as fp8_path
-            x_sorted, hidden, y_sorted, fp8_saved = fp8_path.experts_fwd(shape, route, x_latent, wgu, wde, status, st)
+            hidden, y_sorted, fp8_saved = fp8_path.experts_fwd(shape, route, x_sorted, wgu, wde, status, st)
             h1 = fp8_saved["h1"]
         else:
-            x_sorted = torch.empty(P, L, **bf)
             h1 = torch.empty(P, 2 * F, **bf)
             hidden = torch.empty(P, F, **bf)
             y_sorted = torch.empty(P, L, **bf)
-            _cabi.call("lmoe_experts_fwd", shape, ptr(x_latent), ptr(wgu), ptr(wde), route.struct, ptr(x_sorted), ptr(h1),
-                       ptr(hidden), ptr(y_sorted), ptr(status), st)
+            _cabi.call("lmoe_grouped_fwd", P, E, L, F, ptr(x_sorted), ptr(wgu), ptr(wde), ptr(route.tile_expert),
+                       ptr(route.n_tiles), ptr(h1), ptr(hidden), ptr(y_sorted), ptr(status), st)
 
-        # shared expert and output; routed and hidden_s live side by side in act_cat[T, L+Fs]
-        h1_s = torch.empty(T, 2 * Fs, **bf)
-        act_cat = torch.empty(T, L + Fs, **bf)
-        _cabi.call("lmoe_shared_gateup_fwd", shape, ptr(xb), ptr(wgus), ptr(h1_s), ptr(act_cat), ptr(status), st)
+        # weighted combine, up-projection, shared down-projection, add
         y = torch.empty(T, D, **bf)
         _cabi.call("lmoe_combine_out_fwd", shape, ptr(y_sorted), route.struct, ptr(weights), ptr(act_cat), ptr(wds),
                    ptr(wup), ptr(y), ptr(status), st)
@@ -182,60 +226,69 @@ class LatentMoEFunction(torch.autograd.Function):
         lin = dict(dtype=lin_dtype, device=dev)
         ws = torch.empty(max(16, lib.lmoe_wgrad_workspace_bytes(shape)), dtype=torch.uint8, device=dev)
 
-        # output stage
+        # All buffers first (main stream), then the schedule: GEMMs on the main stream, row kernels beside them.
+        fork = _Fork(dev)
         d_routed = torch.empty(T, L, **bf)
-        d_hidden_s = torch.empty(T, Fs, **bf)
-        _cabi.call("lmoe_combine_out_bwd_dgrad", shape, ptr(dyb), ptr(wup), ptr(wds), ptr(d_routed), ptr(d_hidden_s),
-                   ptr(status), st)
         d_w_up = torch.empty(D, L, **lin)
         d_w_down_s = torch.empty(D, Fs, **lin)
-        _cabi.call("lmoe_combine_out_bwd_wgrad", shape, ptr(dyb), ptr(act_cat), ptr(d_w_up), ptr(d_w_down_s), gtype,
-                   ptr(ws), ws.numel(), ptr(status), st)
         # the three x-side gradients live side by side in dgrad_cat[T, 2Fs+L+E]
         dgrad_cat = torch.empty(T, 2 * Fs + L + E, **bf)
         d_h1_s, d_x_latent, d_logits = dgrad_cat[:, :2 * Fs], dgrad_cat[:, 2 * Fs:2 * Fs + L], dgrad_cat[:, 2 * Fs + L:]
-        _cabi.call("lmoe_swiglu_bwd", T, Fs, ptr(h1_s), ptr(d_hidden_s), ptr(dgrad_cat), 2 * Fs + L + E, None, st)
-
-        # routed experts
         d_y_sorted = torch.empty(P, L, **bf)
         d_weights = torch.empty(T, K, **f32)
-        _cabi.call("lmoe_combine_bwd", shape, ptr(d_routed), ptr(y_sorted), ptr(weights), route.struct, ptr(d_y_sorted),
-                   ptr(d_weights), st)
-        if ctx.fp8_saved is not None:
-            from . import fp8 as fp8_path
-            d_hidden, d_h1, d_x_sorted, d_w_gate_up, d_w_down_e = fp8_path.experts_bwd(shape, route, d_y_sorted,
-                                                                                       ctx.fp8_saved, status, st)
-        else:
-            d_hidden = torch.empty(P, F, **bf)
-            d_h1 = torch.empty(P, 2 * F, **bf)
-            d_x_sorted = torch.empty(P, L, **bf)
-            _cabi.call("lmoe_experts_bwd_dgrad", shape, ptr(d_y_sorted), ptr(h1), ptr(wgu), ptr(wde), route.struct,
-                       ptr(d_hidden), ptr(d_h1), ptr(d_x_sorted), ptr(status), st)
-            d_w_gate_up = torch.empty(E, L, 2 * F, **bf)
-            d_w_down_e = torch.empty(E, F, L, **bf)
-            _cabi.call("lmoe_experts_bwd_wgrad", shape, ptr(x_sorted), ptr(d_h1), ptr(hidden), ptr(d_y_sorted),
-                       route.struct, ptr(d_w_gate_up), ptr(d_w_down_e), ptr(status), st)
-        _cabi.call("lmoe_unpermute_sum_bwd", shape, ptr(d_x_sorted), route.struct, ptr(dgrad_cat), st)
-
-        # router
-        dz = None
-        if d_z is not None:
-            dz = d_z.to(torch.float32).reshape(1).contiguous()
-        _cabi.call("lmoe_gate_topk_bwd", shape, ptr(logits), ptr(sel), ptr(weights), ptr(d_weights), ptr(lse), ptr(dz),
-                   ctx.z_coef, ptr(dgrad_cat), st)
-
-        # x side: dx and the three weight gradients that contract with x
         dx = torch.empty(T, D, **bf)
         d_w_gate_up_s = torch.empty(2 * Fs, D, **lin)
         d_w_down = torch.empty(L, D, **lin)
         d_w_gate = torch.empty(E, D, **lin)
+        dz = None
+        if d_z is not None:
+            dz = d_z.to(torch.float32).reshape(1).contiguous()
+        ld_cat = 2 * Fs + L + E
+
+        # output stage dgrads, then: [adjoint of the combine] beside [output-stage weight gradients]
+        d_hidden_s = None if FUSE_SWIGLU_BWD else torch.empty(T, Fs, **bf)
+        _cabi.call("lmoe_combine_out_bwd_dgrad", shape, ptr(dyb), ptr(wup), ptr(wds), ptr(h1_s), ptr(d_routed),
+                   ptr(d_hidden_s), ptr(dgrad_cat), ptr(status), st)
+        fork.to_side()
+        _cabi.call("lmoe_combine_bwd", shape, ptr(d_routed), ptr(y_sorted), ptr(weights), route.struct, ptr(d_y_sorted),
+                   ptr(d_weights), fork.s)
+        _cabi.call("lmoe_combine_out_bwd_wgrad", shape, ptr(dyb), ptr(act_cat), ptr(d_w_up), ptr(d_w_down_s), gtype,
+                   ptr(ws), ws.numel(), ptr(status), st)
+        fork.to_main()
+
+        if ctx.fp8_saved is not None:
+            from . import fp8 as fp8_path
+            d_hidden, d_h1, d_x_sorted, d_w_gate_up, d_w_down_e = fp8_path.experts_bwd(shape, route, d_y_sorted,
+                                                                                       ctx.fp8_saved, status, st)
+            _cabi.call("lmoe_unpermute_sum_bwd", shape, ptr(d_x_sorted), route.struct, ptr(dgrad_cat), st)
+            _cabi.call("lmoe_gate_topk_bwd", shape, ptr(logits), ptr(sel), ptr(weights), ptr(d_weights), ptr(lse), ptr(dz),
+                       ctx.z_coef, ptr(dgrad_cat), st)
+        else:
+            d_h1 = torch.empty(P, 2 * F, **bf)
+            d_x_sorted = torch.empty(P, L, **bf)
+            d_w_gate_up = torch.empty(E, L, 2 * F, **bf)
+            d_w_down_e = torch.empty(E, F, L, **bf)
+            te, nt = ptr(route.tile_expert), ptr(route.n_tiles)
+            # d_h1 = swiglu'(h1, d_y_sorted * Wd[e]^T) (adjoint fused into the GEMM epilogue), d_x_sorted = d_h1 * Wgu[e]^T
+            d_hidden = None if FUSE_SWIGLU_BWD else torch.empty(P, F, **bf)
+            _cabi.call("lmoe_grouped_bwd_dgrad", P, E, L, F, ptr(d_y_sorted), ptr(h1), ptr(wgu), ptr(wde), te, nt,
+                       ptr(d_hidden), ptr(d_h1), ptr(d_x_sorted), ptr(status), st)
+            # [gather adjoint + router adjoint] beside [routed weight gradients]
+            fork.to_side()
+            _cabi.call("lmoe_unpermute_sum_bwd", shape, ptr(d_x_sorted), route.struct, ptr(dgrad_cat), fork.s)
+            _cabi.call("lmoe_gate_topk_bwd", shape, ptr(logits), ptr(sel), ptr(weights), ptr(d_weights), ptr(lse), ptr(dz),
+                       ctx.z_coef, ptr(dgrad_cat), fork.s)
+            _cabi.call("lmoe_grouped_bwd_wgrad", P, E, L, F, ptr(x_sorted), ptr(d_h1), ptr(hidden), ptr(d_y_sorted),
+                       ptr(route.pad_offsets), ptr(d_w_gate_up), ptr(d_w_down_e), ptr(status), st)
+            fork.to_main()
+
+        # x side: dx and the three weight gradients that contract with x
         _cabi.call("lmoe_xside_bwd", shape, ptr(dgrad_cat), ptr(wgus), ptr(wdn), ptr(wg), ptr(xb), ptr(dx),
                    ptr(d_w_gate_up_s), ptr(d_w_down), ptr(d_w_gate), gtype, ptr(ws), ws.numel(), ptr(status), st)
 
         if DEBUG_SINK is not None:
-            DEBUG_SINK.update(d_routed=d_routed, d_hidden_s=d_hidden_s, d_h1_s=d_h1_s, d_y_sorted=d_y_sorted,
-                              d_weights=d_weights, d_hidden=d_hidden, d_h1=d_h1, d_x_sorted=d_x_sorted,
-                              d_x_latent=d_x_latent, d_logits=d_logits)
+            DEBUG_SINK.update(d_routed=d_routed, d_h1_s=d_h1_s, d_y_sorted=d_y_sorted, d_weights=d_weights, d_h1=d_h1,
+                              d_x_sorted=d_x_sorted, d_x_latent=d_x_latent, d_logits=d_logits)
         def as_param(g, d):
             return g if g.dtype == d else g.to(d)
 

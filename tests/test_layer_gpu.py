@@ -92,13 +92,13 @@ def test_layer_fwd_bwd_matches_oracle(name, aux_grad):
 
     # every intermediate: within the bf16 tolerance of the fp32 oracle, and ~1 ulp from the bf16 model
     rows = route.pos.cpu().long()[out["perm"]]      # padded layout -> canonical sorted order
-    sorted_keys = {"x_sorted", "h1", "hidden", "y_sorted", "d_y_sorted", "d_hidden", "d_h1", "d_x_sorted"}
+    sorted_keys = {"x_sorted", "h1", "hidden", "y_sorted", "d_y_sorted", "d_h1", "d_x_sorted"}
     for k in ("logits", "weights", "x_latent", "x_sorted", "h1", "hidden", "y_sorted", "routed", "h1_s", "hidden_s"):
         got = sink[k].cpu()[rows] if k in sorted_keys else sink[k]
         assert_close(k, got, out[k], 1e-3 if k in ("logits", "weights") else RTOL_BF16)
         assert_matches_bf16_model(k, got, model[k])
-    for k in ("d_routed", "d_hidden_s", "d_h1_s", "d_y_sorted", "d_weights", "d_hidden", "d_h1", "d_x_sorted",
-              "d_x_latent", "d_logits"):
+    # (d_hidden and d_hidden_s never reach memory: the SwiGLU adjoint runs in the epilogue of their GEMMs)
+    for k in ("d_routed", "d_h1_s", "d_y_sorted", "d_weights", "d_h1", "d_x_sorted", "d_x_latent", "d_logits"):
         got = sink[k].cpu()[rows] if k in sorted_keys else sink[k]
         assert_matches_bf16_model(k, got, model[k])
     assert_close("y", y, out["y"])
@@ -108,7 +108,7 @@ def test_layer_fwd_bwd_matches_oracle(name, aux_grad):
     used = route.n_tiles.item() * 128
     pad = route.row_src[:used] < 0
     if pad.any():
-        for k in ("x_sorted", "h1", "hidden", "y_sorted", "d_y_sorted", "d_hidden", "d_h1", "d_x_sorted"):
+        for k in ("x_sorted", "h1", "hidden", "y_sorted", "d_y_sorted", "d_h1", "d_x_sorted"):
             assert sink[k][:used][pad].float().abs().max().item() == 0, k
 
     # gradients: outputs of the path, the 2e-2 criterion applies
