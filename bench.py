@@ -26,6 +26,8 @@ import torch  # noqa: E402
 from swamla_b200 import workloads as inputs  # noqa: E402
 
 METRIC = "LatentMoE fwd+bwd tokens/s"
+# dram__bytes_read.sum + dram__bytes_write.sum of the GEMM launches of one step, from ncu (see profiles/)
+TRAFFIC_BYTES_PER_STEP = {"cfg2": 2161334272}
 CPU_SAMPLE_TOKENS = 1024
 
 
@@ -270,6 +272,25 @@ def main():
     launches = lib.lmoe_launch_count() - launches0
     ms_total = ev0.elapsed_time(ev1)
     clocks = sampler.stop() if rank == 0 else None
+    # per-launch timing of the GEMM kernel over a few extra steps (not part of the timed region)
+    gemm_prof = None
+    if rank == 0:
+        import ctypes
+        prof_steps = 5
+        lib.lmoe_profile_enable(1)
+        for _ in range(prof_steps):
+            zero_grads(layer, x)
+            step(layer, x, dy)
+        torch.cuda.synchronize()
+        ms_, n_ = ctypes.c_float(0), ctypes.c_int(0)
+        lib.lmoe_profile_collect(ctypes.byref(ms_), ctypes.byref(n_))
+        lib.lmoe_profile_enable(0)
+        gemm_prof = (ms_.value / prof_steps, n_.value // prof_steps)
+    elif world > 1:
+        for _ in range(5):
+            zero_grads(layer, x)
+            step(layer, x, dy)
+        torch.cuda.synchronize()
     t = torch.tensor([ms_total], device=dev)
     if dist is not None:
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
@@ -347,10 +368,25 @@ def main():
     pk = peaks()
     flops_step = 3 * w.flops_fwd_per_token() * w.T        # per GPU
     achieved = flops_step / (ms_per_step * 1e-3) / 1e12
-    roofline = {"bound": "tensor", "achieved": achieved, "peak": pk["bf16_tflops"], "unit": "TFLOP/s",
-                "frac": achieved / pk["bf16_tflops"], "traffic": None,
+    # dominant kernel = the tcgen05 GEMM kernel (every GEMM of the step is an instantiation of it): its summed launch
+    # durations, measured here with CUDA events around each launch on its stream over `prof_steps` extra steps
+    gemm_tflops = gemm_ms_step = None
+    gemm_launches = 0
+    if gemm_prof is not None:
+        gemm_ms_step, gemm_launches = gemm_prof
+        gemm_tflops = flops_step / (gemm_ms_step * 1e-3) / 1e12
+    roofline = {"bound": "tensor", "kernel": "lmoe::gemm_kernel (all tcgen05 GEMM launches of a step)",
+                "achieved": gemm_tflops, "peak": pk["bf16_tflops"], "unit": "TFLOP/s",
+                "frac": None if gemm_tflops is None else gemm_tflops / pk["bf16_tflops"],
+                "traffic": TRAFFIC_BYTES_PER_STEP.get(w.name),
+                "traffic_note": "dram read+write bytes of the GEMM launches of one step, from an ncu capture "
+                                "(profiles/); null where no capture exists for this workload",
+                "gemm_ms_per_step": gemm_ms_step, "gemm_launches_per_step": gemm_launches,
+                "algorithmic_flops_per_step": flops_step,
                 "peak_source": f"{pk['source']} cuBLAS bf16 burst (sustained {pk['bf16_tflops_sustained']})",
-                "scope": "whole fwd+bwd step per GPU: 3 x GEMM FLOPs of the forward (router, down, routed, up, shared)",
+                "step_achieved": achieved, "step_frac": achieved / pk["bf16_tflops"],
+                "step_scope": "whole fwd+bwd step per GPU (all kernels, launch gaps included): "
+                              "3 x GEMM FLOPs of the forward (router, down, routed, up, shared)",
                 "flops_per_token_fwd_bwd": 3 * w.flops_fwd_per_token()}
     out = {
         "metric": METRIC, "value": tokens_per_s, "unit": "tokens/s", "n_gpus": world, "steps": args.steps,

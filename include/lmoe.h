@@ -80,6 +80,11 @@ int lmoe_version(void);
 const char* lmoe_status_string(int code);
 /* Number of kernels this library has launched in this process so far (all entry points). */
 int64_t lmoe_launch_count(void);
+/* Optional timing of the tcgen05 GEMM kernel: while enabled, every GEMM launch is bracketed by CUDA events on its
+ * stream; lmoe_profile_collect waits for them and returns the summed duration (ms) and the number of launches
+ * since the last collect.  Host-side measurement aid of the benchmark; off by default. */
+int lmoe_profile_enable(int on);
+int lmoe_profile_collect(float* gemm_ms, int* gemm_launches);
 /* Upper bound of padded routed rows for a shape: roundup(T*K,128) + E*128. */
 int64_t lmoe_padded_rows(const lmoe_shape* s);
 /* Bytes of scratch lmoe_route_permute needs (block histograms). */

@@ -39,6 +39,8 @@ SIGNATURES = {
     "lmoe_version": (c_int, []),
     "lmoe_status_string": (c_char_p, [c_int]),
     "lmoe_launch_count": (c_int64, []),
+    "lmoe_profile_enable": (c_int, [c_int]),
+    "lmoe_profile_collect": (c_int, [P, P]),
     "lmoe_padded_rows": (c_int64, [SP]),
     "lmoe_route_workspace_bytes": (c_size_t, [SP]),
     "lmoe_gemm_workspace_bytes": (c_size_t, [c_int, c_int, c_int]),

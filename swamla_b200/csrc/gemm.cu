@@ -4,6 +4,8 @@
 
 #include <cstring>
 #include <mutex>
+#include <utility>
+#include <vector>
 
 #include "../../include/lmoe.h"
 #include "counters.h"
@@ -86,6 +88,13 @@ static int encode_out(CUtensorMap* map, void* base, bool f32, long long cols, lo
   return r == CUDA_SUCCESS ? 0 : LMOE_ERR_DRIVER;
 }
 
+// ---------------------------------------------------------------- optional per-launch timing of the GEMM kernel
+// When enabled, every GEMM launch is bracketed by CUDA events on its own stream; lmoe_profile_collect synchronises
+// and returns the summed duration.  Used by the benchmark to report the tensor-core kernel's own throughput.
+static std::mutex g_prof_mutex;
+static bool g_prof_enabled = false;
+static std::vector<std::pair<cudaEvent_t, cudaEvent_t>> g_prof_events;
+
 // ---------------------------------------------------------------- dispatch
 template <bool A_MN, bool B_MN, int BN, int EPI, int GRP, int ESZ>
 static int launch_inst(const GemmParams& p, int grid, cudaStream_t stream) {
@@ -100,7 +109,18 @@ static int launch_inst(const GemmParams& p, int grid, cudaStream_t stream) {
     cudaFuncSetAttribute(kfn, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
     configured = true;
   }
+  cudaEvent_t ev0 = nullptr, ev1 = nullptr;
+  if (g_prof_enabled) {
+    cudaEventCreate(&ev0);
+    cudaEventCreate(&ev1);
+    cudaEventRecord(ev0, stream);
+  }
   kfn<<<grid, kGemmThreads, smem, stream>>>(p);
+  if (ev0) {
+    cudaEventRecord(ev1, stream);
+    std::lock_guard<std::mutex> lock(g_prof_mutex);
+    g_prof_events.emplace_back(ev0, ev1);
+  }
   count_launch();
   cudaError_t e = cudaGetLastError();
   return e == cudaSuccess ? 0 : static_cast<int>(e);
@@ -315,6 +335,29 @@ int splitk_reduce(const float* ws, int planes, long long plane_elems, int ws_ld,
 }  // namespace lmoe
 
 // ---------------------------------------------------------------- C ABI
+extern "C" int lmoe_profile_enable(int on) {
+  std::lock_guard<std::mutex> lock(lmoe::g_prof_mutex);
+  lmoe::g_prof_enabled = (on != 0);
+  return 0;
+}
+
+extern "C" int lmoe_profile_collect(float* gemm_ms, int* gemm_launches) {
+  if (!gemm_ms || !gemm_launches) return LMOE_ERR_ARG;
+  std::lock_guard<std::mutex> lock(lmoe::g_prof_mutex);
+  float total = 0.f;
+  for (auto& pr : lmoe::g_prof_events) {
+    cudaEventSynchronize(pr.second);
+    float ms = 0.f;
+    if (cudaEventElapsedTime(&ms, pr.first, pr.second) == cudaSuccess) total += ms;
+    cudaEventDestroy(pr.first);
+    cudaEventDestroy(pr.second);
+  }
+  *gemm_ms = total;
+  *gemm_launches = static_cast<int>(lmoe::g_prof_events.size());
+  lmoe::g_prof_events.clear();
+  return 0;
+}
+
 extern "C" size_t lmoe_gemm_workspace_bytes(int M, int N, int split_k) {
   if (split_k <= 1 || M <= 0 || N <= 0) return 0;
   return static_cast<size_t>(split_k) * M * N * sizeof(float);

@@ -76,6 +76,8 @@ WORKLOADS: Dict[str, Workload] = {
     # the five benchmark configurations
     "cfg1": Workload("cfg1", batch=2, seq=512, dtype="fp32"),
     "cfg2": Workload("cfg2", batch=8, seq=2048, dtype="bf16"),
+    # cfg2's layer on a quarter of the tokens: the small case for multi-pass profiler captures
+    "cfg2_4k": Workload("cfg2_4k", batch=2, seq=2048, dtype="bf16"),
     "cfg3": Workload("cfg3", expert_dim=3072, batch=32, seq=2048, dtype="bf16", zipf_s=1.2),
     "cfg4": Workload("cfg4", batch=64, seq=2048, dtype="fp8"),
     "cfg5": Workload("cfg5", n_experts=64, n_activated=4, batch=16, seq=2048, dtype="bf16", uniform_gate=True),
