@@ -190,11 +190,11 @@ def run_reference(args, w):
     }))
 
 
-def workload_config(w, n_gpus, parallelism):
+def workload_config(w, n_gpus, parallelism, launch="eager"):
     return {
         "workload": f"{w.name}: LatentMoE FFN fwd+bwd, x[{w.batch},{w.seq},{w.D}] {w.dtype} per GPU, "
                     f"E={w.E} top-{w.K} latent={w.L} F={w.F} Fs={w.Fs} n_shared={w.n_shared_experts}",
-        "tokens_per_step_per_gpu": w.T, "parallelism": parallelism,
+        "tokens_per_step_per_gpu": w.T, "parallelism": parallelism, "launch": launch,
         "l2": "per-step working set (~1.5 GB of activations at cfg2) exceeds the 126 MB L2; no explicit flush",
     }
 
@@ -209,6 +209,7 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--ep-mode", default="p2p", choices=["p2p", "nccl"])
+    ap.add_argument("--no-graphs", action="store_true", help="eager launches instead of CUDA-graph replay (N=1)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
 
@@ -244,6 +245,12 @@ def main():
                                          ep_mode=args.ep_mode)
     x = x_host.to(dev).requires_grad_(True)
     dy = dy_host.to(dev)
+    use_graphs = world == 1 and not args.no_graphs
+    eager_layer = layer
+    if use_graphs:
+        # the user-facing way to run a fixed-shape training step: forward and backward replayed as CUDA graphs
+        from swamla_b200.graphs import GraphedLatentMoE
+        layer = GraphedLatentMoE(layer, x)
 
     def barrier():
         if dist is not None:
@@ -278,14 +285,17 @@ def main():
         import ctypes
         prof_steps = 5
         lib.lmoe_profile_enable(1)
-        for _ in range(prof_steps):
-            zero_grads(layer, x)
-            step(layer, x, dy)
+        eager_launches0 = lib.lmoe_launch_count()
+        for _ in range(prof_steps):          # eager launches: events cannot bracket kernels inside a replayed graph
+            zero_grads(eager_layer, x)
+            step(eager_layer, x, dy)
         torch.cuda.synchronize()
         ms_, n_ = ctypes.c_float(0), ctypes.c_int(0)
         lib.lmoe_profile_collect(ctypes.byref(ms_), ctypes.byref(n_))
         lib.lmoe_profile_enable(0)
         gemm_prof = (ms_.value / prof_steps, n_.value // prof_steps)
+        if use_graphs:   # kernels inside the replayed graphs do not pass the library's launch counter: count an eager step
+            launches = (lib.lmoe_launch_count() - eager_launches0) // prof_steps * args.steps
     elif world > 1:
         for _ in range(5):
             zero_grads(layer, x)
@@ -396,7 +406,8 @@ def main():
         "config": workload_config(w, world, "single GPU" if world == 1 else
                                   f"ep{world}: experts sharded {w.E // world} per GPU, tokens data-parallel, "
                                   + ("dispatch/combine by one-sided NVLink stores into symmetric buffers"
-                                     if args.ep_mode == "p2p" else "dispatch/combine all-to-all (NCCL) of latent rows")),
+                                     if args.ep_mode == "p2p" else "dispatch/combine all-to-all (NCCL) of latent rows"),
+                                  launch="CUDA graphs (forward, backward)" if use_graphs else "eager"),
         "clocks": clocks, "gpu_launches": int(launches), "roofline": roofline,
     }
     if e2e is not None:

@@ -81,7 +81,10 @@ struct GemmSmem {
   // one slab = 128 rows x 32 columns: 8 KB in bf16 (64-byte rows), 16 KB in fp32 (128-byte rows)
   static constexpr int kSlabBytes = (EPI == EPI_F32) ? 16384 : 8192;
   static constexpr int kStreams = (EPI == EPI_SWIGLU) ? 3 : (EPI == EPI_SWIGLU_BWD ? 2 : 1);  // gate, up, hidden
-  static constexpr int kStagingBytes = 2 * kStreams * kSlabBytes;  // one buffer per epilogue group
+  // staging buffers per epilogue group: two for the plain bf16 epilogue (its slabs are cheap to produce, so the
+  // read latency of the previous TMA store would otherwise be exposed on every slab), one for the others
+  static constexpr int kBufsPerGroup = (EPI == EPI_BF16) ? 2 : 1;
+  static constexpr int kStagingBytes = 2 * kBufsPerGroup * kStreams * kSlabBytes;
   static constexpr int kBarrierBytes = 256;
   static constexpr int kBudget = 232448 - 1024 - kBarrierBytes - kStagingBytes;
   static constexpr int kStagesMax = kBudget / kStageBytes;
@@ -119,6 +122,7 @@ __device__ __forceinline__ void tma_store_3d(const CUtensorMap* map, const void*
                : "memory");
 }
 __device__ __forceinline__ void tma_store_wait_read_all() { asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory"); }
+__device__ __forceinline__ void tma_store_wait_read_1() { asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory"); }
 
 // One 128 x 32 bf16 slab row (64 bytes) into a 64-byte-swizzled staging buffer: the 16-byte chunk j of
 // row r lands at chunk j ^ ((r >> 1) & 3), which is what a SWIZZLE_64B tensor map expects.
@@ -356,7 +360,8 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_kernel(const __grid_cons
     const int bar_id = 1 + group;
     const int r = q * 32 + lane;        // row of the tile owned by this thread
     const bool issuer = (((warp - 2) & 3) == 0) && lane == 0;
-    uint8_t* sbuf = staging + group * (S::kStreams * S::kSlabBytes);
+    uint8_t* const sbuf0 = staging + group * (S::kBufsPerGroup * S::kStreams * S::kSlabBytes);
+    int buf = 0;  // which of the group's staging buffers the next slab uses
     float deq = 1.0f;
     if (ESZ == 1) deq = (p.deq_a ? p.deq_a[0] : 1.0f) * (p.deq_b ? p.deq_b[0] : 1.0f);
     int acc = 0;
@@ -466,8 +471,14 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_kernel(const __grid_cons
             ph[j] = pack_bf16x2(silu_f(g0) * u0, silu_f(g1) * u1);
           }
         }
-        // the group's staging buffer was last read by the store of its previous slab
-        if (issuer) tma_store_wait_read_all();
+        // the staging buffer about to be written was last read by the store issued kBufsPerGroup slabs ago
+        uint8_t* sbuf = sbuf0 + buf * (S::kStreams * S::kSlabBytes);
+        if (issuer) {
+          if (S::kBufsPerGroup == 2)
+            tma_store_wait_read_1();
+          else
+            tma_store_wait_read_all();
+        }
         epi_bar_sync(bar_id);
         if (EPI == EPI_F32) {
           stage_row_f32(sbuf, r, v);
@@ -497,6 +508,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_kernel(const __grid_cons
           }
           tma_store_commit();
         }
+        if (S::kBufsPerGroup == 2) buf ^= 1;
       }
       if (nk > 0) {
         acc ^= 1;

@@ -285,6 +285,24 @@ __global__ void bias_update_kernel(const int* __restrict__ counts, int E, float 
   history[e] = 0.99f * history[e] + 0.01f * load;
 }
 
+// Kernels of this file that use static shared memory ask for the same (maximum) shared-memory carveout as the GEMM
+// kernel: an SM runs kernels with different carveouts only one after the other, and these kernels are meant to run
+// beside a GEMM of another stream.
+template <typename F>
+static inline void prefer_max_carveout(F* fn) {
+  cudaFuncSetAttribute(fn, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
+}
+static void configure_route_kernels() {
+  static bool done = false;
+  if (done) return;
+  prefer_max_carveout(gate_topk_kernel);
+  prefer_max_carveout(zloss_finalize_kernel);
+  prefer_max_carveout(route_hist_kernel);
+  prefer_max_carveout(route_scan_chunks_kernel);
+  prefer_max_carveout(route_scatter_kernel);
+  done = true;
+}
+
 static inline int check_shape(const lmoe_shape* s) {
   if (!s) return LMOE_ERR_ARG;
   if (s->T <= 0 || s->E <= 0 || s->E > LMOE_MAX_EXPERTS || s->K <= 0 || s->K > LMOE_MAX_TOPK || s->K > s->E)
@@ -303,6 +321,7 @@ extern "C" int lmoe_gate_topk_fwd(const lmoe_shape* s, const float* logits, cons
   if (int rc = check_shape(s)) return rc;
   if (!logits || !expert_bias || !sel || !weights || !lse || !z_partial || !z_loss) return LMOE_ERR_ARG;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
+  configure_route_kernels();
   const int blocks = (s->T + kTopkWarpsPerBlock - 1) / kTopkWarpsPerBlock;
   gate_topk_kernel<<<blocks, kTopkWarpsPerBlock * 32, 0, st>>>(logits, expert_bias, s->T, s->E, s->K, sel, weights, lse,
                                                               z_partial);
@@ -332,6 +351,7 @@ extern "C" int lmoe_route_permute(const lmoe_shape* s, const int32_t* sel, const
       !r->tile_expert || !r->n_tiles)
     return LMOE_ERR_ARG;
   if (workspace_bytes < lmoe_route_workspace_bytes(s)) return LMOE_ERR_WORKSPACE;
+  configure_route_kernels();
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   const int n = s->T * s->K;
   const int chunks = (n + kChunk - 1) / kChunk;
