@@ -116,6 +116,8 @@ __device__ __forceinline__ uint4 pack8f(const float (&f)[8]) {
 // Dispatch: send-order row i (flat = perm[i], token = flat / K, expert e = sel[flat]) goes to the owner of e.
 // MODE 0: row = src[token]                                   (forward: latent activations)
 // MODE 1: row = weights[flat] * src[token], and d_weights[flat] = <src[token], y_ret[i]>   (backward: gradients)
+// A warp takes 32 consecutive rows: each lane resolves the indices of one row (perm -> sel -> offsets / dst_base, a
+// chain of dependent loads paid once per 32 rows), then the warp copies the rows four at a time, 16 bytes per lane.
 template <int MODE>
 __global__ void __launch_bounds__(kEpWarps * 32)
 ep_dispatch_kernel(const uint4* __restrict__ src, const int* __restrict__ perm, const int* __restrict__ sel,
@@ -123,43 +125,79 @@ ep_dispatch_kernel(const uint4* __restrict__ src, const int* __restrict__ perm, 
                    const uint4* __restrict__ y_ret, float* __restrict__ d_weights, int n_rows, int K, int El,
                    int vec_per_row, int capacity_rows, uint4* const* __restrict__ peer_bufs, int* __restrict__ status) {
   const int lane = threadIdx.x & 31;
-  for (long long i = static_cast<long long>(blockIdx.x) * kEpWarps + (threadIdx.x >> 5); i < n_rows;
-       i += static_cast<long long>(gridDim.x) * kEpWarps) {
-    const int flat = perm[i];
-    const int e = sel[flat];
-    const long long token = flat / K;
-    const int drow = dst_base[e] + static_cast<int>(i - offsets[e]);
-    const bool fits = drow < capacity_rows;
-    if (!fits && lane == 0 && status) atomicCAS(status, 0, kStatusEpOverflow);
-    uint4* dst = peer_bufs[e / El] + static_cast<long long>(drow) * vec_per_row;
-    const float w = (MODE == 1) ? weights[flat] : 1.0f;
-    float dot = 0.f;
-    for (int v = lane; v < vec_per_row; v += 32) {
-      const uint4 x = src[token * vec_per_row + v];
-      if (MODE == 0) {
-        if (fits) dst[v] = x;
-      } else {
-        float g[8], yy[8], o[8];
-        unpack8f(x, g);
-        unpack8f(y_ret[i * vec_per_row + v], yy);
-#pragma unroll
-        for (int k = 0; k < 8; ++k) {
-          dot = fmaf(g[k], yy[k], dot);
-          o[k] = w * g[k];
-        }
-        if (fits) dst[v] = pack8f(o);
-      }
+  const long long warp_global = static_cast<long long>(blockIdx.x) * kEpWarps + (threadIdx.x >> 5);
+  const long long warps_total = static_cast<long long>(gridDim.x) * kEpWarps;
+  for (long long base = warp_global * 32; base < n_rows; base += warps_total * 32) {
+    const long long i = base + lane;
+    long long my_token = 0;
+    unsigned long long my_dst = 0;  // 0: row not stored (out of range or beyond the capacity)
+    float my_w = 1.0f;
+    int my_flat = 0;
+    if (i < n_rows) {
+      my_flat = perm[i];
+      const int e = sel[my_flat];
+      my_token = my_flat / K;
+      const int drow = dst_base[e] + static_cast<int>(i - offsets[e]);
+      if (drow < capacity_rows)
+        my_dst = reinterpret_cast<unsigned long long>(peer_bufs[e / El] + static_cast<long long>(drow) * vec_per_row);
+      else if (status)
+        atomicCAS(status, 0, kStatusEpOverflow);
+      if (MODE == 1) my_w = weights[my_flat];
     }
-    if (MODE == 1) {
+    const int rows_here = static_cast<int>(min(32ll, static_cast<long long>(n_rows) - base));
+    for (int j0 = 0; j0 < rows_here; j0 += 4) {
+      long long tok[4];
+      unsigned long long dst[4];
+      float w[4];
 #pragma unroll
-      for (int o = 16; o > 0; o >>= 1) dot += __shfl_xor_sync(0xffffffffu, dot, o);
-      if (lane == 0) d_weights[flat] = dot;
+      for (int u = 0; u < 4; ++u) {
+        const int j = min(j0 + u, 31);
+        tok[u] = __shfl_sync(0xffffffffu, my_token, j);
+        dst[u] = __shfl_sync(0xffffffffu, my_dst, j);
+        w[u] = __shfl_sync(0xffffffffu, my_w, j);
+        if (j0 + u >= rows_here) dst[u] = 0;
+      }
+      float dot[4] = {0.f, 0.f, 0.f, 0.f};
+      for (int v = lane; v < vec_per_row; v += 32) {
+        uint4 x[4], yv[4];
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+          x[u] = src[tok[u] * vec_per_row + v];
+          if (MODE == 1) yv[u] = (j0 + u < rows_here) ? y_ret[(base + j0 + u) * vec_per_row + v] : make_uint4(0, 0, 0, 0);
+        }
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+          if (MODE == 0) {
+            if (dst[u]) reinterpret_cast<uint4*>(dst[u])[v] = x[u];
+          } else {
+            float g[8], yy[8], o[8];
+            unpack8f(x[u], g);
+            unpack8f(yv[u], yy);
+#pragma unroll
+            for (int k = 0; k < 8; ++k) {
+              dot[u] = fmaf(g[k], yy[k], dot[u]);
+              o[k] = w[u] * g[k];
+            }
+            if (dst[u]) reinterpret_cast<uint4*>(dst[u])[v] = pack8f(o);
+          }
+        }
+      }
+      if (MODE == 1) {
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+#pragma unroll
+          for (int o = 16; o > 0; o >>= 1) dot[u] += __shfl_xor_sync(0xffffffffu, dot[u], o);
+          const int fl = __shfl_sync(0xffffffffu, my_flat, min(j0 + u, 31));
+          if (lane == 0 && j0 + u < rows_here) d_weights[fl] = dot[u];
+        }
+      }
     }
   }
 }
 
 // Return: padded local row p (expert j = tile_expert[p / 128]) belongs to source s (walk seg_cum) and is that
-// source's row src_off[s][e] + r in its expert-sorted order; store it into s's return buffer there.
+// source's row src_off[s][e] + r in its expert-sorted order; store it into s's return buffer there.  Same scheme as
+// the dispatch: one lane resolves one row, the warp copies four rows at a time.
 __global__ void __launch_bounds__(kEpWarps * 32)
 ep_return_kernel(const uint4* __restrict__ rows, const int* __restrict__ tile_expert, const int* __restrict__ n_tiles,
                  const int* __restrict__ pad_offsets, const int* __restrict__ seg_cum, const int* __restrict__ src_off,
@@ -168,29 +206,52 @@ ep_return_kernel(const uint4* __restrict__ rows, const int* __restrict__ tile_ex
   const int lane = threadIdx.x & 31;
   const int El = E / G;
   const long long used = min(static_cast<long long>(n_tiles[0]) * LMOE_ROW_PAD, static_cast<long long>(capacity_rows));
-  for (long long p = static_cast<long long>(blockIdx.x) * kEpWarps + (threadIdx.x >> 5); p < used;
-       p += static_cast<long long>(gridDim.x) * kEpWarps) {
-    const int j = tile_expert[p / LMOE_ROW_PAD];
-    const int e = rank * El + j;
-    const int q = static_cast<int>(p - pad_offsets[j]);
-    int s = -1;
-    for (int s2 = G - 1; s2 >= 0; --s2) {
-      if (q >= seg_cum[j * G + s2]) {
-        s = s2;
-        break;
+  const long long warp_global = static_cast<long long>(blockIdx.x) * kEpWarps + (threadIdx.x >> 5);
+  const long long warps_total = static_cast<long long>(gridDim.x) * kEpWarps;
+  for (long long base = warp_global * 32; base < used; base += warps_total * 32) {
+    const long long p = base + lane;
+    unsigned long long my_dst = 0;  // 0: pad row, nothing to return
+    if (p < used) {
+      const int j = tile_expert[p / LMOE_ROW_PAD];
+      const int e = rank * El + j;
+      const int q = static_cast<int>(p - pad_offsets[j]);
+      int s = -1;
+      for (int s2 = G - 1; s2 >= 0; --s2) {
+        if (q >= seg_cum[j * G + s2]) {
+          s = s2;
+          break;
+        }
+      }
+      if (s >= 0) {
+        const int r = q - seg_cum[j * G + s];
+        if (r < counts_all[s * E + e])
+          my_dst = reinterpret_cast<unsigned long long>(peer_ret[s] +
+                                                        static_cast<long long>(src_off[s * E + e] + r) * vec_per_row);
       }
     }
-    if (s < 0) continue;
-    const int r = q - seg_cum[j * G + s];
-    if (r >= counts_all[s * E + e]) continue;  // pad row
-    uint4* dst = peer_ret[s] + static_cast<long long>(src_off[s * E + e] + r) * vec_per_row;
-    const uint4* srow = rows + p * vec_per_row;
-    for (int v = lane; v < vec_per_row; v += 32) dst[v] = srow[v];
+    const int rows_here = static_cast<int>(min(32ll, used - base));
+    for (int j0 = 0; j0 < rows_here; j0 += 4) {
+      unsigned long long dst[4];
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        dst[u] = __shfl_sync(0xffffffffu, my_dst, min(j0 + u, 31));
+        if (j0 + u >= rows_here) dst[u] = 0;
+      }
+      for (int v = lane; v < vec_per_row; v += 32) {
+        uint4 x[4];
+#pragma unroll
+        for (int u = 0; u < 4; ++u)
+          x[u] = dst[u] ? rows[(base + j0 + u) * vec_per_row + v] : make_uint4(0, 0, 0, 0);
+#pragma unroll
+        for (int u = 0; u < 4; ++u)
+          if (dst[u]) reinterpret_cast<uint4*>(dst[u])[v] = x[u];
+      }
+    }
   }
 }
 
 static inline int grid_rows(long long rows) {
-  long long b = (rows + kEpWarps - 1) / kEpWarps;
+  long long b = (rows + kEpWarps * 32 - 1) / (kEpWarps * 32);  // a warp takes 32 rows per pass
   if (b > 148ll * 16) b = 148ll * 16;
   if (b < 1) b = 1;
   return static_cast<int>(b);

@@ -114,6 +114,90 @@ gate_topk_kernel(const float* __restrict__ logits, const float* __restrict__ bia
   }
 }
 
+// Same result for E = 32 * PER: lane l holds the PER CONSECUTIVE experts l*PER .. l*PER+PER-1, so "lower expert index
+// first" is "lower lane first, then lower slot inside the lane": the arg-max of a round is one redux (maximum key), one
+// ballot (which lanes hold it) and a find-first-set, instead of two reductions.
+template <int PER>
+__global__ void __launch_bounds__(kTopkWarpsPerBlock * 32)
+gate_topk_blocked_kernel(const float* __restrict__ logits, const float* __restrict__ bias, int T, int K,
+                         int* __restrict__ sel, float* __restrict__ weights, float* __restrict__ lse_out,
+                         float* __restrict__ z_partial) {
+  constexpr int E = 32 * PER;
+  __shared__ float s_lse2[kTopkWarpsPerBlock];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int t = blockIdx.x * kTopkWarpsPerBlock + warp;
+  float lse2 = 0.f;
+  if (t < T) {
+    float x[PER], aff[PER];
+    unsigned key[PER];
+    const float* row = logits + static_cast<long long>(t) * E + lane * PER;
+    float mx = -CUDART_INF_F;
+#pragma unroll
+    for (int j = 0; j < PER; ++j) {
+      x[j] = row[j];
+      mx = fmaxf(mx, x[j]);
+      aff[j] = sigmoid_f(x[j]);
+      const unsigned u = __float_as_uint((aff[j] + bias[lane * PER + j]) + 0.0f);
+      key[j] = (u & 0x80000000u) ? ~u : (u | 0x80000000u);
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+    float se = 0.f;
+#pragma unroll
+    for (int j = 0; j < PER; ++j) se += expf(x[j] - mx);
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) se += __shfl_xor_sync(0xffffffffu, se, o);
+    const float lse = mx + logf(se);
+    lse2 = lse * lse;
+    if (lane == 0) lse_out[t] = lse;
+
+    float my_aff = 0.f;
+    int my_idx = 0;
+    float aff_sum = 0.f;
+    for (int k = 0; k < K; ++k) {
+      unsigned bk = 0u;
+      int bj = 0;
+#pragma unroll
+      for (int j = 0; j < PER; ++j) {
+        if (key[j] > bk) {  // strict: the lowest slot wins a tie inside the lane
+          bk = key[j];
+          bj = j;
+        }
+      }
+      const unsigned wmax = __reduce_max_sync(0xffffffffu, bk);
+      const unsigned holders = __ballot_sync(0xffffffffu, bk == wmax);
+      const int wl = __ffs(holders) - 1;  // lowest lane = lowest expert index among the maxima
+      float la = 0.f;
+#pragma unroll
+      for (int j = 0; j < PER; ++j)
+        if (j == bj) la = aff[j];
+      const float ba = __shfl_sync(0xffffffffu, la, wl);
+      const int bi = __shfl_sync(0xffffffffu, lane * PER + bj, wl);
+      if (lane == wl) {
+#pragma unroll
+        for (int j = 0; j < PER; ++j)
+          if (j == bj) key[j] = 0u;
+      }
+      if (lane == k) {
+        my_aff = ba;
+        my_idx = bi;
+      }
+      aff_sum += ba;
+    }
+    if (lane < K) {
+      sel[static_cast<long long>(t) * K + lane] = my_idx;
+      weights[static_cast<long long>(t) * K + lane] = my_aff / (aff_sum + 1e-9f);
+    }
+  }
+  if (lane == 0) s_lse2[warp] = lse2;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    float s = 0.f;
+    for (int i = 0; i < kTopkWarpsPerBlock; ++i) s += s_lse2[i];
+    z_partial[blockIdx.x] = s;
+  }
+}
+
 // Deterministic final reduction of the z-loss partials (fixed order, one block).
 __global__ void __launch_bounds__(256) zloss_finalize_kernel(const float* __restrict__ partial, int n, float scale,
                                                              float* __restrict__ z_loss) {
@@ -323,8 +407,15 @@ extern "C" int lmoe_gate_topk_fwd(const lmoe_shape* s, const float* logits, cons
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   configure_route_kernels();
   const int blocks = (s->T + kTopkWarpsPerBlock - 1) / kTopkWarpsPerBlock;
-  gate_topk_kernel<<<blocks, kTopkWarpsPerBlock * 32, 0, st>>>(logits, expert_bias, s->T, s->E, s->K, sel, weights, lse,
-                                                              z_partial);
+  const int thr = kTopkWarpsPerBlock * 32;
+  switch (s->E) {  // blocked layout when the expert count is a multiple of the warp size
+    case 32: gate_topk_blocked_kernel<1><<<blocks, thr, 0, st>>>(logits, expert_bias, s->T, s->K, sel, weights, lse, z_partial); break;
+    case 64: gate_topk_blocked_kernel<2><<<blocks, thr, 0, st>>>(logits, expert_bias, s->T, s->K, sel, weights, lse, z_partial); break;
+    case 128: gate_topk_blocked_kernel<4><<<blocks, thr, 0, st>>>(logits, expert_bias, s->T, s->K, sel, weights, lse, z_partial); break;
+    case 256: gate_topk_blocked_kernel<8><<<blocks, thr, 0, st>>>(logits, expert_bias, s->T, s->K, sel, weights, lse, z_partial); break;
+    default:
+      gate_topk_kernel<<<blocks, thr, 0, st>>>(logits, expert_bias, s->T, s->E, s->K, sel, weights, lse, z_partial);
+  }
   count_launch(2);
   zloss_finalize_kernel<<<1, 256, 0, st>>>(z_partial, blocks, z_coef / static_cast<float>(s->T), z_loss);
   cudaError_t e = cudaGetLastError();
