@@ -90,7 +90,7 @@ class ClockSampler:
                 "reasons": sorted(reasons)}
 
 
-def build_layer(w, rank, device, ep_group=None, ep_mode="p2p"):
+def build_layer(w, rank, device, ep_group=None, ep_mode="p2p_dedup"):
     """The layer with seed-0 parameters (identical on every rank) and this rank's own tokens (seed = rank).
     With `ep_group` the routed experts are sharded: this rank keeps experts [rank*E/G, (rank+1)*E/G)."""
     from swamla_b200.layer import LatentMoELayer
@@ -208,7 +208,7 @@ def main():
     ap.add_argument("--workload", default=None)
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
-    ap.add_argument("--ep-mode", default="p2p", choices=["p2p", "nccl"])
+    ap.add_argument("--ep-mode", default="p2p_dedup", choices=["p2p_dedup", "p2p", "nccl"])
     ap.add_argument("--no-graphs", action="store_true", help="eager launches instead of CUDA-graph replay (N=1)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
@@ -405,8 +405,10 @@ def main():
         "data": "synthetic",
         "config": workload_config(w, world, "single GPU" if world == 1 else
                                   f"ep{world}: experts sharded {w.E // world} per GPU, tokens data-parallel, "
-                                  + ("dispatch/combine by one-sided NVLink stores into symmetric buffers"
-                                     if args.ep_mode == "p2p" else "dispatch/combine all-to-all (NCCL) of latent rows"),
+                                  + {"p2p_dedup": "one-sided NVLink stores, one row per (token, destination rank), "
+                                                  "partial sums on the owner",
+                                     "p2p": "one-sided NVLink stores into symmetric buffers, one row per (token, expert)",
+                                     "nccl": "dispatch/combine all-to-all (NCCL) of latent rows"}[args.ep_mode],
                                   launch="CUDA graphs (forward, backward)" if use_graphs else "eager"),
         "clocks": clocks, "gpu_launches": int(launches), "roofline": roofline,
     }

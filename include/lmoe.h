@@ -164,6 +164,7 @@ int lmoe_shared_gateup_fwd(const lmoe_shape* s, const void* x, const void* w_gat
 /* Weighted combine, latent up-projection, shared down-projection and the final add:
  *   routed[t] = sum_k weights[t,k] * y_sorted[pos[t*K+k]]   -> act_cat[:, :L]
  *   y = hidden_s * w_down_s^T + routed * w_up^T             -> y[T,D] bf16
+ * y_sorted == NULL: act_cat[:, :L] already holds the routed rows (r and weights are then unused).
  * Replaces models/moe.py:837, 778-782 (scatter + sum), 728 (up_proj), 69 (shared down_proj), 731. */
 int lmoe_combine_out_fwd(const lmoe_shape* s, const void* y_sorted, const lmoe_route* r, const float* weights,
                          void* act_cat, const void* w_down_s, const void* w_up, void* y, int32_t* status, void* stream);
@@ -292,6 +293,40 @@ int lmoe_ep_dispatch_bwd(const void* d_routed, const void* y_ret, const float* w
 int lmoe_ep_return(const void* rows, const int32_t* tile_expert, const int32_t* n_tiles, const int32_t* pad_offsets,
                    const int32_t* seg_cum, const int32_t* src_off, const int32_t* counts_all, int G, int E, int rank,
                    int L, int64_t capacity_rows, void* const* peer_ret, void* stream);
+
+/* De-duplicated one-sided exchange: one row per (token, destination RANK) instead of one per (token, expert).  The
+ * source stores token t's latent row once into the staging slot [rank*stride + t] of every rank that owns one of its
+ * experts, plus per routed row the words the owner needs (padded row, combine weight); the owner gathers its padded
+ * layout locally, and after the grouped GEMMs reduces a token's result rows to ONE row per (token, owner) before it
+ * stores them back (ret[owner*stride + t] at the source), where lmoe_epd_sum adds the owners' partial sums.  Partial
+ * sums travel in bf16.  `stride` = slot count per source (>= every rank's token count), the same on all ranks.
+ * Symmetric buffers per rank: stage [G*stride, L] bf16, meta [capacity_rows] of {int32 slot, fp32 weight},
+ * mask [G*stride] uint32, slots [G*stride*K] int32, ret [G*stride, L] bf16, dw [stride*K] fp32.
+ * The peer_* arguments are DEVICE arrays of G device pointers.  Tables come from lmoe_ep_tables; `pos` is the inverse
+ * of the routing permutation (lmoe_invert_perm).  No counterpart in the reference (data parallelism only,
+ * train.py:944-949; the sharding follows aidocs/moe.md:940-997).
+ *   lmoe_epd_send           peer_meta != NULL: rows + mask/slots/meta (forward).  NULL: rows only (backward; pos,
+ *                           offsets, dst_base, weights, peer_mask, peer_slots unused).  Overflow -> status 201.
+ *   lmoe_epd_gather         n_slots = G*stride (a row whose slot word is outside [0, n_slots) is left a pad row).
+ *                           y_sorted == NULL: out[p] = stage[slot(p)], pad rows zero.  Otherwise the adjoint of the
+ *                           combine: out[p] = w_p * stage[slot(p)], d_w_row[p] = <stage[slot(p)], y_sorted[p]>.
+ *   lmoe_epd_reduce_return  d_w_row == NULL: weighted sums sum_k w_k rows[p_k] (forward).  Otherwise plain sums and
+ *                           d_w_row[p_k] -> peer_dw[source][t*K + k] (backward).
+ *   lmoe_epd_sum            out[t] (row stride ld_out elements) = sum over the owners of token t of ret[g*stride + t] */
+int lmoe_epd_send(const void* src_rows, const int32_t* sel, const int32_t* pos, const int32_t* offsets,
+                  const int32_t* dst_base, const float* weights, int64_t T, int K, int E, int G, int rank, int L,
+                  int64_t capacity_rows, int64_t stride, void* const* peer_stage, void* const* peer_meta,
+                  void* const* peer_mask, void* const* peer_slots, int32_t* status, void* stream);
+int lmoe_epd_gather(const void* stage, const void* meta, const int32_t* tile_expert, const int32_t* n_tiles,
+                    const int32_t* pad_offsets, const int32_t* seg_cum, const int32_t* counts_all, int G, int E, int rank,
+                    int L, int64_t capacity_rows, int64_t n_slots, const void* y_sorted, void* out_rows, float* d_w_row,
+                    void* stream);
+int lmoe_epd_reduce_return(const void* rows, const void* meta, const void* mask, const int32_t* slots,
+                           const float* d_w_row, const int32_t* src_off, const int32_t* counts_all, int G, int E, int rank,
+                           int K, int L, int64_t stride, int64_t capacity_rows, void* const* peer_ret,
+                           void* const* peer_dw, void* stream);
+int lmoe_epd_sum(const void* ret, const int32_t* sel, int64_t T, int K, int E, int G, int L, int64_t stride, void* out,
+                 int64_t ld_out, void* stream);
 
 /* ---- FP8 (e4m3) expert path ----
  * Per-tensor dynamic scaling, the "tensorwise" recipe named by optimization/fp8_native.py:103-110 (torchao

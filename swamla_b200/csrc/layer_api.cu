@@ -192,12 +192,14 @@ extern "C" int lmoe_combine_out_fwd(const lmoe_shape* s, const void* y_sorted, c
                                     void* act_cat, const void* w_down_s, const void* w_up, void* y, int32_t* status,
                                     void* stream) {
   if (int rc = check_dims(s)) return rc;
-  if (!y_sorted || !r || !weights || !act_cat || !w_down_s || !w_up || !y) return LMOE_ERR_ARG;
+  if (!act_cat || !w_down_s || !w_up || !y) return LMOE_ERR_ARG;
+  if (y_sorted && (!r || !weights)) return LMOE_ERR_ARG;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   const long long ld = s->L + s->Fs;
   bf16* routed = static_cast<bf16*>(act_cat);
   bf16* hidden_s = routed + s->L;
-  if (int rc = combine_rows(y_sorted, r->pos, weights, s->T, s->K, s->L, routed, ld, st)) return rc;
+  if (y_sorted)
+    if (int rc = combine_rows(y_sorted, r->pos, weights, s->T, s->K, s->L, routed, ld, st)) return rc;
   // y = hidden_s * Wd_s^T + routed * Wup^T : two K segments into one accumulator
   GemmCall c = dense(hidden_s, ld, 0, w_down_s, s->Fs, 0, s->T, s->D, s->Fs, y, s->D, EPI_BF16, status, stream);
   c.nseg = 2;

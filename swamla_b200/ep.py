@@ -455,3 +455,244 @@ def latent_moe_ep_p2p(x2d, w_gate, w_down, w_up, w_gate_up_s, w_down_s, w_gate_u
                       z_coef, group, bufs: SymmetricBuffers):
     return ExpertParallelP2P.apply(x2d, w_gate, w_down, w_up, w_gate_up_s, w_down_s, w_gate_up_loc, w_down_e_loc,
                                    expert_bias, int(top_k), float(z_coef), group, bufs)
+
+
+# ======================================================================================================
+# De-duplicated one-sided exchange (csrc/ep_dedup.cu): one row per (token, destination rank) each way.
+# ======================================================================================================
+class DedupBuffers:
+    """Symmetric buffers of the de-duplicated exchange and their peer pointer tables.
+
+    stage_x / stage_dy [G*stride, L]  staging slots: token t of source s lands in slot s*stride + t (fwd / bwd)
+    ret_y / ret_dx     [G*stride, L]  one partial-sum row per (owner g, token t) coming back: slot g*stride + t
+    meta [capacity] {slot, weight}, mask [G*stride], slots [G*stride*K]   routing words written by the sources
+    dw [stride*K]                     gating gradients coming back in backward
+    stride = the largest token count of any rank.  The expert layout capacity is as in ``SymmetricBuffers``.
+    One forward must be followed by its backward before the next forward reuses the buffers.
+    """
+
+    def __init__(self, group, T: int, K: int, L: int, El: int, capacity_factor: float, device):
+        import torch.distributed._symmetric_memory as symm_mem
+        G = dist.get_world_size(group)
+        t = torch.tensor([T], dtype=torch.int64, device=device)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX, group=group)       # symmetric allocations: same size everywhere
+        self.stride = int(t.item())
+        self.K = K
+        self.capacity = (int(capacity_factor * self.stride * K) + 127) // 128 * 128 + El * 128
+        n = G * self.stride
+        rows = lambda: symm_mem.empty(n, L, dtype=BF, device=device)
+        self.stage_x, self.stage_dy, self.ret_y, self.ret_dx = rows(), rows(), rows(), rows()
+        self.meta = symm_mem.empty(self.capacity, dtype=torch.int64, device=device)
+        self.mask = symm_mem.empty(n, dtype=torch.int32, device=device)
+        self.slots = symm_mem.empty(n * K, dtype=torch.int32, device=device)
+        self.dw = symm_mem.empty(self.stride * K, dtype=torch.float32, device=device)
+        bufs = (self.stage_x, self.stage_dy, self.ret_y, self.ret_dx, self.meta, self.mask, self.slots, self.dw)
+        self.handles = [symm_mem.rendezvous(b, group) for b in bufs]
+        ptrs = lambda h: torch.tensor(list(h.buffer_ptrs), dtype=torch.int64, device=device)
+        (self.peer_stage_x, self.peer_stage_dy, self.peer_ret_y, self.peer_ret_dx, self.peer_meta, self.peer_mask,
+         self.peer_slots, self.peer_dw) = (ptrs(h) for h in self.handles)
+        self.sync_word = torch.zeros(1, dtype=torch.int32, device=device)
+        self.side = torch.cuda.Stream(device=device)
+
+    def barrier(self, group):
+        """Stream-ordered barrier across the ranks (a collective on one word)."""
+        dist.all_reduce(self.sync_word, group=group)
+
+
+class ExpertParallelDedup(torch.autograd.Function):
+    """Expert-parallel forward/backward over the de-duplicated exchange (see the banner above)."""
+
+    @staticmethod
+    def forward(ctx, x, w_gate, w_down, w_up, w_gate_up_s, w_down_s, w_gate_up_loc, w_down_e_loc, expert_bias,
+                top_k: int, z_coef: float, group, bufs: DedupBuffers):
+        if not x.is_cuda:
+            raise _cabi.LmoeError("the LatentMoE path runs on a CUDA device only (no CPU fallback)")
+        lib = _cabi.load()
+        G, rank = dist.get_world_size(group), dist.get_rank(group)
+        dev = x.device
+        T, D = x.shape
+        El, L, F2 = w_gate_up_loc.shape
+        E, F, Fs, K = El * G, F2 // 2, w_down_s.shape[1], top_k
+        shape = make_shape(T, D, L, E, K, F, Fs)
+        st = _stream()
+        bf = dict(dtype=BF, device=dev)
+        f32 = dict(dtype=torch.float32, device=dev)
+        i32 = dict(dtype=torch.int32, device=dev)
+        P, stride = bufs.capacity, bufs.stride
+        if T > stride or K != bufs.K:
+            raise _cabi.LmoeError("more tokens than the symmetric buffers were sized for")
+
+        xb = _as_bf16(x)
+        wg, wdn, wup = _as_bf16(w_gate), _as_bf16(w_down), _as_bf16(w_up)
+        wgus, wds = _as_bf16(w_gate_up_s), _as_bf16(w_down_s)
+        wgu, wde = _as_bf16(w_gate_up_loc), _as_bf16(w_down_e_loc)
+        bias = expert_bias.to(torch.float32).contiguous()
+        status = torch.zeros(1, **i32)
+
+        logits = torch.empty(T, E, **f32)
+        x_latent = torch.empty(T, L, **bf)
+        _cabi.call("lmoe_xproj_fwd", shape, ptr(xb), ptr(wg), ptr(wdn), ptr(logits), ptr(x_latent), ptr(status), st)
+        sel = torch.empty(T, K, **i32)
+        weights = torch.empty(T, K, **f32)
+        lse = torch.empty(T, **f32)
+        z_partial = torch.empty((T + 7) // 8, **f32)
+        z_loss = torch.empty(1, **f32)
+        _cabi.call("lmoe_gate_topk_fwd", shape, ptr(logits), ptr(bias), float(z_coef), ptr(sel), ptr(weights), ptr(lse),
+                   ptr(z_partial), ptr(z_loss), st)
+        route = RouteTables(shape, dev)
+        ws = torch.empty(max(16, lib.lmoe_route_workspace_bytes(shape)), dtype=torch.uint8, device=dev)
+        _cabi.call("lmoe_route_permute", shape, ptr(sel), route.struct, ptr(ws), ws.numel(), st)
+        # the histogram exchange is also the barrier that orders this step's peer stores after every
+        # rank's previous use of its buffers
+        counts_all = torch.empty(G, E, **i32)
+        dist.all_gather_into_tensor(counts_all, route.counts.contiguous(), group=group)
+
+        src_off = torch.empty(G * E, **i32)
+        dst_base = torch.empty(E, **i32)
+        seg_cum = torch.empty(El * G, **i32)
+        pad_offsets = torch.empty(El + 1, **i32)
+        tile_expert = torch.empty(P // 128, **i32)
+        n_tiles = torch.empty(1, **i32)
+        _cabi.call("lmoe_ep_tables", ptr(counts_all), G, E, rank, P, ptr(src_off), ptr(dst_base), ptr(seg_cum),
+                   ptr(pad_offsets), ptr(tile_expert), ptr(n_tiles), ptr(status), st)
+        inv = torch.empty(T * K, **i32)
+        _cabi.call("lmoe_invert_perm", ptr(route.perm), T * K, ptr(inv), st)
+        # the stores over NVLink run on a side stream, beside the shared-expert GEMM (which needs no exchange)
+        main, side = torch.cuda.current_stream(), bufs.side
+        ready = torch.cuda.Event()
+        ready.record(main)
+        side.wait_event(ready)
+        sst = side.cuda_stream
+        _cabi.call("lmoe_epd_send", ptr(x_latent), ptr(sel), ptr(inv), ptr(route.offsets), ptr(dst_base), ptr(weights), T,
+                   K, E, G, rank, L, P, stride, ptr(bufs.peer_stage_x), ptr(bufs.peer_meta), ptr(bufs.peer_mask),
+                   ptr(bufs.peer_slots), ptr(status), sst)
+        sent = torch.cuda.Event()
+        sent.record(side)
+        h1_s = torch.empty(T, 2 * Fs, **bf)
+        act_cat = torch.empty(T, L + Fs, **bf)
+        _cabi.call("lmoe_shared_gateup_fwd", shape, ptr(xb), ptr(wgus), ptr(h1_s), ptr(act_cat), ptr(status), st)
+        main.wait_event(sent)
+        bufs.barrier(group)                                   # all rows and routing words have landed
+
+        x_in = torch.empty(P, L, **bf)
+        _cabi.call("lmoe_epd_gather", ptr(bufs.stage_x), ptr(bufs.meta), ptr(tile_expert), ptr(n_tiles), ptr(pad_offsets),
+                   ptr(seg_cum), ptr(counts_all), G, E, rank, L, P, G * stride, None, ptr(x_in), None, st)
+        h1 = torch.empty(P, 2 * F, **bf)
+        hidden = torch.empty(P, F, **bf)
+        y_sorted = torch.empty(P, L, **bf)
+        _cabi.call("lmoe_grouped_fwd", P, El, L, F, ptr(x_in), ptr(wgu), ptr(wde), ptr(tile_expert), ptr(n_tiles),
+                   ptr(h1), ptr(hidden), ptr(y_sorted), ptr(status), st)
+        _cabi.call("lmoe_epd_reduce_return", ptr(y_sorted), ptr(bufs.meta), ptr(bufs.mask), ptr(bufs.slots), None,
+                   ptr(src_off), ptr(counts_all), G, E, rank, K, L, stride, P, ptr(bufs.peer_ret_y), None, st)
+        bufs.barrier(group)                                   # all partial sums have landed in ret_y
+
+        _cabi.call("lmoe_epd_sum", ptr(bufs.ret_y), ptr(sel), T, K, E, G, L, stride, ptr(act_cat), L + Fs, st)
+        y = torch.empty(T, D, **bf)
+        _cabi.call("lmoe_combine_out_fwd", shape, None, None, None, ptr(act_cat), ptr(wds), ptr(wup), ptr(y),
+                   ptr(status), st)
+
+        ctx.shape, ctx.group, ctx.z_coef, ctx.status, ctx.bufs = shape, group, float(z_coef), status, bufs
+        ctx.dims = (G, rank, El, P)
+        ctx.dtypes = [t.dtype for t in (x, w_gate, w_down, w_up, w_gate_up_s, w_down_s, w_gate_up_loc, w_down_e_loc)]
+        ctx.save_for_backward(xb, wg, wdn, wup, wgus, wds, wgu, wde, logits, sel, weights, lse, act_cat, h1_s, x_in, h1,
+                              hidden, y_sorted, counts_all, src_off, seg_cum, pad_offsets, tile_expert, n_tiles)
+        global_counts = counts_all.sum(0, dtype=torch.int32)
+        ctx.mark_non_differentiable(sel, global_counts)
+        out = y if x.dtype == BF else y.to(x.dtype)
+        return out, z_loss.reshape(()), sel, global_counts
+
+    @staticmethod
+    def backward(ctx, dy, d_z, _d_sel, _d_counts):
+        (xb, wg, wdn, wup, wgus, wds, wgu, wde, logits, sel, weights, lse, act_cat, h1_s, x_in, h1, hidden, y_sorted,
+         counts_all, src_off, seg_cum, pad_offsets, tile_expert, n_tiles) = ctx.saved_tensors
+        shape, group, status, bufs = ctx.shape, ctx.group, ctx.status, ctx.bufs
+        G, rank, El, P = ctx.dims
+        T, D, L, E, K, F, Fs = shape.T, shape.D, shape.L, shape.E, shape.K, shape.F, shape.Fs
+        dev = xb.device
+        st = _stream()
+        lib = _cabi.load()
+        bf = dict(dtype=BF, device=dev)
+        f32 = dict(dtype=torch.float32, device=dev)
+        stride = bufs.stride
+        if dy is None:
+            dy = torch.zeros(T, D, **bf)
+        dyb = _as_bf16(dy.reshape(T, D))
+        dt = ctx.dtypes
+        lin_dtype = torch.float32 if any(d == torch.float32 for d in dt[1:6]) else BF
+        gtype = _cabi.F32 if lin_dtype == torch.float32 else _cabi.BF16
+        lin = dict(dtype=lin_dtype, device=dev)
+        ws = torch.empty(max(16, lib.lmoe_wgrad_workspace_bytes(shape)), dtype=torch.uint8, device=dev)
+
+        d_routed = torch.empty(T, L, **bf)
+        dgrad_cat = torch.empty(T, 2 * Fs + L + E, **bf)
+        d_hidden_s = torch.empty(T, Fs, **bf)
+        _cabi.call("lmoe_combine_out_bwd_dgrad", shape, ptr(dyb), ptr(wup), ptr(wds), ptr(h1_s), ptr(d_routed),
+                   ptr(d_hidden_s), ptr(dgrad_cat), ptr(status), st)
+        main, side = torch.cuda.current_stream(), bufs.side
+        ready = torch.cuda.Event()
+        ready.record(main)
+        side.wait_event(ready)
+        sst = side.cuda_stream
+        _cabi.call("lmoe_epd_send", ptr(d_routed), ptr(sel), None, None, None, None, T, K, E, G, rank, L, P, stride,
+                   ptr(bufs.peer_stage_dy), None, None, None, ptr(status), sst)
+        sent = torch.cuda.Event()
+        sent.record(side)
+        # local work that needs no exchange overlaps the peers' stores
+        d_w_up = torch.empty(D, L, **lin)
+        d_w_down_s = torch.empty(D, Fs, **lin)
+        _cabi.call("lmoe_combine_out_bwd_wgrad", shape, ptr(dyb), ptr(act_cat), ptr(d_w_up), ptr(d_w_down_s), gtype,
+                   ptr(ws), ws.numel(), ptr(status), st)
+        main.wait_event(sent)
+        bufs.barrier(group)                                   # all gradient rows have landed in stage_dy
+
+        # adjoint of the weighted combine on the owner: d_y rows and the gating gradients of its rows
+        dy_in = torch.empty(P, L, **bf)
+        d_w_row = torch.empty(P, **f32)
+        _cabi.call("lmoe_epd_gather", ptr(bufs.stage_dy), ptr(bufs.meta), ptr(tile_expert), ptr(n_tiles),
+                   ptr(pad_offsets), ptr(seg_cum), ptr(counts_all), G, E, rank, L, P, G * stride, ptr(y_sorted), ptr(dy_in),
+                   ptr(d_w_row), st)
+        d_h1 = torch.empty(P, 2 * F, **bf)
+        d_x_sorted = torch.empty(P, L, **bf)
+        d_hidden = torch.empty(P, F, **bf)
+        _cabi.call("lmoe_grouped_bwd_dgrad", P, El, L, F, ptr(dy_in), ptr(h1), ptr(wgu), ptr(wde), ptr(tile_expert),
+                   ptr(n_tiles), ptr(d_hidden), ptr(d_h1), ptr(d_x_sorted), ptr(status), st)
+        ready2 = torch.cuda.Event()
+        ready2.record(main)
+        side.wait_event(ready2)
+        _cabi.call("lmoe_epd_reduce_return", ptr(d_x_sorted), ptr(bufs.meta), ptr(bufs.mask), ptr(bufs.slots),
+                   ptr(d_w_row), ptr(src_off), ptr(counts_all), G, E, rank, K, L, stride, P, ptr(bufs.peer_ret_dx),
+                   ptr(bufs.peer_dw), sst)
+        returned = torch.cuda.Event()
+        returned.record(side)
+        # the shard's weight gradients need no exchange: they run beside the return stores
+        d_w_gate_up = torch.empty(El, L, 2 * F, **bf)
+        d_w_down_e = torch.empty(El, F, L, **bf)
+        _cabi.call("lmoe_grouped_bwd_wgrad", P, El, L, F, ptr(x_in), ptr(d_h1), ptr(hidden), ptr(dy_in),
+                   ptr(pad_offsets), ptr(d_w_gate_up), ptr(d_w_down_e), ptr(status), st)
+        main.wait_event(returned)
+        bufs.barrier(group)                                   # partial sums in ret_dx, gating gradients in dw
+
+        d_x_latent = dgrad_cat[:, 2 * Fs:]
+        _cabi.call("lmoe_epd_sum", ptr(bufs.ret_dx), ptr(sel), T, K, E, G, L, stride, ptr(d_x_latent), 2 * Fs + L + E, st)
+        dz = None if d_z is None else d_z.to(torch.float32).reshape(1).contiguous()
+        _cabi.call("lmoe_gate_topk_bwd", shape, ptr(logits), ptr(sel), ptr(weights), ptr(bufs.dw), ptr(lse), ptr(dz),
+                   ctx.z_coef, ptr(dgrad_cat), st)
+        dx = torch.empty(T, D, **bf)
+        d_w_gate_up_s = torch.empty(2 * Fs, D, **lin)
+        d_w_down = torch.empty(L, D, **lin)
+        d_w_gate = torch.empty(E, D, **lin)
+        _cabi.call("lmoe_xside_bwd", shape, ptr(dgrad_cat), ptr(wgus), ptr(wdn), ptr(wg), ptr(xb), ptr(dx),
+                   ptr(d_w_gate_up_s), ptr(d_w_down), ptr(d_w_gate), gtype, ptr(ws), ws.numel(), ptr(status), st)
+
+        def as_param(g, d):
+            return g if g.dtype == d else g.to(d)
+
+        return (as_param(dx, dt[0]), as_param(d_w_gate, dt[1]), as_param(d_w_down, dt[2]), as_param(d_w_up, dt[3]),
+                as_param(d_w_gate_up_s, dt[4]), as_param(d_w_down_s, dt[5]), as_param(d_w_gate_up, dt[6]),
+                as_param(d_w_down_e, dt[7]), None, None, None, None, None)
+
+
+def latent_moe_ep_dedup(x2d, w_gate, w_down, w_up, w_gate_up_s, w_down_s, w_gate_up_loc, w_down_e_loc, expert_bias,
+                        top_k, z_coef, group, bufs: DedupBuffers):
+    return ExpertParallelDedup.apply(x2d, w_gate, w_down, w_up, w_gate_up_s, w_down_s, w_gate_up_loc, w_down_e_loc,
+                                     expert_bias, int(top_k), float(z_coef), group, bufs)

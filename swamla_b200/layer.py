@@ -153,8 +153,11 @@ class LatentMoELayer(nn.Module):
         # routed experts; this rank then holds experts [rank*E/G, (rank+1)*E/G) only.  Absent -> all experts.
         self.ep_group = getattr(config, "ep_group", None)
         self.ep_size = _ep_size(self.ep_group)
-        # "p2p": one-sided stores over NVLink into symmetric buffers; "nccl": all-to-all through NCCL
-        self.ep_mode = getattr(config, "ep_mode", "p2p")
+        # "p2p_dedup": one-sided stores over NVLink, one row per (token, destination rank), partial sums on the owner;
+        # "p2p": one row per (token, expert), bit-identical to the single-GPU layer; "nccl": all-to-all through NCCL
+        self.ep_mode = getattr(config, "ep_mode", "p2p_dedup")
+        if self.ep_mode not in ("p2p_dedup", "p2p", "nccl"):
+            raise ValueError("ep_mode must be 'p2p_dedup', 'p2p' or 'nccl'")
         # incoming-buffer capacity of a shard, as a multiple of this rank's own row count T*K (p2p mode)
         self.ep_capacity_factor = float(getattr(config, "ep_capacity_factor", 2.0))
         self._ep_bufs = None
@@ -183,7 +186,14 @@ class LatentMoELayer(nn.Module):
                 shared.gate_up_proj.weight, shared.down_proj.weight,
                 self.experts.gate_up_weight, self.experts.down_weight,
                 self.router.expert_bias, self.n_activated, self.router.z_loss_coef)
-        if self.ep_size > 1 and self.ep_mode == "p2p":
+        if self.ep_size > 1 and self.ep_mode == "p2p_dedup":
+            from .ep import DedupBuffers, latent_moe_ep_dedup
+            T = x_flat.shape[0]
+            if self._ep_bufs is None or self._ep_bufs.stride < T:
+                self._ep_bufs = DedupBuffers(self.ep_group, T, self.n_activated, self.latent_dim, self.experts.n_experts,
+                                             self.ep_capacity_factor, x.device)
+            y, z_loss, sel, counts = latent_moe_ep_dedup(*args, self.ep_group, self._ep_bufs)
+        elif self.ep_size > 1 and self.ep_mode == "p2p":
             # one-sided NVLink stores into the peers' padded expert layout (symmetric buffers owned by the layer;
             # one forward must be followed by its backward before the next forward reuses them)
             from .ep import SymmetricBuffers, latent_moe_ep_p2p

@@ -81,12 +81,22 @@ def _ep_worker(rank, world, port, tmpdir, mode):
         (y1, dx1, l1), (y2, dx2, l2) = outs
         # routing is local and identical; a row's result does not depend on where it sits in an expert's segment
         assert torch.equal(l1.router._last_selected_experts, l2.router._last_selected_experts)
-        assert torch.equal(y1, y2), (y1.float() - y2.float()).abs().max().item()
-        assert torch.equal(dx1, dx2)
-        for name in ("router.gate.weight", "down_proj.weight", "up_proj.weight", "shared_experts.0.gate_up_proj.weight",
-                     "shared_experts.0.down_proj.weight"):
-            a, b = dict(l1.named_parameters())[name].grad, dict(l2.named_parameters())[name].grad
-            assert torch.equal(a, b), name
+        dense = ("router.gate.weight", "down_proj.weight", "up_proj.weight", "shared_experts.0.gate_up_proj.weight",
+                 "shared_experts.0.down_proj.weight")
+        if mode == "p2p_dedup":
+            # partial sums per owner travel in bf16: one more rounding than the single-GPU combine, so the comparison
+            # is within the bf16 tolerance of the path (rtol 2e-2) instead of bit for bit
+            for a, b, what in [(y2, y1, "y"), (dx2, dx1, "dx")] + [
+                    (dict(l2.named_parameters())[n].grad, dict(l1.named_parameters())[n].grad, n) for n in dense]:
+                ok, rep = R.within_tolerance(a.float().cpu(), b.float().cpu(), 2e-2)
+                assert ok, (what, rep)
+                assert R.closeness(a.float().cpu(), b.float().cpu(), 2e-2)["rel_fro"] < 5e-3, what
+        else:
+            assert torch.equal(y1, y2), (y1.float() - y2.float()).abs().max().item()
+            assert torch.equal(dx1, dx2)
+            for name in dense:
+                a, b = dict(l1.named_parameters())[name].grad, dict(l2.named_parameters())[name].grad
+                assert torch.equal(a, b), name
         # expert shard gradients: the owner sums over the tokens of ALL ranks
         for name in ("experts.gate_up_weight", "experts.down_weight"):
             full = dict(l1.named_parameters())[name].grad.float()          # this rank's tokens, all experts
@@ -104,9 +114,9 @@ def _ep_worker(rank, world, port, tmpdir, mode):
 
 
 @pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs 2 GPUs")
-@pytest.mark.parametrize("mode", ["nccl", "p2p"])
+@pytest.mark.parametrize("mode", ["nccl", "p2p", "p2p_dedup"])
 def test_expert_parallel_layer_matches_single_gpu_layer(tmp_path, mode):
     import torch.multiprocessing as mp
-    port = 29600 + (os.getpid() % 300) + (7 if mode == "p2p" else 0)
+    port = 29600 + (os.getpid() % 300) + {"nccl": 0, "p2p": 7, "p2p_dedup": 13}[mode]
     mp.spawn(_ep_worker, args=(2, port, str(tmp_path), mode), nprocs=2, join=True)
     assert (tmp_path / "ok0").exists() and (tmp_path / "ok1").exists()
