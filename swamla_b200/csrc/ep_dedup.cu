@@ -286,6 +286,18 @@ static inline int epd_last_err() {
   cudaError_t e = cudaGetLastError();
   return e == cudaSuccess ? 0 : static_cast<int>(e);
 }
+// The exchange kernels run on a side stream beside GEMMs of the main stream.  An SM runs kernels with different
+// shared-memory carveouts only one after the other, so they ask for the GEMM kernel's (maximum) carveout.
+static void epd_configure() {
+  static bool done = false;
+  if (done) return;
+  const int c = cudaSharedmemCarveoutMaxShared;
+  cudaFuncSetAttribute(epd_send_kernel<true>, cudaFuncAttributePreferredSharedMemoryCarveout, c);
+  cudaFuncSetAttribute(epd_send_kernel<false>, cudaFuncAttributePreferredSharedMemoryCarveout, c);
+  cudaFuncSetAttribute(epd_reduce_return_kernel<true>, cudaFuncAttributePreferredSharedMemoryCarveout, c);
+  cudaFuncSetAttribute(epd_reduce_return_kernel<false>, cudaFuncAttributePreferredSharedMemoryCarveout, c);
+  done = true;
+}
 static inline bool epd_dims_ok(int K, int E, int G, int rank, int L, int64_t stride) {
   return K > 0 && K <= 32 && G > 0 && G <= 256 && E > 0 && (E % G) == 0 && rank >= 0 && rank < G && L > 0 &&
          (L & 7) == 0 && L <= kEpdMaxVecPerLane * 256 && stride > 0 && stride * G < (1ll << 31);
@@ -305,6 +317,7 @@ extern "C" int lmoe_epd_send(const void* src_rows, const int32_t* sel, const int
   if (!epd_dims_ok(K, E, G, rank, L, stride) || T <= 0 || T > stride || capacity_rows <= 0 ||
       capacity_rows >= (1ll << 31))
     return LMOE_ERR_SHAPE;
+  epd_configure();
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   const int grid = epd_grid(T);
   if (with_meta)
@@ -354,6 +367,7 @@ extern "C" int lmoe_epd_reduce_return(const void* rows, const void* meta, const 
   if ((d_w_row == nullptr) != (peer_dw == nullptr)) return LMOE_ERR_ARG;
   if (!epd_dims_ok(K, E, G, rank, L, stride) || capacity_rows <= 0 || capacity_rows >= (1ll << 31))
     return LMOE_ERR_SHAPE;
+  epd_configure();
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   const int grid = epd_grid(static_cast<long long>(G) * stride);
   if (d_w_row)

@@ -380,6 +380,10 @@ static void configure_route_kernels() {
   static bool done = false;
   if (done) return;
   prefer_max_carveout(gate_topk_kernel);
+  prefer_max_carveout(gate_topk_blocked_kernel<1>);
+  prefer_max_carveout(gate_topk_blocked_kernel<2>);
+  prefer_max_carveout(gate_topk_blocked_kernel<4>);
+  prefer_max_carveout(gate_topk_blocked_kernel<8>);
   prefer_max_carveout(zloss_finalize_kernel);
   prefer_max_carveout(route_hist_kernel);
   prefer_max_carveout(route_scan_chunks_kernel);
