@@ -234,6 +234,20 @@ int lmoe_grouped_bwd_dgrad(int64_t P, int E, int L, int F, const void* d_y_sorte
 int lmoe_grouped_bwd_wgrad(int64_t P, int E, int L, int F, const void* x_sorted, const void* d_h1, const void* hidden,
                            const void* d_y_sorted, const int32_t* pad_offsets, void* d_w_gate_up, void* d_w_down,
                            int32_t* status, void* stream);
+
+/* The same two entry points with the A operand of the gate_up GEMMs GATHERED by the TMA unit instead of read from a
+ * materialised x_sorted: padded row i is row row_index[i * index_stride] / index_div of src_rows[n_src_rows, L] (bf16, row
+ * stride L); a negative entry reads row `zero_row`, which the caller keeps all zero (pad rows of the routed layout).
+ * With row_index = lmoe_route.row_src (flat index t*K + k) and index_div = K this removes the gather kernel of models/moe.py:749-757 (the
+ * x[token_indices] copy) and the x_sorted buffer. */
+int lmoe_grouped_fwd_gather(int64_t P, int E, int L, int F, const void* src_rows, int64_t n_src_rows,
+                            const int32_t* row_index, int index_stride, int index_div, int64_t zero_row, const void* w_gate_up,
+                            const void* w_down, const int32_t* tile_expert, const int32_t* n_tiles, void* h1, void* hidden,
+                            void* y_sorted, int32_t* status, void* stream);
+int lmoe_grouped_bwd_wgrad_gather(int64_t P, int E, int L, int F, const void* src_rows, int64_t n_src_rows,
+                                  const int32_t* row_index, int index_stride, int index_div, int64_t zero_row, const void* d_h1,
+                                  const void* hidden, const void* d_y_sorted, const int32_t* pad_offsets,
+                                  void* d_w_gate_up, void* d_w_down, int32_t* status, void* stream);
 /* The single GEMMs behind the three calls above, for hosts that schedule them individually:
  * out[P,N] = a[P,K] * B[e] with B stacked [E,K,N] (b_mn = 1) or [E,N,K] (b_mn = 0); out[e][M,N] = a[rows_e,M]^T b[rows_e,N]. */
 int lmoe_grouped_rows_bf16(int64_t P, int E, int K, int N, const void* a, const void* b, int b_mn,

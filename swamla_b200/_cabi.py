@@ -78,6 +78,10 @@ SIGNATURES = {
     "lmoe_ep_dispatch": (c_int, [P, P, P, P, P, c_int64, c_int, c_int, c_int, c_int, c_int64, P, P, P]),
     "lmoe_ep_dispatch_bwd": (c_int, [P, P, P, P, P, P, P, c_int64, c_int, c_int, c_int, c_int, c_int64, P, P, P, P]),
     "lmoe_ep_return": (c_int, [P, P, P, P, P, P, P, c_int, c_int, c_int, c_int, c_int64, P, P]),
+    "lmoe_grouped_fwd_gather": (c_int, [c_int64, c_int, c_int, c_int, P, c_int64, P, c_int, c_int, c_int64, P, P, P, P, P,
+                                         P, P, P, P]),
+    "lmoe_grouped_bwd_wgrad_gather": (c_int, [c_int64, c_int, c_int, c_int, P, c_int64, P, c_int, c_int, c_int64, P, P, P,
+                                               P, P, P, P, P]),
     "lmoe_epd_send": (c_int, [P, P, P, P, P, P, c_int64, c_int, c_int, c_int, c_int, c_int, c_int64, c_int64, P, P, P, P,
                                P, P]),
     "lmoe_epd_gather": (c_int, [P, P, P, P, P, P, P, c_int, c_int, c_int, c_int, c_int64, c_int64, P, P, P, P]),

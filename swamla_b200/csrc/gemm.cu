@@ -178,6 +178,14 @@ int launch_gemm(const GemmCall& c) {
                      ((c.ld_aux * 2) & 15) != 0))
     return LMOE_ERR_SHAPE;
 
+  const bool gather = c.a_rows != nullptr;
+  if (gather) {
+    const bool shape_ok = (c.grp == GRP_M && !c.a_mn) || (c.grp == GRP_K && c.a_mn);
+    if (!shape_ok || esz != 2 || c.nseg != 1 || c.a_src_rows <= 0 || c.a_rows_stride <= 0 || c.a_rows_div <= 0 || c.a_zero_row < 0 ||
+        c.a_zero_row >= c.a_src_rows)
+      return LMOE_ERR_ARG;
+  }
+
   GemmParams p;
   memset(&p, 0, sizeof(p));
   // ---- tile geometry ----
@@ -208,7 +216,10 @@ int launch_gemm(const GemmCall& c) {
     if (c.grp == GRP_K) {
       // both operands are [padded rows, extent] row-major and contract over rows
       if (!c.a_mn || !c.b_mn) return LMOE_ERR_ARG;
-      rc = encode_2d(&p.tmA[s], c.A[s], c.M, c.padded_rows, c.lda[s], bk, esz);
+      if (gather)  // box of one row: the kernel gathers the contraction rows four at a time
+        rc = encode_2d(&p.tmA[s], c.A[s], c.M, c.a_src_rows, c.lda[s], 1, esz);
+      else
+        rc = encode_2d(&p.tmA[s], c.A[s], c.M, c.padded_rows, c.lda[s], bk, esz);
       if (rc) return rc;
       rc = encode_2d(&p.tmB[s], c.B[s], c.N, c.padded_rows, c.ldb[s], bk, esz);
       if (rc) return rc;
@@ -219,7 +230,9 @@ int launch_gemm(const GemmCall& c) {
     if (K <= 0) return LMOE_ERR_SHAPE;
     p.seg_kiters[s] = (K + bk - 1) / bk;
     // A
-    if (!c.a_mn)
+    if (gather)
+      rc = encode_2d(&p.tmA[s], c.A[s], K, c.a_src_rows, c.lda[s], 1, esz);
+    else if (!c.a_mn)
       rc = encode_2d(&p.tmA[s], c.A[s], K, rows_total, c.lda[s], kBM, esz);
     else
       rc = encode_2d(&p.tmA[s], c.A[s], c.M, K, c.lda[s], bk, esz);
@@ -279,6 +292,10 @@ int launch_gemm(const GemmCall& c) {
   p.deq_b = c.deq_b;
   p.aux = c.aux;
   p.ld_aux = c.ld_aux;
+  p.a_rows = c.a_rows;
+  p.a_rows_stride = c.a_rows_stride;
+  p.a_rows_div = c.a_rows_div;
+  p.a_zero_row = c.a_zero_row;
   p.status = c.status;
   (void)ch;
   if (c.grp == GRP_M && (!c.tile_expert || !c.n_m_tiles)) return LMOE_ERR_ARG;

@@ -70,6 +70,13 @@ struct alignas(64) GemmParams {
   const float* deq_b;
   const void* aux;         // EPI_SWIGLU_BWD: h1 [rows, 2*N] bf16 (gate | up), row stride ld_aux elements
   long long ld_aux;
+  // Gathered A operand (bf16, one K segment): row i of the padded routed layout is row
+  // a_rows[i * a_rows_stride] / a_rows_div of the tensor behind tmA[0] (negative entry: a_zero_row, a row of zeros).  GRP_M with K-major A gathers the tile's M rows,
+  // GRP_K (MN-major A) gathers the contraction rows.  NULL: A is read in place.
+  const int* a_rows;
+  int a_rows_stride;
+  int a_rows_div;
+  int a_zero_row;
   int* status;
 };
 
@@ -243,9 +250,86 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_kernel(const __grid_cons
     return n;
   };
 
+  // B tile of one pipeline stage (issued by one thread)
+  auto load_b = [&](uint8_t* sb, uint64_t* bar, const Tile& t, int s, int kcoord) {
+    const int grp_rows = (GRP == GRP_M) ? t.grp * p.b_group_rows : 0;
+    if (!B_MN) {
+      if (kSwiglu) {
+        const int nh = t.nt * (BN / 2);
+        tma_load_2d(sb, &p.tmB[s], bar, kcoord, grp_rows + nh);
+        tma_load_2d(sb + (BN / 2) * 128, &p.tmB[s], bar, kcoord, grp_rows + p.half + nh);
+      } else {
+        tma_load_2d(sb, &p.tmB[s], bar, kcoord, grp_rows + t.nt * BN);
+      }
+    } else {
+#pragma unroll
+      for (int j = 0; j < BN / CH; ++j) {
+        constexpr int kHalfChunks = BN / (2 * CH);
+        int ncol;
+        if (kSwiglu) {
+          const int nh = t.nt * (BN / 2);
+          ncol = (j < kHalfChunks) ? (nh + j * CH) : (p.half + nh + (j - kHalfChunks) * CH);
+        } else {
+          ncol = t.nt * BN + j * CH;
+        }
+        tma_load_2d(sb + j * CH_BYTES, &p.tmB[s], bar, ncol, grp_rows + kcoord);
+      }
+    }
+  };
+
   if (warp == 0) {
     // =========================== TMA producer ===========================
-    if (lane == 0) {
+    if (ESZ == 2 && GRP != GRP_NONE && p.a_rows != nullptr) {
+      // Gathered A: the whole warp runs the loop; lane l issues the gather of four rows (l-th group of four) of
+      // every stage, lane 0 also arms the barrier and loads B.  A stage holds 128 rows of 128 bytes either way
+      // (K-major: 128 tile rows; MN-major: two chunks of 64 contraction rows), i.e. 32 gathers of 512 bytes.
+      static_assert(kBM * kBKBytes == 32 * 4 * 128, "one gather of four rows per lane");
+      auto load_idx = [&](long long first_row) {
+        int4 v;
+        const int* q = p.a_rows + first_row * p.a_rows_stride;
+        v.x = q[0];
+        v.y = q[p.a_rows_stride];
+        v.z = q[2 * p.a_rows_stride];
+        v.w = q[3 * p.a_rows_stride];
+        v.x = v.x < 0 ? p.a_zero_row : v.x / p.a_rows_div;
+        v.y = v.y < 0 ? p.a_zero_row : v.y / p.a_rows_div;
+        v.z = v.z < 0 ? p.a_zero_row : v.z / p.a_rows_div;
+        v.w = v.w < 0 ? p.a_zero_row : v.w / p.a_rows_div;
+        return v;
+      };
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      for (int id = blockIdx.x; id < total_tiles && ok; id += gridDim.x) {
+        const Tile t = decode(id);
+        int4 idx = make_int4(0, 0, 0, 0);
+        if (!A_MN) idx = load_idx(static_cast<long long>(t.m0) + 4 * lane);
+        for (int kit = t.kb; kit < t.ke; ++kit) {
+          if (A_MN) idx = load_idx(static_cast<long long>(t.krow0) + kit * BK_E + 4 * (lane & 15));
+          if (!mbar_wait(&bar_empty[stage], phase ^ 1, abort_flag, p.status, kStatusProducerTimeout)) {
+            ok = false;
+            break;
+          }
+          uint8_t* sa = smem + stage * S::kStageBytes;
+          uint8_t* sb = sa + S::kABytes;
+          if (lane == 0) mbar_expect_tx(&bar_full[stage], S::kStageBytes);
+          __syncwarp();
+          const int kcoord = t.krow0 + kit * BK_E;
+          if (!A_MN) {
+            tma_gather4_2d(sa + lane * 512, &p.tmA[0], &bar_full[stage], kit * BK_E, idx.x, idx.y, idx.z, idx.w);
+          } else {
+            const int j = lane >> 4;  // which 64-column chunk of the tile's M extent
+            tma_gather4_2d(sa + j * CH_BYTES + (lane & 15) * 512, &p.tmA[0], &bar_full[stage], t.m0 + j * CH, idx.x,
+                           idx.y, idx.z, idx.w);
+          }
+          if (lane == 0) load_b(sb, &bar_full[stage], t, 0, kcoord);
+          if (++stage == STAGES) {
+            stage = 0;
+            phase ^= 1;
+          }
+        }
+      }
+    } else if (lane == 0) {
       int stage = 0;
       uint32_t phase = 0;
       bool ok = true;
@@ -263,7 +347,6 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_kernel(const __grid_cons
             uint8_t* sb = sa + S::kABytes;
             mbar_expect_tx(&bar_full[stage], S::kStageBytes);
             const int kcoord = t.krow0 + kit * BK_E;  // element (K-major) or row (MN-major) coordinate along K
-            // ---- A ----
             if (!A_MN) {
               tma_load_2d(sa, &p.tmA[s], &bar_full[stage], kcoord, t.m0);
             } else {
@@ -271,30 +354,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_kernel(const __grid_cons
               for (int j = 0; j < kBM / CH; ++j)
                 tma_load_2d(sa + j * CH_BYTES, &p.tmA[s], &bar_full[stage], t.m0 + j * CH, kcoord);
             }
-            // ---- B ----
-            const int grp_rows = (GRP == GRP_M) ? t.grp * p.b_group_rows : 0;
-            if (!B_MN) {
-              if (kSwiglu) {
-                const int nh = t.nt * (BN / 2);
-                tma_load_2d(sb, &p.tmB[s], &bar_full[stage], kcoord, grp_rows + nh);
-                tma_load_2d(sb + (BN / 2) * 128, &p.tmB[s], &bar_full[stage], kcoord, grp_rows + p.half + nh);
-              } else {
-                tma_load_2d(sb, &p.tmB[s], &bar_full[stage], kcoord, grp_rows + t.nt * BN);
-              }
-            } else {
-#pragma unroll
-              for (int j = 0; j < BN / CH; ++j) {
-                constexpr int kHalfChunks = BN / (2 * CH);
-                int ncol;
-                if (kSwiglu) {
-                  const int nh = t.nt * (BN / 2);
-                  ncol = (j < kHalfChunks) ? (nh + j * CH) : (p.half + nh + (j - kHalfChunks) * CH);
-                } else {
-                  ncol = t.nt * BN + j * CH;
-                }
-                tma_load_2d(sb + j * CH_BYTES, &p.tmB[s], &bar_full[stage], ncol, grp_rows + kcoord);
-              }
-            }
+            load_b(sb, &bar_full[stage], t, s, kcoord);
             if (++stage == STAGES) {
               stage = 0;
               phase ^= 1;

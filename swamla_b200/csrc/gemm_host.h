@@ -30,6 +30,14 @@ struct GemmCall {
   long long ldc2 = 0;
   const void* aux = nullptr;     // EPI_SWIGLU_BWD: h1 [rows, 2N] bf16; C is then d_h1 [rows, 2N]
   long long ld_aux = 0;
+  // Gathered A (bf16, nseg == 1, GRP_M with K-major A or GRP_K): A[0] is the SOURCE tensor [a_src_rows, K or M]
+  // and padded row i reads its row a_rows[i * a_rows_stride] / a_rows_div; a negative entry reads row a_zero_row,
+  // which the caller keeps all zero.
+  const int* a_rows = nullptr;
+  int a_rows_stride = 1;
+  int a_rows_div = 1;
+  long long a_src_rows = 0;
+  int a_zero_row = 0;
   int split_k = 1;               // >1 (GRP_NONE, EPI_F32): C is a [split_k, M, N] workspace of partial sums
   // grouping
   long long padded_rows = 0;         // GRP_M / GRP_K: rows of the padded routed layout (upper bound)

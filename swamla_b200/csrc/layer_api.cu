@@ -131,9 +131,30 @@ extern "C" int lmoe_shared_gateup_fwd(const lmoe_shape* s, const void* x, const 
   return launch_gemm(c);
 }
 
-extern "C" int lmoe_grouped_fwd(int64_t P, int E, int L, int F, const void* x_sorted, const void* w_gate_up,
-                                const void* w_down, const int32_t* tile_expert, const int32_t* n_tiles, void* h1,
-                                void* hidden, void* y_sorted, int32_t* status, void* stream) {
+// Gathered A operand of the routed GEMMs: padded row i is row row_index[i * index_stride] / index_div of src_rows.
+struct GatherA {
+  const int32_t* row_index = nullptr;
+  int index_stride = 1;
+  int index_div = 1;
+  long long n_src_rows = 0;
+  long long zero_row = 0;
+};
+static int apply_gather(GemmCall& c, const GatherA* g) {
+  if (!g) return 0;
+  if (!g->row_index || g->index_stride <= 0 || g->index_div <= 0 || g->n_src_rows <= 0 || g->n_src_rows >= (1ll << 31) || g->zero_row < 0 ||
+      g->zero_row >= g->n_src_rows)
+    return LMOE_ERR_ARG;
+  c.a_rows = g->row_index;
+  c.a_rows_stride = g->index_stride;
+  c.a_rows_div = g->index_div;
+  c.a_src_rows = g->n_src_rows;
+  c.a_zero_row = static_cast<int>(g->zero_row);
+  return 0;
+}
+
+static int grouped_fwd_impl(int64_t P, int E, int L, int F, const void* x_sorted, const GatherA* g, const void* w_gate_up,
+                            const void* w_down, const int32_t* tile_expert, const int32_t* n_tiles, void* h1,
+                            void* hidden, void* y_sorted, int32_t* status, void* stream) {
   if (!x_sorted || !w_gate_up || !w_down || !tile_expert || !n_tiles || !h1 || !hidden || !y_sorted) return LMOE_ERR_ARG;
   if (P <= 0 || (P % LMOE_ROW_PAD) != 0 || E <= 0 || (L % 64) != 0 || (F % 64) != 0) return LMOE_ERR_SHAPE;
   // h1 = x_sorted * Wgu[e]  (Wgu stacked [E*L, 2F], N contiguous), hidden = silu(gate) * up
@@ -160,9 +181,10 @@ extern "C" int lmoe_grouped_fwd(int64_t P, int E, int L, int F, const void* x_so
   a.n_m_tiles = n_tiles;
   a.status = status;
   a.stream = static_cast<cudaStream_t>(stream);
+  GemmCall b = a;
+  if (int rc = apply_gather(a, g)) return rc;
   if (int rc = launch_gemm(a)) return rc;
   // y_sorted = hidden * Wd[e]  (Wd stacked [E*F, L], N contiguous)
-  GemmCall b = a;
   b.epi = EPI_BF16;
   b.A[0] = hidden;
   b.lda[0] = F;
@@ -175,6 +197,28 @@ extern "C" int lmoe_grouped_fwd(int64_t P, int E, int L, int F, const void* x_so
   b.C2 = nullptr;
   b.b_group_rows = F;
   return launch_gemm(b);
+}
+
+extern "C" int lmoe_grouped_fwd(int64_t P, int E, int L, int F, const void* x_sorted, const void* w_gate_up,
+                                const void* w_down, const int32_t* tile_expert, const int32_t* n_tiles, void* h1,
+                                void* hidden, void* y_sorted, int32_t* status, void* stream) {
+  return grouped_fwd_impl(P, E, L, F, x_sorted, nullptr, w_gate_up, w_down, tile_expert, n_tiles, h1, hidden, y_sorted,
+                          status, stream);
+}
+
+extern "C" int lmoe_grouped_fwd_gather(int64_t P, int E, int L, int F, const void* src_rows, int64_t n_src_rows,
+                                       const int32_t* row_index, int index_stride, int index_div, int64_t zero_row,
+                                       const void* w_gate_up, const void* w_down, const int32_t* tile_expert,
+                                       const int32_t* n_tiles, void* h1, void* hidden, void* y_sorted, int32_t* status,
+                                       void* stream) {
+  GatherA g;
+  g.row_index = row_index;
+  g.index_stride = index_stride;
+  g.index_div = index_div;
+  g.n_src_rows = n_src_rows;
+  g.zero_row = zero_row;
+  return grouped_fwd_impl(P, E, L, F, src_rows, &g, w_gate_up, w_down, tile_expert, n_tiles, h1, hidden, y_sorted, status,
+                          stream);
 }
 
 extern "C" int lmoe_experts_fwd(const lmoe_shape* s, const void* x_latent, const void* w_gate_up, const void* w_down,
@@ -374,9 +418,10 @@ extern "C" int lmoe_experts_bwd_dgrad(const lmoe_shape* s, const void* d_y_sorte
                                 r->tile_expert, r->n_tiles, d_hidden, d_h1, d_x_sorted, status, stream);
 }
 
-extern "C" int lmoe_grouped_bwd_wgrad(int64_t P, int E, int L, int F, const void* x_sorted, const void* d_h1,
-                                      const void* hidden, const void* d_y_sorted, const int32_t* pad_offsets,
-                                      void* d_w_gate_up, void* d_w_down, int32_t* status, void* stream) {
+static int grouped_bwd_wgrad_impl(int64_t P, int E, int L, int F, const void* x_sorted, const GatherA* g,
+                                  const void* d_h1, const void* hidden, const void* d_y_sorted,
+                                  const int32_t* pad_offsets, void* d_w_gate_up, void* d_w_down, int32_t* status,
+                                  void* stream) {
   if (!x_sorted || !d_h1 || !hidden || !d_y_sorted || !pad_offsets || !d_w_gate_up || !d_w_down) return LMOE_ERR_ARG;
   if (P <= 0 || (P % LMOE_ROW_PAD) != 0 || E <= 0 || (L % 64) != 0 || (F % 64) != 0) return LMOE_ERR_SHAPE;
   // d_Wgu[e][L,2F] = x_sorted[rows_e]^T * d_h1[rows_e]
@@ -399,9 +444,10 @@ extern "C" int lmoe_grouped_bwd_wgrad(int64_t P, int E, int L, int F, const void
   a.pad_offsets = pad_offsets;
   a.status = status;
   a.stream = static_cast<cudaStream_t>(stream);
+  GemmCall b = a;
+  if (int rc = apply_gather(a, g)) return rc;
   if (int rc = launch_gemm(a)) return rc;
   // d_Wd[e][F,L] = hidden[rows_e]^T * d_y_sorted[rows_e]
-  GemmCall b = a;
   b.A[0] = hidden;
   b.lda[0] = F;
   b.B[0] = d_y_sorted;
@@ -412,6 +458,28 @@ extern "C" int lmoe_grouped_bwd_wgrad(int64_t P, int E, int L, int F, const void
   b.ldc = L;
   b.c_group_stride = static_cast<long long>(F) * L;
   return launch_gemm(b);
+}
+
+extern "C" int lmoe_grouped_bwd_wgrad(int64_t P, int E, int L, int F, const void* x_sorted, const void* d_h1,
+                                      const void* hidden, const void* d_y_sorted, const int32_t* pad_offsets,
+                                      void* d_w_gate_up, void* d_w_down, int32_t* status, void* stream) {
+  return grouped_bwd_wgrad_impl(P, E, L, F, x_sorted, nullptr, d_h1, hidden, d_y_sorted, pad_offsets, d_w_gate_up,
+                                d_w_down, status, stream);
+}
+
+extern "C" int lmoe_grouped_bwd_wgrad_gather(int64_t P, int E, int L, int F, const void* src_rows, int64_t n_src_rows,
+                                             const int32_t* row_index, int index_stride, int index_div, int64_t zero_row,
+                                             const void* d_h1, const void* hidden, const void* d_y_sorted,
+                                             const int32_t* pad_offsets, void* d_w_gate_up, void* d_w_down,
+                                             int32_t* status, void* stream) {
+  GatherA g;
+  g.row_index = row_index;
+  g.index_stride = index_stride;
+  g.index_div = index_div;
+  g.n_src_rows = n_src_rows;
+  g.zero_row = zero_row;
+  return grouped_bwd_wgrad_impl(P, E, L, F, src_rows, &g, d_h1, hidden, d_y_sorted, pad_offsets, d_w_gate_up, d_w_down,
+                                status, stream);
 }
 
 extern "C" int lmoe_experts_bwd_wgrad(const lmoe_shape* s, const void* x_sorted, const void* d_h1, const void* hidden,

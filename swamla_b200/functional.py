@@ -26,6 +26,11 @@ DEBUG_FORCE_SEL: Optional[torch.Tensor] = None
 # slower than GEMM + streaming kernel (cfg2: 164 us vs 37 + 90 us for the routed experts).
 import os as _os
 FUSE_SWIGLU_BWD = _os.environ.get("LMOE_FUSE_SWIGLU_BWD", "0") == "1"
+# LMOE_TMA_GATHER=1: the gate_up GEMMs (forward and weight gradient) read the latent rows through TMA gathers
+# (tile::gather4) driven by the routing table, with no gather kernel and no x_sorted buffer (P*L*2 bytes less memory).
+# Off by default: results are bit-identical but four-row gathers of 128-byte rows sustained only about 8 GB/s per SM
+# (cfg2: forward gate_up GEMM 185 us instead of 89 us + 27 us gather kernel, weight gradient 246 us instead of 69 us).
+TMA_GATHER = _os.environ.get("LMOE_TMA_GATHER", "0") == "1"
 
 
 def _stream() -> int:
@@ -131,9 +136,11 @@ class LatentMoEFunction(torch.autograd.Function):
         f32 = dict(dtype=torch.float32, device=dev)
 
         # router + latent down-projection
-        fork = _Fork(dev)
         logits = torch.empty(T, E, **f32)
-        x_latent = torch.empty(T, L, **bf)
+        # one extra row of zeros after the T latent rows: the pad rows of the routed layout gather it
+        x_latent_ext = torch.empty(T + 1, L, **bf)
+        x_latent_ext[T].zero_()
+        x_latent = x_latent_ext[:T]
         _cabi.call("lmoe_xproj_fwd", shape, ptr(xb), ptr(wg), ptr(wdn), ptr(logits), ptr(x_latent), ptr(status), st)
         sel = torch.empty(T, top_k, dtype=torch.int32, device=dev)
         weights = torch.empty(T, top_k, **f32)
@@ -143,26 +150,25 @@ class LatentMoEFunction(torch.autograd.Function):
         route = RouteTables(shape, dev)
         P = route.padded_rows
         ws = torch.empty(max(16, lib.lmoe_route_workspace_bytes(shape)), dtype=torch.uint8, device=dev)
-        x_sorted = torch.empty(P, L, **bf)
+        gather = TMA_GATHER and not fp8 and L % 128 == 0   # whole 128-column tiles of the weight gradient
+        x_sorted = None if (gather and DEBUG_SINK is None) else torch.empty(P, L, **bf)
         h1_s = torch.empty(T, 2 * Fs, **bf)
         act_cat = torch.empty(T, L + Fs, **bf)
         if DEBUG_FORCE_SEL is not None:
             forced = DEBUG_FORCE_SEL.to(device=dev, dtype=torch.int32).contiguous()
             aff = torch.sigmoid(logits).gather(1, forced.long())
             forced_w = (aff / (aff.sum(-1, keepdim=True) + 1e-9)).contiguous()
-        # side stream: top-k, routing tables, gather (latency- and HBM-bound) beside the shared-expert GEMM
-        fork.to_side()
+        # One stream in forward: the routing kernels use static shared memory that does not fit on an SM beside a GEMM
+        # CTA, so on a second stream they would only wait for the shared-expert GEMM to drain.
         _cabi.call("lmoe_gate_topk_fwd", shape, ptr(logits), ptr(bias), float(z_coef), ptr(sel), ptr(weights), ptr(lse),
-                   ptr(z_partial), ptr(z_loss), fork.s)
+                   ptr(z_partial), ptr(z_loss), st)
         if DEBUG_FORCE_SEL is not None:
-            fork.to_main()
             sel, weights = forced, forced_w
-            fork.to_side()
-        _cabi.call("lmoe_route_permute", shape, ptr(sel), route.struct, ptr(ws), ws.numel(), fork.s)
-        _cabi.call("lmoe_gather_rows", ptr(x_latent), ptr(route.row_src), top_k, P, L, ptr(route.n_tiles), ptr(x_sorted),
-                   fork.s)
+        _cabi.call("lmoe_route_permute", shape, ptr(sel), route.struct, ptr(ws), ws.numel(), st)
+        if x_sorted is not None:
+            _cabi.call("lmoe_gather_rows", ptr(x_latent), ptr(route.row_src), top_k, P, L, ptr(route.n_tiles),
+                       ptr(x_sorted), st)
         _cabi.call("lmoe_shared_gateup_fwd", shape, ptr(xb), ptr(wgus), ptr(h1_s), ptr(act_cat), ptr(status), st)
-        fork.to_main()
 
         # routed experts in the padded layout
         fp8_saved = None
@@ -174,8 +180,14 @@ class LatentMoEFunction(torch.autograd.Function):
             h1 = torch.empty(P, 2 * F, **bf)
             hidden = torch.empty(P, F, **bf)
             y_sorted = torch.empty(P, L, **bf)
-            _cabi.call("lmoe_grouped_fwd", P, E, L, F, ptr(x_sorted), ptr(wgu), ptr(wde), ptr(route.tile_expert),
-                       ptr(route.n_tiles), ptr(h1), ptr(hidden), ptr(y_sorted), ptr(status), st)
+            if gather:
+                # the TMA unit gathers the latent rows of every tile (row_src holds t*K + k; pad rows -> the zero row)
+                _cabi.call("lmoe_grouped_fwd_gather", P, E, L, F, ptr(x_latent_ext), T + 1, ptr(route.row_src), 1, top_k, T,
+                           ptr(wgu), ptr(wde), ptr(route.tile_expert), ptr(route.n_tiles), ptr(h1), ptr(hidden),
+                           ptr(y_sorted), ptr(status), st)
+            else:
+                _cabi.call("lmoe_grouped_fwd", P, E, L, F, ptr(x_sorted), ptr(wgu), ptr(wde), ptr(route.tile_expert),
+                           ptr(route.n_tiles), ptr(h1), ptr(hidden), ptr(y_sorted), ptr(status), st)
 
         # weighted combine, up-projection, shared down-projection, add
         y = torch.empty(T, D, **bf)
@@ -194,8 +206,9 @@ class LatentMoEFunction(torch.autograd.Function):
             ctx.save_for_backward(xb, wg, wdn, wup, wgus, wds, none, none, logits, sel, weights, lse, none, h1, none,
                                   y_sorted, act_cat, h1_s)
         else:
-            ctx.save_for_backward(xb, wg, wdn, wup, wgus, wds, wgu, wde, logits, sel, weights, lse, x_sorted, h1, hidden,
-                                  y_sorted, act_cat, h1_s)
+            ctx.save_for_backward(xb, wg, wdn, wup, wgus, wds, wgu, wde, logits, sel, weights, lse,
+                                  x_latent_ext if gather else x_sorted, h1, hidden, y_sorted, act_cat, h1_s)
+        ctx.gather = gather
         ctx.mark_non_differentiable(sel, route.counts)
         if DEBUG_SINK is not None:
             DEBUG_SINK.update(logits=logits, x_latent=x_latent, sel=sel, weights=weights, lse=lse, route=route,
@@ -278,8 +291,13 @@ class LatentMoEFunction(torch.autograd.Function):
             _cabi.call("lmoe_unpermute_sum_bwd", shape, ptr(d_x_sorted), route.struct, ptr(dgrad_cat), fork.s)
             _cabi.call("lmoe_gate_topk_bwd", shape, ptr(logits), ptr(sel), ptr(weights), ptr(d_weights), ptr(lse), ptr(dz),
                        ctx.z_coef, ptr(dgrad_cat), fork.s)
-            _cabi.call("lmoe_grouped_bwd_wgrad", P, E, L, F, ptr(x_sorted), ptr(d_h1), ptr(hidden), ptr(d_y_sorted),
-                       ptr(route.pad_offsets), ptr(d_w_gate_up), ptr(d_w_down_e), ptr(status), st)
+            if ctx.gather:   # x_sorted is the latent rows [T + 1, L] here, gathered by the TMA unit
+                _cabi.call("lmoe_grouped_bwd_wgrad_gather", P, E, L, F, ptr(x_sorted), T + 1, ptr(route.row_src), 1, K, T,
+                           ptr(d_h1), ptr(hidden), ptr(d_y_sorted), ptr(route.pad_offsets), ptr(d_w_gate_up),
+                           ptr(d_w_down_e), ptr(status), st)
+            else:
+                _cabi.call("lmoe_grouped_bwd_wgrad", P, E, L, F, ptr(x_sorted), ptr(d_h1), ptr(hidden), ptr(d_y_sorted),
+                           ptr(route.pad_offsets), ptr(d_w_gate_up), ptr(d_w_down_e), ptr(status), st)
             fork.to_main()
 
         # x side: dx and the three weight gradients that contract with x
