@@ -27,6 +27,36 @@ from ._cabi import Route, ptr
 from .functional import BF, RouteTables, _as_bf16, _stream, make_shape
 
 
+def expert_shard_parameter_names(model: torch.nn.Module) -> List[str]:
+    """Names (as in ``model.named_parameters()``) of the expert-sharded parameters of every expert-parallel layer."""
+    return [n for n, p_ in model.named_parameters() if getattr(p_, "expert_shard", False)]
+
+
+def ddp_ignore_expert_shards(model: torch.nn.Module, average_like_ddp: bool = True) -> List[str]:
+    """Prepare ``model`` for ``DistributedDataParallel`` (the reference wraps the model at ``train.py:944-949``).
+
+    The expert shards are different tensors on every rank and their gradients are already complete on the owner
+    (sums over the tokens of all ranks), so DDP must neither broadcast nor all-reduce them: their names are put into
+    ``model._ddp_params_and_buffers_to_ignore``, which DDP reads at construction.  DDP AVERAGES the replicated
+    parameters' gradients over the G ranks; with ``average_like_ddp`` the shard gradients are divided by G through a
+    gradient hook so that all parameters see the same loss scaling (mean over the global batch).
+    Call it once, before wrapping; returns the ignored names."""
+    names = expert_shard_parameter_names(model)
+    ignored = list(getattr(model, "_ddp_params_and_buffers_to_ignore", []))
+    model._ddp_params_and_buffers_to_ignore = ignored + [n for n in names if n not in ignored]
+    if average_like_ddp:
+        for mod in model.modules():
+            group = getattr(mod, "ep_group", None)
+            if group is None or not hasattr(mod, "gate_up_weight"):
+                continue
+            scale = 1.0 / dist.get_world_size(group)
+            for p_ in (mod.gate_up_weight, mod.down_weight):
+                if not getattr(p_, "_ep_grad_hook", False):
+                    p_.register_hook(lambda g, s=scale: g * s)
+                    p_._ep_grad_hook = True
+    return names
+
+
 def splits_from_counts(counts_all: torch.Tensor, rank: int) -> Tuple[List[int], List[int]]:
     """counts_all[G, E] (rows every source routes to every expert) -> (send_splits, recv_splits) of ``rank``:
     rows it sends to each destination rank and rows it receives from each source rank."""

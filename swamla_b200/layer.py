@@ -37,19 +37,59 @@ class SwiGLUExpert(nn.Module):
 
 class LatentBatchedExperts(nn.Module):
     """Routed expert weights in the reference layout (``models/moe.py:562-600``):
-    ``gate_up_weight`` [E, latent, 2*d_ff] and ``down_weight`` [E, d_ff, latent]."""
+    ``gate_up_weight`` [E, latent, 2*d_ff] and ``down_weight`` [E, d_ff, latent].
 
-    def __init__(self, n_experts: int, latent_dim: int, d_ff: int, bias: bool = False):
+    Under expert parallelism (``ep_group`` of G ranks) the parameters hold this rank's contiguous block of
+    ``n_experts`` = E_global / G experts, while ``state_dict`` keeps the reference's layout: saving gathers the
+    blocks of all ranks into the full [E_global, ...] tensors (a collective: every rank of the group calls
+    ``state_dict()``), loading accepts the full tensors (each rank takes its block) or block-shaped ones.  So a
+    checkpoint written by the reference (``train.py:1470-1506``) loads into any group size and the other way round."""
+
+    def __init__(self, n_experts: int, latent_dim: int, d_ff: int, bias: bool = False, ep_group=None):
         super().__init__()
         if bias:
             raise NotImplementedError("config.bias=True is not supported on this path (no preset uses it)")
         self.n_experts, self.latent_dim, self.d_ff = n_experts, latent_dim, d_ff
+        self.ep_group = ep_group
+        self.ep_size = _ep_size(ep_group)
         self.gate_up_weight = nn.Parameter(torch.empty(n_experts, latent_dim, 2 * d_ff))
         self.down_weight = nn.Parameter(torch.empty(n_experts, d_ff, latent_dim))
         self.register_parameter("gate_up_bias", None)
         self.register_parameter("down_bias", None)
         nn.init.normal_(self.gate_up_weight, mean=0.0, std=0.02)         # moe.py:599-600
         nn.init.normal_(self.down_weight, mean=0.0, std=0.02)
+        if self.ep_size > 1:
+            # the owner's gradient is already the sum over the tokens of ALL ranks: a data-parallel wrapper must
+            # not reduce these parameters again (see ep.ddp_ignore_expert_shards)
+            self.gate_up_weight.expert_shard = True
+            self.down_weight.expert_shard = True
+
+    def _ep_rank(self) -> int:
+        import torch.distributed as dist
+        return dist.get_rank(self.ep_group)
+
+    def _save_to_state_dict(self, destination, prefix, keep_vars):
+        super()._save_to_state_dict(destination, prefix, keep_vars)
+        if self.ep_size == 1:
+            return
+        import torch.distributed as dist
+        for name in ("gate_up_weight", "down_weight"):
+            shard = getattr(self, name).detach().contiguous()
+            full = torch.empty((self.ep_size * shard.shape[0],) + tuple(shard.shape[1:]), dtype=shard.dtype,
+                               device=shard.device)
+            dist.all_gather_into_tensor(full, shard, group=self.ep_group)   # rank order = expert order
+            destination[prefix + name] = full
+
+    def _load_from_state_dict(self, state_dict, prefix, local_metadata, strict, missing_keys, unexpected_keys,
+                              error_msgs):
+        if self.ep_size > 1:
+            lo = self._ep_rank() * self.n_experts
+            for name in ("gate_up_weight", "down_weight"):
+                t = state_dict.get(prefix + name)
+                if t is not None and t.shape[0] == self.ep_size * self.n_experts:
+                    state_dict[prefix + name] = t[lo:lo + self.n_experts]     # a view; the caller's dict is a copy
+        super()._load_from_state_dict(state_dict, prefix, local_metadata, strict, missing_keys, unexpected_keys,
+                                      error_msgs)
 
 
 class AuxLossFreeRouter(nn.Module):
@@ -163,7 +203,8 @@ class LatentMoELayer(nn.Module):
         self._ep_bufs = None
         if n_experts % self.ep_size:
             raise ValueError("the expert count must be divisible by the expert-parallel group size")
-        self.experts = LatentBatchedExperts(n_experts // self.ep_size, latent_dim, latent_expert_dim, bias=False)
+        self.experts = LatentBatchedExperts(n_experts // self.ep_size, latent_dim, latent_expert_dim, bias=False,
+                                            ep_group=self.ep_group)
         self.router = AuxLossFreeRouter(d_model=d_model, n_experts=n_experts, top_k=n_activated, z_loss_coef=z_loss_coef)
         # `config.moe_fp8 = True`: routed expert GEMMs in e4m3 with per-tensor dynamic scaling
         self.fp8_experts = bool(getattr(config, "moe_fp8", False))

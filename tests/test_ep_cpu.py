@@ -82,3 +82,57 @@ def test_regroup_tables_contract():
     assert recv_pos[:130].tolist() == list(range(130)) and recv_pos[130].item() == 256
     assert recv_pos[131:].tolist() == list(range(130, 135))
     assert (row_src[135:256] == -1).all() and row_src[256].item() == 130 and (row_src[257:] == -1).all()
+
+
+def _ckpt_worker(rank, world, port, tmpdir):
+    sys.path.insert(0, ROOT)
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        from oracle import inputs
+        from swamla_b200.ep import ddp_ignore_expert_shards, expert_shard_parameter_names
+        from swamla_b200.layer import LatentMoELayer
+        w = inputs.WORKLOADS["tiny_ragged"]
+        params, buffers, _, _ = inputs.make_inputs(w, seed=0)
+        full_state = {**params, **buffers}                                     # the reference's state_dict layout
+        cfg = w.config()
+        cfg.ep_group = dist.group.WORLD
+        layer = LatentMoELayer(cfg)
+        El = w.E // world
+        assert layer.experts.gate_up_weight.shape[0] == El
+        # a reference checkpoint (all experts) loads into the sharded layer: every rank takes its block
+        layer.load_state_dict(full_state, strict=True)
+        for name in ("gate_up_weight", "down_weight"):
+            assert torch.equal(getattr(layer.experts, name), params["experts." + name][rank * El:(rank + 1) * El])
+        assert full_state["experts.gate_up_weight"].shape[0] == w.E              # the caller's dict is untouched
+        # saving gathers the blocks back into the reference layout, identical on every rank
+        saved = layer.state_dict()
+        assert set(saved) == set(full_state)
+        for k, v in full_state.items():
+            assert saved[k].shape == v.shape and torch.equal(saved[k].to(v.dtype), v), k
+        # block-shaped tensors load as well (a checkpoint written per rank)
+        shard_state = dict(full_state)
+        for name in ("experts.gate_up_weight", "experts.down_weight"):
+            shard_state[name] = full_state[name][rank * El:(rank + 1) * El] + 1.0
+        layer.load_state_dict(shard_state, strict=True)
+        assert torch.equal(layer.experts.down_weight, shard_state["experts.down_weight"])
+        # DDP: the shards are ignored, their gradients scaled like DDP's average
+        model = torch.nn.Sequential(layer)
+        names = ddp_ignore_expert_shards(model)
+        assert names == ["0.experts.gate_up_weight", "0.experts.down_weight"] == expert_shard_parameter_names(model)
+        assert model._ddp_params_and_buffers_to_ignore == names
+        ddp = torch.nn.parallel.DistributedDataParallel(model)
+        reduced = {n for n, p_ in ddp.module.named_parameters()} - set(ddp.parameters_to_ignore)
+        assert "0.experts.gate_up_weight" not in reduced and "0.router.gate.weight" in reduced
+        layer.experts.gate_up_weight.grad = None
+        (layer.experts.gate_up_weight.sum() * 3.0).backward()
+        assert torch.allclose(layer.experts.gate_up_weight.grad, torch.full_like(layer.experts.gate_up_weight, 3.0 / world))
+        open(os.path.join(tmpdir, f"ok{rank}"), "w").write("ok")
+    finally:
+        dist.destroy_process_group()
+
+
+def test_expert_shards_keep_the_reference_state_dict_layout_and_stay_out_of_ddp(tmp_path):
+    port = 29500 + ((os.getpid() + 211) % 500)
+    mp.spawn(_ckpt_worker, args=(2, port, str(tmp_path)), nprocs=2, join=True)
+    assert (tmp_path / "ok0").exists() and (tmp_path / "ok1").exists()
