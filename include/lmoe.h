@@ -262,6 +262,18 @@ int lmoe_gather_rows(const void* src, const int32_t* index, int div, int64_t row
  * order; out has row stride ld_out elements.  (models/moe.py:837,778-782 as a primitive.) */
 int lmoe_combine_rows(const void* rows_in, const int32_t* index, const float* weights, int T, int K, int L, void* out,
                       int64_t ld_out, void* stream);
+/* out[t] = addend[t] + sum_k weights[t*K+k] * rows_in[index[t*K+k]]  (weights == NULL: plain sum); fp32 accumulation in
+ * slot order, bf16 out.  Row strides ld_addend / ld_out in elements.  The add of the routed sum onto another branch's
+ * result: models/moe.py:366 (MoELayer: shared_output + routed_output) and its adjoint on the x side. */
+int lmoe_combine_rows_add(const void* rows_in, const int32_t* index, const float* weights, const void* addend,
+                          int64_t ld_addend, int T, int K, int L, void* out, int64_t ld_out, void* stream);
+
+/* Dense SwiGLU up-projection: h1[M, 2H] = A[M, K] * W[2H, K]^T (gate = first H outputs), hidden[M, H] = silu(gate) * up,
+ * both bf16, SwiGLU in the GEMM epilogue.  H a multiple of 32.  Replaces the first half of SwiGLUExpert.forward
+ * (models/moe.py:63-67) for any width. */
+int lmoe_gemm_swiglu_bf16(int M, int H, int K, const void* A, int64_t lda, const void* W, int64_t ldw, void* h1,
+                          int64_t ld_h1, void* hidden, int64_t ld_hidden, int32_t* status, void* stream);
+
 /* Adjoint of lmoe_combine_rows over `rows` rows: flat = row_to_flat[r] (t = flat / K);
  * d_y_rows[r] = weights[flat] * d_routed[t], d_weights[flat] = <d_routed[t], y_rows[r]>; zeros where flat < 0. */
 int lmoe_combine_bwd_rows(const void* d_routed, const void* y_rows, const float* weights, const int32_t* row_to_flat,

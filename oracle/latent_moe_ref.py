@@ -88,6 +88,10 @@ def layer_forward(params: Dict[str, torch.Tensor], buffers: Dict[str, torch.Tens
                   use_torch_topk: bool = False) -> Dict[str, torch.Tensor]:
     """models/moe.py:702-784,786-839 (LatentMoELayer.forward and helpers).
 
+    Without ``down_proj.weight`` / ``up_proj.weight`` in ``params`` this is the non-latent ``MoELayer``
+    (models/moe.py:344-372 forward, 437-482 grouped path, 484-537 expert GEMMs): the experts read x itself and
+    their weighted sum is added to the shared expert's output directly.
+
     Returns every intermediate the kernels are checked against.
     ``sel_override`` forces the routing decision (used to compare the float
     path on identical routing when a near-tie flips a selection).
@@ -117,7 +121,8 @@ def layer_forward(params: Dict[str, torch.Tensor], buffers: Dict[str, torch.Tens
         weights = sa / (sa.sum(-1, keepdim=True) + 1e-9)
 
     # 3. latent down-projection                                                # moe.py:722
-    x_latent = x_flat @ params["down_proj.weight"].t()
+    latent = "down_proj.weight" in params
+    x_latent = x_flat @ params["down_proj.weight"].t() if latent else x_flat   # MoELayer: moe.py:361
 
     # 4. grouped experts                                                       # moe.py:736-784
     counts, offsets, perm = route_permute(sel, E)                              # moe.py:757
@@ -136,7 +141,7 @@ def layer_forward(params: Dict[str, torch.Tensor], buffers: Dict[str, torch.Tens
     routed = y_exp.view(T, top_k, L).sum(dim=1)                                # moe.py:782
 
     # 5./6. up-projection and final add (dropout p=0)                          # moe.py:728-734
-    routed_out = routed @ params["up_proj.weight"].t()
+    routed_out = routed @ params["up_proj.weight"].t() if latent else routed   # MoELayer: moe.py:366
     y = (shared + routed_out).view(B, S, D)
     return dict(y=y, aux_loss=z_loss, logits=logits, sel=sel, weights=weights, counts=counts,
                 offsets=offsets, perm=perm, x_latent=x_latent, x_sorted=x_sorted, h1=h1, hidden=hidden,

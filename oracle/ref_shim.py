@@ -1,4 +1,4 @@
-"""Runs the UNMODIFIED reference ``LatentMoELayer`` on CPU (TEST INFRASTRUCTURE).
+"""Runs the UNMODIFIED reference ``LatentMoELayer`` / ``MoELayer`` on CPU (TEST INFRASTRUCTURE).
 
 The reference module imports its two device-only entry points from
 ``moe_triton`` (``models/moe.py:21-29``); both need a GPU.  After import they
@@ -65,9 +65,11 @@ def load_reference_moe():
 
 
 def build_reference_layer(workload, params, buffers):
-    """Reference ``LatentMoELayer(config)`` loaded with the given state."""
+    """Reference ``LatentMoELayer(config)`` (or ``MoELayer(config)`` for a non-latent workload) loaded with the
+    given state, built through the reference's own factory (``models/moe.py:869-882``)."""
     moe = load_reference_moe()
-    layer = moe.LatentMoELayer(workload.config())
+    layer = moe.create_moe_layer(workload.config(), use_latent=getattr(workload, "latent", True))
+    assert type(layer).__name__ == ("LatentMoELayer" if getattr(workload, "latent", True) else "MoELayer")
     state = dict(params)
     state.update(buffers)
     missing, unexpected = layer.load_state_dict(state, strict=True)

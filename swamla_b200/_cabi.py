@@ -78,6 +78,8 @@ SIGNATURES = {
     "lmoe_ep_dispatch": (c_int, [P, P, P, P, P, c_int64, c_int, c_int, c_int, c_int, c_int64, P, P, P]),
     "lmoe_ep_dispatch_bwd": (c_int, [P, P, P, P, P, P, P, c_int64, c_int, c_int, c_int, c_int, c_int64, P, P, P, P]),
     "lmoe_ep_return": (c_int, [P, P, P, P, P, P, P, c_int, c_int, c_int, c_int, c_int64, P, P]),
+    "lmoe_combine_rows_add": (c_int, [P, P, P, P, c_int64, c_int, c_int, c_int, P, c_int64, P]),
+    "lmoe_gemm_swiglu_bf16": (c_int, [c_int, c_int, c_int, P, c_int64, P, c_int64, P, c_int64, P, c_int64, P, P]),
     "lmoe_grouped_fwd_gather": (c_int, [c_int64, c_int, c_int, c_int, P, c_int64, P, c_int, c_int, c_int64, P, P, P, P, P,
                                          P, P, P, P]),
     "lmoe_grouped_bwd_wgrad_gather": (c_int, [c_int64, c_int, c_int, c_int, P, c_int64, P, c_int, c_int, c_int64, P, P, P,

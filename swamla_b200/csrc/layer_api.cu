@@ -131,6 +131,17 @@ extern "C" int lmoe_shared_gateup_fwd(const lmoe_shape* s, const void* x, const 
   return launch_gemm(c);
 }
 
+extern "C" int lmoe_gemm_swiglu_bf16(int M, int H, int K, const void* A, int64_t lda, const void* W, int64_t ldw,
+                                     void* h1, int64_t ld_h1, void* hidden, int64_t ld_hidden, int32_t* status,
+                                     void* stream) {
+  if (!A || !W || !h1 || !hidden || M <= 0 || H <= 0 || K <= 0) return LMOE_ERR_ARG;
+  if ((H % 32) != 0 || ld_h1 < 2ll * H || ld_hidden < H) return LMOE_ERR_SHAPE;
+  GemmCall c = dense(A, lda, 0, W, ldw, 0, M, H, K, h1, ld_h1, EPI_SWIGLU, status, stream);
+  c.C2 = hidden;
+  c.ldc2 = ld_hidden;
+  return launch_gemm(c);
+}
+
 // Gathered A operand of the routed GEMMs: padded row i is row row_index[i * index_stride] / index_div of src_rows.
 struct GatherA {
   const int32_t* row_index = nullptr;

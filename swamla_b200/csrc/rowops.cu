@@ -46,15 +46,17 @@ gather_rows_kernel(const uint4* __restrict__ src, const int* __restrict__ row_sr
   }
 }
 
-// out[t] = sum_k w[t,k] * y[pos[t*K+k]]   (w == nullptr: plain sum).  Slot order k = 0..K-1, fp32.
+// out[t] = (addend[t] +) sum_k w[t,k] * y[pos[t*K+k]]   (w == nullptr: plain sum).  Slot order k = 0..K-1, fp32.
 __global__ void __launch_bounds__(kRowWarps * 32)
 combine_kernel(const uint4* __restrict__ y, const int* __restrict__ pos, const float* __restrict__ w, int T, int K,
-               int vec_per_row, uint4* __restrict__ out, long long out_ld_vec) {
+               int vec_per_row, uint4* __restrict__ out, long long out_ld_vec, const uint4* __restrict__ addend,
+               long long addend_ld_vec) {
   const int lane = threadIdx.x & 31;
   for (long long t = static_cast<long long>(blockIdx.x) * kRowWarps + (threadIdx.x >> 5); t < T;
        t += static_cast<long long>(gridDim.x) * kRowWarps) {
     for (int v = lane; v < vec_per_row; v += 32) {
       float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+      if (addend) unpack8(addend[t * addend_ld_vec + v], acc);
       for (int k = 0; k < K; ++k) {
         const long long i = t * K + k;
         const float wk = w ? w[i] : 1.0f;
@@ -215,7 +217,8 @@ int combine_rows(const void* y_sorted, const int* pos, const float* w, int T, in
                  cudaStream_t st) {
   if ((L & 7) != 0 || (out_ld & 7) != 0) return LMOE_ERR_SHAPE;
   combine_kernel<<<grid_for(T, kRowWarps), kRowWarps * 32, 0, st>>>(static_cast<const uint4*>(y_sorted), pos, w, T, K,
-                                                                    L / 8, static_cast<uint4*>(out), out_ld / 8);
+                                                                    L / 8, static_cast<uint4*>(out), out_ld / 8, nullptr,
+                                                                    0);
   return last_error();
 }
 
@@ -293,6 +296,16 @@ extern "C" int lmoe_combine_rows(const void* rows_in, const int32_t* index, cons
                                  void* out, int64_t ld_out, void* stream) {
   if (!rows_in || !index || !out || T <= 0 || K <= 0) return LMOE_ERR_ARG;
   return combine_rows(rows_in, index, weights, T, K, L, out, ld_out, static_cast<cudaStream_t>(stream));
+}
+
+extern "C" int lmoe_combine_rows_add(const void* rows_in, const int32_t* index, const float* weights, const void* addend,
+                                     int64_t ld_addend, int T, int K, int L, void* out, int64_t ld_out, void* stream) {
+  if (!rows_in || !index || !addend || !out || T <= 0 || K <= 0) return LMOE_ERR_ARG;
+  if ((L & 7) != 0 || (ld_out & 7) != 0 || (ld_addend & 7) != 0 || ld_out < L || ld_addend < L) return LMOE_ERR_SHAPE;
+  combine_kernel<<<grid_for(T, kRowWarps), kRowWarps * 32, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const uint4*>(rows_in), index, weights, T, K, L / 8, static_cast<uint4*>(out), ld_out / 8,
+      static_cast<const uint4*>(addend), ld_addend / 8);
+  return last_error();
 }
 
 extern "C" int lmoe_combine_bwd_rows(const void* d_routed, const void* y_rows, const float* weights,

@@ -1,4 +1,4 @@
-"""Drop-in ``LatentMoELayer`` for Orolol/swamla (``models/moe.py:603-866``).
+"""Drop-in ``LatentMoELayer`` (and the non-latent ``MoELayer``) for Orolol/swamla (``models/moe.py:603-866``, ``294-559``).
 
 Same constructor (one ``config`` object read with ``getattr``), same ``forward(x)`` signature,
 attributes, buffers and ``state_dict`` keys as the reference module, so it replaces it behind
@@ -263,8 +263,81 @@ class LatentMoELayer(nn.Module):
         return self.router.get_load_balance_stats()
 
 
+class BatchedExperts(nn.Module):
+    """Routed expert weights of the non-latent layer in the reference layout (``models/moe.py:72-109``):
+    ``gate_up_weight`` [E, d_model, 2*d_ff] and ``down_weight`` [E, d_ff, d_model]."""
+
+    def __init__(self, n_experts: int, d_model: int, d_ff: int, bias: bool = False):
+        super().__init__()
+        if bias:
+            raise NotImplementedError("config.bias=True is not supported on this path (no preset uses it)")
+        self.n_experts, self.d_model, self.d_ff = n_experts, d_model, d_ff
+        self.gate_up_weight = nn.Parameter(torch.empty(n_experts, d_model, 2 * d_ff))
+        self.down_weight = nn.Parameter(torch.empty(n_experts, d_ff, d_model))
+        self.register_parameter("gate_up_bias", None)
+        self.register_parameter("down_bias", None)
+        nn.init.normal_(self.gate_up_weight, mean=0.0, std=0.02)         # moe.py:106-109
+        nn.init.normal_(self.down_weight, mean=0.0, std=0.02)
+
+
+class MoELayer(nn.Module):
+    """The non-latent mixture-of-experts layer (``models/moe.py:294-559``): same constructor, ``forward(x)``, attributes
+    and ``state_dict`` keys as the reference class; the experts work at the model width on the kernels of
+    ``liblmoe.so`` (``functional_moe.py``).  Single GPU, bf16."""
+
+    def __init__(self, config):
+        super().__init__()
+        self.config = config
+        d_model = config.n_embd
+        n_experts = getattr(config, "n_experts", 32)
+        n_shared = getattr(config, "n_shared_experts", 1)
+        n_activated = getattr(config, "n_activated", 3)
+        expert_dim = getattr(config, "expert_dim", d_model)
+        bias = getattr(config, "bias", False)
+        z_loss_coef = getattr(config, "router_z_loss_coef", 0.001)
+        if bias:
+            raise NotImplementedError("config.bias=True is not supported on this path (no preset uses it)")
+        if n_shared != 1:
+            raise NotImplementedError("this path implements n_shared_experts == 1 (every preset uses 1)")
+        if getattr(config, "ep_group", None) is not None or getattr(config, "moe_fp8", False):
+            raise NotImplementedError("expert parallelism and FP8 are provided for the latent layer only")
+        self.n_experts, self.n_shared, self.n_activated = n_experts, n_shared, n_activated
+        self.d_model, self.expert_dim = d_model, expert_dim
+        self.shared_experts = nn.ModuleList([SwiGLUExpert(d_model, expert_dim, bias=False) for _ in range(n_shared)])
+        self.experts = BatchedExperts(n_experts, d_model, expert_dim, bias=False)
+        self.router = AuxLossFreeRouter(d_model=d_model, n_experts=n_experts, top_k=n_activated, z_loss_coef=z_loss_coef)
+        self.dropout = nn.Dropout(getattr(config, "dropout", 0.0))
+        self.aux_loss = torch.tensor(0.0)
+        if d_model % 64 or expert_dim % 64 or n_experts % 8:
+            raise ValueError("kernel constraints: n_embd and expert_dim multiples of 64, expert count a multiple of 8")
+        if n_experts > 256 or n_activated > 32:
+            raise ValueError("kernel constraints: at most 256 routed experts and top-32")
+
+    def forward(self, x: torch.Tensor) -> torch.Tensor:
+        from .functional_moe import moe
+        batch_size, seq_len, d_model = x.shape
+        x_flat = x.reshape(-1, d_model)
+        shared = self.shared_experts[0]
+        y, z_loss, sel, counts = moe(x_flat, self.router.gate.weight, shared.gate_up_proj.weight,
+                                     shared.down_proj.weight, self.experts.gate_up_weight, self.experts.down_weight,
+                                     self.router.expert_bias, self.n_activated, self.router.z_loss_coef)
+        self.aux_loss = z_loss                                            # moe.py:358
+        if self.training:                                                 # moe.py:237-240
+            self.router._last_selected_experts = sel
+            self.router._last_counts = counts
+            self.router._last_num_tokens = x_flat.shape[0]
+        y = self.dropout(y)                                               # moe.py:367
+        return y.view(batch_size, seq_len, d_model)
+
+    def get_aux_loss(self) -> torch.Tensor:
+        return self.aux_loss
+
+    def get_load_balance_stats(self) -> dict:
+        return self.router.get_load_balance_stats()
+
+
 def create_moe_layer(config, use_latent: bool = False):
-    """``models/moe.py:869-882``.  Only the latent branch is provided by this package."""
+    """``models/moe.py:869-882``: the latent layer when asked for, else the non-latent one."""
     if use_latent or getattr(config, "use_latent_moe", False):
         return LatentMoELayer(config)
-    raise NotImplementedError("the non-latent MoELayer is outside this package; use the reference's")
+    return MoELayer(config)

@@ -34,19 +34,20 @@ class Workload:
     zipf_beta: float = 0.25
     uniform_gate: bool = False   # router gate ~ U(-1/sqrt(D), 1/sqrt(D))
     router_z_loss_coef: float = 0.001
+    latent: bool = True          # False: the non-latent MoELayer (models/moe.py:294-559): experts work at width D
     extra: dict = field(default_factory=dict)
 
     # ---- derived sizes, following models/moe.py:630-685 ----
     @property
     def D(self) -> int: return self.n_embd
     @property
-    def L(self) -> int: return self.n_embd // self.latent_ratio
+    def L(self) -> int: return self.n_embd // self.latent_ratio if self.latent else self.n_embd
     @property
-    def E(self) -> int: return self.n_experts * self.latent_ratio
+    def E(self) -> int: return self.n_experts * self.latent_ratio if self.latent else self.n_experts
     @property
-    def K(self) -> int: return self.n_activated * self.latent_ratio
+    def K(self) -> int: return self.n_activated * self.latent_ratio if self.latent else self.n_activated
     @property
-    def F(self) -> int: return self.expert_dim // self.latent_ratio
+    def F(self) -> int: return self.expert_dim // self.latent_ratio if self.latent else self.expert_dim
     @property
     def Fs(self) -> int: return self.expert_dim
     @property
@@ -58,12 +59,14 @@ class Workload:
             n_embd=self.n_embd, n_experts=self.n_experts, n_activated=self.n_activated,
             n_shared_experts=self.n_shared_experts, latent_ratio=self.latent_ratio,
             expert_dim=self.expert_dim, bias=False, dropout=0.0,
-            router_z_loss_coef=self.router_z_loss_coef, use_latent_moe=True,
+            router_z_loss_coef=self.router_z_loss_coef, use_latent_moe=self.latent,
         )
 
     def flops_fwd_per_token(self) -> int:
         """GEMM FLOPs only: router + down + routed + up + shared."""
         D, L, E, K, F, Fs = self.D, self.L, self.E, self.K, self.F, self.Fs
+        if not self.latent:
+            return 2 * D * E + 6 * K * D * F + 6 * self.n_shared_experts * D * Fs
         return 2 * D * E + 2 * D * L + 6 * K * L * F + 2 * L * D + 6 * self.n_shared_experts * D * Fs
 
 
@@ -81,12 +84,18 @@ WORKLOADS: Dict[str, Workload] = {
     "cfg3": Workload("cfg3", expert_dim=3072, batch=32, seq=2048, dtype="bf16", zipf_s=1.2),
     "cfg4": Workload("cfg4", batch=64, seq=2048, dtype="fp8"),
     "cfg5": Workload("cfg5", n_experts=64, n_activated=4, batch=16, seq=2048, dtype="bf16", uniform_gate=True),
+    # the non-latent MoELayer (the other branch of create_moe_layer)
+    "tiny_moe": Workload("tiny_moe", n_embd=256, n_experts=8, n_activated=2, expert_dim=128, batch=2, seq=96, latent=False),
+    "tiny_moe_ragged": Workload("tiny_moe_ragged", n_embd=256, n_experts=16, n_activated=3, expert_dim=128, batch=1, seq=131,
+                                latent=False),
+    "moe_1b": Workload("moe_1b", n_embd=1024, n_experts=32, n_activated=3, expert_dim=1024, batch=2, seq=2048,
+                       dtype="bf16", latent=False),
 }
 
 
 def param_shapes(w: Workload) -> Dict[str, tuple]:
     """state_dict key -> shape, in the reference's registration order."""
-    shapes = {
+    shapes = {} if not w.latent else {
         "down_proj.weight": (w.L, w.D),
         "up_proj.weight": (w.D, w.L),
     }

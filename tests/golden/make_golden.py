@@ -1,5 +1,5 @@
 """Generates the golden fixtures in this directory by running the UNMODIFIED
-reference module (models/moe.py: LatentMoELayer) on CPU in fp32 through
+reference module (models/moe.py: LatentMoELayer, and MoELayer for the tiny_moe* fixtures) on CPU in fp32 through
 oracle/ref_shim.py.  Needs the reference source tree; run from the repo root:
 
     python tests/golden/make_golden.py
@@ -59,3 +59,5 @@ if __name__ == "__main__":
     make("tiny", True)
     make("tiny_ragged", True)
     make("cfg1", False)
+    make("tiny_moe", True)           # the non-latent MoELayer (models/moe.py:294-559)
+    make("tiny_moe_ragged", True)

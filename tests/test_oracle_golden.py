@@ -13,7 +13,7 @@ def _check_digest(t: torch.Tensor, d: dict, rtol=1e-5, atol=1e-6):
     assert abs(flat.double().pow(2).sum().sqrt().item() - d["l2"]) <= rtol * max(d["l2"], 1e-12) + atol
 
 
-@pytest.mark.parametrize("name", ["tiny", "tiny_ragged", "cfg1"])
+@pytest.mark.parametrize("name", ["tiny", "tiny_ragged", "cfg1", "tiny_moe", "tiny_moe_ragged"])
 def test_oracle_matches_reference_fixture(name):
     fx = torch.load(golden_path(name), weights_only=False)
     w = inputs.WORKLOADS[name]
@@ -82,8 +82,9 @@ def test_grouped_gemm_matches_dense_masked_einsum():
 
 
 @pytest.mark.skipif(not ref_shim.available(), reason="reference source tree not present")
-def test_oracle_matches_live_reference_module():
-    w = inputs.WORKLOADS["tiny"]
+@pytest.mark.parametrize("name", ["tiny", "tiny_moe"])
+def test_oracle_matches_live_reference_module(name):
+    w = inputs.WORKLOADS[name]
     params, buffers, x, dy = inputs.make_inputs(w, seed=7)
     ro, rg, _ = ref_shim.run_reference(w, params, buffers, x, dy, aux_grad=0.5)
     o, g = R.layer_forward_backward(params, buffers, x, dy, w.K, aux_grad=0.5)
