@@ -381,6 +381,21 @@ int lmoe_grouped_rows_fp8(int64_t P, int E, int K, int N, const void* aq, const 
 int lmoe_grouped_wgrad_fp8(int64_t P, int E, int M, int N, const void* aq, const void* bq, const float* deq_a,
                            const float* deq_b, const int32_t* pad_offsets, void* out, int32_t* status, void* stream);
 
+/* The steps either side of the layer in the reference's block, x_out = x + ffn(ffn_norm(x)) (models/mla_block.py:83-85,
+ * 159), as fused row kernels: RMSNorm (models/normalization.py:25-39; fp32 arithmetic on bf16 rows, one read and one
+ * write instead of the five element-wise passes of the eager module), the residual add, and ONE backward kernel for the
+ * adjoint of the norm plus the residual branch:
+ *   lmoe_rmsnorm_fwd   xn[T,D] = weight * x * rstd,  rstd[t] = rsqrt(mean(x[t]^2) + eps)  (x, xn bf16; weight, rstd fp32)
+ *   lmoe_add_bf16      out = a + b over n bf16 elements (n % 8 == 0)
+ *   lmoe_rmsnorm_bwd   dx = rstd * (g - x * rstd^2 * mean(g * x)) + d_residual (nullable), g = d_xn * weight;
+ *                      d_weight[D] fp32 = sum_t d_xn * x * rstd, summed in a fixed order (deterministic)
+ * D a multiple of 8, D <= 2048.  workspace: lmoe_rmsnorm_workspace_bytes(D). */
+size_t lmoe_rmsnorm_workspace_bytes(int D);
+int lmoe_rmsnorm_fwd(const void* x, const float* weight, float eps, int64_t T, int D, void* xn, float* rstd, void* stream);
+int lmoe_add_bf16(const void* a, const void* b, void* out, int64_t n, void* stream);
+int lmoe_rmsnorm_bwd(const void* x, const float* weight, const float* rstd, const void* d_xn, const void* d_residual,
+                     int64_t T, int D, void* dx, float* d_weight, void* workspace, size_t workspace_bytes, void* stream);
+
 /* ---- router bias update (after backward) ----
  * load = histogram(sel) (= counts); bias -= gamma * sign(load - T*K/E); history = .99 history + .01 load.
  * Replaces models/moe.py:254-275. */

@@ -95,6 +95,10 @@ SIGNATURES = {
     "lmoe_grouped_gateup_fp8": (c_int, [c_int64, c_int, c_int, c_int, P, P, P, P, P, P, P, P, P, P]),
     "lmoe_grouped_rows_fp8": (c_int, [c_int64, c_int, c_int, c_int, P, P, c_int, P, P, P, P, P, P, P]),
     "lmoe_grouped_wgrad_fp8": (c_int, [c_int64, c_int, c_int, c_int, P, P, P, P, P, P, P, P]),
+    "lmoe_rmsnorm_workspace_bytes": (c_size_t, [c_int]),
+    "lmoe_rmsnorm_fwd": (c_int, [P, P, c_float, c_int64, c_int, P, P, P]),
+    "lmoe_add_bf16": (c_int, [P, P, P, c_int64, P]),
+    "lmoe_rmsnorm_bwd": (c_int, [P, P, P, P, P, c_int64, c_int, P, P, P, c_size_t, P]),
     "lmoe_router_bias_update": (c_int, [SP, P, c_float, P, P, P]),
     "lmoe_cast_f32_to_bf16": (c_int, [P, P, c_int64, P]),
     "lmoe_cast_bf16_to_f32": (c_int, [P, P, c_int64, P]),

@@ -53,6 +53,29 @@ def make(name: str, backward: bool):
     print(name, os.path.getsize(path), "bytes")
 
 
+def make_rmsnorm():
+    """Reference RMSNorm (models/normalization.py:13-39) forward and backward in fp32 on seeded inputs."""
+    models_dir = os.path.join(ref_shim.REFERENCE_ROOT, "models")
+    if models_dir not in sys.path:
+        sys.path.insert(0, models_dir)
+    from normalization import RMSNorm  # the reference class, unmodified
+    g = torch.Generator().manual_seed(11)
+    T, D = 37, 256
+    x = torch.randn(T, D, generator=g).requires_grad_(True)
+    w = (1.0 + 0.1 * torch.randn(D, generator=g))
+    dy = torch.randn(T, D, generator=g)
+    norm = RMSNorm(D, eps=1e-6)
+    with torch.no_grad():
+        norm.weight.copy_(w)
+    y = norm(x)
+    (y * dy).sum().backward()
+    fx = dict(seed=11, T=T, D=D, eps=1e-6, y=y.detach().clone(), dx=x.grad.clone(), dw=norm.weight.grad.clone(),
+              x_l2=x.detach().double().pow(2).sum().sqrt().item())
+    path = os.path.join(HERE, "rmsnorm.pt")
+    torch.save(fx, path)
+    print("rmsnorm", os.path.getsize(path), "bytes")
+
+
 if __name__ == "__main__":
     if not ref_shim.available():
         sys.exit("reference tree not found; fixtures can only be regenerated where it is present")
@@ -61,3 +84,4 @@ if __name__ == "__main__":
     make("cfg1", False)
     make("tiny_moe", True)           # the non-latent MoELayer (models/moe.py:294-559)
     make("tiny_moe_ragged", True)
+    make_rmsnorm()
