@@ -19,7 +19,10 @@ import sys
 
 import torch
 
-REFERENCE_ROOT = os.environ.get("SWAMLA_REFERENCE_ROOT", "/root/reference")
+# the reference checkout: $SWAMLA_REFERENCE_ROOT, else a directory "reference" beside this repository
+REFERENCE_ROOT = os.environ.get(
+    "SWAMLA_REFERENCE_ROOT",
+    os.path.join(os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__)))), "reference"))
 
 
 def available() -> bool:
