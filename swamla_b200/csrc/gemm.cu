@@ -10,6 +10,7 @@
 #include "../../include/lmoe.h"
 #include "counters.h"
 #include "gemm.cuh"
+#include "gemm_pair.cuh"
 #include "gemm_host.h"
 
 namespace lmoe {
@@ -163,6 +164,126 @@ static int dispatch(const GemmCall& c, int bn, const GemmParams& p, int grid, cu
   }
 }
 
+// ---------------------------------------------------------------- CTA-pair kernel (dense GEMMs)
+// LMOE_PAIR_GEMM=1: dense bf16 GEMMs with at least 256 rows and 256 columns run on CTA pairs (gemm_pair.cuh).
+static int g_pair_gemm = -1;  // -1: not yet read from the environment
+static bool pair_gemm_enabled() {
+  if (g_pair_gemm < 0) {
+    const char* e = getenv("LMOE_PAIR_GEMM");
+    g_pair_gemm = (e && e[0] == '1') ? 1 : 0;
+  }
+  return g_pair_gemm == 1;
+}
+
+template <bool A_MN, bool B_MN, int EPI>
+static int launch_pair_inst(const GemmParams& p, long long total_tiles, cudaStream_t stream) {
+  auto kfn = gemm_pair_kernel<A_MN, B_MN, EPI>;
+  constexpr int smem = PairSmem<EPI>::kTotal;
+  static int max_pairs = 0;
+  if (max_pairs == 0) {
+    cudaError_t e = cudaFuncSetAttribute(kfn, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+    if (e != cudaSuccess) return static_cast<int>(e);
+    cudaFuncSetAttribute(kfn, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
+    // how many pairs the device holds at once (SM pairs must share a cluster-capable group)
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(2 * (num_sms() / 2), 1, 1);
+    cfg.blockDim = dim3(kGemmThreads, 1, 1);
+    cfg.dynamicSmemBytes = smem;
+    cudaLaunchAttribute attr;
+    attr.id = cudaLaunchAttributeClusterDimension;
+    attr.val.clusterDim.x = 2;
+    attr.val.clusterDim.y = 1;
+    attr.val.clusterDim.z = 1;
+    cfg.attrs = &attr;
+    cfg.numAttrs = 1;
+    int n = 0;
+    if (cudaOccupancyMaxActiveClusters(&n, kfn, &cfg) != cudaSuccess || n <= 0) {
+      cudaGetLastError();
+      n = num_sms() / 2;
+    }
+    max_pairs = n;
+  }
+  const int pairs = static_cast<int>(total_tiles < max_pairs ? total_tiles : max_pairs);
+  cudaEvent_t ev0 = nullptr, ev1 = nullptr;
+  if (g_prof_enabled) {
+    cudaEventCreate(&ev0);
+    cudaEventCreate(&ev1);
+    cudaEventRecord(ev0, stream);
+  }
+  kfn<<<2 * pairs, kGemmThreads, smem, stream>>>(p);
+  if (ev0) {
+    cudaEventRecord(ev1, stream);
+    std::lock_guard<std::mutex> lock(g_prof_mutex);
+    g_prof_events.emplace_back(ev0, ev1);
+  }
+  count_launch();
+  cudaError_t e = cudaGetLastError();
+  return e == cudaSuccess ? 0 : static_cast<int>(e);
+}
+
+// Same contract as launch_gemm for a dense bf16 GEMM (GRP_NONE; EPI_BF16, EPI_F32 with optional split-K, EPI_SWIGLU).
+static int launch_gemm_pair(const GemmCall& c) {
+  const bool swiglu = (c.epi == EPI_SWIGLU);
+  const int bk = kBKBytes / 2;
+  GemmParams p;
+  memset(&p, 0, sizeof(p));
+  const int m_tiles = (c.M + 255) / 256;
+  const int split = c.split_k > 1 ? c.split_k : 1;
+  const int n_per_tile = swiglu ? 128 : 256;
+  const int n_tiles = (c.N + n_per_tile - 1) / n_per_tile;
+  for (int s = 0; s < c.nseg; ++s) {
+    if (!c.A[s] || !c.B[s]) return LMOE_ERR_ARG;
+    const int K = c.Kseg[s];
+    if (K <= 0) return LMOE_ERR_SHAPE;
+    p.seg_kiters[s] = (K + bk - 1) / bk;
+    int rc = !c.a_mn ? encode_2d(&p.tmA[s], c.A[s], K, c.M, c.lda[s], kBM, 2)
+                     : encode_2d(&p.tmA[s], c.A[s], c.M, K, c.lda[s], bk, 2);
+    if (rc) return rc;
+    const int n_b_total = swiglu ? 2 * c.N : c.N;
+    rc = !c.b_mn ? encode_2d(&p.tmB[s], c.B[s], K, n_b_total, c.ldb[s], 128, 2)   // this CTA's half: 128 rows of B
+                 : encode_2d(&p.tmB[s], c.B[s], n_b_total, K, c.ldb[s], bk, 2);
+    if (rc) return rc;
+  }
+  {
+    const bool f32 = (c.epi == EPI_F32);
+    const long long cols = swiglu ? 2ll * c.N : c.N;
+    long long planes = 1, plane_elems = 0;
+    if (split > 1) {
+      planes = split;
+      plane_elems = c.c_group_stride;
+      if (plane_elems < static_cast<long long>(c.M) * c.ldc) return LMOE_ERR_ARG;
+    }
+    int rc = encode_out(&p.tmC, c.C, f32, cols, c.M, planes, c.ldc, plane_elems);
+    if (rc) return rc;
+    if (swiglu) {
+      rc = encode_out(&p.tmC2, c.C2, false, c.N, c.M, 1, c.ldc2, 0);
+      if (rc) return rc;
+    }
+  }
+  p.nseg = c.nseg;
+  p.M = c.M;
+  p.N = c.N;
+  p.m_tiles = m_tiles;
+  p.n_tiles = n_tiles;
+  p.split_k = split;
+  p.half = c.N;
+  p.status = c.status;
+  const long long total = static_cast<long long>(m_tiles) * n_tiles * split;
+  const int key = c.a_mn | (c.b_mn << 1) | (c.epi << 2);
+  switch (key) {
+    case 0 | (EPI_BF16 << 2): return launch_pair_inst<false, false, EPI_BF16>(p, total, c.stream);
+    case 1 | (EPI_BF16 << 2): return launch_pair_inst<true, false, EPI_BF16>(p, total, c.stream);
+    case 2 | (EPI_BF16 << 2): return launch_pair_inst<false, true, EPI_BF16>(p, total, c.stream);
+    case 3 | (EPI_BF16 << 2): return launch_pair_inst<true, true, EPI_BF16>(p, total, c.stream);
+    case 0 | (EPI_F32 << 2): return launch_pair_inst<false, false, EPI_F32>(p, total, c.stream);
+    case 1 | (EPI_F32 << 2): return launch_pair_inst<true, false, EPI_F32>(p, total, c.stream);
+    case 2 | (EPI_F32 << 2): return launch_pair_inst<false, true, EPI_F32>(p, total, c.stream);
+    case 3 | (EPI_F32 << 2): return launch_pair_inst<true, true, EPI_F32>(p, total, c.stream);
+    case 0 | (EPI_SWIGLU << 2): return launch_pair_inst<false, false, EPI_SWIGLU>(p, total, c.stream);
+    default: return LMOE_ERR_ARG;
+  }
+}
+
 int launch_gemm(const GemmCall& c) {
   if (c.nseg < 1 || c.nseg > 3 || !c.C || c.M <= 0 || c.N <= 0) return LMOE_ERR_ARG;
   if (c.split_k > 1 && (c.epi != EPI_F32 || c.nseg != 1 || c.grp != GRP_NONE)) return LMOE_ERR_ARG;
@@ -179,6 +300,10 @@ int launch_gemm(const GemmCall& c) {
     return LMOE_ERR_SHAPE;
 
   const bool gather = c.a_rows != nullptr;
+  if (pair_gemm_enabled() && c.grp == GRP_NONE && esz == 2 && !gather && c.bn == 0 && c.M >= 256 &&
+      (swiglu ? 2 * c.N : c.N) >= 256 &&
+      (c.epi == EPI_BF16 || c.epi == EPI_F32 || (swiglu && !c.a_mn && !c.b_mn)))
+    return launch_gemm_pair(c);
   if (gather) {
     const bool shape_ok = (c.grp == GRP_M && !c.a_mn) || (c.grp == GRP_K && c.a_mn);
     if (!shape_ok || esz != 2 || c.nseg != 1 || c.a_src_rows <= 0 || c.a_rows_stride <= 0 || c.a_rows_div <= 0 || c.a_zero_row < 0 ||
@@ -381,6 +506,12 @@ extern "C" int lmoe_profile_collect(float* gemm_ms, int* gemm_launches) {
 extern "C" size_t lmoe_gemm_workspace_bytes(int M, int N, int split_k) {
   if (split_k <= 1 || M <= 0 || N <= 0) return 0;
   return static_cast<size_t>(split_k) * M * N * sizeof(float);
+}
+
+extern "C" int lmoe_pair_gemm_enable(int on) {
+  const int before = lmoe::pair_gemm_enabled() ? 1 : 0;
+  lmoe::g_pair_gemm = on ? 1 : 0;
+  return before;
 }
 
 extern "C" int lmoe_gemm_bf16(int M, int N, int K, const void* A, int64_t lda, int a_mn, const void* B, int64_t ldb,

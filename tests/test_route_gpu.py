@@ -62,7 +62,8 @@ def near_tie_rows(scores, sel_a, sel_b):
     return bad, unexplained
 
 
-@pytest.mark.parametrize("T,E,K", [(1024, 128, 12), (131, 32, 8), (1, 16, 4), (4096, 256, 16), (777, 8, 8)])
+@pytest.mark.parametrize("T,E,K", [(1024, 128, 12), (131, 32, 8), (1, 16, 4), (4096, 256, 16), (777, 8, 8),
+                                   (65, 256, 32), (200, 64, 32), (33, 32, 32), (500, 48, 7)])   # top-k and expert limits
 def test_topk_matches_oracle(T, E, K):
     g = torch.Generator().manual_seed(T + E)
     logits = torch.randn(T, E, generator=g) * 0.7
@@ -90,9 +91,14 @@ def test_topk_tie_rule_lower_index_first():
     sel, w, _, _ = run_topk(logits, bias, 3)
     assert sel[0].tolist() == [7, 0, 1]
     torch.testing.assert_close(w[0], torch.full((3,), 1 / 3))
+    # ties inside one lane's block of experts and across lanes (256 experts: 8 per lane)
+    logits = torch.zeros(9, 256)
+    logits[:, [13, 14, 200, 8]] = 1.0
+    sel, _, _, _ = run_topk(logits, torch.zeros(256), 6)
+    assert sel[3].tolist() == [8, 13, 14, 200, 0, 1]
 
 
-@pytest.mark.parametrize("T,E,K", [(1024, 128, 12), (131, 32, 8), (1, 16, 4), (5000, 256, 16), (3, 8, 8)])
+@pytest.mark.parametrize("T,E,K", [(1024, 128, 12), (131, 32, 8), (1, 16, 4), (5000, 256, 16), (3, 8, 8), (700, 256, 32)])
 def test_route_permute_matches_oracle_bit_exact(T, E, K):
     g = torch.Generator().manual_seed(T * 3 + K)
     sel = torch.stack([torch.randperm(E, generator=g)[:K] for _ in range(T)])
