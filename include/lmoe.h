@@ -90,8 +90,8 @@ int64_t lmoe_padded_rows(const lmoe_shape* s);
 /* Bytes of scratch lmoe_route_permute needs (block histograms). */
 size_t lmoe_route_workspace_bytes(const lmoe_shape* s);
 
-/* Dense bf16 GEMMs with at least 256 rows and 256 columns can run on CTA pairs (tcgen05 cta_group::2: two SMs share a
- * 256 x 256 tile, each loading half of B).  Off unless the environment has LMOE_PAIR_GEMM=1; this call switches it for
+/* Dense bf16 GEMMs with at least 256 rows and 256 columns run on CTA pairs (tcgen05 cta_group::2: two SMs share a
+ * 256 x 256 tile, each loading half of B).  On unless the environment has LMOE_PAIR_GEMM=0; this call switches it for
  * the process and returns the previous setting (0 / 1).  Results are identical up to the summation order inside the
  * tensor cores.  No counterpart in the reference (a kernel-selection switch). */
 int lmoe_pair_gemm_enable(int on);

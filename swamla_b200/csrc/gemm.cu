@@ -165,15 +165,17 @@ static int dispatch(const GemmCall& c, int bn, const GemmParams& p, int grid, cu
 }
 
 // ---------------------------------------------------------------- CTA-pair kernel (dense GEMMs)
-// LMOE_PAIR_GEMM=1: dense bf16 GEMMs with at least 256 rows and 256 columns run on CTA pairs (gemm_pair.cuh).
+// Dense bf16 GEMMs with at least 256 rows and 256 columns run on CTA pairs (gemm_pair.cuh) unless LMOE_PAIR_GEMM=0.
 static int g_pair_gemm = -1;  // -1: not yet read from the environment
 static bool pair_gemm_enabled() {
   if (g_pair_gemm < 0) {
     const char* e = getenv("LMOE_PAIR_GEMM");
-    g_pair_gemm = (e && e[0] == '1') ? 1 : 0;
+    g_pair_gemm = (e && e[0] == '0') ? 0 : 1;
   }
   return g_pair_gemm == 1;
 }
+
+bool pair_gemm_applies(int M, int N) { return pair_gemm_enabled() && M >= 256 && N >= 256; }
 
 template <bool A_MN, bool B_MN, int EPI>
 static int launch_pair_inst(const GemmParams& p, long long total_tiles, cudaStream_t stream) {
@@ -300,8 +302,7 @@ int launch_gemm(const GemmCall& c) {
     return LMOE_ERR_SHAPE;
 
   const bool gather = c.a_rows != nullptr;
-  if (pair_gemm_enabled() && c.grp == GRP_NONE && esz == 2 && !gather && c.bn == 0 && c.M >= 256 &&
-      (swiglu ? 2 * c.N : c.N) >= 256 &&
+  if (c.grp == GRP_NONE && esz == 2 && !gather && c.bn != 128 && pair_gemm_applies(c.M, swiglu ? 2 * c.N : c.N) &&
       (c.epi == EPI_BF16 || c.epi == EPI_F32 || (swiglu && !c.a_mn && !c.b_mn)))
     return launch_gemm_pair(c);
   if (gather) {

@@ -56,6 +56,9 @@ int launch_gemm(const GemmCall& c);
 
 int num_sms();
 
+// True when dense GEMMs of this size run on CTA pairs (256 x 256 tiles over two SMs) rather than one CTA per 128 x 256 tile.
+bool pair_gemm_applies(int M, int N);
+
 // out[rows, cols] = sum over `planes` of ws[plane][row0 + r][col0 + c]; fp32 or bf16 output.
 int splitk_reduce(const float* ws, int planes, long long plane_elems, int ws_ld, int row0, int col0, int rows, int cols,
                   void* out, long long out_ld, int out_f32, cudaStream_t stream);

@@ -51,9 +51,10 @@ GemmCall dense(const void* A, long long lda, int a_mn, const void* B, long long 
 // Number of k-slices for a weight gradient with an M x N output contracting over K rows, from a cost model in
 // units of one k-block of main loop: waves x (k-blocks per slice + epilogue) + the reduce traffic of the planes.
 int wgrad_split(int M, int N, int K) {
-  const long long tiles = static_cast<long long>((M + 127) / 128) * ((N + 255) / 256);
+  const bool pair = pair_gemm_applies(M, N);  // 256 x 256 tiles on SM pairs: half the tiles, half the units
+  const long long tiles = static_cast<long long>((M + (pair ? 255 : 127)) / (pair ? 256 : 128)) * ((N + 255) / 256);
   const int kiters = (K + 63) / 64;  // bf16 k-blocks of 64 rows
-  const int sms = num_sms();
+  const int sms = pair ? num_sms() / 2 : num_sms();
   const double kblock_us = 0.40;                                       // 128 x 256 x 64 on one SM
   const double plane_us = 2.0 * M * N * 4.0 / 6.5e6;                   // write + read of one fp32 plane at HBM rate
   int best = 1;
