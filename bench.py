@@ -378,14 +378,15 @@ def main():
     pk = peaks()
     flops_step = 3 * w.flops_fwd_per_token() * w.T        # per GPU
     achieved = flops_step / (ms_per_step * 1e-3) / 1e12
-    # dominant kernel = the tcgen05 GEMM kernel (every GEMM of the step is an instantiation of it): its summed launch
+    # dominant kernel = the tcgen05 GEMM kernels (every GEMM of the step is an instantiation of one of the two): their summed launch
     # durations, measured here with CUDA events around each launch on its stream over `prof_steps` extra steps
     gemm_tflops = gemm_ms_step = None
     gemm_launches = 0
     if gemm_prof is not None:
         gemm_ms_step, gemm_launches = gemm_prof
         gemm_tflops = flops_step / (gemm_ms_step * 1e-3) / 1e12
-    roofline = {"bound": "tensor", "kernel": "lmoe::gemm_kernel (all tcgen05 GEMM launches of a step)",
+    roofline = {"bound": "tensor", "kernel": "lmoe::gemm_pair_kernel (dense, cta_group::2) + lmoe::gemm_kernel (grouped): all tcgen05 GEMM "
+                          "launches of a step",
                 "achieved": gemm_tflops, "peak": pk["bf16_tflops"], "unit": "TFLOP/s",
                 "frac": None if gemm_tflops is None else gemm_tflops / pk["bf16_tflops"],
                 "traffic": TRAFFIC_BYTES_PER_STEP.get(w.name),
