@@ -136,3 +136,81 @@ def test_expert_shards_keep_the_reference_state_dict_layout_and_stay_out_of_ddp(
     port = 29500 + ((os.getpid() + 211) % 500)
     mp.spawn(_ckpt_worker, args=(2, port, str(tmp_path)), nprocs=2, join=True)
     assert (tmp_path / "ok0").exists() and (tmp_path / "ok1").exists()
+
+
+def _dedup_worker(rank, world, port, tmpdir):
+    """The de-duplicated exchange in torch over gloo: one row per (token, destination rank) out, one partial-sum row
+    per (token, owner) back; must reproduce the single-rank oracle's routed output."""
+    sys.path.insert(0, ROOT)
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        from oracle import inputs, latent_moe_ref as R, ep_ref
+        w = inputs.WORKLOADS["tiny_ragged"]
+        params, buffers, _, _ = inputs.make_inputs(w, seed=0)
+        g = torch.Generator().manual_seed(300 + rank)
+        T = 40 + 9 * rank
+        x = torch.randn(1, T, w.D, generator=g)
+        E, K, L, El = w.E, w.K, w.L, w.E // world
+        with torch.no_grad():
+            ref = R.layer_forward(params, buffers, x, K)
+        counts_all = [torch.zeros(E, dtype=torch.int64) for _ in range(world)]
+        dist.all_gather(counts_all, ref["counts"])
+        counts_all = torch.stack(counts_all)
+        tables = ep_ref.dedup_send_tables(ref["sel"], ref["weights"], counts_all, rank)
+        # fewer rows than one per (token, expert) travel, and every routed row is described exactly once
+        assert sum(len(t["tokens"]) for t in tables) <= T * min(K, world)
+        assert sum(len(t["meta_rows"]) for t in tables) == T * K
+        # "stores": every rank hands each destination its rows and routing words (object all-to-all stands in for NVLink)
+        send = [dict(src=rank, tok=t["tokens"], rows=ref["x_latent"][t["tokens"]], mask=t["mask"], slots=t["slots"],
+                     meta_rows=t["meta_rows"], meta_tok=t["meta_tok"], meta_w=t["meta_w"]) for t in tables]
+        gathered = [None] * world
+        dist.all_gather_object(gathered, send)
+        incoming = [gathered[s][rank] for s in range(world)]                    # what every source wrote into this rank
+        # owner: padded layout from the staged rows
+        _, _, pad_offsets, tile_expert, n_tiles = ep_ref.regroup_tables(counts_all.to(torch.int32), rank)
+        P = n_tiles * 128
+        x_in = torch.zeros(P, L)
+        w_row = torch.zeros(P)
+        filled = torch.zeros(P, dtype=torch.bool)
+        for m in incoming:
+            stage = torch.zeros(int(m["mask"].numel()), L)
+            stage[m["tok"]] = m["rows"]
+            assert not filled[m["meta_rows"]].any()                              # no two routed rows share a padded row
+            x_in[m["meta_rows"]] = stage[m["meta_tok"]]
+            w_row[m["meta_rows"]] = m["meta_w"]
+            filled[m["meta_rows"]] = True
+        tot = counts_all[:, rank * El:(rank + 1) * El].sum(0)
+        for j in range(El):                                                      # exactly the valid rows are filled
+            seg = filled[pad_offsets[j]:pad_offsets[j + 1]]
+            assert seg[:tot[j]].all() and not seg[tot[j]:].any()
+        lo, hi = rank * El, (rank + 1) * El
+        h1 = R.grouped_gemm(x_in, params["experts.gate_up_weight"][lo:hi], pad_offsets)
+        gate, up = h1.chunk(2, -1)
+        y_sorted = R.grouped_gemm(torch.nn.functional.silu(gate) * up, params["experts.down_weight"][lo:hi], pad_offsets)
+        # owner: one weighted partial sum per (source, token)
+        back = []
+        for m in incoming:
+            part = torch.zeros(int(m["mask"].numel()), L)
+            for t in m["tok"].tolist():
+                for k in range(K):
+                    if (int(m["mask"][t]) >> k) & 1:
+                        p = int(m["slots"][t, k])
+                        part[t] += w_row[p] * y_sorted[p]
+            back.append(dict(tok=m["tok"], rows=part[m["tok"]]))
+        returned = [None] * world
+        dist.all_gather_object(returned, back)
+        routed = torch.zeros(T, L)
+        for owner in range(world):                                               # source: add the owners' partial sums
+            r = returned[owner][rank]
+            routed[r["tok"]] += r["rows"]
+        torch.testing.assert_close(routed, ref["routed"], rtol=1e-5, atol=1e-6)
+        open(os.path.join(tmpdir, f"ok{rank}"), "w").write("ok")
+    finally:
+        dist.destroy_process_group()
+
+
+def test_dedup_exchange_reproduces_single_rank_oracle(tmp_path):
+    port = 29500 + ((os.getpid() + 97) % 500)
+    mp.spawn(_dedup_worker, args=(2, port, str(tmp_path)), nprocs=2, join=True)
+    assert (tmp_path / "ok0").exists() and (tmp_path / "ok1").exists()
