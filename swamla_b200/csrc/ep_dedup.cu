@@ -28,6 +28,11 @@ namespace lmoe {
 
 constexpr int kStatusEpdOverflow = 201;
 constexpr int kEpdWarps = 8;
+// The send kernel runs beside the shared-expert GEMM, whose SwiGLU epilogue takes 152 registers per thread: with its ten
+// warps spread 3/3/2/2 over the four register files of an SM, the fullest ones keep 1,792 registers free.  A block of
+// four warps (one per register file, 1,024 registers each at 32 per thread) fits there; a block of eight does not and
+// would wait for the GEMM to drain (measured: no overlap at all with eight warps).
+constexpr int kEpdSendWarps = 4;
 constexpr int kEpdMaxVecPerLane = 4;  // rows of up to 4 * 32 * 8 = 1024 elements
 
 __device__ __forceinline__ void epd_unpack(const uint4& v, float (&f)[8]) {
@@ -50,15 +55,15 @@ __device__ __forceinline__ uint4 epd_pack(const float (&f)[8]) {
 // Source side.  One warp per token; lane k < K resolves top-k slot k.
 // WITH_META: also writes mask / slots / meta (forward); without it only the rows travel (backward reuses the tables).
 template <bool WITH_META>
-__global__ void __launch_bounds__(kEpdWarps * 32)
+__global__ void __launch_bounds__(kEpdSendWarps * 32)
 epd_send_kernel(const uint4* __restrict__ src, const int* __restrict__ sel, const int* __restrict__ pos,
                 const int* __restrict__ offsets, const int* __restrict__ dst_base, const float* __restrict__ weights,
                 int T, int K, int El, int G, int rank, int vec_per_row, int capacity_rows, int stride,
                 uint4* const* __restrict__ peer_stage, int2* const* __restrict__ peer_meta,
                 unsigned* const* __restrict__ peer_mask, int* const* __restrict__ peer_slots, int* __restrict__ status) {
   const int lane = threadIdx.x & 31;
-  const int warps_total = gridDim.x * kEpdWarps;
-  for (int t = blockIdx.x * kEpdWarps + (threadIdx.x >> 5); t < T; t += warps_total) {
+  const int warps_total = gridDim.x * kEpdSendWarps;
+  for (int t = blockIdx.x * kEpdSendWarps + (threadIdx.x >> 5); t < T; t += warps_total) {
     int g = -1, drow = -1;
     float w = 0.f;
     if (lane < K) {
@@ -319,15 +324,25 @@ extern "C" int lmoe_epd_send(const void* src_rows, const int32_t* sel, const int
     return LMOE_ERR_SHAPE;
   epd_configure();
   cudaStream_t st = static_cast<cudaStream_t>(stream);
-  const int grid = epd_grid(T);
+  // Forward (beside the SwiGLU GEMM, 152 registers per thread): one block per SM, so that whichever of the two kernels
+  // reaches an SM first, the other still fits beside it.  Backward (beside a GEMM with a plain epilogue): registers are
+  // no limit, eight blocks per SM leave the thread slots the GEMM CTA needs.
+  long long blocks = (T + kEpdSendWarps - 1) / kEpdSendWarps;
+  int sms = 0, device = 0;
+  if (cudaGetDevice(&device) != cudaSuccess ||
+      cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device) != cudaSuccess || sms <= 0)
+    sms = 148;
+  const long long cap = with_meta ? sms : 8ll * sms;
+  if (blocks > cap) blocks = cap;
+  const int grid = static_cast<int>(blocks);
   if (with_meta)
-    epd_send_kernel<true><<<grid, kEpdWarps * 32, 0, st>>>(
+    epd_send_kernel<true><<<grid, kEpdSendWarps * 32, 0, st>>>(
         static_cast<const uint4*>(src_rows), sel, pos, offsets, dst_base, weights, static_cast<int>(T), K, E / G, G, rank,
         L / 8, static_cast<int>(capacity_rows), static_cast<int>(stride), reinterpret_cast<uint4* const*>(peer_stage),
         reinterpret_cast<int2* const*>(peer_meta), reinterpret_cast<unsigned* const*>(peer_mask),
         reinterpret_cast<int* const*>(peer_slots), status);
   else
-    epd_send_kernel<false><<<grid, kEpdWarps * 32, 0, st>>>(
+    epd_send_kernel<false><<<grid, kEpdSendWarps * 32, 0, st>>>(
         static_cast<const uint4*>(src_rows), sel, nullptr, nullptr, nullptr, nullptr, static_cast<int>(T), K, E / G, G,
         rank, L / 8, static_cast<int>(capacity_rows), static_cast<int>(stride),
         reinterpret_cast<uint4* const*>(peer_stage), nullptr, nullptr, nullptr, status);

@@ -593,14 +593,17 @@ class ExpertParallelDedup(torch.autograd.Function):
         ready.record(main)
         side.wait_event(ready)
         sst = side.cuda_stream
+        # the GEMM is queued first: its CTAs take their place on every SM, and the send kernel's small blocks (four
+        # warps, 32 registers per thread) fit into what the GEMM leaves free; the other way round the send's blocks
+        # fill the SMs' thread slots and the GEMM waits for them to drain
+        h1_s = torch.empty(T, 2 * Fs, **bf)
+        act_cat = torch.empty(T, L + Fs, **bf)
+        _cabi.call("lmoe_shared_gateup_fwd", shape, ptr(xb), ptr(wgus), ptr(h1_s), ptr(act_cat), ptr(status), st)
         _cabi.call("lmoe_epd_send", ptr(x_latent), ptr(sel), ptr(inv), ptr(route.offsets), ptr(dst_base), ptr(weights), T,
                    K, E, G, rank, L, P, stride, ptr(bufs.peer_stage_x), ptr(bufs.peer_meta), ptr(bufs.peer_mask),
                    ptr(bufs.peer_slots), ptr(status), sst)
         sent = torch.cuda.Event()
         sent.record(side)
-        h1_s = torch.empty(T, 2 * Fs, **bf)
-        act_cat = torch.empty(T, L + Fs, **bf)
-        _cabi.call("lmoe_shared_gateup_fwd", shape, ptr(xb), ptr(wgus), ptr(h1_s), ptr(act_cat), ptr(status), st)
         main.wait_event(sent)
         bufs.barrier(group)                                   # all rows and routing words have landed
 
