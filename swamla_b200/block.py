@@ -92,7 +92,17 @@ class NormedResidualFFN(nn.Module):
 
     def forward(self, x: torch.Tensor) -> torch.Tensor:
         B, S, D = x.shape
-        xn, x_pass = _NormAndPass.apply(x.reshape(-1, D), self.ffn_norm.weight, self.ffn_norm.eps)
+        xn, x_pass = _norm_and_pass(x.reshape(-1, D), self.ffn_norm.weight, self.ffn_norm.eps)
         y = self.ffn(xn.view(B, S, D))
-        out = _Add.apply(x_pass, y.reshape(-1, D))
+        out = _add(x_pass, y.reshape(-1, D))
         return (out if x.dtype == BF else out.to(x.dtype)).view(B, S, D)
+
+
+@torch.compiler.disable   # opaque to torch.compile (ctypes calls into the kernel library)
+def _norm_and_pass(x2d, weight, eps):
+    return _NormAndPass.apply(x2d, weight, eps)
+
+
+@torch.compiler.disable
+def _add(a, b):
+    return _Add.apply(a, b)

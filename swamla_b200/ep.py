@@ -248,6 +248,7 @@ class ExpertParallelLatentMoE(torch.autograd.Function):
                 as_param(d_w_down_e, dt[7]), None, None, None, None)
 
 
+@torch.compiler.disable   # opaque to torch.compile: the layer runs as an eager call between compiled regions
 def latent_moe_ep(x2d, w_gate, w_down, w_up, w_gate_up_s, w_down_s, w_gate_up_loc, w_down_e_loc, expert_bias, top_k,
                   z_coef, group):
     """Functional form; the expert weights are this rank's shard.  Returns (y, aux_loss, sel, global counts)."""
@@ -481,6 +482,7 @@ class ExpertParallelP2P(torch.autograd.Function):
                 as_param(d_w_down_e, dt[7]), None, None, None, None, None)
 
 
+@torch.compiler.disable   # opaque to torch.compile: the layer runs as an eager call between compiled regions
 def latent_moe_ep_p2p(x2d, w_gate, w_down, w_up, w_gate_up_s, w_down_s, w_gate_up_loc, w_down_e_loc, expert_bias, top_k,
                       z_coef, group, bufs: SymmetricBuffers):
     return ExpertParallelP2P.apply(x2d, w_gate, w_down, w_up, w_gate_up_s, w_down_s, w_gate_up_loc, w_down_e_loc,
@@ -725,6 +727,7 @@ class ExpertParallelDedup(torch.autograd.Function):
                 as_param(d_w_down_e, dt[7]), None, None, None, None, None)
 
 
+@torch.compiler.disable   # opaque to torch.compile: the layer runs as an eager call between compiled regions
 def latent_moe_ep_dedup(x2d, w_gate, w_down, w_up, w_gate_up_s, w_down_s, w_gate_up_loc, w_down_e_loc, expert_bias,
                         top_k, z_coef, group, bufs: DedupBuffers):
     return ExpertParallelDedup.apply(x2d, w_gate, w_down, w_up, w_gate_up_s, w_down_s, w_gate_up_loc, w_down_e_loc,

@@ -318,6 +318,7 @@ class LatentMoEFunction(torch.autograd.Function):
         return grads + (None, None, None, None)
 
 
+@torch.compiler.disable   # opaque to torch.compile: the layer runs as an eager call between compiled regions
 def latent_moe(x2d: torch.Tensor, w_gate, w_down, w_up, w_gate_up_s, w_down_s, w_gate_up, w_down_e, expert_bias,
                top_k: int, z_coef: float, fp8: bool = False):
     """Functional form on a [T, D] activation.  Returns (y [T,D], aux_loss scalar, sel [T,K] int32, counts [E] int32).

@@ -166,6 +166,7 @@ class MoEFunction(torch.autograd.Function):
                 as_param(d_w_down_s, dt[3]), as_param(d_w_gate_up, dt[4]), as_param(d_w_down_e, dt[5]), None, None, None)
 
 
+@torch.compiler.disable   # opaque to torch.compile: the layer runs as an eager call between compiled regions
 def moe(x2d: torch.Tensor, w_gate, w_gate_up_s, w_down_s, w_gate_up, w_down_e, expert_bias, top_k: int, z_coef: float):
     """Functional form on a [T, D] activation.  Returns (y [T,D], aux_loss scalar, sel [T,K] int32, counts [E] int32)."""
     return MoEFunction.apply(x2d, w_gate, w_gate_up_s, w_down_s, w_gate_up, w_down_e, expert_bias, int(top_k),

@@ -35,6 +35,8 @@ class Workload:
     uniform_gate: bool = False   # router gate ~ U(-1/sqrt(D), 1/sqrt(D))
     router_z_loss_coef: float = 0.001
     latent: bool = True          # False: the non-latent MoELayer (models/moe.py:294-559): experts work at width D
+    literal_counts: bool = False # True: n_experts / n_activated are the layer's own counts (config.latent_n_experts /
+                                 # latent_n_activated, models/moe.py:639-646) instead of being scaled by latent_ratio
     extra: dict = field(default_factory=dict)
 
     # ---- derived sizes, following models/moe.py:630-685 ----
@@ -43,9 +45,11 @@ class Workload:
     @property
     def L(self) -> int: return self.n_embd // self.latent_ratio if self.latent else self.n_embd
     @property
-    def E(self) -> int: return self.n_experts * self.latent_ratio if self.latent else self.n_experts
+    def E(self) -> int:
+        return self.n_experts * self.latent_ratio if (self.latent and not self.literal_counts) else self.n_experts
     @property
-    def K(self) -> int: return self.n_activated * self.latent_ratio if self.latent else self.n_activated
+    def K(self) -> int:
+        return self.n_activated * self.latent_ratio if (self.latent and not self.literal_counts) else self.n_activated
     @property
     def F(self) -> int: return self.expert_dim // self.latent_ratio if self.latent else self.expert_dim
     @property
@@ -55,12 +59,15 @@ class Workload:
 
     def config(self) -> SimpleNamespace:
         """The object handed to ``LatentMoELayer(config)`` (read with getattr)."""
-        return SimpleNamespace(
+        cfg = SimpleNamespace(
             n_embd=self.n_embd, n_experts=self.n_experts, n_activated=self.n_activated,
             n_shared_experts=self.n_shared_experts, latent_ratio=self.latent_ratio,
             expert_dim=self.expert_dim, bias=False, dropout=0.0,
             router_z_loss_coef=self.router_z_loss_coef, use_latent_moe=self.latent,
         )
+        if self.literal_counts:
+            cfg.latent_n_experts, cfg.latent_n_activated = self.n_experts, self.n_activated
+        return cfg
 
     def flops_fwd_per_token(self) -> int:
         """GEMM FLOPs only: router + down + routed + up + shared."""
@@ -84,6 +91,10 @@ WORKLOADS: Dict[str, Workload] = {
     "cfg3": Workload("cfg3", expert_dim=3072, batch=32, seq=2048, dtype="bf16", zipf_s=1.2),
     "cfg4": Workload("cfg4", batch=64, seq=2048, dtype="fp8"),
     "cfg5": Workload("cfg5", n_experts=64, n_activated=4, batch=16, seq=2048, dtype="bf16", uniform_gate=True),
+    # secondary reading of the benchmark text: 32 experts / top-3 (64 / top-4) taken literally as the layer's counts
+    "cfg2_literal": Workload("cfg2_literal", batch=8, seq=2048, dtype="bf16", literal_counts=True),
+    "cfg5_literal": Workload("cfg5_literal", n_experts=64, n_activated=4, batch=16, seq=2048, dtype="bf16",
+                             uniform_gate=True, literal_counts=True),
     # the non-latent MoELayer (the other branch of create_moe_layer)
     "tiny_moe": Workload("tiny_moe", n_embd=256, n_experts=8, n_activated=2, expert_dim=128, batch=2, seq=96, latent=False),
     "tiny_moe_ragged": Workload("tiny_moe_ragged", n_embd=256, n_experts=16, n_activated=3, expert_dim=128, batch=1, seq=131,

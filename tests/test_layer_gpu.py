@@ -221,3 +221,35 @@ def test_layer_refuses_cpu_tensors():
     layer = LatentMoELayer(w.config())
     with pytest.raises(_cabi.LmoeError):
         layer(torch.randn(1, 4, w.D))
+
+
+def test_layer_under_torch_compile_matches_eager():
+    """The reference trains with torch.compile(model) (train.py:936-940): the layer is an opaque eager call inside a
+    compiled module and must give the same bits and gradients as without compilation."""
+    import torch.nn as nn
+    w = inputs.WORKLOADS["tiny_ragged"]
+    params, buffers, x, dy = inputs.make_inputs(w)
+    layer = build_layer(w, params, buffers, torch.bfloat16).train()
+
+    class Wrapped(nn.Module):                      # some compilable work either side of the layer
+        def __init__(self, ffn):
+            super().__init__()
+            self.ffn = ffn
+
+        def forward(self, t):
+            return self.ffn(t * 1.5) + t
+
+    model = Wrapped(layer)
+    compiled = torch.compile(model, backend="aot_eager")   # dynamo + AOT autograd, no code generation needed
+    outs = []
+    for fn in (model, compiled):
+        for p_ in layer.parameters():
+            p_.grad = None
+        xg = x.to("cuda:0").to(torch.bfloat16).requires_grad_(True)
+        y = fn(xg)
+        (y.float() * dy.to("cuda:0").to(torch.bfloat16).float()).sum().backward()
+        outs.append((y.detach(), xg.grad, layer.experts.gate_up_weight.grad.clone(), layer.get_aux_loss().detach().clone()))
+    torch.cuda.synchronize()
+    for a, b in zip(outs[0], outs[1]):
+        torch.testing.assert_close(a.float(), b.float(), rtol=2e-2, atol=2e-2 * a.float().abs().max().item())
+    assert torch.equal(outs[0][2], outs[1][2])     # the layer itself computes the same bits
