@@ -1,7 +1,7 @@
 #!/usr/bin/env python
 """Benchmark of the LatentMoE feed-forward path: forward+backward tokens/s.
 
-    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--workload cfgX]
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--workload cfgX] [--timeline]
 
 One step = one forward+backward of the layer over one batch of synthetic tokens.  Rank 0 prints ONE
 JSON line.  ``value`` is timed with CUDA events with inputs resident in HBM; ``e2e`` is the same step
@@ -117,6 +117,31 @@ def build_layer(w, rank, device, ep_group=None, ep_mode="p2p_dedup"):
     return layer, x.to(torch.bfloat16), dy.to(torch.bfloat16)
 
 
+def print_timeline(layer, x, dy, rank, min_us=0.0):
+    """Device timeline of one eager fwd+bwd step after warm-up (CUDA activity records of torch.profiler): start offset,
+    duration and gap to the previous kernel, per kernel.  Diagnostic output (--timeline), not a benchmark line."""
+    from torch.profiler import ProfilerActivity, profile
+    for _ in range(4):
+        zero_grads(layer, x)
+        step(layer, x, dy)
+    torch.cuda.synchronize()
+    with profile(activities=[ProfilerActivity.CUDA]) as prof:
+        for _ in range(2):
+            zero_grads(layer, x)
+            step(layer, x, dy)
+        torch.cuda.synchronize()
+    evs = [e for e in prof.events() if e.device_type == torch.autograd.DeviceType.CUDA]
+    evs.sort(key=lambda e: e.time_range.start)
+    last = evs[len(evs) // 2:]                       # the second of the two profiled steps
+    t0 = prev = last[0].time_range.start
+    for e in last:
+        d = e.time_range.end - e.time_range.start
+        if d >= min_us:
+            print(f"r{rank} {e.time_range.start - t0:9.1f} us +{d:7.1f}  gap {e.time_range.start - prev:7.1f}  {e.name[:90]}")
+        prev = max(prev, e.time_range.end)
+    print(f"r{rank} step span {max(e.time_range.end for e in last) - t0:.1f} us, {len(last)} kernels", flush=True)
+
+
 def time_steps(layer, x, dy, steps, warmup):
     """ms per fwd+bwd step on this rank alone (CUDA events on the current stream)."""
     for _ in range(warmup):
@@ -210,6 +235,8 @@ def main():
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--ep-mode", default="p2p_dedup", choices=["p2p_dedup", "p2p", "nccl"])
     ap.add_argument("--no-graphs", action="store_true", help="eager launches instead of CUDA-graph replay (N=1)")
+    ap.add_argument("--timeline", action="store_true",
+                    help="print the per-kernel device timeline of one eager step (rank 0 and the last rank) and exit")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
 
@@ -245,6 +272,20 @@ def main():
                                          ep_mode=args.ep_mode)
     x = x_host.to(dev).requires_grad_(True)
     dy = dy_host.to(dev)
+    if args.timeline:
+        if dist is not None:
+            dist.barrier()
+        if rank in (0, world - 1):
+            print_timeline(layer, x, dy, rank)
+        else:                                        # the other ranks run the same steps so that the exchange completes
+            for _ in range(6):
+                zero_grads(layer, x)
+                step(layer, x, dy)
+            torch.cuda.synchronize()
+        if dist is not None:
+            dist.barrier()
+            dist.destroy_process_group()
+        return
     use_graphs = world == 1 and not args.no_graphs
     eager_layer = layer
     if use_graphs:
