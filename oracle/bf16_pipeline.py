@@ -58,7 +58,9 @@ def forward_backward(params: Dict[str, torch.Tensor], buffers, x, dy, top_k: int
     dy = rb(dy).reshape(-1, D)
     T = x.shape[0]
     K = top_k
-    Wg, Wdn, Wup = p["router.gate.weight"], p["down_proj.weight"], p["up_proj.weight"]
+    latent = "down_proj.weight" in p      # False: the non-latent MoELayer (experts read x, their sum is added directly)
+    Wg = p["router.gate.weight"]
+    Wdn, Wup = (p["down_proj.weight"], p["up_proj.weight"]) if latent else (None, None)
     Wgus, Wds = p["shared_experts.0.gate_up_proj.weight"], p["shared_experts.0.down_proj.weight"]
     Wgu, Wde = p["experts.gate_up_weight"], p["experts.down_weight"]
     E, L, _ = Wgu.shape
@@ -70,7 +72,7 @@ def forward_backward(params: Dict[str, torch.Tensor], buffers, x, dy, top_k: int
         sel = sel_override
         a = torch.gather(torch.sigmoid(logits), 1, sel)
         w = a / (a.sum(-1, keepdim=True) + 1e-9)
-    x_latent = rb(x @ Wdn.t())
+    x_latent = rb(x @ Wdn.t()) if latent else x
     counts, offsets, perm = R.route_permute(sel, E)
     tok = perm // K
     x_sorted = x_latent[tok]
@@ -87,15 +89,23 @@ def forward_backward(params: Dict[str, torch.Tensor], buffers, x, dy, top_k: int
     for k in range(K):                                     # slot order, fp32 accumulate
         rows = inv[torch.arange(T) * K + k]
         routed = routed + w[:, k:k + 1] * y_sorted[rows]
-    routed = rb(routed)
     h1_s = rb(x @ Wgus.t())
     gs, us = h1_s.chunk(2, -1)
     hidden_s = rb(F.silu(gs) * us)
-    y = rb(hidden_s @ Wds.t() + routed @ Wup.t())
+    if latent:
+        routed = rb(routed)
+        y = rb(hidden_s @ Wds.t() + routed @ Wup.t())
+    else:
+        # the shared expert's output is stored in bf16, then the weighted expert rows are added to it in fp32 (slot order)
+        y = rb(hidden_s @ Wds.t())
+        for k in range(K):
+            y = y + w[:, k:k + 1] * y_sorted[inv[torch.arange(T) * K + k]]
+        y = rb(y)
+        routed = rb(routed)
     lse = torch.logsumexp(logits, -1)
 
     # ---- backward ----
-    d_routed = rb(dy @ Wup)
+    d_routed = rb(dy @ Wup) if latent else dy
     d_hidden_s = rb(dy @ Wds)
     d_h1_s = _swiglu_bwd(h1_s, d_hidden_s)
     d_y_sorted = rb(w_sorted[:, None] * d_routed[tok])
@@ -111,7 +121,8 @@ def forward_backward(params: Dict[str, torch.Tensor], buffers, x, dy, top_k: int
     d_x_latent = torch.zeros(T, L)
     for k in range(K):
         d_x_latent = d_x_latent + d_x_sorted[inv[torch.arange(T) * K + k]]
-    d_x_latent = rb(d_x_latent)
+    if latent:
+        d_x_latent = rb(d_x_latent)
     a = torch.gather(torch.sigmoid(logits), 1, sel)
     S_ = a.sum(-1, keepdim=True) + 1e-9
     d_a = (d_w - (d_w * w).sum(-1, keepdim=True)) / S_
@@ -120,14 +131,20 @@ def forward_backward(params: Dict[str, torch.Tensor], buffers, x, dy, top_k: int
     if aux_grad != 0.0:
         d_logits = d_logits + aux_grad * z_coef * 2.0 * lse[:, None] * torch.exp(logits - lse[:, None]) / T
     d_logits = rb(d_logits)
-    dx = rb(d_h1_s @ Wgus + d_x_latent @ Wdn + d_logits @ Wg)
+    if latent:
+        dx = rb(d_h1_s @ Wgus + d_x_latent @ Wdn + d_logits @ Wg)
+    else:
+        # dense part stored in bf16, then the expert-path rows are added in fp32 (slot order)
+        dx = rb(d_h1_s @ Wgus + d_logits @ Wg)
+        for k in range(K):
+            dx = dx + d_x_sorted[inv[torch.arange(T) * K + k]]
+        dx = rb(dx)
 
     pg = rb if param_grads_bf16 else (lambda t: t)
     grads = {
         "x": dx.view(B, S, D),
         "router.gate.weight": pg(d_logits.t() @ x),
-        "down_proj.weight": pg(d_x_latent.t() @ x),
-        "up_proj.weight": pg(dy.t() @ routed),
+        **({"down_proj.weight": pg(d_x_latent.t() @ x), "up_proj.weight": pg(dy.t() @ routed)} if latent else {}),
         "shared_experts.0.gate_up_proj.weight": pg(d_h1_s.t() @ x),
         "shared_experts.0.down_proj.weight": pg(dy.t() @ hidden_s),
         "experts.gate_up_weight": rb(torch.stack([xs_q[offsets[e]:offsets[e + 1]].t() @ dh1_q[offsets[e]:offsets[e + 1]]

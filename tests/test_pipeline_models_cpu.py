@@ -13,7 +13,7 @@ def _oracle(w, params, buffers, x, dy, aux_grad, sel=None):
                                     sel_override=sel)
 
 
-@pytest.mark.parametrize("name", ["tiny", "tiny_ragged"])
+@pytest.mark.parametrize("name", ["tiny", "tiny_ragged", "tiny_moe", "tiny_moe_ragged"])
 @pytest.mark.parametrize("aux_grad", [0.0, 2.0])
 def test_bf16_pipeline_model_is_within_tolerance_of_fp32_oracle(name, aux_grad):
     w = inputs.WORKLOADS[name]
@@ -23,7 +23,7 @@ def test_bf16_pipeline_model_is_within_tolerance_of_fp32_oracle(name, aux_grad):
                                                         sel_override=out["sel"])
     assert torch.equal(model["sel"], out["sel"]) and torch.equal(model["perm"], out["perm"])
     for k in ("y", "x_latent", "h1", "hidden", "y_sorted", "routed", "h1_s", "hidden_s"):
-        ok, rep = R.within_tolerance(model[k], out[k], 2e-2)
+        ok, rep = R.within_tolerance(model[k].reshape(out[k].shape), out[k], 2e-2)
         assert ok, (k, rep)
     for k, ref in grads.items():
         ok, rep = R.within_tolerance(model_grads[k], ref, 2e-2)
