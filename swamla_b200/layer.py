@@ -200,6 +200,10 @@ class LatentMoELayer(nn.Module):
             raise ValueError("ep_mode must be 'p2p_dedup', 'p2p' or 'nccl'")
         # incoming-buffer capacity of a shard, as a multiple of this rank's own row count T*K (p2p mode)
         self.ep_capacity_factor = float(getattr(config, "ep_capacity_factor", 2.0))
+        # The exchange buffers are symmetric allocations sized for the largest token count of any rank; they are
+        # (re)allocated collectively, so every rank must outgrow them in the same forward.  `config.ep_max_tokens`
+        # sizes them once for the largest batch a rank will ever see (default: the first forward's maximum).
+        self.ep_max_tokens = int(getattr(config, "ep_max_tokens", 0) or 0)
         self._ep_bufs = None
         if n_experts % self.ep_size:
             raise ValueError("the expert count must be divisible by the expert-parallel group size")
@@ -231,8 +235,8 @@ class LatentMoELayer(nn.Module):
             from .ep import DedupBuffers, latent_moe_ep_dedup
             T = x_flat.shape[0]
             if self._ep_bufs is None or self._ep_bufs.stride < T:
-                self._ep_bufs = DedupBuffers(self.ep_group, T, self.n_activated, self.latent_dim, self.experts.n_experts,
-                                             self.ep_capacity_factor, x.device)
+                self._ep_bufs = DedupBuffers(self.ep_group, max(T, self.ep_max_tokens), self.n_activated, self.latent_dim,
+                                             self.experts.n_experts, self.ep_capacity_factor, x.device)
             y, z_loss, sel, counts = latent_moe_ep_dedup(*args, self.ep_group, self._ep_bufs)
         elif self.ep_size > 1 and self.ep_mode == "p2p":
             # one-sided NVLink stores into the peers' padded expert layout (symmetric buffers owned by the layer;
@@ -240,8 +244,8 @@ class LatentMoELayer(nn.Module):
             from .ep import SymmetricBuffers, latent_moe_ep_p2p
             n_send = x_flat.shape[0] * self.n_activated
             if self._ep_bufs is None or self._ep_bufs.n_send_max < n_send:
-                self._ep_bufs = SymmetricBuffers(self.ep_group, n_send, self.latent_dim, self.experts.n_experts,
-                                                 self.ep_capacity_factor, x.device)
+                self._ep_bufs = SymmetricBuffers(self.ep_group, max(n_send, self.ep_max_tokens * self.n_activated),
+                                                 self.latent_dim, self.experts.n_experts, self.ep_capacity_factor, x.device)
             y, z_loss, sel, counts = latent_moe_ep_p2p(*args, self.ep_group, self._ep_bufs)
         elif self.ep_size > 1:
             from .ep import latent_moe_ep
