@@ -1,7 +1,7 @@
 #!/usr/bin/env python
 """Benchmark of the LatentMoE feed-forward path: forward+backward tokens/s.
 
-    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--workload cfgX] [--timeline]
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--workload cfgX]
 
 One step = one forward+backward of the layer over one batch of synthetic tokens.  Rank 0 prints ONE
 JSON line.  ``value`` is timed with CUDA events with inputs resident in HBM; ``e2e`` is the same step
@@ -26,8 +26,10 @@ import torch  # noqa: E402
 from swamla_b200 import workloads as inputs  # noqa: E402
 
 METRIC = "LatentMoE fwd+bwd tokens/s"
-# dram__bytes_read.sum + dram__bytes_write.sum of the GEMM launches of one step, from ncu (see profiles/)
-TRAFFIC_BYTES_PER_STEP = {"cfg2": 2161334272}
+# dram__bytes_read.sum + dram__bytes_write.sum of ALL tcgen05 GEMM launches of one step (ncu, one capture per kernel
+# change, scaled from the 4,096-token case to the workload's token count); None: no capture of the current kernels
+TRAFFIC_BYTES_PER_STEP = {}
+SUSTAINED_SECONDS = 2.0
 CPU_SAMPLE_TOKENS = 1024
 
 
@@ -72,7 +74,7 @@ class ClockSampler:
         except subprocess.TimeoutExpired:
             self.proc.kill()
         self.thread.join(timeout=2)
-        sm, mx, reasons = [], None, set()
+        sm, mx, reasons, power = [], None, set(), []
         names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
         for r in self.rows:
             if len(r) < 7:
@@ -80,14 +82,93 @@ class ClockSampler:
             try:
                 sm.append(float(r[0]))
                 mx = float(r[1])
+                power.append(float(r[2]))
             except ValueError:
                 continue
             for n, v in zip(names, r[3:7]):
                 if v.lower().startswith("active"):
                     reasons.add(n)
         sm.sort()
+        power.sort()
         return {"sm_mhz": sm[len(sm) // 2] if sm else None, "sm_max_mhz": mx, "samples": len(sm),
-                "reasons": sorted(reasons)}
+                "power_w": power[len(power) // 2] if power else None, "reasons": sorted(reasons)}
+
+
+def tokens_of_rank(w, rank, x0=None, dy0=None):
+    """(x, dy) of one rank, fp32 on the host: rank 0 uses the workload's canonical tokens, rank r > 0 its own seed."""
+    if rank == 0:
+        if x0 is None:
+            _, _, x0, dy0 = inputs.make_inputs(w, seed=0)
+        return x0, dy0
+    g = torch.Generator("cpu").manual_seed(1000 + rank)
+    shape = (w.batch, w.seq, w.D)
+    return torch.randn(shape, generator=g), torch.randn(shape, generator=g)
+
+
+def ep_parity(w, ep_layer, single, rank, world, dev, dist):
+    """One fwd+bwd of the expert-parallel layer (every rank on its own tokens) against the single-GPU layer holding
+    ALL experts, run by rank 0 over the tokens of all ranks.  Compared on rank 0: its y and dx rows, the routing of
+    its tokens, the global load histogram, the gradient of its expert shard (a sum over the tokens of all ranks)
+    and the replicated parameters' gradients summed over the ranks.  Returns the report dict on rank 0, None
+    elsewhere."""
+    from swamla_b200 import _cabi
+    x_host, dy_host = tokens_of_rank(w, rank)
+    xg = x_host.to(torch.bfloat16).to(dev).requires_grad_(True)
+    zero_grads(ep_layer, xg)
+    y = ep_layer(xg)
+    y.backward(dy_host.to(torch.bfloat16).to(dev))
+    status = 0
+    try:
+        ep_layer.check_status()
+    except _cabi.LmoeError as e:                        # keep going: the report carries the code
+        status = int(str(e).split("device status ")[1].split()[0])
+    replicated = {}
+    for name, p in ep_layer.named_parameters():
+        if not getattr(p, "expert_shard", False):
+            g = p.grad.float()
+            dist.all_reduce(g)
+            replicated[name] = g
+    st = torch.tensor([status], device=dev)
+    dist.all_reduce(st, op=dist.ReduceOp.MAX)
+    if rank != 0:
+        return None
+    from oracle.latent_moe_ref import closeness      # the checker's error report only; nothing of the oracle is timed
+    xs, dys = zip(*[tokens_of_rank(w, r) for r in range(world)])
+    xa = torch.cat([t.reshape(-1, w.D) for t in xs]).to(torch.bfloat16).to(dev).reshape(1, -1, w.D).requires_grad_(True)
+    dya = torch.cat([t.reshape(-1, w.D) for t in dys]).to(torch.bfloat16).to(dev).reshape(1, -1, w.D)
+    zero_grads(single, xa)
+    ya = single(xa)
+    ya.backward(dya)
+    single.check_status()
+    T, El = w.T, w.E // world
+    rep = {"status": int(st.item()), "tokens_compared": T, "tokens_single_gpu_run": T * world}
+    rep["routing_equal"] = bool(torch.equal(single.router._last_selected_experts[:T], ep_layer.router._last_selected_experts)
+                                and torch.equal(single.router._last_counts, ep_layer.router._last_counts))
+    rel = lambda a, b: closeness(a.float(), b.float(), 2e-2)
+    worst = 0.0
+    r_ = rel(y.detach().reshape(-1, w.D), ya.detach().reshape(-1, w.D)[:T]); rep["y_rel_fro"] = r_["rel_fro"]
+    worst = max(worst, r_["max_ratio"])
+    r_ = rel(xg.grad.reshape(-1, w.D), xa.grad.reshape(-1, w.D)[:T]); rep["dx_rel_fro"] = r_["rel_fro"]
+    worst = max(worst, r_["max_ratio"])
+    named1 = dict(single.named_parameters())
+    shard = 0.0
+    for name, p in ep_layer.named_parameters():
+        if getattr(p, "expert_shard", False):
+            r_ = rel(p.grad, named1[name].grad[:El])
+            shard = max(shard, r_["rel_fro"])
+            worst = max(worst, r_["max_ratio"])
+    rep["shard_grad_rel_fro"] = shard
+    dense = 0.0
+    for name, g in replicated.items():
+        r_ = rel(g, named1[name].grad)
+        dense = max(dense, r_["rel_fro"])
+        worst = max(worst, r_["max_ratio"])
+    rep["replicated_grad_rel_fro"] = dense
+    rep["max_elementwise_ratio_to_2e-2_bound"] = worst
+    rep["reference"] = "the same layer with all experts on one GPU (itself checked against the fp32 oracle in tests/)"
+    rep["ok"] = bool(rep["status"] == 0 and rep["routing_equal"] and worst <= 3.0 and
+                     max(rep["y_rel_fro"], rep["dx_rel_fro"], shard, dense) <= 1e-2)
+    return rep
 
 
 def build_layer(w, rank, device, ep_group=None, ep_mode="p2p_dedup"):
@@ -95,10 +176,7 @@ def build_layer(w, rank, device, ep_group=None, ep_mode="p2p_dedup"):
     With `ep_group` the routed experts are sharded: this rank keeps experts [rank*E/G, (rank+1)*E/G)."""
     from swamla_b200.layer import LatentMoELayer
     params, buffers, x, dy = inputs.make_inputs(w, seed=0)
-    if rank != 0:
-        g = torch.Generator("cpu").manual_seed(1000 + rank)
-        x = torch.randn(x.shape, generator=g)
-        dy = torch.randn(dy.shape, generator=g)
+    x, dy = tokens_of_rank(w, rank, x, dy)
     cfg = w.config()
     if w.dtype == "fp8":
         cfg.moe_fp8 = True          # routed expert GEMMs in e4m3 with per-tensor scaling (BASELINE cfg 4)
@@ -115,31 +193,6 @@ def build_layer(w, rank, device, ep_group=None, ep_mode="p2p_dedup"):
     layer.load_state_dict(state, strict=True)
     layer = layer.to(device).to(torch.bfloat16).train()
     return layer, x.to(torch.bfloat16), dy.to(torch.bfloat16)
-
-
-def print_timeline(layer, x, dy, rank, min_us=0.0):
-    """Device timeline of one eager fwd+bwd step after warm-up (CUDA activity records of torch.profiler): start offset,
-    duration and gap to the previous kernel, per kernel.  Diagnostic output (--timeline), not a benchmark line."""
-    from torch.profiler import ProfilerActivity, profile
-    for _ in range(4):
-        zero_grads(layer, x)
-        step(layer, x, dy)
-    torch.cuda.synchronize()
-    with profile(activities=[ProfilerActivity.CUDA]) as prof:
-        for _ in range(2):
-            zero_grads(layer, x)
-            step(layer, x, dy)
-        torch.cuda.synchronize()
-    evs = [e for e in prof.events() if e.device_type == torch.autograd.DeviceType.CUDA]
-    evs.sort(key=lambda e: e.time_range.start)
-    last = evs[len(evs) // 2:]                       # the second of the two profiled steps
-    t0 = prev = last[0].time_range.start
-    for e in last:
-        d = e.time_range.end - e.time_range.start
-        if d >= min_us:
-            print(f"r{rank} {e.time_range.start - t0:9.1f} us +{d:7.1f}  gap {e.time_range.start - prev:7.1f}  {e.name[:90]}")
-        prev = max(prev, e.time_range.end)
-    print(f"r{rank} step span {max(e.time_range.end for e in last) - t0:.1f} us, {len(last)} kernels", flush=True)
 
 
 def time_steps(layer, x, dy, steps, warmup):
@@ -233,10 +286,9 @@ def main():
     ap.add_argument("--workload", default=None)
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--no-sustained", action="store_true", help="skip the second, seconds-long timed region (N=1)")
     ap.add_argument("--ep-mode", default="p2p_dedup", choices=["p2p_dedup", "p2p", "nccl"])
     ap.add_argument("--no-graphs", action="store_true", help="eager launches instead of CUDA-graph replay (N=1)")
-    ap.add_argument("--timeline", action="store_true",
-                    help="print the per-kernel device timeline of one eager step (rank 0 and the last rank) and exit")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
 
@@ -259,33 +311,34 @@ def main():
     from swamla_b200 import _cabi
     lib = _cabi.load()
     same_workload_1gpu = None
-    if world > 1 and rank == 0:
-        # the same per-GPU workload on ONE GPU with all experts local: the denominator of the
-        # expert-parallel scaling efficiency (measured here because N=1 defaults to another workload)
-        l1, xh1, dyh1 = build_layer(w, 0, dev)
-        x1 = xh1.to(dev).requires_grad_(True)
-        ms1 = time_steps(l1, x1, dyh1.to(dev), max(3, args.steps // 2), args.warmup)
-        same_workload_1gpu = w.T / (ms1 * 1e-3)
-        del l1, x1, xh1, dyh1
-        torch.cuda.empty_cache()
+    parity = None
     layer, x_host, dy_host = build_layer(w, rank, dev, ep_group=dist.group.WORLD if world > 1 else None,
                                          ep_mode=args.ep_mode)
     x = x_host.to(dev).requires_grad_(True)
     dy = dy_host.to(dev)
-    if args.timeline:
-        if dist is not None:
-            dist.barrier()
-        if rank in (0, world - 1):
-            print_timeline(layer, x, dy, rank)
-        else:                                        # the other ranks run the same steps so that the exchange completes
-            for _ in range(6):
-                zero_grads(layer, x)
-                step(layer, x, dy)
-            torch.cuda.synchronize()
-        if dist is not None:
-            dist.barrier()
+    if world > 1:
+        # Before anything is timed: the expert-parallel step must reproduce the single-GPU layer on the real config.
+        l1 = xh1 = dyh1 = None
+        if rank == 0:
+            l1, xh1, dyh1 = build_layer(w, 0, dev)
+        parity = ep_parity(w, layer, l1, rank, world, dev, dist)
+        flag = torch.tensor([1 if (rank != 0 or parity["ok"]) else 0], device=dev)
+        dist.all_reduce(flag, op=dist.ReduceOp.MIN)
+        if flag.item() == 0:
+            if rank == 0:
+                print(json.dumps({"metric": METRIC, "error": "expert-parallel step does not match the single-GPU layer",
+                                  "ep_parity": parity, "n_gpus": world}))
             dist.destroy_process_group()
-        return
+            sys.exit(1)
+        if rank == 0:
+            # the same per-GPU workload on ONE GPU with all experts local: the denominator of the
+            # expert-parallel scaling efficiency (measured here because N=1 defaults to another workload)
+            x1 = xh1.to(dev).requires_grad_(True)
+            ms1 = time_steps(l1, x1, dyh1.to(dev), max(3, args.steps // 2), args.warmup)
+            same_workload_1gpu = w.T / (ms1 * 1e-3)
+            del l1, x1, xh1, dyh1
+            torch.cuda.empty_cache()
+        dist.barrier()
     use_graphs = world == 1 and not args.no_graphs
     eager_layer = layer
     if use_graphs:
@@ -320,6 +373,25 @@ def main():
     launches = lib.lmoe_launch_count() - launches0
     ms_total = ev0.elapsed_time(ev1)
     clocks = sampler.stop() if rank == 0 else None
+    # A second, longer measurement (N=1 only): blocks of `steps` steps back to back for about SUSTAINED_SECONDS, so that
+    # the GPU reaches the clocks it holds under a lasting load; median and best block, clocks and power sampled beside.
+    sustained = None
+    if world == 1 and not args.no_sustained:
+        n_blocks = max(10, int(SUSTAINED_SECONDS * 1e3 / max(ms_total, 1e-3)) + 1)
+        s2 = ClockSampler(local_rank)
+        s2.start()
+        evs = [torch.cuda.Event(enable_timing=True) for _ in range(n_blocks + 1)]
+        evs[0].record()
+        for b in range(n_blocks):
+            for _ in range(args.steps):
+                zero_grads(layer, x)
+                step(layer, x, dy)
+            evs[b + 1].record()
+        torch.cuda.synchronize()
+        c2 = s2.stop()
+        per = sorted(evs[b].elapsed_time(evs[b + 1]) / args.steps for b in range(n_blocks))
+        sustained = {"blocks": n_blocks, "steps_per_block": args.steps, "seconds": evs[0].elapsed_time(evs[-1]) * 1e-3,
+                     "ms_per_step_median": per[len(per) // 2], "ms_per_step_min": per[0], "clocks": c2}
     # per-launch timing of the GEMM kernel over a few extra steps (not part of the timed region)
     gemm_prof = None
     if rank == 0:
@@ -431,8 +503,8 @@ def main():
                 "achieved": gemm_tflops, "peak": pk["bf16_tflops"], "unit": "TFLOP/s",
                 "frac": None if gemm_tflops is None else gemm_tflops / pk["bf16_tflops"],
                 "traffic": TRAFFIC_BYTES_PER_STEP.get(w.name),
-                "traffic_note": "dram read+write bytes of the GEMM launches of one step, from an ncu capture "
-                                "(profiles/); null where no capture exists for this workload",
+                "traffic_note": "dram read+write bytes of all tcgen05 GEMM launches of one step from an ncu capture of "
+                                "the current kernels; null where none exists for this workload",
                 "gemm_ms_per_step": gemm_ms_step, "gemm_launches_per_step": gemm_launches,
                 "algorithmic_flops_per_step": flops_step,
                 "peak_source": f"{pk['source']} cuBLAS bf16 burst (sustained {pk['bf16_tflops_sustained']})",
@@ -454,10 +526,24 @@ def main():
                                   launch="CUDA graphs (forward, backward)" if use_graphs else "eager"),
         "clocks": clocks, "gpu_launches": int(launches), "roofline": roofline,
     }
+    if sustained is not None:
+        tps = w.T / (sustained["ms_per_step_median"] * 1e-3)
+        sustained["tokens_per_s_median"] = tps
+        sustained["step_tflops_median"] = tps * 3 * w.flops_fwd_per_token() / 1e12
+        if pk["bf16_tflops_sustained"]:
+            sustained["step_frac_of_sustained_peak"] = sustained["step_tflops_median"] / pk["bf16_tflops_sustained"]
+            sustained["peak_sustained_tflops"] = pk["bf16_tflops_sustained"]
+        out["sustained"] = sustained
     if e2e is not None:
         out["e2e"] = e2e
+    if parity is not None:
+        out["ep_parity"] = parity
     if same_workload_1gpu is not None:
         out["tokens_per_s_1gpu_same_workload"] = same_workload_1gpu
+        out["efficiency_same_workload"] = tokens_per_s / (world * same_workload_1gpu)
+        out["efficiency_note"] = ("efficiency_same_workload = value / (n_gpus x tokens_per_s_1gpu_same_workload): the same "
+                                  "per-GPU workload with all experts on one GPU, eager launches, measured in this run by "
+                                  "rank 0; the default N=1 line is another workload (cfg2, CUDA graphs)")
     if world == 1 and not args.no_cpu_baseline:
         threads = os.cpu_count() or 1
         v, secs = cpu_baseline(w, threads)

@@ -404,7 +404,8 @@ int lmoe_rmsnorm_bwd(const void* x, const float* weight, const float* rstd, cons
 
 /* ---- router bias update (after backward) ----
  * load = histogram(sel) (= counts); bias -= gamma * sign(load - T*K/E); history = .99 history + .01 load.
- * Replaces models/moe.py:254-275. */
+ * T*K is read from the histogram (sum of counts), so `counts` may be the sum of several ranks' histograms
+ * (expert parallelism) whatever their token counts; s->T is not used.  Replaces models/moe.py:254-275. */
 int lmoe_router_bias_update(const lmoe_shape* s, const int32_t* counts, float gamma, float* expert_bias,
                             float* load_history, void* stream);
 

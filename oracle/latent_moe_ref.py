@@ -53,7 +53,7 @@ def route_permute(sel: torch.Tensor, n_experts: int):
     """models/moe_triton.py:36-78 (fused_moe_routing), canonical order."""
     flat = sel.reshape(-1)
     counts = torch.bincount(flat, minlength=n_experts).to(torch.int64)         # moe_triton.py:60-62
-    offsets = torch.zeros(n_experts + 1, dtype=torch.int64)
+    offsets = torch.zeros(n_experts + 1, dtype=torch.int64, device=flat.device)
     offsets[1:] = torch.cumsum(counts, 0)                                      # moe_triton.py:65-66
     perm = torch.argsort(flat, stable=True)                                    # moe_triton.py:12-33,73-76
     return counts, offsets, perm

@@ -23,6 +23,7 @@
 
 #include "../../include/lmoe.h"
 #include "counters.h"
+#include "device_once.h"
 
 namespace lmoe {
 
@@ -294,14 +295,15 @@ static inline int epd_last_err() {
 // The exchange kernels run on a side stream beside GEMMs of the main stream.  An SM runs kernels with different
 // shared-memory carveouts only one after the other, so they ask for the GEMM kernel's (maximum) carveout.
 static void epd_configure() {
-  static bool done = false;
-  if (done) return;
+  static PerDeviceOnce once;
+  once.run([] {
   const int c = cudaSharedmemCarveoutMaxShared;
   cudaFuncSetAttribute(epd_send_kernel<true>, cudaFuncAttributePreferredSharedMemoryCarveout, c);
   cudaFuncSetAttribute(epd_send_kernel<false>, cudaFuncAttributePreferredSharedMemoryCarveout, c);
   cudaFuncSetAttribute(epd_reduce_return_kernel<true>, cudaFuncAttributePreferredSharedMemoryCarveout, c);
   cudaFuncSetAttribute(epd_reduce_return_kernel<false>, cudaFuncAttributePreferredSharedMemoryCarveout, c);
-  done = true;
+  return 0;
+  });
 }
 static inline bool epd_dims_ok(int K, int E, int G, int rank, int L, int64_t stride) {
   return K > 0 && K <= 32 && G > 0 && G <= 256 && E > 0 && (E % G) == 0 && rank >= 0 && rank < G && L > 0 &&

@@ -9,6 +9,7 @@
 
 #include "../../include/lmoe.h"
 #include "counters.h"
+#include "device_once.h"
 #include "gemm.cuh"
 #include "gemm_pair.cuh"
 #include "gemm_host.h"
@@ -36,14 +37,16 @@ static EncodeTiledFn encode_fn() {
 }
 
 int num_sms() {
-  static int n = 0;
-  if (n == 0) {
-    int dev = 0;
-    cudaGetDevice(&dev);
-    cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev);
-    if (n <= 0) n = 148;
-  }
-  return n;
+  static PerDeviceOnce once;
+  static int n[kMaxDevices] = {};
+  const int dev = current_device();
+  once.run([&] {
+    int v = 0;
+    if (cudaDeviceGetAttribute(&v, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || v <= 0) v = 148;
+    n[dev] = v;
+    return 0;
+  });
+  return n[dev];
 }
 
 // Operand map: 2-D over a row-major [outer, inner] tensor of 16-bit (esz 2) or 8-bit (esz 1) elements,
@@ -101,15 +104,16 @@ template <bool A_MN, bool B_MN, int BN, int EPI, int GRP, int ESZ>
 static int launch_inst(const GemmParams& p, int grid, cudaStream_t stream) {
   auto kfn = gemm_kernel<A_MN, B_MN, BN, EPI, GRP, ESZ>;
   constexpr int smem = GemmSmem<BN, EPI>::kTotal;
-  static bool configured = false;
-  if (!configured) {
-    cudaError_t e = cudaFuncSetAttribute(kfn, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
-    if (e != cudaSuccess) return static_cast<int>(e);
-    // ask for the largest shared-memory carveout so that what the GEMM leaves unused stays available to small
-    // kernels of other streams running beside it
-    cudaFuncSetAttribute(kfn, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
-    configured = true;
-  }
+  static PerDeviceOnce once;  // one per template instantiation
+  if (int rc = once.run([&] {
+        cudaError_t e = cudaFuncSetAttribute(kfn, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+        if (e != cudaSuccess) return static_cast<int>(e);
+        // ask for the largest shared-memory carveout so that what the GEMM leaves unused stays available to small
+        // kernels of other streams running beside it
+        cudaFuncSetAttribute(kfn, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
+        return 0;
+      }))
+    return rc;
   cudaEvent_t ev0 = nullptr, ev1 = nullptr;
   if (g_prof_enabled) {
     cudaEventCreate(&ev0);
@@ -181,8 +185,10 @@ template <bool A_MN, bool B_MN, int EPI>
 static int launch_pair_inst(const GemmParams& p, long long total_tiles, cudaStream_t stream) {
   auto kfn = gemm_pair_kernel<A_MN, B_MN, EPI>;
   constexpr int smem = PairSmem<EPI>::kTotal;
-  static int max_pairs = 0;
-  if (max_pairs == 0) {
+  static PerDeviceOnce once;  // one per template instantiation
+  static int max_pairs_dev[kMaxDevices] = {};
+  const int dev = current_device();
+  if (int rc = once.run([&] {
     cudaError_t e = cudaFuncSetAttribute(kfn, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
     if (e != cudaSuccess) return static_cast<int>(e);
     cudaFuncSetAttribute(kfn, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
@@ -203,8 +209,11 @@ static int launch_pair_inst(const GemmParams& p, long long total_tiles, cudaStre
       cudaGetLastError();
       n = num_sms() / 2;
     }
-    max_pairs = n;
-  }
+    max_pairs_dev[dev] = n;
+    return 0;
+  }))
+    return rc;
+  const int max_pairs = max_pairs_dev[dev];
   const int pairs = static_cast<int>(total_tiles < max_pairs ? total_tiles : max_pairs);
   cudaEvent_t ev0 = nullptr, ev1 = nullptr;
   if (g_prof_enabled) {

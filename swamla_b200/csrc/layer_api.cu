@@ -97,6 +97,8 @@ extern "C" const char* lmoe_status_string(int code) {
     case kStatusProducerTimeout: return "device: TMA producer wait timed out";
     case kStatusMmaTimeout: return "device: MMA issuer wait timed out";
     case kStatusEpilogueTimeout: return "device: epilogue wait timed out";
+    case 201: return "device: an expert-parallel shard received more rows than its buffers hold (raise ep_capacity_factor); "
+                     "the excess rows were dropped and the results of that step are wrong";
     default: return code > 0 ? cudaGetErrorString(static_cast<cudaError_t>(code)) : "unknown error";
   }
 }

@@ -8,6 +8,7 @@
 
 #include "../../include/lmoe.h"
 #include "counters.h"
+#include "device_once.h"
 
 namespace lmoe {
 
@@ -357,12 +358,25 @@ route_scatter_kernel(const int* __restrict__ sel, int n, int E, const int* __res
   }
 }
 
-// Router bias update from the routing histogram.
-__global__ void bias_update_kernel(const int* __restrict__ counts, int E, float expected, float gamma,
-                                   float* __restrict__ bias, float* __restrict__ history) {
-  const int e = blockIdx.x * blockDim.x + threadIdx.x;
+// Router bias update from the routing histogram.  The expected load per expert is taken from the histogram itself
+// (sum of the counts / E = tokens * K / E): a histogram summed over several ranks then gives the global figure
+// whatever the ranks' own token counts were.  One block; E <= LMOE_MAX_EXPERTS threads carry one expert each.
+__global__ void __launch_bounds__(LMOE_MAX_EXPERTS)
+bias_update_kernel(const int* __restrict__ counts, int E, float gamma, float* __restrict__ bias,
+                   float* __restrict__ history) {
+  __shared__ long long total_s;
+  const int e = threadIdx.x;
+  const int c = (e < E) ? counts[e] : 0;
+  if (e == 0) total_s = 0;
+  __syncthreads();
+  long long part = c;
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) part += __shfl_xor_sync(0xffffffffu, part, o);
+  if ((e & 31) == 0) atomicAdd(reinterpret_cast<unsigned long long*>(&total_s), static_cast<unsigned long long>(part));
+  __syncthreads();
   if (e >= E) return;
-  const float load = static_cast<float>(counts[e]);
+  const float expected = static_cast<float>(static_cast<double>(total_s) / static_cast<double>(E));
+  const float load = static_cast<float>(c);
   const float d = load - expected;
   const float sg = (d > 0.f) ? 1.f : ((d < 0.f) ? -1.f : 0.f);
   bias[e] -= gamma * sg;
@@ -377,8 +391,8 @@ static inline void prefer_max_carveout(F* fn) {
   cudaFuncSetAttribute(fn, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
 }
 static void configure_route_kernels() {
-  static bool done = false;
-  if (done) return;
+  static PerDeviceOnce once;
+  once.run([] {
   prefer_max_carveout(gate_topk_kernel);
   prefer_max_carveout(gate_topk_blocked_kernel<1>);
   prefer_max_carveout(gate_topk_blocked_kernel<2>);
@@ -388,7 +402,8 @@ static void configure_route_kernels() {
   prefer_max_carveout(route_hist_kernel);
   prefer_max_carveout(route_scan_chunks_kernel);
   prefer_max_carveout(route_scatter_kernel);
-  done = true;
+  return 0;
+  });
 }
 
 static inline int check_shape(const lmoe_shape* s) {
@@ -471,7 +486,6 @@ constexpr size_t kStaticRouteScratchInts = LMOE_STATIC_ROUTE_SCRATCH_BYTES / siz
 static __device__ __align__(256) int g_route_scratch[kStaticRouteScratchInts];
 
 namespace {
-constexpr int kMaxDevices = 64;
 std::mutex g_static_scratch_mutex;
 int* g_static_scratch_ptr[kMaxDevices] = {nullptr};
 
@@ -502,6 +516,7 @@ extern "C" int lmoe_route_permute_static(const lmoe_shape* s, const int32_t* sel
   if (lmoe_route_workspace_bytes(s) > LMOE_STATIC_ROUTE_SCRATCH_BYTES) return LMOE_ERR_TOO_LARGE;
   int* chunk_hist = nullptr;
   if (int rc = static_route_scratch(&chunk_hist)) return rc;
+  configure_route_kernels();
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   const int n = s->T * s->K;
   const int chunks = (n + kChunk - 1) / kChunk;
@@ -522,10 +537,9 @@ extern "C" int lmoe_router_bias_update(const lmoe_shape* s, const int32_t* count
                                        float* load_history, void* stream) {
   if (int rc = check_shape(s)) return rc;
   if (!counts || !expert_bias || !load_history) return LMOE_ERR_ARG;
-  const float expected = static_cast<float>(s->T) * static_cast<float>(s->K) / static_cast<float>(s->E);
   count_launch();
-  bias_update_kernel<<<(s->E + 127) / 128, 128, 0, static_cast<cudaStream_t>(stream)>>>(counts, s->E, expected, gamma,
-                                                                                        expert_bias, load_history);
+  bias_update_kernel<<<1, LMOE_MAX_EXPERTS, 0, static_cast<cudaStream_t>(stream)>>>(counts, s->E, gamma, expert_bias,
+                                                                                    load_history);
   cudaError_t e = cudaGetLastError();
   return e == cudaSuccess ? 0 : static_cast<int>(e);
 }

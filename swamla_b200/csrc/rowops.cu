@@ -7,6 +7,7 @@
 
 #include "../../include/lmoe.h"
 #include "counters.h"
+#include "device_once.h"
 #include "rowops.h"
 
 namespace lmoe {
@@ -262,11 +263,11 @@ extern "C" int lmoe_gate_topk_bwd(const lmoe_shape* s, const float* logits, cons
   if (s->E > LMOE_MAX_EXPERTS || s->K > 32) return LMOE_ERR_SHAPE;
   const long long ld = 2ll * s->Fs + s->L + s->E;
   __nv_bfloat16* d_logits = static_cast<__nv_bfloat16*>(dgrad_cat) + 2ll * s->Fs + s->L;
-  static bool configured = false;
-  if (!configured) {  // same shared-memory carveout as the GEMM kernel it runs beside
+  static PerDeviceOnce once;
+  once.run([] {  // same shared-memory carveout as the GEMM kernel it runs beside
     cudaFuncSetAttribute(gate_bwd_kernel, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
-    configured = true;
-  }
+    return 0;
+  });
   gate_bwd_kernel<<<grid_for(s->T, kRowWarps), kRowWarps * 32, 0, static_cast<cudaStream_t>(stream)>>>(
       logits, sel, weights, d_weights, lse, d_z, z_coef / static_cast<float>(s->T), s->T, s->E, s->K, d_logits, ld);
   return last_error();

@@ -22,7 +22,7 @@ from typing import List, Tuple
 import torch
 import torch.distributed as dist
 
-from . import _cabi
+from . import _cabi, status as status_monitor
 from ._cabi import Route, ptr
 from .functional import BF, RouteTables, _as_bf16, _stream, make_shape
 
@@ -55,6 +55,27 @@ def ddp_ignore_expert_shards(model: torch.nn.Module, average_like_ddp: bool = Tr
                     p_.register_hook(lambda g, s=scale: g * s)
                     p_._ep_grad_hook = True
     return names
+
+
+def gather_full_state_dict(model: torch.nn.Module) -> dict:
+    """``model.state_dict()`` with every expert shard replaced by the full [E_global, ...] tensor of the reference's
+    layout (``models/moe.py:582-586``), identical on every rank.  A COLLECTIVE: every rank of each layer's
+    expert-parallel group must call it (``model.state_dict()`` itself is local and returns the rank's block).  In the
+    reference's loop (``train.py:1470-1506``) call it on all ranks before the ``master_process`` guard and save the
+    result on rank 0."""
+    state = model.state_dict()
+    for prefix, mod in model.named_modules():
+        group = getattr(mod, "ep_group", None)
+        if group is None or not hasattr(mod, "gate_up_weight") or getattr(mod, "ep_size", 1) == 1:
+            continue
+        for name in ("gate_up_weight", "down_weight"):
+            key = f"{prefix}.{name}" if prefix else name
+            shard = state[key].detach().contiguous()
+            full = torch.empty((mod.ep_size * shard.shape[0],) + tuple(shard.shape[1:]), dtype=shard.dtype,
+                               device=shard.device)
+            dist.all_gather_into_tensor(full, shard, group=group)           # rank order = expert order
+            state[key] = full
+    return state
 
 
 def splits_from_counts(counts_all: torch.Tensor, rank: int) -> Tuple[List[int], List[int]]:
@@ -166,6 +187,7 @@ class ExpertParallelLatentMoE(torch.autograd.Function):
                               h1_s, x_sorted, h1, hidden, recv_pos, row_src, pad_offsets, tile_expert, n_tiles)
         global_counts = counts_all.sum(0, dtype=torch.int32)
         ctx.mark_non_differentiable(sel, global_counts)
+        status_monitor.post(status, "expert-parallel LatentMoE forward")
         out = y if x.dtype == BF else y.to(x.dtype)
         return out, z_loss.reshape(()), sel, global_counts
 
@@ -239,6 +261,8 @@ class ExpertParallelLatentMoE(torch.autograd.Function):
         d_w_gate = torch.empty(E, D, **lin)
         _cabi.call("lmoe_xside_bwd", shape, ptr(dgrad_cat), ptr(wgus), ptr(wdn), ptr(wg), ptr(xb), ptr(dx),
                    ptr(d_w_gate_up_s), ptr(d_w_down), ptr(d_w_gate), gtype, ptr(ws), ws.numel(), ptr(status), st)
+
+        status_monitor.post(status, "expert-parallel LatentMoE backward")
 
         def as_param(g, d):
             return g if g.dtype == d else g.to(d)
@@ -390,6 +414,7 @@ class ExpertParallelP2P(torch.autograd.Function):
                               hidden, counts_all, src_off, dst_base, seg_cum, pad_offsets, tile_expert, n_tiles)
         global_counts = counts_all.sum(0, dtype=torch.int32)
         ctx.mark_non_differentiable(sel, global_counts)
+        status_monitor.post(status, "expert-parallel LatentMoE forward")
         out = y if x.dtype == BF else y.to(x.dtype)
         return out, z_loss.reshape(()), sel, global_counts
 
@@ -473,6 +498,8 @@ class ExpertParallelP2P(torch.autograd.Function):
         d_w_gate = torch.empty(E, D, **lin)
         _cabi.call("lmoe_xside_bwd", shape, ptr(dgrad_cat), ptr(wgus), ptr(wdn), ptr(wg), ptr(xb), ptr(dx),
                    ptr(d_w_gate_up_s), ptr(d_w_down), ptr(d_w_gate), gtype, ptr(ws), ws.numel(), ptr(status), st)
+
+        status_monitor.post(status, "expert-parallel LatentMoE backward")
 
         def as_param(g, d):
             return g if g.dtype == d else g.to(d)
@@ -633,6 +660,7 @@ class ExpertParallelDedup(torch.autograd.Function):
                               hidden, y_sorted, counts_all, src_off, seg_cum, pad_offsets, tile_expert, n_tiles)
         global_counts = counts_all.sum(0, dtype=torch.int32)
         ctx.mark_non_differentiable(sel, global_counts)
+        status_monitor.post(status, "expert-parallel LatentMoE forward")
         out = y if x.dtype == BF else y.to(x.dtype)
         return out, z_loss.reshape(()), sel, global_counts
 
@@ -718,6 +746,8 @@ class ExpertParallelDedup(torch.autograd.Function):
         d_w_gate = torch.empty(E, D, **lin)
         _cabi.call("lmoe_xside_bwd", shape, ptr(dgrad_cat), ptr(wgus), ptr(wdn), ptr(wg), ptr(xb), ptr(dx),
                    ptr(d_w_gate_up_s), ptr(d_w_down), ptr(d_w_gate), gtype, ptr(ws), ws.numel(), ptr(status), st)
+
+        status_monitor.post(status, "expert-parallel LatentMoE backward")
 
         def as_param(g, d):
             return g if g.dtype == d else g.to(d)

@@ -11,16 +11,11 @@ from typing import Optional
 
 import torch
 
-from . import _cabi
+from . import _cabi, _testing, status as status_monitor
 from ._cabi import Route, Shape, ptr
 
 BF = torch.bfloat16
 
-# When set to a dict, the next forward/backward stores its intermediates there (parity tests).
-DEBUG_SINK: Optional[dict] = None
-# Test hook: an int [T, K] tensor that replaces the top-k selection of the next forward, so that the
-# float path can be compared with a reference run whose near-tie selections differ.
-DEBUG_FORCE_SEL: Optional[torch.Tensor] = None
 # SwiGLU adjoint inside the epilogue of the dgrad GEMMs (no d_hidden round trip) instead of a streaming kernel.
 # Off by default: the epilogue's row-wise reads of the saved gate/up are uncoalesced and the fused kernel measured
 # slower than GEMM + streaming kernel (cfg2: 164 us vs 37 + 90 us for the routed experts).
@@ -102,7 +97,8 @@ def make_shape(T, D, L, E, K, F, Fs, n_shared=1) -> Shape:
 
 
 def check_status(status: torch.Tensor) -> None:
-    """Reads the device status word (synchronises); raises if a kernel wait gave up."""
+    """Reads one device status word now (synchronises); raises if a kernel reported a failure.  The layers use the
+    non-blocking monitor in ``status.py`` instead; this form serves tests and callers of the functional API."""
     code = int(status.item())
     if code != 0:
         raise _cabi.LmoeError(f"device status {code}: {_cabi.status_string(code)}")
@@ -151,19 +147,16 @@ class LatentMoEFunction(torch.autograd.Function):
         P = route.padded_rows
         ws = torch.empty(max(16, lib.lmoe_route_workspace_bytes(shape)), dtype=torch.uint8, device=dev)
         gather = TMA_GATHER and not fp8 and L % 128 == 0   # whole 128-column tiles of the weight gradient
-        x_sorted = None if (gather and DEBUG_SINK is None) else torch.empty(P, L, **bf)
+        x_sorted = None if (gather and not _testing.capturing()) else torch.empty(P, L, **bf)
         h1_s = torch.empty(T, 2 * Fs, **bf)
         act_cat = torch.empty(T, L + Fs, **bf)
-        if DEBUG_FORCE_SEL is not None:
-            forced = DEBUG_FORCE_SEL.to(device=dev, dtype=torch.int32).contiguous()
-            aff = torch.sigmoid(logits).gather(1, forced.long())
-            forced_w = (aff / (aff.sum(-1, keepdim=True) + 1e-9)).contiguous()
         # One stream in forward: the routing kernels use static shared memory that does not fit on an SM beside a GEMM
         # CTA, so on a second stream they would only wait for the shared-expert GEMM to drain.
         _cabi.call("lmoe_gate_topk_fwd", shape, ptr(logits), ptr(bias), float(z_coef), ptr(sel), ptr(weights), ptr(lse),
                    ptr(z_partial), ptr(z_loss), st)
-        if DEBUG_FORCE_SEL is not None:
-            sel, weights = forced, forced_w
+        forced = _testing.forced_selection(logits)
+        if forced is not None:
+            sel, weights = forced
         _cabi.call("lmoe_route_permute", shape, ptr(sel), route.struct, ptr(ws), ws.numel(), st)
         if x_sorted is not None:
             _cabi.call("lmoe_gather_rows", ptr(x_latent), ptr(route.row_src), top_k, P, L, ptr(route.n_tiles),
@@ -210,10 +203,10 @@ class LatentMoEFunction(torch.autograd.Function):
                                   x_latent_ext if gather else x_sorted, h1, hidden, y_sorted, act_cat, h1_s)
         ctx.gather = gather
         ctx.mark_non_differentiable(sel, route.counts)
-        if DEBUG_SINK is not None:
-            DEBUG_SINK.update(logits=logits, x_latent=x_latent, sel=sel, weights=weights, lse=lse, route=route,
-                              x_sorted=x_sorted, h1=h1, hidden=hidden, y_sorted=y_sorted, h1_s=h1_s, hidden_s=hidden_s,
-                              routed=routed, status=status)
+        _testing.capture(logits=logits, x_latent=x_latent, sel=sel, weights=weights, lse=lse, route=route,
+                         x_sorted=x_sorted, h1=h1, hidden=hidden, y_sorted=y_sorted, h1_s=h1_s, hidden_s=hidden_s,
+                         routed=routed, status=status)
+        status_monitor.post(status, "LatentMoE forward")
         out = y if x.dtype == BF else y.to(x.dtype)
         return out, z_loss.reshape(()), sel, route.counts
 
@@ -304,9 +297,9 @@ class LatentMoEFunction(torch.autograd.Function):
         _cabi.call("lmoe_xside_bwd", shape, ptr(dgrad_cat), ptr(wgus), ptr(wdn), ptr(wg), ptr(xb), ptr(dx),
                    ptr(d_w_gate_up_s), ptr(d_w_down), ptr(d_w_gate), gtype, ptr(ws), ws.numel(), ptr(status), st)
 
-        if DEBUG_SINK is not None:
-            DEBUG_SINK.update(d_routed=d_routed, d_h1_s=d_h1_s, d_y_sorted=d_y_sorted, d_weights=d_weights, d_h1=d_h1,
-                              d_x_sorted=d_x_sorted, d_x_latent=d_x_latent, d_logits=d_logits)
+        _testing.capture(d_routed=d_routed, d_h1_s=d_h1_s, d_y_sorted=d_y_sorted, d_weights=d_weights, d_h1=d_h1,
+                         d_x_sorted=d_x_sorted, d_x_latent=d_x_latent, d_logits=d_logits)
+        status_monitor.post(status, "LatentMoE backward")
         def as_param(g, d):
             return g if g.dtype == d else g.to(d)
 

@@ -65,10 +65,9 @@ class MoEFunction(torch.autograd.Function):
         z_loss = torch.empty(1, **f32)
         _cabi.call("lmoe_gate_topk_fwd", shape, ptr(logits), ptr(bias), float(z_coef), ptr(sel), ptr(weights), ptr(lse),
                    ptr(z_partial), ptr(z_loss), st)
-        if functional.DEBUG_FORCE_SEL is not None:      # test hook: replace the selection (near-tie comparisons)
-            sel = functional.DEBUG_FORCE_SEL.to(device=dev, dtype=torch.int32).contiguous()
-            aff = torch.sigmoid(logits).gather(1, sel.long())
-            weights = (aff / (aff.sum(-1, keepdim=True) + 1e-9)).contiguous()
+        forced = functional._testing.forced_selection(logits)      # parity tests only
+        if forced is not None:
+            sel, weights = forced
         route = RouteTables(shape, dev)
         P = route.padded_rows
         ws = torch.empty(max(16, lib.lmoe_route_workspace_bytes(shape)), dtype=torch.uint8, device=dev)
@@ -98,6 +97,7 @@ class MoEFunction(torch.autograd.Function):
         ctx.save_for_backward(xb, wg, wgus, wds, wgu, wde, logits, sel, weights, lse, x_sorted, h1, hidden, y_sorted, h1_s,
                               hidden_s)
         ctx.mark_non_differentiable(sel, route.counts)
+        functional.status_monitor.post(status, "MoE forward")
         out = y if x.dtype == BF else y.to(x.dtype)
         return out, z_loss.reshape(()), sel, route.counts
 
@@ -162,6 +162,7 @@ class MoEFunction(torch.autograd.Function):
         def as_param(g, d):
             return g if g.dtype == d else g.to(d)
 
+        functional.status_monitor.post(status, "MoE backward")
         return (as_param(dx, dt[0]), as_param(d_w_gate, dt[1]), as_param(d_w_gate_up_s, dt[2]),
                 as_param(d_w_down_s, dt[3]), as_param(d_w_gate_up, dt[4]), as_param(d_w_down_e, dt[5]), None, None, None)
 

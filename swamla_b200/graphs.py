@@ -27,7 +27,9 @@ class _Core(nn.Module):
 class GraphedLatentMoE(nn.Module):
     """``GraphedLatentMoE(layer, sample_x)(x)``: same result as ``layer(x)`` for inputs of ``sample_x``'s shape and
     dtype.  ``layer.aux_loss``, ``router._last_selected_experts`` and ``router._last_counts`` refer to static buffers
-    that every replay overwrites.  Parameters must keep their storage (in-place optimizer updates are fine)."""
+    that every replay overwrites; they are attached to the router again on every training-mode call, so the
+    reference's per-step ``update_bias_from_last_forward()`` (``models/moe.py:244-252``, which clears them) keeps
+    working across replays.  Parameters must keep their storage (in-place optimizer updates are fine)."""
 
     def __init__(self, layer, sample_x: torch.Tensor, num_warmup_iters: int = 3):
         super().__init__()
@@ -35,11 +37,20 @@ class GraphedLatentMoE(nn.Module):
             raise ValueError("graph replay is for single-GPU layers (expert-parallel steps issue collectives)")
         self.layer = layer
         sample = sample_x.detach().clone().requires_grad_(True)
+        was_training = layer.training
+        layer.train()                      # capture in training mode so that the routing outputs are recorded
         self._graphed = torch.cuda.make_graphed_callables(_Core(layer), (sample,), num_warmup_iters=num_warmup_iters)
+        r = layer.router
+        # static buffers of the captured forward: every replay rewrites them in place
+        self._static = (r._last_selected_experts, r._last_counts, r._last_num_tokens)
+        layer.train(was_training)
 
     def forward(self, x: torch.Tensor) -> torch.Tensor:
         y, aux = self._graphed(x)
         self.layer.aux_loss = aux
+        if self.layer.training:
+            r = self.layer.router
+            r._last_selected_experts, r._last_counts, r._last_num_tokens = self._static
         return y
 
     def get_aux_loss(self):

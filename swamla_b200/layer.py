@@ -10,7 +10,7 @@ from __future__ import annotations
 import torch
 import torch.nn as nn
 
-from . import _cabi
+from . import _cabi, status as status_monitor
 from .functional import latent_moe, make_shape, _stream
 
 
@@ -40,10 +40,12 @@ class LatentBatchedExperts(nn.Module):
     ``gate_up_weight`` [E, latent, 2*d_ff] and ``down_weight`` [E, d_ff, latent].
 
     Under expert parallelism (``ep_group`` of G ranks) the parameters hold this rank's contiguous block of
-    ``n_experts`` = E_global / G experts, while ``state_dict`` keeps the reference's layout: saving gathers the
-    blocks of all ranks into the full [E_global, ...] tensors (a collective: every rank of the group calls
-    ``state_dict()``), loading accepts the full tensors (each rank takes its block) or block-shaped ones.  So a
-    checkpoint written by the reference (``train.py:1470-1506``) loads into any group size and the other way round."""
+    ``n_experts`` = E_global / G experts.  ``state_dict()`` issues NO collective: it returns this rank's block, so
+    the reference's rank-0-only save (``train.py:1471,1486``) cannot hang the other ranks; the checkpoint in the
+    reference's layout (full [E_global, ...] tensors) comes from ``ep.gather_full_state_dict(model)``, which every
+    rank of the group calls.  Loading accepts the full tensors (each rank takes its block) or block-shaped ones, so
+    a checkpoint written by the reference (``train.py:1470-1506``) loads into any group size and the other way
+    round."""
 
     def __init__(self, n_experts: int, latent_dim: int, d_ff: int, bias: bool = False, ep_group=None):
         super().__init__()
@@ -67,18 +69,6 @@ class LatentBatchedExperts(nn.Module):
     def _ep_rank(self) -> int:
         import torch.distributed as dist
         return dist.get_rank(self.ep_group)
-
-    def _save_to_state_dict(self, destination, prefix, keep_vars):
-        super()._save_to_state_dict(destination, prefix, keep_vars)
-        if self.ep_size == 1:
-            return
-        import torch.distributed as dist
-        for name in ("gate_up_weight", "down_weight"):
-            shard = getattr(self, name).detach().contiguous()
-            full = torch.empty((self.ep_size * shard.shape[0],) + tuple(shard.shape[1:]), dtype=shard.dtype,
-                               device=shard.device)
-            dist.all_gather_into_tensor(full, shard, group=self.ep_group)   # rank order = expert order
-            destination[prefix + name] = full
 
     def _load_from_state_dict(self, state_dict, prefix, local_metadata, strict, missing_keys, unexpected_keys,
                               error_msgs):
@@ -114,7 +104,10 @@ class AuxLossFreeRouter(nn.Module):
         """``models/moe.py:244-275``: bias -= gamma * sign(load - T*K/E), after backward."""
         if self._last_counts is None:
             return
+        status_monitor.poll()            # a step whose kernels reported a failure raises here (or at the next forward)
         counts, T = self._last_counts, self._last_num_tokens
+        # the kernel takes the expected load T*K/E from the histogram itself (sum of counts / E), so a histogram
+        # summed over expert-parallel ranks with different token counts gives the same update on every rank
         shape = make_shape(T, 8, 64, self.n_experts, self.top_k, 64, 8)
         if self.expert_bias.dtype != torch.float32 or self.load_history.dtype != torch.float32:
             # inference-style casts of the buffers: update in fp32, store back
@@ -224,6 +217,7 @@ class LatentMoELayer(nn.Module):
             raise ValueError("kernel constraints: at most 256 routed experts and top-32")
 
     def forward(self, x: torch.Tensor) -> torch.Tensor:
+        status_monitor.poll()            # raises if an earlier step's kernels reported a failure (no synchronisation)
         batch_size, seq_len, d_model = x.shape
         x_flat = x.reshape(-1, d_model)
         shared = self.shared_experts[0]
@@ -256,9 +250,14 @@ class LatentMoELayer(nn.Module):
         if self.training:                                                 # moe.py:237-240
             self.router._last_selected_experts = sel
             self.router._last_counts = counts
-            self.router._last_num_tokens = x_flat.shape[0] * self.ep_size
+            self.router._last_num_tokens = x_flat.shape[0]
         y = self.dropout(y)                                               # moe.py:732
         return y.view(batch_size, seq_len, d_model)
+
+    def check_status(self) -> None:
+        """Waits for the steps queued so far and raises ``LmoeError`` if one of them reported a device failure
+        (a bounded wait that expired, or an expert-parallel shard that received more rows than its buffers hold)."""
+        status_monitor.poll(block=True)
 
     def get_aux_loss(self) -> torch.Tensor:
         return self.aux_loss
@@ -317,8 +316,13 @@ class MoELayer(nn.Module):
         if n_experts > 256 or n_activated > 32:
             raise ValueError("kernel constraints: at most 256 routed experts and top-32")
 
+    def check_status(self) -> None:
+        """Waits for the steps queued so far and raises ``LmoeError`` if one of them reported a device failure."""
+        status_monitor.poll(block=True)
+
     def forward(self, x: torch.Tensor) -> torch.Tensor:
         from .functional_moe import moe
+        status_monitor.poll()
         batch_size, seq_len, d_model = x.shape
         x_flat = x.reshape(-1, d_model)
         shared = self.shared_experts[0]

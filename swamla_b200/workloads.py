@@ -91,6 +91,8 @@ WORKLOADS: Dict[str, Workload] = {
     "cfg3": Workload("cfg3", expert_dim=3072, batch=32, seq=2048, dtype="bf16", zipf_s=1.2),
     "cfg4": Workload("cfg4", batch=64, seq=2048, dtype="fp8"),
     "cfg5": Workload("cfg5", n_experts=64, n_activated=4, batch=16, seq=2048, dtype="bf16", uniform_gate=True),
+    # cfg5's layer (E=256, top-16, uniform gate) on a token count the CPU oracle finishes in seconds
+    "cfg5_2k": Workload("cfg5_2k", n_experts=64, n_activated=4, batch=1, seq=2048, dtype="bf16", uniform_gate=True),
     # secondary reading of the benchmark text: 32 experts / top-3 (64 / top-4) taken literally as the layer's counts
     "cfg2_literal": Workload("cfg2_literal", batch=8, seq=2048, dtype="bf16", literal_counts=True),
     "cfg5_literal": Workload("cfg5_literal", n_experts=64, n_activated=4, batch=16, seq=2048, dtype="bf16",

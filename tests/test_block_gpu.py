@@ -127,13 +127,13 @@ def test_block_with_moe_layer_matches_oracle(name):
         for p_ in block.parameters():
             p_.grad = None
         xg = x.to("cuda:0").to(torch.bfloat16).requires_grad_(True)
-        functional.DEBUG_FORCE_SEL = force
+        functional._testing.FORCE_SEL = force
         try:
             out = block(xg)
             (out.float() * dy.to("cuda:0").to(torch.bfloat16).float()).sum().backward()
             torch.cuda.synchronize()
         finally:
-            functional.DEBUG_FORCE_SEL = None
+            functional._testing.FORCE_SEL = None
         return out, xg
 
     ref_out, ref_dx, ref_grads, ref_sel = oracle()

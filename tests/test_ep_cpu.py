@@ -105,8 +105,13 @@ def _ckpt_worker(rank, world, port, tmpdir):
         for name in ("gate_up_weight", "down_weight"):
             assert torch.equal(getattr(layer.experts, name), params["experts." + name][rank * El:(rank + 1) * El])
         assert full_state["experts.gate_up_weight"].shape[0] == w.E              # the caller's dict is untouched
-        # saving gathers the blocks back into the reference layout, identical on every rank
-        saved = layer.state_dict()
+        # state_dict() is local (no collective: a rank-0-only save cannot hang) and returns this rank's block
+        local = layer.state_dict()
+        assert set(local) == set(full_state)
+        assert torch.equal(local["experts.down_weight"], params["experts.down_weight"][rank * El:(rank + 1) * El])
+        # the collective helper gathers the blocks back into the reference layout, identical on every rank
+        from swamla_b200.ep import gather_full_state_dict
+        saved = gather_full_state_dict(layer)
         assert set(saved) == set(full_state)
         for k, v in full_state.items():
             assert saved[k].shape == v.shape and torch.equal(saved[k].to(v.dtype), v), k

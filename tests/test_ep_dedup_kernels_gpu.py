@@ -17,7 +17,7 @@ def _ptrs(tensors, dev):
 class _Ranks:
     """G ranks' inputs, tables and exchange buffers on one device."""
 
-    def __init__(self, G, E, K, L, tokens, seed):
+    def __init__(self, G, E, K, L, tokens, seed, capacity_factor=2.0):
         from swamla_b200 import _cabi
         from swamla_b200.functional import RouteTables, make_shape
         self.G, self.E, self.K, self.L, self.El = G, E, K, L, E // G
@@ -27,7 +27,7 @@ class _Ranks:
         i32, f32 = dict(dtype=torch.int32, device=dev), dict(dtype=torch.float32, device=dev)
         self.T = tokens
         self.stride = max(tokens)
-        self.P = (2 * self.stride * K + 127) // 128 * 128 + self.El * 128
+        self.P = (int(capacity_factor * self.stride * K) + 127) // 128 * 128 + self.El * 128
         self.sel = [torch.stack([torch.randperm(E, generator=g)[:K] for _ in range(t)]).to(torch.int32) for t in tokens]
         self.w = [torch.rand(t, K, generator=g) + 0.1 for t in tokens]
         self.x = [torch.randn(t, L, generator=g).to(BF) for t in tokens]
@@ -62,9 +62,12 @@ class _Ranks:
             self.route.append(route)
             self.inv.append(inv)
             self.tab.append(t)
-        self.cpu_tables = [ep_ref.dedup_send_tables(self.sel[r].long(), self.w[r], self.counts_all_cpu, r) for r in range(G)]
+        self.cpu_tables = None
+        if capacity_factor >= 2.0:       # the CPU statement of the contract describes layouts that fit
+            self.cpu_tables = [ep_ref.dedup_send_tables(self.sel[r].long(), self.w[r], self.counts_all_cpu, r)
+                               for r in range(G)]
 
-    def send(self, with_meta):
+    def send(self, with_meta, expect_status=0):
         from swamla_b200 import _cabi
         G, E, K, L = self.G, self.E, self.K, self.L
         stage = self.stage_x if with_meta else self.stage_dy
@@ -82,7 +85,7 @@ class _Ranks:
                            K, E, G, r, L, self.P, self.stride, p_stage.data_ptr(), None, None, None, self.status.data_ptr(),
                            self.st)
         torch.cuda.synchronize()
-        assert self.status.item() == 0
+        assert self.status.item() == expect_status
 
     def gather(self, r, y_sorted=None):
         from swamla_b200 import _cabi
@@ -205,3 +208,32 @@ def test_dedup_exchange_kernels_match_contract(G, E, K, L, tokens):
         assert err <= 2.0 ** -7 * exp.abs().max().item(), err
         assert torch.equal(R.dw[s][:tokens[s] * K].view(tokens[s], K).cpu(), exp_dw)   # gating gradients are copies
     assert R.status.item() == 0
+
+
+def test_shard_overflow_raises_status_201_and_drops_rows_without_faulting():
+    """A shard that receives more rows than its static capacity: the tables kernel and the send kernel both raise
+    device status 201, every access stays inside the buffers (excess rows are dropped by bounds checks), and the host
+    side turns the status into an exception."""
+    from swamla_b200 import _cabi, status as status_monitor
+    G, E, K, L = 2, 16, 8, 128
+    tokens = (600, 500)                                     # ~550 rows per expert -> 5120 padded rows per shard
+    R = _Ranks(G, E, K, L, tokens, seed=5, capacity_factor=0.3)
+    assert R.P < 5120                                       # capacity 2560 rows: the layout cannot fit
+    assert R.status.item() == 201                           # raised by lmoe_ep_tables already
+    R.status.zero_()
+    R.send(with_meta=True, expect_status=201)               # ... and by the send kernel for the rows it drops
+    for r in range(G):
+        used = int(R.tab[r]["n_tiles"].item()) * 128
+        assert used <= R.P
+        x_in, _ = R.gather(r)                               # bounded by the capacity; rows that fit are exact copies
+        meta = R.meta[r].cpu()
+        slot = (meta & 0xffffffff).to(torch.int32).long()
+        ok = (slot >= 0)[:used]
+        assert ok.any()
+        stage = R.stage_x[r].float().cpu()
+        assert torch.equal(x_in[:used].float().cpu()[ok], stage[slot[:used][ok]])
+    assert "more rows than its buffers hold" in _cabi.status_string(201)
+    status_monitor.post(R.status, "overflow test")
+    with pytest.raises(_cabi.LmoeError, match="201"):
+        status_monitor.poll(block=True)
+    assert status_monitor.pending() == 0

@@ -79,6 +79,7 @@ def _ep_worker(rank, world, port, tmpdir, mode):
             outs.append((y.detach(), xg.grad, layer))
         torch.cuda.synchronize()
         (y1, dx1, l1), (y2, dx2, l2) = outs
+        l2.check_status()                           # no overflow (201), no expired wait (101-103) on any step
         # routing is local and identical; a row's result does not depend on where it sits in an expert's segment
         assert torch.equal(l1.router._last_selected_experts, l2.router._last_selected_experts)
         dense = ("router.gate.weight", "down_proj.weight", "up_proj.weight", "shared_experts.0.gate_up_proj.weight",
@@ -108,6 +109,12 @@ def _ep_worker(rank, world, port, tmpdir, mode):
         c1 = l1.router._last_counts.clone()
         dist.all_reduce(c1)
         assert torch.equal(c1, l2.router._last_counts)
+        # the ranks hold different token counts (200 vs 257): the bias update takes the expected load from the summed
+        # histogram, so the replicated selection bias stays identical on every rank
+        l2.router.update_bias_from_last_forward()
+        biases = [torch.empty_like(l2.router.expert_bias) for _ in range(world)]
+        dist.all_gather(biases, l2.router.expert_bias)
+        assert all(torch.equal(b_, biases[0]) for b_ in biases) and biases[0].abs().max().item() > 0
         open(os.path.join(tmpdir, f"ok{rank}"), "w").write("ok")
     finally:
         dist.destroy_process_group()

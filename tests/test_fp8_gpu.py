@@ -67,13 +67,13 @@ def test_layer_fp8_experts(aux_grad):
     layer = layer.to("cuda:0").to(torch.bfloat16).train()
     xg = x.to("cuda:0").to(torch.bfloat16).requires_grad_(True)
     sink = {}
-    functional.DEBUG_SINK = sink
+    functional._testing.SINK = sink
     try:
         y = layer(xg)
         ((y.float() * dy.to("cuda:0").to(torch.bfloat16).float()).sum() + aux_grad * layer.get_aux_loss()).backward()
         torch.cuda.synchronize()
     finally:
-        functional.DEBUG_SINK = None
+        functional._testing.SINK = None
     assert sink["status"].item() == 0
     sel = sink["sel"].cpu().long()
     pr = {k: inputs.round_to_bf16(v) for k, v in params.items()}

@@ -38,3 +38,11 @@ def test_graph_replay_matches_eager_bit_for_bit():
         assert torch.equal(y1, y2) and torch.equal(dx1, dx2) and torch.equal(a1, a2) and torch.equal(c1, c2), it
         for k in g1:
             assert torch.equal(g1[k], g2[k]), (it, k)
+        # the reference's training loop updates the selection bias after every backward (models/moe.py:244-252);
+        # the update clears the router's "last forward" state, which a replay must attach again
+        for layer in (eager, captured):
+            layer.router.update_bias_from_last_forward()
+        for name in ("expert_bias", "load_history", "update_count"):
+            assert torch.equal(getattr(eager.router, name), getattr(captured.router, name)), (it, name)
+        assert int(captured.router.update_count) == it + 1
+    assert eager.router.expert_bias.abs().max().item() > 0

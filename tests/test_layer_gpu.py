@@ -45,10 +45,10 @@ def assert_matches_bf16_model(name, test, model):
     assert rep["rel_fro"] <= 2.5e-3 and rep["max_ratio"] <= 1.5 and rep["frac_out"] <= 1e-5, f"{name} vs bf16 pipeline model: {rep}"
 
 
-@pytest.mark.parametrize("name", ["tiny", "tiny_ragged", "cfg1"])
+@pytest.mark.parametrize("name", ["tiny", "tiny_ragged", "cfg1", "cfg5_2k"])
 @pytest.mark.parametrize("aux_grad", [0.0, 3.0])
 def test_layer_fwd_bwd_matches_oracle(name, aux_grad):
-    if name == "cfg1" and aux_grad != 0.0:
+    if name in ("cfg1", "cfg5_2k") and aux_grad != 0.0:
         pytest.skip("one aux-loss case per size is enough for the big shape")
     from oracle import bf16_pipeline
     from swamla_b200 import functional
@@ -58,14 +58,14 @@ def test_layer_fwd_bwd_matches_oracle(name, aux_grad):
     layer.train()
     xg = x.to("cuda:0").to(torch.bfloat16).requires_grad_(True)
     sink = {}
-    functional.DEBUG_SINK = sink
+    functional._testing.SINK = sink
     try:
         y = layer(xg)
         loss = (y.float() * dy.to("cuda:0").to(torch.bfloat16).float()).sum() + aux_grad * layer.get_aux_loss()
         loss.backward()
         torch.cuda.synchronize()
     finally:
-        functional.DEBUG_SINK = None
+        functional._testing.SINK = None
     assert sink["status"].item() == 0
     assert y.dtype == torch.bfloat16 and y.shape == x.shape
 
@@ -179,7 +179,7 @@ def test_layer_fp32_master_weights_against_golden_fixture(name):
     # Second pass on the reference's own selection (test hook): the float path and every gradient
     # against the fixture, and the bias update bit-exact.
     from swamla_b200 import functional
-    functional.DEBUG_FORCE_SEL = ref_sel
+    functional._testing.FORCE_SEL = ref_sel
     try:
         y = layer(xg)
         check("y (reference selection)", y, fx["y"])
@@ -192,7 +192,7 @@ def test_layer_fp32_master_weights_against_golden_fixture(name):
                 assert g.dtype == torch.float32
                 check(f"grad {k}", g, d)
     finally:
-        functional.DEBUG_FORCE_SEL = None
+        functional._testing.FORCE_SEL = None
     layer.router.update_bias_from_last_forward()
     torch.testing.assert_close(layer.router.expert_bias.cpu(), fx["expert_bias_after_update"], rtol=0, atol=0)
     torch.testing.assert_close(layer.router.load_history.cpu(), fx["load_history_after_update"], rtol=1e-6, atol=1e-7)

@@ -51,14 +51,14 @@ def test_moe_layer_fwd_bwd_matches_oracle(name, aux_grad):
         for p_ in layer.parameters():
             p_.grad = None
         xg = x.to("cuda:0").to(torch.bfloat16).requires_grad_(True)
-        functional.DEBUG_FORCE_SEL = force
+        functional._testing.FORCE_SEL = force
         try:
             y = layer(xg)
             loss = (y.float() * dy.to("cuda:0").to(torch.bfloat16).float()).sum() + aux_grad * layer.get_aux_loss()
             loss.backward()
             torch.cuda.synchronize()
         finally:
-            functional.DEBUG_FORCE_SEL = None
+            functional._testing.FORCE_SEL = None
         return y, xg
 
     def oracle(sel_override=None):
@@ -112,14 +112,14 @@ def test_moe_layer_fp32_against_golden_fixture(name):
         ok, rep = R.within_tolerance(flat, d["sample"], RTOL_BF16)
         assert ok, f"{what} vs reference fixture: {rep}"
 
-    functional.DEBUG_FORCE_SEL = ref_sel                          # the float path on the reference's own selection
+    functional._testing.FORCE_SEL = ref_sel                          # the float path on the reference's own selection
     try:
         y = layer(xg)
         check("y", y, fx["y"])
         assert abs(layer.get_aux_loss().item() - fx["aux_loss"]) <= 2e-3 * abs(fx["aux_loss"])
         ((y * dy.to("cuda:0")).sum() + fx["aux_grad"] * layer.get_aux_loss()).backward()
     finally:
-        functional.DEBUG_FORCE_SEL = None
+        functional._testing.FORCE_SEL = None
     named = dict(layer.named_parameters())
     assert set(fx["grads"]) - {"x"} == set(named)
     for k, d in fx["grads"].items():
