@@ -130,7 +130,8 @@ def test_full_size_outputs_and_gradients_match_fp32_oracle(name):
         rows = differ.nonzero().flatten()
         kth = scores[rows].gather(1, free["sel"][rows])[:, -1]                    # the oracle's K-th score
         ours = scores[rows].gather(1, sel[rows]).min(1).values                    # our lowest selected score
-        assert (kth - ours).abs().max().item() < 1e-4
+        # (logits contract over 1,024 products in another order and on the tensor cores' fp32 accumulators)
+        assert (kth - ours).abs().max().item() < 5e-4
     del free
     out, grads = R.layer_forward_backward(pr, bufs, xr, dyr, w.K, z_loss_coef=w.router_z_loss_coef, sel_override=sel)
     assert torch.equal(counts, out["counts"])
