@@ -96,6 +96,18 @@ size_t lmoe_route_workspace_bytes(const lmoe_shape* s);
  * tensor cores.  No counterpart in the reference (a kernel-selection switch). */
 int lmoe_pair_gemm_enable(int on);
 
+/* The routed expert chain in ONE kernel per direction.  Forward: gate_up GEMM -> SwiGLU -> down GEMM per 128-row tile,
+ * the hidden activation goes from the first GEMM's epilogue into the second GEMM's operand through shared memory
+ * (models/moe.py:814-828 in one pass).  Backward: d_hidden GEMM -> SwiGLU adjoint -> d_x GEMM, d_hidden never reaches
+ * memory.  lmoe_grouped_fwd / lmoe_grouped_bwd_dgrad (and lmoe_experts_fwd / lmoe_experts_bwd_dgrad built on them) use
+ * it whenever lmoe_chain_applies(L, F) is 1: bf16, L a multiple of 64 up to 256, F a multiple of 64; otherwise they
+ * launch the separate grouped GEMMs.  On unless the environment has LMOE_CHAIN=0; lmoe_chain_enable switches it for the
+ * process and returns the previous setting.  Forward results are bit-identical to the separate GEMMs, backward ones
+ * agree to one bf16 ulp (another summation order of d_x over the 2F columns).  No counterpart in the reference (a
+ * kernel-selection switch). */
+int lmoe_chain_enable(int on);
+int lmoe_chain_applies(int L, int F);
+
 /* ---- generic dense GEMM on tcgen05 (building block; also the unit-test hook) ----
  * C[M,N] = A[M,K] * B[N,K]^T with fp32 accumulation in tensor memory.
  *   a_mn = 0: A stored [M,K] row-major (lda = row stride);  a_mn = 1: A stored [K,M] row-major.

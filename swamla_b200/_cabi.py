@@ -44,6 +44,8 @@ SIGNATURES = {
     "lmoe_padded_rows": (c_int64, [SP]),
     "lmoe_route_workspace_bytes": (c_size_t, [SP]),
     "lmoe_pair_gemm_enable": (c_int, [c_int]),
+    "lmoe_chain_enable": (c_int, [c_int]),
+    "lmoe_chain_applies": (c_int, [c_int, c_int]),
     "lmoe_gemm_workspace_bytes": (c_size_t, [c_int, c_int, c_int]),
     "lmoe_gemm_bf16": (c_int, [c_int, c_int, c_int, P, c_int64, c_int, P, c_int64, c_int, P, c_int64, c_int, c_int, P,
                                c_size_t, P, P]),

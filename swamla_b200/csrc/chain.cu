@@ -1,0 +1,87 @@
+// Host launcher of the routed expert chain kernel (chain.cuh): tensor maps, grid sizing, the on/off switch.
+#include <cuda.h>
+#include <cuda_runtime.h>
+
+#include <cstdlib>
+#include <cstring>
+
+#include "../../include/lmoe.h"
+#include "chain.cuh"
+#include "counters.h"
+#include "device_once.h"
+#include "gemm_host.h"
+
+namespace lmoe {
+
+static int g_chain = -1;  // -1: not yet read from the environment (LMOE_CHAIN=0 switches the kernel off)
+static bool chain_enabled() {
+  if (g_chain < 0) {
+    const char* e = getenv("LMOE_CHAIN");
+    g_chain = (e && e[0] == '0') ? 0 : 1;
+  }
+  return g_chain == 1;
+}
+
+bool chain_applies(int L, int F) {
+  return chain_enabled() && L >= 64 && L <= kChainMaxL && (L % 64) == 0 && F >= 64 && (F % 64) == 0;
+}
+
+template <int MODE>
+static int launch_chain_inst(const ChainParams& p, int grid, cudaStream_t stream) {
+  auto kfn = chain_kernel<MODE>;
+  constexpr int smem = ChainSmem<MODE>::kTotal;
+  static PerDeviceOnce once;
+  if (int rc = once.run([&] {
+        cudaError_t e = cudaFuncSetAttribute(kfn, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+        if (e != cudaSuccess) return static_cast<int>(e);
+        cudaFuncSetAttribute(kfn, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
+        return 0;
+      }))
+    return rc;
+  kfn<<<grid, kGemmThreads, smem, stream>>>(p);
+  count_launch();
+  cudaError_t e = cudaGetLastError();
+  return e == cudaSuccess ? 0 : static_cast<int>(e);
+}
+
+int launch_chain(int mode, long long P, int E, int L, int F, const void* a, const void* w_gate_up, const void* w_down,
+                 const int* tile_expert, const int* n_tiles, void* h1, void* mid, void* out, int* status,
+                 cudaStream_t stream) {
+  if (!a || !w_gate_up || !w_down || !tile_expert || !n_tiles || !h1 || !mid || !out) return LMOE_ERR_ARG;
+  if (P <= 0 || (P % kBM) != 0 || E <= 0 || !chain_applies(L, F)) return LMOE_ERR_SHAPE;
+  ChainParams p;
+  memset(&p, 0, sizeof(p));
+  int rc = encode_2d(&p.tmA, a, L, P, L, kBM, 2);
+  if (rc) return rc;
+  const long long wgu_rows = static_cast<long long>(E) * L, wd_rows = static_cast<long long>(E) * F;
+  if (mode == CHAIN_FWD) {
+    if ((rc = encode_2d(&p.tmB1, w_gate_up, 2ll * F, wgu_rows, 2ll * F, 64, 2))) return rc;
+    if ((rc = encode_2d(&p.tmB2, w_down, L, wd_rows, L, 64, 2))) return rc;
+    if ((rc = encode_2d(&p.tmMid, mid, F, P, F, kBM, 2))) return rc;            // hidden [P, F]
+  } else {
+    if ((rc = encode_2d(&p.tmB1, w_down, L, wd_rows, L, 64, 2))) return rc;
+    if ((rc = encode_2d(&p.tmB2, w_gate_up, 2ll * F, wgu_rows, 2ll * F, L < 128 ? L : 128, 2))) return rc;
+    if ((rc = encode_2d(&p.tmMid, mid, 2ll * F, P, 2ll * F, kBM, 2))) return rc;  // d_h1 [P, 2F]
+  }
+  if ((rc = encode_out(&p.tmAux, h1, false, 2ll * F, P, 1, 2ll * F, 0))) return rc;
+  if ((rc = encode_out(&p.tmOut, out, false, L, P, 1, L, 0))) return rc;
+  p.L = L;
+  p.F = F;
+  p.max_tiles = static_cast<int>(P / kBM);
+  p.tile_expert = tile_expert;
+  p.n_tiles = n_tiles;
+  p.status = status;
+  const int sms = num_sms();
+  const int grid = p.max_tiles < sms ? p.max_tiles : sms;
+  return mode == CHAIN_FWD ? launch_chain_inst<CHAIN_FWD>(p, grid, stream) : launch_chain_inst<CHAIN_BWD>(p, grid, stream);
+}
+
+}  // namespace lmoe
+
+extern "C" int lmoe_chain_enable(int on) {
+  const int before = lmoe::chain_enabled() ? 1 : 0;
+  lmoe::g_chain = on ? 1 : 0;
+  return before;
+}
+
+extern "C" int lmoe_chain_applies(int L, int F) { return lmoe::chain_applies(L, F) ? 1 : 0; }

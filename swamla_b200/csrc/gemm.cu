@@ -51,7 +51,7 @@ int num_sms() {
 
 // Operand map: 2-D over a row-major [outer, inner] tensor of 16-bit (esz 2) or 8-bit (esz 1) elements,
 // 128-byte swizzle; the inner box extent is always 128 bytes.
-static int encode_2d(CUtensorMap* map, const void* base, long long inner, long long outer, long long ld_elems,
+int encode_2d(CUtensorMap* map, const void* base, long long inner, long long outer, long long ld_elems,
                      int box_outer, int esz) {
   EncodeTiledFn fn = encode_fn();
   if (!fn) return LMOE_ERR_DRIVER;
@@ -70,7 +70,7 @@ static int encode_2d(CUtensorMap* map, const void* base, long long inner, long l
 
 // Output map: 3-D {cols, rows, planes}; one 128 x 32 slab per store.  bf16: 64-byte rows in shared
 // memory (SWIZZLE_64B); fp32: 128-byte rows (SWIZZLE_128B).
-static int encode_out(CUtensorMap* map, void* base, bool f32, long long cols, long long rows, long long planes,
+int encode_out(CUtensorMap* map, void* base, bool f32, long long cols, long long rows, long long planes,
                       long long ld_elems, long long plane_elems) {
   EncodeTiledFn fn = encode_fn();
   if (!fn) return LMOE_ERR_DRIVER;

@@ -1,5 +1,6 @@
 // Host-side description of one launch of the tcgen05 GEMM kernel (internal to the library).
 #pragma once
+#include <cuda.h>
 #include <cuda_runtime.h>
 #include <stdint.h>
 
@@ -55,6 +56,23 @@ struct GemmCall {
 int launch_gemm(const GemmCall& c);
 
 int num_sms();
+
+// Tensor maps.  encode_2d: a row-major [outer, inner] tensor of 16-bit (esz 2) or 8-bit (esz 1) elements, box
+// {128 bytes, box_outer rows}, 128-byte swizzle (operand loads, and stores from a buffer in the same layout).
+// encode_out: 3-D {cols, rows, planes}, box {32 columns, 128 rows, 1}: bf16 with 64-byte swizzle or fp32 with
+// 128-byte swizzle (epilogue slabs; also usable as a load of such slabs).
+int encode_2d(CUtensorMap* map, const void* base, long long inner, long long outer, long long ld_elems, int box_outer,
+              int esz);
+int encode_out(CUtensorMap* map, void* base, bool f32, long long cols, long long rows, long long planes,
+               long long ld_elems, long long plane_elems);
+
+// The routed expert chain (chain.cuh) in one launch.  mode 0 (forward): a = x_sorted [P, L], h1 [P, 2F] and
+// mid = hidden [P, F] and out = y_sorted [P, L] are written.  mode 1 (backward): a = d_y_sorted, h1 is read,
+// mid = d_h1 [P, 2F] and out = d_x_sorted [P, L] are written.
+bool chain_applies(int L, int F);
+int launch_chain(int mode, long long P, int E, int L, int F, const void* a, const void* w_gate_up, const void* w_down,
+                 const int* tile_expert, const int* n_tiles, void* h1, void* mid, void* out, int* status,
+                 cudaStream_t stream);
 
 // True when dense GEMMs of this size run on CTA pairs (256 x 256 tiles over two SMs) rather than one CTA per 128 x 256 tile.
 bool pair_gemm_applies(int M, int N);

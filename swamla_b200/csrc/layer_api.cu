@@ -5,6 +5,7 @@
 
 #include "../../include/lmoe.h"
 #include "counters.h"
+#include "chain.cuh"
 #include "gemm.cuh"
 #include "gemm_host.h"
 #include "rowops.h"
@@ -171,6 +172,10 @@ static int grouped_fwd_impl(int64_t P, int E, int L, int F, const void* x_sorted
                             void* hidden, void* y_sorted, int32_t* status, void* stream) {
   if (!x_sorted || !w_gate_up || !w_down || !tile_expert || !n_tiles || !h1 || !hidden || !y_sorted) return LMOE_ERR_ARG;
   if (P <= 0 || (P % LMOE_ROW_PAD) != 0 || E <= 0 || (L % 64) != 0 || (F % 64) != 0) return LMOE_ERR_SHAPE;
+  // one kernel for gate_up -> SwiGLU -> down per 128-row tile when the latent width fits the second accumulator
+  if (!g && chain_applies(L, F))
+    return launch_chain(CHAIN_FWD, P, E, L, F, x_sorted, w_gate_up, w_down, tile_expert, n_tiles, h1, hidden, y_sorted,
+                        status, static_cast<cudaStream_t>(stream));
   // h1 = x_sorted * Wgu[e]  (Wgu stacked [E*L, 2F], N contiguous), hidden = silu(gate) * up
   GemmCall a;
   a.a_mn = 0;
@@ -374,6 +379,10 @@ extern "C" int lmoe_grouped_bwd_dgrad(int64_t P, int E, int L, int F, const void
   if (!d_y_sorted || !h1 || !w_gate_up || !w_down || !tile_expert || !n_tiles || !d_h1 || !d_x_sorted)
     return LMOE_ERR_ARG;
   if (P <= 0 || (P % LMOE_ROW_PAD) != 0 || E <= 0 || (L % 64) != 0 || (F % 64) != 0) return LMOE_ERR_SHAPE;
+  // one kernel for d_hidden -> SwiGLU adjoint -> d_x_sorted per 128-row tile (d_hidden is not written then)
+  if (chain_applies(L, F))
+    return launch_chain(CHAIN_BWD, P, E, L, F, d_y_sorted, w_gate_up, w_down, tile_expert, n_tiles, const_cast<void*>(h1),
+                        d_h1, d_x_sorted, status, static_cast<cudaStream_t>(stream));
   // d_hidden[P,F] = d_y_sorted[P,L] * Wd[e]^T : Wd[e] is [F,L] = [N,K] row-major -> K-major B
   GemmCall a;
   a.a_mn = 0;

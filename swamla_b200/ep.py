@@ -24,7 +24,7 @@ import torch.distributed as dist
 
 from . import _cabi, status as status_monitor
 from ._cabi import Route, ptr
-from .functional import BF, RouteTables, _as_bf16, _stream, make_shape
+from .functional import BF, RouteTables, _as_bf16, _stream, d_hidden_scratch, make_shape
 
 
 def expert_shard_parameter_names(model: torch.nn.Module) -> List[str]:
@@ -241,7 +241,7 @@ class ExpertParallelLatentMoE(torch.autograd.Function):
             _cabi.call("lmoe_gather_rows", ptr(d_y_recv), ptr(row_src), 1, P, L, ptr(n_tiles), ptr(d_y_sorted), st)
             d_h1 = torch.empty(P, 2 * F, **bf)
             d_x_sorted = torch.empty(P, L, **bf)
-            d_hidden = torch.empty(P, F, **bf)
+            d_hidden = d_hidden_scratch(lib, P, L, F, **bf)
             _cabi.call("lmoe_grouped_bwd_dgrad", P, El, L, F, ptr(d_y_sorted), ptr(h1), ptr(wgu), ptr(wde),
                        ptr(tile_expert), ptr(n_tiles), ptr(d_hidden), ptr(d_h1), ptr(d_x_sorted), ptr(status), st)
             _cabi.call("lmoe_grouped_bwd_wgrad", P, El, L, F, ptr(x_sorted), ptr(d_h1), ptr(hidden), ptr(d_y_sorted),
@@ -469,7 +469,7 @@ class ExpertParallelP2P(torch.autograd.Function):
 
         d_h1 = torch.empty(P, 2 * F, **bf)
         d_x_sorted = torch.empty(P, L, **bf)
-        d_hidden = torch.empty(P, F, **bf)
+        d_hidden = d_hidden_scratch(lib, P, L, F, **bf)
         _cabi.call("lmoe_grouped_bwd_dgrad", P, El, L, F, ptr(bufs.dy_in), ptr(h1), ptr(wgu), ptr(wde), ptr(tile_expert),
                    ptr(n_tiles), ptr(d_hidden), ptr(d_h1), ptr(d_x_sorted), ptr(status), st)
         ready2 = torch.cuda.Event()
@@ -716,7 +716,7 @@ class ExpertParallelDedup(torch.autograd.Function):
                    ptr(d_w_row), st)
         d_h1 = torch.empty(P, 2 * F, **bf)
         d_x_sorted = torch.empty(P, L, **bf)
-        d_hidden = torch.empty(P, F, **bf)
+        d_hidden = d_hidden_scratch(lib, P, L, F, **bf)
         _cabi.call("lmoe_grouped_bwd_dgrad", P, El, L, F, ptr(dy_in), ptr(h1), ptr(wgu), ptr(wde), ptr(tile_expert),
                    ptr(n_tiles), ptr(d_hidden), ptr(d_h1), ptr(d_x_sorted), ptr(status), st)
         ready2 = torch.cuda.Event()

@@ -16,16 +16,17 @@ from ._cabi import Route, Shape, ptr
 
 BF = torch.bfloat16
 
-# SwiGLU adjoint inside the epilogue of the dgrad GEMMs (no d_hidden round trip) instead of a streaming kernel.
-# Off by default: the epilogue's row-wise reads of the saved gate/up are uncoalesced and the fused kernel measured
-# slower than GEMM + streaming kernel (cfg2: 164 us vs 37 + 90 us for the routed experts).
-import os as _os
-FUSE_SWIGLU_BWD = _os.environ.get("LMOE_FUSE_SWIGLU_BWD", "0") == "1"
 # LMOE_TMA_GATHER=1: the gate_up GEMMs (forward and weight gradient) read the latent rows through TMA gathers
 # (tile::gather4) driven by the routing table, with no gather kernel and no x_sorted buffer (P*L*2 bytes less memory).
-# Off by default: results are bit-identical but four-row gathers of 128-byte rows sustained only about 8 GB/s per SM
-# (cfg2: forward gate_up GEMM 185 us instead of 89 us + 27 us gather kernel, weight gradient 246 us instead of 69 us).
+# Off by default: results are bit-identical but four-row gathers of 128-byte rows sustained only about 8 GB/s per SM.
+import os as _os
 TMA_GATHER = _os.environ.get("LMOE_TMA_GATHER", "0") == "1"
+
+
+def d_hidden_scratch(lib, P, L, F, **kw):
+    """The [P, F] scratch of the routed dgrad stage, or None when the chain kernel (which never writes d_hidden)
+    serves this shape."""
+    return None if lib.lmoe_chain_applies(L, F) else torch.empty(P, F, **kw)
 
 
 def _stream() -> int:
@@ -252,7 +253,7 @@ class LatentMoEFunction(torch.autograd.Function):
         ld_cat = 2 * Fs + L + E
 
         # output stage dgrads, then: [adjoint of the combine] beside [output-stage weight gradients]
-        d_hidden_s = None if FUSE_SWIGLU_BWD else torch.empty(T, Fs, **bf)
+        d_hidden_s = torch.empty(T, Fs, **bf)
         _cabi.call("lmoe_combine_out_bwd_dgrad", shape, ptr(dyb), ptr(wup), ptr(wds), ptr(h1_s), ptr(d_routed),
                    ptr(d_hidden_s), ptr(dgrad_cat), ptr(status), st)
         fork.to_side()
@@ -275,8 +276,8 @@ class LatentMoEFunction(torch.autograd.Function):
             d_w_gate_up = torch.empty(E, L, 2 * F, **bf)
             d_w_down_e = torch.empty(E, F, L, **bf)
             te, nt = ptr(route.tile_expert), ptr(route.n_tiles)
-            # d_h1 = swiglu'(h1, d_y_sorted * Wd[e]^T) (adjoint fused into the GEMM epilogue), d_x_sorted = d_h1 * Wgu[e]^T
-            d_hidden = None if FUSE_SWIGLU_BWD else torch.empty(P, F, **bf)
+            # d_h1 = swiglu'(h1, d_y_sorted * Wd[e]^T), d_x_sorted = d_h1 * Wgu[e]^T: one chained kernel
+            d_hidden = d_hidden_scratch(lib, P, L, F, **bf)
             _cabi.call("lmoe_grouped_bwd_dgrad", P, E, L, F, ptr(d_y_sorted), ptr(h1), ptr(wgu), ptr(wde), te, nt,
                        ptr(d_hidden), ptr(d_h1), ptr(d_x_sorted), ptr(status), st)
             # [gather adjoint + router adjoint] beside [routed weight gradients]
