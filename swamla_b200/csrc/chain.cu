@@ -68,6 +68,12 @@ int launch_chain(int mode, long long P, int E, int L, int F, const void* a, cons
   p.L = L;
   p.F = F;
   p.max_tiles = static_cast<int>(P / kBM);
+  {
+    const char* e = getenv("LMOE_CHAIN_PREFETCH");
+    p.prefetch_a = (e && e[0] == '0') ? 0 : 1;
+    const char* c = getenv("LMOE_CHAIN_CONTIG");
+    p.contiguous = (c && c[0] == '1') ? 1 : 0;
+  }
   p.tile_expert = tile_expert;
   p.n_tiles = n_tiles;
   p.status = status;
@@ -85,3 +91,15 @@ extern "C" int lmoe_chain_enable(int on) {
 }
 
 extern "C" int lmoe_chain_applies(int L, int F) { return lmoe::chain_applies(L, F) ? 1 : 0; }
+
+#ifdef LMOE_CHAIN_TRACE
+// Development aid: copies CTA 0's event trace of the last chain launch to the host and clears it.
+extern "C" int lmoe_chain_trace_read(long long* host, int* counts) {
+  cudaDeviceSynchronize();
+  cudaMemcpyFromSymbol(host, lmoe::g_chain_trace, sizeof(long long) * 3 * lmoe::kTraceSlots * 2);
+  cudaMemcpyFromSymbol(counts, lmoe::g_chain_trace_n, sizeof(int) * 3);
+  int zero[3] = {0, 0, 0};
+  cudaMemcpyToSymbol(lmoe::g_chain_trace_n, zero, sizeof(zero));
+  return 0;
+}
+#endif

@@ -14,8 +14,10 @@
 // Replaces, per direction, two grouped GEMM launches plus (backward) the streaming SwiGLU-adjoint kernel:
 // `hidden` is read back from HBM by nobody in forward, and d_hidden never exists in memory.
 //
-// One CTA per SM walks tiles t = blockIdx.x, blockIdx.x + gridDim.x, ...; a tile belongs to one expert
-// (tile_expert).  Roles (320 threads):
+// One CTA per SM walks a CONTIGUOUS range of tiles (ceil(n_tiles / grid) each); a tile belongs to one expert
+// (tile_expert).  Contiguous ranges keep a CTA on the same expert for several tiles in a row, so after the first tile
+// its weight slices come from L2 at L2 latency; with a round-robin assignment all CTAs that share an expert would ask
+// for the same weight lines at the same moment and every load would see the latency of the one HBM fetch behind it.  Roles (320 threads):
 //   warp 0      TMA producer.  The tile's A operand (128 x L, K-major) is resident for the whole tile; the weight
 //               slices stream through a ring of 16 KB stages in exactly the order the MMA warp consumes them
 //   warp 1      MMA issuer (one thread) and owner of the 512 tensor-memory columns:
@@ -47,10 +49,32 @@ struct alignas(64) ChainParams {
   CUtensorMap tmOut;  // store of the second GEMM's result [P, L] box {32, 128} (64-byte swizzle)
   int L, F;
   int max_tiles;            // capacity of the padded layout in tiles
+  int prefetch_a;           // 1: prefetch the next tile's A operand into L2
+  int contiguous;           // 1: contiguous tile range per CTA; 0: round-robin
   const int* tile_expert;
   const int* n_tiles;       // device scalar: tiles in use
   int* status;
 };
+
+// Development aid (compiled only with -DLMOE_CHAIN_TRACE): CTA 0 records (tag, globaltimer) pairs per role.
+#ifdef LMOE_CHAIN_TRACE
+constexpr int kTraceSlots = 4096;
+__device__ long long g_chain_trace[3][kTraceSlots][2];
+__device__ int g_chain_trace_n[3];
+__device__ __forceinline__ void chain_trace(int role, int tag) {
+  if (blockIdx.x != 0) return;
+  const int i = g_chain_trace_n[role];
+  if (i >= kTraceSlots) return;
+  long long t;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+  g_chain_trace[role][i][0] = tag;
+  g_chain_trace[role][i][1] = t;
+  g_chain_trace_n[role] = i + 1;
+}
+#define CHAIN_TRACE(role, tag) chain_trace(role, tag)
+#else
+#define CHAIN_TRACE(role, tag)
+#endif
 
 template <int MODE>
 struct ChainSmem {
@@ -70,6 +94,11 @@ __device__ __forceinline__ void tma_load_3d(void* smem_dst, const CUtensorMap* m
       "cp.async.bulk.tensor.3d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];"
       ::"r"(smem_u32(smem_dst)), "l"(reinterpret_cast<uint64_t>(map)), "r"(smem_u32(bar)), "r"(c0), "r"(c1), "r"(c2)
       : "memory");
+}
+__device__ __forceinline__ void tma_prefetch_2d(const CUtensorMap* map, int c0, int c1) {
+  asm volatile("cp.async.bulk.prefetch.tensor.2d.L2.global.tile [%0, {%1, %2}];" ::"l"(reinterpret_cast<uint64_t>(map)),
+               "r"(c0), "r"(c1)
+               : "memory");
 }
 // AND-reduction of a predicate over the 256 epilogue threads (named barrier 3).
 __device__ __forceinline__ bool epi_all_and(bool pred) {
@@ -138,8 +167,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1) chain_kernel(const __grid_con
   uint64_t* const acc2_full = a2_empty + 1;              // [1]
   uint64_t* const acc2_empty = acc2_full + 1;            // [1]
   uint64_t* const gu_full = acc2_empty + 1;              // [2] (BWD)
-  uint64_t* const gu_empty = gu_full + 2;                // [2] (BWD)
-  uint32_t* const tmem_slot = reinterpret_cast<uint32_t*>(gu_empty + 2);
+  uint32_t* const tmem_slot = reinterpret_cast<uint32_t*>(gu_full + 2);
   volatile int* const abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5;
@@ -158,7 +186,6 @@ __global__ void __launch_bounds__(kGemmThreads, 1) chain_kernel(const __grid_con
       mbar_init(&acc1_full[i], 1);
       mbar_init(&acc1_empty[i], 8);
       mbar_init(&gu_full[i], 1);
-      mbar_init(&gu_empty[i], 8);
     }
     mbar_init(a2_full, 1);
     mbar_init(a2_empty, 1);
@@ -191,11 +218,16 @@ __global__ void __launch_bounds__(kGemmThreads, 1) chain_kernel(const __grid_con
   struct Cur {
     int tile, c;
   };
-  auto valid = [&](const Cur& k) { return k.tile < n_tiles; };
+  // p.contiguous: CTA b takes tiles [b * per, (b + 1) * per); otherwise tiles b, b + grid, b + 2 * grid, ...
+  const int tiles_per_cta = (n_tiles + static_cast<int>(gridDim.x) - 1) / static_cast<int>(gridDim.x);
+  const int tile_step = p.contiguous ? 1 : static_cast<int>(gridDim.x);
+  const int tile_begin = p.contiguous ? static_cast<int>(blockIdx.x) * tiles_per_cta : static_cast<int>(blockIdx.x);
+  const int tile_end = p.contiguous ? min(tile_begin + tiles_per_cta, n_tiles) : n_tiles;
+  auto valid = [&](const Cur& k) { return k.tile < tile_end; };
   auto next = [&](Cur k) {
     if (++k.c == NC) {
       k.c = 0;
-      k.tile += gridDim.x;
+      k.tile += tile_step;
     }
     return k;
   };
@@ -207,10 +239,12 @@ __global__ void __launch_bounds__(kGemmThreads, 1) chain_kernel(const __grid_con
       uint32_t phase = 0;
       bool ok = true;
       auto acquire = [&](uint32_t bytes) -> uint8_t* {  // next ring stage, armed for `bytes`
+        CHAIN_TRACE(0, 31);
         if (!mbar_wait(&ring_empty[stage], phase ^ 1, abort_flag, p.status, kStatusProducerTimeout)) {
           ok = false;
           return nullptr;
         }
+        CHAIN_TRACE(0, 32);
         mbar_expect_tx(&ring_full[stage], bytes);
         return ring + stage * kChainStageBytes;
       };
@@ -222,6 +256,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1) chain_kernel(const __grid_con
       };
       int tiles_loaded = 0;  // tiles whose A operand has been requested
       auto emit_g1 = [&](const Cur& k, int gi) {
+        CHAIN_TRACE(0, 30);
         const int e = p.tile_expert[k.tile];
         const int m0 = k.tile * kBM;
         if (k.c == 0) {  // the tile's A operand, k-block by k-block as the previous tile's last chunk releases them
@@ -234,21 +269,13 @@ __global__ void __launch_bounds__(kGemmThreads, 1) chain_kernel(const __grid_con
             tma_load_2d(a1 + kb * 16384, &p.tmA, &a1_full[kb], kb * 64, m0);
           }
           ++tiles_loaded;
+          // the A operand of the tile after this one: bring it into L2 a whole tile period ahead, so that its load
+          // (which can only start when this tile's last chunk releases the buffer) does not wait for HBM
+          const int nt_tile = k.tile + tile_step;
+          if (p.prefetch_a && nt_tile < tile_end)
+            for (int kb = 0; kb < KB1; ++kb) tma_prefetch_2d(&p.tmA, kb * 64, nt_tile * kBM);
         }
         if (!ok) return;
-        if (!FWD) {  // saved gate / up of this chunk: four 128 x 32 slabs (group 0: gate, up; group 1: gate, up)
-          const int b = gi & 1;
-          if (!mbar_wait(&gu_empty[b], ((gi >> 1) & 1) ^ 1, abort_flag, p.status, kStatusProducerTimeout)) {
-            ok = false;
-            return;
-          }
-          mbar_expect_tx(&gu_full[b], 32768);
-          uint8_t* dst = aux + b * 32768;
-          for (int gr = 0; gr < 2; ++gr) {
-            tma_load_3d(dst + gr * 16384, &p.tmAux, &gu_full[b], k.c * 64 + gr * 32, m0, 0);
-            tma_load_3d(dst + gr * 16384 + 8192, &p.tmAux, &gu_full[b], F + k.c * 64 + gr * 32, m0, 0);
-          }
-        }
         if (FWD) {
           // one stage per k-block: gate columns [c*64, +64) and up columns [F + c*64, +64) of Wgu[e] rows [kb*64, +64)
           for (int kb = 0; kb < KB1; ++kb) {
@@ -271,6 +298,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1) chain_kernel(const __grid_con
         }
       };
       auto emit_g2 = [&](const Cur& k) {
+        CHAIN_TRACE(0, 35);
         const int e = p.tile_expert[k.tile];
         if (FWD) {
           // rows [c*64, +64) of Wd[e], 128 output columns per stage (two 64-wide MN-major chunks)
@@ -296,7 +324,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1) chain_kernel(const __grid_con
             }
         }
       };
-      Cur cur{static_cast<int>(blockIdx.x), 0};
+      Cur cur{tile_begin, 0};
       int gi = 0;
       if (valid(cur)) emit_g1(cur, 0);
       while (ok && valid(cur)) {
@@ -341,6 +369,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1) chain_kernel(const __grid_con
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + b * 128;
         const uint32_t a_par = tiles_g1 & 1;
+        CHAIN_TRACE(1, 1);
         if (FWD) {
           constexpr uint32_t idesc = make_idesc(1u, 1u, false, true, kBM, 128);
           for (int kb = 0; kb < KB1; ++kb) {
@@ -389,6 +418,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1) chain_kernel(const __grid_con
         }
         if (k.c == 0) ++tiles_g1;
         umma_commit(&acc1_full[b]);
+        CHAIN_TRACE(1, 2);
       };
       auto issue_g2 = [&](const Cur& k, int gi) {
         if (k.c == 0) {
@@ -398,11 +428,13 @@ __global__ void __launch_bounds__(kGemmThreads, 1) chain_kernel(const __grid_con
           }
           ++tiles_g2;
         }
+        CHAIN_TRACE(1, 3);
         if (!mbar_wait(a2_full, gi & 1, abort_flag, p.status, kStatusMmaTimeout)) {
           ok = false;
           return;
         }
         tc_fence_after();
+        CHAIN_TRACE(1, 4);
         if (FWD) {
           for (int s = 0; s < NH; ++s) {
             const int n_this = min(128, L - s * 128);
@@ -434,9 +466,10 @@ __global__ void __launch_bounds__(kGemmThreads, 1) chain_kernel(const __grid_con
             }
         }
         umma_commit(a2_empty);                       // the A2 buffer may be rewritten once these MMAs have read it
+        CHAIN_TRACE(1, 5);
         if (k.c == NC - 1) umma_commit(acc2_full);   // the tile's result is complete
       };
-      Cur cur{static_cast<int>(blockIdx.x), 0};
+      Cur cur{tile_begin, 0};
       int gi = 0;
       if (valid(cur)) issue_g1(cur, 0);
       while (ok && valid(cur)) {
@@ -460,12 +493,32 @@ __global__ void __launch_bounds__(kGemmThreads, 1) chain_kernel(const __grid_con
     uint8_t* const out_slab = outb + group * 8192;
     int tiles_done = 0;
     bool ok = true;
-    Cur cur{static_cast<int>(blockIdx.x), 0};
+    Cur cur{tile_begin, 0};
+    // Backward: the saved gate / up of chunk `k` (four 128 x 32 slabs: group 0 gate, up; group 1 gate, up) staged by TMA
+    // into buffer `b`.  Issued by one epilogue thread two chunks ahead of their use: the buffer of chunk g is free as
+    // soon as every epilogue thread has passed chunk g's first barrier (its rows are in registers by then), so no
+    // "empty" barrier is needed, and the lead of two chunk periods covers the HBM latency.
+    auto load_gu = [&](const Cur& k, int b) {
+      mbar_expect_tx(&gu_full[b], 32768);
+      uint8_t* dst = aux + b * 32768;
+      const int row0 = k.tile * kBM;
+      for (int gr = 0; gr < 2; ++gr) {
+        tma_load_3d(dst + gr * 16384, &p.tmAux, &gu_full[b], k.c * 64 + gr * 32, row0, 0);
+        tma_load_3d(dst + gr * 16384 + 8192, &p.tmAux, &gu_full[b], F + k.c * 64 + gr * 32, row0, 0);
+      }
+    };
+    if (!FWD && chunk_issuer && valid(cur)) {
+      load_gu(cur, 0);
+      const Cur c1 = next(cur);
+      if (valid(c1)) load_gu(c1, 1);
+    }
     for (int gi = 0; valid(cur); ++gi, cur = next(cur)) {
       const int b = gi & 1;
       const int m0 = cur.tile * kBM;
       // ---------------- chunk epilogue ----------------
+      if (chunk_issuer) CHAIN_TRACE(2, 10);
       if (!mbar_wait(&acc1_full[b], (gi >> 1) & 1, abort_flag, p.status, kStatusEpilogueTimeout)) ok = false;
+      if (chunk_issuer) CHAIN_TRACE(2, 11);
       if (!FWD && ok && !mbar_wait(&gu_full[b], (gi >> 1) & 1, abort_flag, p.status, kStatusEpilogueTimeout)) ok = false;
       tc_fence_after();
       uint32_t pa[16], pb[16], pc[16];
@@ -497,10 +550,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1) chain_kernel(const __grid_con
           slab_read_row(gu, r, sg);
           slab_read_row(gu + 8192, r, su);
           __syncwarp();
-          if (lane == 0) {
-            mbar_arrive(&acc1_empty[b]);
-            mbar_arrive(&gu_empty[b]);
-          }
+          if (lane == 0) mbar_arrive(&acc1_empty[b]);
 #pragma unroll
           for (int j = 0; j < 16; ++j) {
             // d_hidden is rounded to bf16 first (what a stored d_hidden would hold), then
@@ -523,10 +573,17 @@ __global__ void __launch_bounds__(kGemmThreads, 1) chain_kernel(const __grid_con
       }
       // The A2 buffer (and, forward, the gate/up slabs) may be rewritten once the second GEMM of the previous chunk
       // has read it and the stores issued from it have read their source.
+      if (chunk_issuer) CHAIN_TRACE(2, 12);
       if (ok && !mbar_wait(a2_empty, (gi & 1) ^ 1, abort_flag, p.status, kStatusEpilogueTimeout)) ok = false;
+      if (chunk_issuer) CHAIN_TRACE(2, 13);
       if (chunk_issuer) tma_store_wait_read_all();
+      if (chunk_issuer) CHAIN_TRACE(2, 14);
       ok = epi_all_and(ok);  // every epilogue thread reaches this barrier on every chunk, whatever its waits returned
       if (!ok) break;
+      if (!FWD && chunk_issuer) {  // every thread holds its gate / up rows in registers: refill the buffer (chunk gi + 2)
+        const Cur c2 = next(next(cur));
+        if (valid(c2)) load_gu(c2, b);
+      }
       if (FWD) {
         uint8_t* slabs = aux + group * 16384;
         stage_row_bf16(slabs, r, pa);
@@ -537,8 +594,10 @@ __global__ void __launch_bounds__(kGemmThreads, 1) chain_kernel(const __grid_con
         a2_write_half(a2 + 16384, r, group, pb);
       }
       fence_proxy_async_smem();
+      if (chunk_issuer) CHAIN_TRACE(2, 15);
       epi_all_sync();
       if (chunk_issuer) {
+        CHAIN_TRACE(2, 16);
         mbar_arrive(a2_full);  // the MMA warp may issue the second GEMM of this chunk
         if (FWD) {
           for (int gr = 0; gr < 2; ++gr) {
@@ -554,7 +613,9 @@ __global__ void __launch_bounds__(kGemmThreads, 1) chain_kernel(const __grid_con
       }
       if (cur.c != NC - 1) continue;
       // ---------------- tile epilogue: the second GEMM's accumulator -> bf16 -> [P, L] ----------------
+      if (chunk_issuer) CHAIN_TRACE(2, 20);
       if (!mbar_wait(acc2_full, tiles_done & 1, abort_flag, p.status, kStatusEpilogueTimeout)) ok = false;
+      if (chunk_issuer) CHAIN_TRACE(2, 21);
       tc_fence_after();
       ok = epi_all_and(ok);
       if (!ok) break;
@@ -589,6 +650,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1) chain_kernel(const __grid_con
         }
       }
       ++tiles_done;
+      if (chunk_issuer) CHAIN_TRACE(2, 22);
     }
     if (group_issuer) tma_store_wait0();  // shared memory must outlive the last reads
   }
