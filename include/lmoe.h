@@ -243,12 +243,15 @@ int lmoe_xside_bwd(const lmoe_shape* s, const void* dgrad_cat, const void* w_gat
  * The routed-expert stages again, but on a caller-chosen padded row count P (multiple of 128) and expert
  * count E (the local shard), with the tile tables given directly.  lmoe_experts_* above are these plus the
  * single-GPU gather.  Same reference lines: models/moe.py:814-828 and their adjoints. */
+/* pad_offsets [E + 1] (first padded row of every expert, as lmoe_route / lmoe_ep_tables write it; may be NULL): lets the
+ * chain kernel put two tiles of the same expert on a CTA pair that shares the expert's weight loads. */
 int lmoe_grouped_fwd(int64_t P, int E, int L, int F, const void* x_sorted, const void* w_gate_up, const void* w_down,
-                     const int32_t* tile_expert, const int32_t* n_tiles, void* h1, void* hidden, void* y_sorted,
-                     int32_t* status, void* stream);
+                     const int32_t* tile_expert, const int32_t* n_tiles, const int32_t* pad_offsets, void* h1,
+                     void* hidden, void* y_sorted, int32_t* status, void* stream);
 int lmoe_grouped_bwd_dgrad(int64_t P, int E, int L, int F, const void* d_y_sorted, const void* h1, const void* w_gate_up,
-                           const void* w_down, const int32_t* tile_expert, const int32_t* n_tiles, void* d_hidden,
-                           void* d_h1, void* d_x_sorted, int32_t* status, void* stream);
+                           const void* w_down, const int32_t* tile_expert, const int32_t* n_tiles,
+                           const int32_t* pad_offsets, void* d_hidden, void* d_h1, void* d_x_sorted, int32_t* status,
+                           void* stream);
 int lmoe_grouped_bwd_wgrad(int64_t P, int E, int L, int F, const void* x_sorted, const void* d_h1, const void* hidden,
                            const void* d_y_sorted, const int32_t* pad_offsets, void* d_w_gate_up, void* d_w_down,
                            int32_t* status, void* stream);

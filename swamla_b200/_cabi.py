@@ -66,8 +66,8 @@ SIGNATURES = {
     "lmoe_unpermute_sum_bwd": (c_int, [SP, P, RP, P, P]),
     "lmoe_gate_topk_bwd": (c_int, [SP, P, P, P, P, P, P, c_float, P, P]),
     "lmoe_xside_bwd": (c_int, [SP, P, P, P, P, P, P, P, P, P, c_int, P, c_size_t, P, P]),
-    "lmoe_grouped_fwd": (c_int, [c_int64, c_int, c_int, c_int, P, P, P, P, P, P, P, P, P, P]),
-    "lmoe_grouped_bwd_dgrad": (c_int, [c_int64, c_int, c_int, c_int, P, P, P, P, P, P, P, P, P, P, P]),
+    "lmoe_grouped_fwd": (c_int, [c_int64, c_int, c_int, c_int, P, P, P, P, P, P, P, P, P, P, P]),
+    "lmoe_grouped_bwd_dgrad": (c_int, [c_int64, c_int, c_int, c_int, P, P, P, P, P, P, P, P, P, P, P, P]),
     "lmoe_grouped_bwd_wgrad": (c_int, [c_int64, c_int, c_int, c_int, P, P, P, P, P, P, P, P, P]),
     "lmoe_grouped_rows_bf16": (c_int, [c_int64, c_int, c_int, c_int, P, P, c_int, P, P, P, P, P]),
     "lmoe_grouped_wgrad_bf16": (c_int, [c_int64, c_int, c_int, c_int, P, P, P, P, P, P]),

@@ -82,7 +82,7 @@ struct ChainSmem {
   // FWD: gate/up slabs on their way to h1 (2 groups x 2 x 8 KB); BWD: saved gate/up staged by TMA, two chunks deep
   static constexpr int kAuxBytes = (MODE == CHAIN_FWD) ? 32768 : 65536;
   static constexpr int kOutBytes = 16384;  // one 128 x 32 bf16 slab per epilogue group
-  static constexpr int kBarrierBytes = 1024;
+  static constexpr int kBarrierBytes = 2048;  // barriers, and the pair kernel's per-expert prefix table
   static constexpr int kFixed = kChainA1Bytes + kA2Bytes + kAuxBytes + kOutBytes;
   static constexpr int kStages = (232448 - 1024 - kBarrierBytes - kFixed) / kChainStageBytes;
   static constexpr int kTotal = 1024 + kFixed + kStages * kChainStageBytes + kBarrierBytes;

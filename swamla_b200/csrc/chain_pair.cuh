@@ -1,0 +1,629 @@
+// The routed expert chain (chain.cuh) on CTA PAIRS (tcgen05 cta_group::2): two CTAs of a cluster work on two 128-row
+// tiles of the SAME expert and share every weight slice.
+//
+// Why: the chain is bound by what an SM can pull out of L2 (about 65 GB/s per SM with all SMs loading), and per
+// 128-row tile that is mostly the expert's weights (384 KB of weights against 64 KB of activations at L = F = 256).
+// In a pair each CTA loads HALF of every weight slice (its half of the N extent), the MMA with M = 256 reads both
+// halves, and each CTA keeps the accumulators of its own 128 rows in its own tensor memory: half the weight traffic
+// per tile.
+//
+// Pairs are formed inside an expert's run of tiles (tiles 2j and 2j+1 of expert e); an expert with an odd number of
+// tiles ends with a pair whose second CTA recomputes the first tile and stores nothing.  pad_offsets[E+1] (rows, multiples
+// of 128, fewer than 2^23 tiles) gives the runs; the pair index -> (expert, tile) map comes from a small per-expert table
+// in shared memory.
+//
+// Roles per CTA as in chain.cuh.  Differences (as in gemm_pair.cuh):
+//   * rank 0's "full" barriers collect the bytes of BOTH CTAs' loads (the loads name rank 0's barrier through its
+//     shared::cluster address; no multicast load anywhere);
+//   * only rank 0 issues MMAs; its tcgen05.commit arrives at the barriers of both CTAs (ring / A / A2 "empty",
+//     accumulator "full");
+//   * the epilogue warps of both CTAs release accumulators on rank 0's barriers (16 arrivals), and both CTAs' chunk
+//     issuers report their A2 buffer on rank 0's barrier (2 arrivals);
+//   * cluster barriers after set-up and before tear-down.
+// L must be a multiple of 128 (each CTA's half of the second GEMM's N extent is whole 64-wide chunks).
+#pragma once
+#include "chain.cuh"
+
+namespace lmoe {
+
+struct alignas(64) ChainPairParams {
+  CUtensorMap tmA;    // [P, L] box {64, 128}
+  CUtensorMap tmB1;   // FWD: Wgu [E*L, 2F] box {64, 64};   BWD: Wd [E*F, L] box {64 k, 32 rows}
+  CUtensorMap tmB2;   // FWD: Wd [E*F, L] box {64, 64};     BWD: Wgu [E*L, 2F] box {64 k, L/2 rows}
+  CUtensorMap tmAux;  // h1 [P, 2F] box {32, 128} (64-byte swizzle): FWD store, BWD load
+  CUtensorMap tmMid;  // box {64, 128} (128-byte swizzle): FWD hidden [P, F]; BWD d_h1 [P, 2F]
+  CUtensorMap tmOut;  // [P, L] box {32, 128} (64-byte swizzle)
+  int L, F, E;
+  int max_tiles;
+  int prefetch_a;
+  const int* pad_offsets;   // [E + 1] first padded row of every expert (multiples of 128)
+  int* status;
+};
+
+__device__ __forceinline__ bool mbar_try_wait_cluster(uint64_t* bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n"
+      ".reg .pred p;\n"
+      "mbarrier.try_wait.parity.acquire.cluster.shared::cta.b64 p, [%1], %2;\n"
+      "selp.u32 %0, 1, 0, p;\n"
+      "}\n"
+      : "=r"(ok)
+      : "r"(smem_u32(bar)), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+// Bounded wait with cluster-scope acquire: for barriers that threads of the OTHER CTA arrive on after writing memory
+// this CTA's tensor-core operations will read.
+__device__ __forceinline__ bool mbar_wait_cluster(uint64_t* bar, uint32_t parity, volatile int* abort_flag, int* status,
+                                                  int code) {
+  if (mbar_try_wait_cluster(bar, parity)) return true;
+  const long long t0 = clock64();
+  uint32_t spins = 0;
+  while (!mbar_try_wait_cluster(bar, parity)) {
+    if ((++spins & 63u) == 0u) {
+      if (*abort_flag) return false;
+      if (clock64() - t0 > kWaitBudgetCycles) {
+        *abort_flag = 1;
+        if (status) atomicCAS(status, 0, code);
+        return false;
+      }
+    }
+  }
+  return true;
+}
+
+template <int MODE>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads, 1)
+chain_pair_kernel(const __grid_constant__ ChainPairParams p) {
+  using S = ChainSmem<MODE>;
+  constexpr int STAGES = S::kStages;
+  constexpr bool FWD = (MODE == CHAIN_FWD);
+  constexpr uint32_t TMEM_COLS = 512;
+  constexpr uint32_t ACC2_COL = 256;
+
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t* const a1 = smem;
+  uint8_t* const a2 = a1 + kChainA1Bytes;
+  uint8_t* const aux = a2 + S::kA2Bytes;
+  uint8_t* const outb = aux + S::kAuxBytes;
+  uint8_t* const ring = outb + S::kOutBytes;
+  uint64_t* const bars = reinterpret_cast<uint64_t*>(ring + STAGES * kChainStageBytes);
+  uint64_t* const ring_full = bars;                      // rank 0's: bytes of both CTAs
+  uint64_t* const ring_empty = ring_full + STAGES;       // local: one commit arrival
+  uint64_t* const a1_full = ring_empty + STAGES;         // [4] rank 0's
+  uint64_t* const a1_empty = a1_full + 4;                // [4] local
+  uint64_t* const acc1_full = a1_empty + 4;              // [2] local
+  uint64_t* const acc1_empty = acc1_full + 2;            // [2] rank 0's: 16 arrivals
+  uint64_t* const a2_full = acc1_empty + 2;              // [1] rank 0's: 2 arrivals
+  uint64_t* const a2_empty = a2_full + 1;                // [1] local
+  uint64_t* const acc2_full = a2_empty + 1;              // [1] local
+  uint64_t* const acc2_empty = acc2_full + 1;            // [1] rank 0's: 16 arrivals
+  uint64_t* const gu_full = acc2_empty + 1;              // [2] local (BWD)
+  uint32_t* const tmem_slot = reinterpret_cast<uint32_t*>(gu_full + 2);
+  volatile int* const abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+  int* const etab = reinterpret_cast<int*>(tmem_slot + 2);  // [E + 1] per-expert table (<= 257 ints), see below
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const uint32_t rank = cluster_ctarank();
+
+  if (threadIdx.x == 0) {
+    for (int i = 0; i < STAGES; ++i) {
+      mbar_init(&ring_full[i], 1);
+      mbar_init(&ring_empty[i], 1);
+    }
+    for (int i = 0; i < 4; ++i) {
+      mbar_init(&a1_full[i], 1);
+      mbar_init(&a1_empty[i], 1);
+    }
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(&acc1_full[i], 1);
+      mbar_init(&acc1_empty[i], 16);
+      mbar_init(&gu_full[i], 1);
+    }
+    mbar_init(a2_full, 2);
+    mbar_init(a2_empty, 1);
+    mbar_init(acc2_full, 1);
+    mbar_init(acc2_empty, 16);
+    *abort_flag = 0;
+    fence_mbar_init();
+    tma_prefetch_desc(&p.tmA);
+    tma_prefetch_desc(&p.tmB1);
+    tma_prefetch_desc(&p.tmB2);
+    tma_prefetch_desc(&p.tmAux);
+    tma_prefetch_desc(&p.tmMid);
+    tma_prefetch_desc(&p.tmOut);
+  }
+  // Per-expert table in shared memory: etab[e] = first tile of expert e (low 23 bits) | number of experts before e with
+  // an odd tile count (high 9 bits).  Pairs before expert e = (first_tile(e) - first_tile(0) + odd_before(e)) / 2.
+  const int E = p.E;
+  {
+    const int cap_rows = p.max_tiles * kBM;
+    if (static_cast<int>(threadIdx.x) <= E) etab[threadIdx.x] = min(p.pad_offsets[threadIdx.x], cap_rows) / kBM;
+    __syncthreads();
+    if (warp == 0) {  // lane l scans experts 8l .. 8l+7, a shuffle scan joins the lanes
+      int odd[8], sum = 0;
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        const int e = lane * 8 + i;
+        odd[i] = (e < E) ? ((etab[e + 1] - etab[e]) & 1) : 0;
+        sum += odd[i];
+      }
+      int incl = sum;
+#pragma unroll
+      for (int o = 1; o < 32; o <<= 1) {
+        const int t = __shfl_up_sync(0xffffffffu, incl, o);
+        if (lane >= o) incl += t;
+      }
+      __syncwarp();  // every lane has read its nine entries before any is rewritten
+      int run = incl - sum;
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        const int e = lane * 8 + i;
+        if (e < E) etab[e] |= run << 23;
+        run += odd[i];
+        if (e + 1 == E) etab[E] |= run << 23;
+      }
+    }
+  }
+  if (warp == 1) {
+    tmem_alloc_pair(tmem_slot, TMEM_COLS);
+    tmem_relinquish_pair();
+    tc_fence_before();
+  }
+  __syncthreads();
+  cluster_sync_all();  // both CTAs' barriers are initialised before any remote arrival or load completion
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  // ---- schedule: identical arithmetic in every role of both CTAs ----
+  const int L = p.L, F = p.F;
+  const int KB1 = L / 64;   // k-blocks of the first GEMM
+  const int NC = F / 64;    // chunks per tile
+  auto first_tile = [&](int e) { return etab[e] & 0x7fffff; };
+  auto pairs_before = [&](int e) { return ((etab[e] & 0x7fffff) - (etab[0] & 0x7fffff) + (etab[e] >> 23)) >> 1; };
+  const int n_pairs = pairs_before(E);
+  const int cluster_id = static_cast<int>(blockIdx.x) >> 1;
+  const int n_clusters = static_cast<int>(gridDim.x) >> 1;
+  struct Cur {
+    int pid, c;   // pair index, chunk
+    int e;        // expert of the pair
+    int tile;     // the 128-row tile this CTA loads (its own, or the pair's first one when it has none)
+    int live;     // 1: this CTA's tile exists and its results are stored
+  };
+  auto locate = [&](int pid, int c) {
+    Cur k;
+    k.pid = pid;
+    k.c = c;
+    k.e = 0;
+    k.tile = 0;
+    k.live = 0;
+    if (pid >= n_pairs) return k;
+    int lo = 0, hi = E - 1;  // largest e with pairs_before(e) <= pid
+    while (lo < hi) {
+      const int mid = (lo + hi + 1) >> 1;
+      if (pairs_before(mid) <= pid) lo = mid;
+      else hi = mid - 1;
+    }
+    k.e = lo;
+    const int t1 = first_tile(lo + 1);
+    const int first = first_tile(lo) + 2 * (pid - pairs_before(lo));
+    const int own = first + static_cast<int>(rank);
+    k.live = own < t1 ? 1 : 0;
+    k.tile = k.live ? own : first;
+    return k;
+  };
+  auto valid = [&](const Cur& k) { return k.pid < n_pairs; };
+  auto next = [&](const Cur& k) {
+    if (k.c + 1 < NC) {
+      Cur n = k;
+      n.c = k.c + 1;
+      return n;
+    }
+    return locate(k.pid + n_clusters, 0);
+  };
+
+  if (warp == 0) {
+    // ======================================= TMA producer (both CTAs) =======================================
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      // next ring stage; rank 0 arms its "full" barrier for the bytes of BOTH CTAs; returns this CTA's stage buffer
+      // and leaves the shared::cluster address of rank 0's barrier in `full0`
+      uint32_t full0 = 0;
+      auto acquire = [&](uint32_t bytes_per_cta) -> uint8_t* {
+        if (!mbar_wait(&ring_empty[stage], phase ^ 1, abort_flag, p.status, kStatusProducerTimeout)) {
+          ok = false;
+          return nullptr;
+        }
+        if (rank == 0) mbar_expect_tx(&ring_full[stage], 2 * bytes_per_cta);
+        full0 = mapa_shared(smem_u32(&ring_full[stage]), 0);
+        return ring + stage * kChainStageBytes;
+      };
+      auto advance = [&]() {
+        if (++stage == STAGES) {
+          stage = 0;
+          phase ^= 1;
+        }
+      };
+      int tiles_loaded = 0;
+      auto emit_g1 = [&](const Cur& k) {
+        const int m0 = k.tile * kBM;
+        if (k.c == 0) {  // this CTA's A operand, k-block by k-block as the previous tile's last chunk releases them
+          for (int kb = 0; kb < KB1 && ok; ++kb) {
+            if (!mbar_wait(&a1_empty[kb], (tiles_loaded & 1) ^ 1, abort_flag, p.status, kStatusProducerTimeout)) {
+              ok = false;
+              break;
+            }
+            if (rank == 0) mbar_expect_tx(&a1_full[kb], 2 * 16384);
+            tma_load_2d_pair(a1 + kb * 16384, &p.tmA, mapa_shared(smem_u32(&a1_full[kb]), 0), kb * 64, m0);
+          }
+          ++tiles_loaded;
+          if (p.prefetch_a) {  // the A operand of this CTA's next tile: into L2 a whole tile period ahead
+            const Cur nx = locate(k.pid + n_clusters, 0);
+            if (valid(nx))
+              for (int kb = 0; kb < KB1; ++kb) tma_prefetch_2d(&p.tmA, kb * 64, nx.tile * kBM);
+          }
+        }
+        if (!ok) return;
+        if (FWD) {
+          // this CTA's half of the chunk's B: rank 0 the 64 gate columns, rank 1 the 64 up columns of Wgu[e];
+          // two k-blocks (8 KB each) per stage
+          const int col = static_cast<int>(rank) * F + k.c * 64;
+          for (int kb = 0; kb < KB1; kb += 2) {
+            const int nkb = min(2, KB1 - kb);
+            uint8_t* st = acquire(nkb * 8192);
+            if (!st) return;
+            for (int h = 0; h < nkb; ++h) tma_load_2d_pair(st + h * 8192, &p.tmB1, full0, col, k.e * L + (kb + h) * 64);
+            advance();
+          }
+        } else {
+          // rows [c*64 + rank*32, +32) of Wd[e] (this CTA's half of the chunk's d_hidden columns): 4 KB per k-block,
+          // all k-blocks of the chunk in one stage
+          uint8_t* st = acquire(KB1 * 4096);
+          if (!st) return;
+          for (int kb = 0; kb < KB1; ++kb)
+            tma_load_2d_pair(st + kb * 4096, &p.tmB1, full0, kb * 64, k.e * F + k.c * 64 + static_cast<int>(rank) * 32);
+          advance();
+        }
+      };
+      auto emit_g2 = [&](const Cur& k) {
+        const int half = L / 2;  // this CTA's share of the second GEMM's N extent
+        if (FWD) {
+          // rows [c*64, +64) of Wd[e], columns [rank*L/2, +L/2): L/128 MN-major chunks of 8 KB
+          uint8_t* st = acquire(half * 128);
+          if (!st) return;
+          for (int j = 0; j < half / 64; ++j)
+            tma_load_2d_pair(st + j * 8192, &p.tmB2, full0, static_cast<int>(rank) * half + j * 64, k.e * F + k.c * 64);
+          advance();
+        } else {
+          // Wgu[e] rows [rank*L/2, +L/2) (output columns of d_x), k columns [c*64, +64) (gate part), then the up part
+          for (int part = 0; part < 2; ++part) {
+            uint8_t* st = acquire(half * 128);
+            if (!st) return;
+            tma_load_2d_pair(st, &p.tmB2, full0, part * F + k.c * 64, k.e * L + static_cast<int>(rank) * half);
+            advance();
+          }
+        }
+      };
+      Cur cur = locate(cluster_id, 0);
+      if (valid(cur)) emit_g1(cur);
+      while (ok && valid(cur)) {
+        const Cur nx = next(cur);
+        if (valid(nx)) emit_g1(nx);
+        if (!ok) break;
+        emit_g2(cur);
+        cur = nx;
+      }
+    }
+  } else if (warp == 1) {
+    // ==================================== MMA issuer (rank 0 only) ====================================
+    if (lane == 0 && rank == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      auto wait_stage = [&]() -> uint32_t {
+        if (!mbar_wait(&ring_full[stage], phase, abort_flag, p.status, kStatusMmaTimeout)) {
+          ok = false;
+          return 0u;
+        }
+        tc_fence_after();
+        return smem_u32(ring + stage * kChainStageBytes);
+      };
+      auto release_stage = [&]() {
+        umma_commit_pair(&ring_empty[stage], 0x3);
+        if (++stage == STAGES) {
+          stage = 0;
+          phase ^= 1;
+        }
+      };
+      const uint32_t a1_addr = smem_u32(a1), a2_addr = smem_u32(a2);
+      int tiles_g1 = 0, tiles_g2 = 0;
+      auto issue_g1 = [&](const Cur& k, int gi) {
+        const int b = gi & 1;
+        if (!mbar_wait_cluster(&acc1_empty[b], ((gi >> 1) & 1) ^ 1, abort_flag, p.status, kStatusMmaTimeout)) {
+          ok = false;
+          return;
+        }
+        tc_fence_after();
+        const uint32_t d_tmem = tmem_base + b * 128;
+        const uint32_t a_par = tiles_g1 & 1;
+        if (FWD) {
+          constexpr uint32_t idesc = make_idesc(1u, 1u, false, true, 256, 128);
+          for (int kb = 0; kb < KB1; kb += 2) {
+            const uint32_t sb = wait_stage();
+            if (!ok) return;
+            const int nkb = min(2, KB1 - kb);
+            for (int h = 0; h < nkb; ++h) {
+              if (k.c == 0) {
+                if (!mbar_wait(&a1_full[kb + h], a_par, abort_flag, p.status, kStatusMmaTimeout)) {
+                  ok = false;
+                  return;
+                }
+                tc_fence_after();
+              }
+#pragma unroll
+              for (int kk = 0; kk < 4; ++kk) {
+                const uint64_t da = make_smem_desc_sw128(a1_addr + (kb + h) * 16384 + kk * 32, 0, 1024);
+                const uint64_t db = make_smem_desc_sw128(sb + h * 8192 + kk * 2048, 8192, 1024);
+                umma_f16_pair(d_tmem, da, db, idesc, (kb + h > 0 || kk > 0) ? 1u : 0u);
+              }
+              if (k.c == NC - 1) umma_commit_pair(&a1_empty[kb + h], 0x3);
+            }
+            release_stage();
+          }
+        } else {
+          constexpr uint32_t idesc = make_idesc(1u, 1u, false, false, 256, 64);
+          const uint32_t sb = wait_stage();
+          if (!ok) return;
+          for (int kb = 0; kb < KB1; ++kb) {
+            if (k.c == 0) {
+              if (!mbar_wait(&a1_full[kb], a_par, abort_flag, p.status, kStatusMmaTimeout)) {
+                ok = false;
+                return;
+              }
+              tc_fence_after();
+            }
+#pragma unroll
+            for (int kk = 0; kk < 4; ++kk) {
+              const uint64_t da = make_smem_desc_sw128(a1_addr + kb * 16384 + kk * 32, 0, 1024);
+              const uint64_t db = make_smem_desc_sw128(sb + kb * 4096 + kk * 32, 0, 1024);
+              umma_f16_pair(d_tmem, da, db, idesc, (kb > 0 || kk > 0) ? 1u : 0u);
+            }
+            if (k.c == NC - 1) umma_commit_pair(&a1_empty[kb], 0x3);
+          }
+          release_stage();
+        }
+        if (k.c == 0) ++tiles_g1;
+        umma_commit_pair(&acc1_full[b], 0x3);
+      };
+      auto issue_g2 = [&](const Cur& k, int gi) {
+        if (k.c == 0) {
+          if (!mbar_wait_cluster(acc2_empty, (tiles_g2 & 1) ^ 1, abort_flag, p.status, kStatusMmaTimeout)) {
+            ok = false;
+            return;
+          }
+          ++tiles_g2;
+        }
+        // both CTAs' epilogue warps have written their A2 buffers (cluster-scope acquire: one of them is remote)
+        if (!mbar_wait_cluster(a2_full, gi & 1, abort_flag, p.status, kStatusMmaTimeout)) {
+          ok = false;
+          return;
+        }
+        tc_fence_after();
+        const uint32_t idesc = make_idesc(1u, 1u, false, FWD, 256, static_cast<uint32_t>(L));
+        if (FWD) {
+          const uint32_t sb = wait_stage();
+          if (!ok) return;
+#pragma unroll
+          for (int kk = 0; kk < 4; ++kk) {
+            const uint64_t da = make_smem_desc_sw128(a2_addr + kk * 32, 0, 1024);
+            const uint64_t db = make_smem_desc_sw128(sb + kk * 2048, 8192, 1024);
+            umma_f16_pair(tmem_base + ACC2_COL, da, db, idesc, (k.c > 0 || kk > 0) ? 1u : 0u);
+          }
+          release_stage();
+        } else {
+          for (int part = 0; part < 2; ++part) {
+            const uint32_t sb = wait_stage();
+            if (!ok) return;
+#pragma unroll
+            for (int kk = 0; kk < 4; ++kk) {
+              const uint64_t da = make_smem_desc_sw128(a2_addr + part * 16384 + kk * 32, 0, 1024);
+              const uint64_t db = make_smem_desc_sw128(sb + kk * 32, 0, 1024);
+              umma_f16_pair(tmem_base + ACC2_COL, da, db, idesc, (k.c > 0 || part > 0 || kk > 0) ? 1u : 0u);
+            }
+            release_stage();
+          }
+        }
+        umma_commit_pair(a2_empty, 0x3);
+        if (k.c == NC - 1) umma_commit_pair(acc2_full, 0x3);
+      };
+      Cur cur = locate(cluster_id, 0);
+      int gi = 0;
+      if (valid(cur)) issue_g1(cur, 0);
+      while (ok && valid(cur)) {
+        const Cur nx = next(cur);
+        if (valid(nx)) issue_g1(nx, gi + 1);
+        if (!ok) break;
+        issue_g2(cur, gi);
+        cur = nx;
+        ++gi;
+      }
+    }
+  } else {
+    // ============================= epilogue (both CTAs, own 128 rows) =============================
+    const int q = warp & 3;
+    const int group = (warp - 2) >> 2;
+    const int bar_id = 1 + group;
+    const int r = q * 32 + lane;
+    const bool chunk_issuer = (warp == 2 && lane == 0);
+    const bool group_issuer = (((warp - 2) & 3) == 0) && lane == 0;
+    const uint32_t lane_addr = tmem_base + (static_cast<uint32_t>(q * 32) << 16);
+    uint8_t* const out_slab = outb + group * 8192;
+    // rank 0's barriers that this CTA's epilogue arrives on
+    const uint32_t acc1_empty0[2] = {mapa_shared(smem_u32(&acc1_empty[0]), 0), mapa_shared(smem_u32(&acc1_empty[1]), 0)};
+    const uint32_t acc2_empty0 = mapa_shared(smem_u32(acc2_empty), 0);
+    const uint32_t a2_full0 = mapa_shared(smem_u32(a2_full), 0);
+    int tiles_done = 0;
+    bool ok = true;
+    Cur cur = locate(cluster_id, 0);
+    // Backward: saved gate / up of a chunk staged by TMA two chunks ahead (see chain.cuh); local to each CTA.
+    auto load_gu = [&](const Cur& k, int b) {
+      mbar_expect_tx(&gu_full[b], 32768);
+      uint8_t* dst = aux + b * 32768;
+      const int row0 = k.tile * kBM;
+      for (int gr = 0; gr < 2; ++gr) {
+        tma_load_3d(dst + gr * 16384, &p.tmAux, &gu_full[b], k.c * 64 + gr * 32, row0, 0);
+        tma_load_3d(dst + gr * 16384 + 8192, &p.tmAux, &gu_full[b], F + k.c * 64 + gr * 32, row0, 0);
+      }
+    };
+    if (!FWD && chunk_issuer && valid(cur)) {
+      load_gu(cur, 0);
+      const Cur c1 = next(cur);
+      if (valid(c1)) load_gu(c1, 1);
+    }
+    for (int gi = 0; valid(cur); ++gi, cur = next(cur)) {
+      const int b = gi & 1;
+      const int m0 = cur.tile * kBM;
+      // ---------------- chunk epilogue ----------------
+      if (!mbar_wait(&acc1_full[b], (gi >> 1) & 1, abort_flag, p.status, kStatusEpilogueTimeout)) ok = false;
+      if (!FWD && ok && !mbar_wait(&gu_full[b], (gi >> 1) & 1, abort_flag, p.status, kStatusEpilogueTimeout)) ok = false;
+      tc_fence_after();
+      uint32_t pa[16], pb[16], pc[16];
+      if (ok) {
+        if (FWD) {
+          float v[32], u[32];
+          tmem_ld32(lane_addr + b * 128 + group * 32, v);        // gate
+          tmem_ld32(lane_addr + b * 128 + 64 + group * 32, u);   // up
+          tmem_ld_wait();
+          tc_fence_before();
+          __syncwarp();
+          if (lane == 0) mbar_arrive_cluster(acc1_empty0[b]);
+#pragma unroll
+          for (int j = 0; j < 16; ++j) {
+            pa[j] = pack_bf16x2(v[2 * j], v[2 * j + 1]);
+            pb[j] = pack_bf16x2(u[2 * j], u[2 * j + 1]);
+            const float g0 = __uint_as_float(pa[j] << 16), g1 = __uint_as_float(pa[j] & 0xffff0000u);
+            const float u0 = __uint_as_float(pb[j] << 16), u1 = __uint_as_float(pb[j] & 0xffff0000u);
+            pc[j] = pack_bf16x2(silu_f(g0) * u0, silu_f(g1) * u1);
+          }
+        } else {
+          float v[32];
+          tmem_ld32(lane_addr + b * 128 + group * 32, v);        // d_hidden
+          tmem_ld_wait();
+          tc_fence_before();
+          uint32_t sg[16], su[16];
+          const uint8_t* gu = aux + b * 32768 + group * 16384;
+          slab_read_row(gu, r, sg);
+          slab_read_row(gu + 8192, r, su);
+          __syncwarp();
+          if (lane == 0) mbar_arrive_cluster(acc1_empty0[b]);
+#pragma unroll
+          for (int j = 0; j < 16; ++j) {
+            const uint32_t dh2 = pack_bf16x2(v[2 * j], v[2 * j + 1]);
+            const float dh[2] = {__uint_as_float(dh2 << 16), __uint_as_float(dh2 & 0xffff0000u)};
+            const float g[2] = {__uint_as_float(sg[j] << 16), __uint_as_float(sg[j] & 0xffff0000u)};
+            const float uu[2] = {__uint_as_float(su[j] << 16), __uint_as_float(su[j] & 0xffff0000u)};
+            float dg[2], du[2];
+#pragma unroll
+            for (int t = 0; t < 2; ++t) {
+              const float s = 1.0f / (1.0f + __expf(-g[t]));
+              du[t] = dh[t] * g[t] * s;
+              dg[t] = dh[t] * uu[t] * s * (1.0f + g[t] * (1.0f - s));
+            }
+            pa[j] = pack_bf16x2(dg[0], dg[1]);
+            pb[j] = pack_bf16x2(du[0], du[1]);
+          }
+        }
+      }
+      if (ok && !mbar_wait(a2_empty, (gi & 1) ^ 1, abort_flag, p.status, kStatusEpilogueTimeout)) ok = false;
+      if (chunk_issuer) tma_store_wait_read_all();
+      ok = epi_all_and(ok);
+      if (!ok) break;
+      if (!FWD && chunk_issuer) {  // every thread holds its gate / up rows in registers: refill the buffer (chunk gi + 2)
+        const Cur c2 = next(next(cur));
+        if (valid(c2)) load_gu(c2, b);
+      }
+      if (FWD) {
+        uint8_t* slabs = aux + group * 16384;
+        stage_row_bf16(slabs, r, pa);
+        stage_row_bf16(slabs + 8192, r, pb);
+        a2_write_half(a2, r, group, pc);
+      } else {
+        a2_write_half(a2, r, group, pa);
+        a2_write_half(a2 + 16384, r, group, pb);
+      }
+      fence_proxy_async_smem();
+      epi_all_sync();
+      if (chunk_issuer) {
+        mbar_arrive_cluster(a2_full0);  // release at cluster scope: the MMAs issued by rank 0 read this CTA's A2 buffer
+        if (cur.live) {
+          if (FWD) {
+            for (int gr = 0; gr < 2; ++gr) {
+              tma_store_3d(&p.tmAux, aux + gr * 16384, cur.c * 64 + gr * 32, m0, 0);
+              tma_store_3d(&p.tmAux, aux + gr * 16384 + 8192, F + cur.c * 64 + gr * 32, m0, 0);
+            }
+            tma_store_2d(&p.tmMid, a2, cur.c * 64, m0);
+          } else {
+            tma_store_2d(&p.tmMid, a2, cur.c * 64, m0);
+            tma_store_2d(&p.tmMid, a2 + 16384, F + cur.c * 64, m0);
+          }
+        }
+        tma_store_commit();
+      }
+      if (cur.c != NC - 1) continue;
+      // ---------------- tile epilogue ----------------
+      if (!mbar_wait(acc2_full, tiles_done & 1, abort_flag, p.status, kStatusEpilogueTimeout)) ok = false;
+      tc_fence_after();
+      ok = epi_all_and(ok);
+      if (!ok) break;
+      const int slabs = L / kSlabCols;
+      const int last = ((slabs - 1 - group) >= 0) ? group + ((slabs - 1 - group) & ~1) : -1;
+      if (last < 0) {
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive_cluster(acc2_empty0);
+      }
+#pragma unroll 1
+      for (int c = group; c < slabs; c += 2) {
+        float v[32];
+        tmem_ld32(lane_addr + ACC2_COL + c * 32, v);
+        tmem_ld_wait();
+        if (c == last) {
+          tc_fence_before();
+          __syncwarp();
+          if (lane == 0) mbar_arrive_cluster(acc2_empty0);
+        }
+        if (!cur.live) continue;  // uniform over the CTA: a tile-less second CTA only drains its accumulator
+        uint32_t pk[16];
+#pragma unroll
+        for (int j = 0; j < 16; ++j) pk[j] = pack_bf16x2(v[2 * j], v[2 * j + 1]);
+        if (group_issuer) tma_store_wait_read_all();
+        epi_bar_sync(bar_id);
+        stage_row_bf16(out_slab, r, pk);
+        fence_proxy_async_smem();
+        epi_bar_sync(bar_id);
+        if (group_issuer) {
+          tma_store_3d(&p.tmOut, out_slab, c * kSlabCols, m0, 0);
+          tma_store_commit();
+        }
+      }
+      ++tiles_done;
+    }
+    if (group_issuer) tma_store_wait0();
+  }
+
+  // ---- teardown: every role of both CTAs falls through to here, also after an abort ----
+  tc_fence_before();
+  __syncthreads();
+  cluster_sync_all();  // neither CTA leaves (or frees tensor memory) while its partner may still signal it
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc_pair(tmem_base, TMEM_COLS);
+  }
+}
+
+}  // namespace lmoe

@@ -70,9 +70,11 @@ int encode_out(CUtensorMap* map, void* base, bool f32, long long cols, long long
 // mid = hidden [P, F] and out = y_sorted [P, L] are written.  mode 1 (backward): a = d_y_sorted, h1 is read,
 // mid = d_h1 [P, 2F] and out = d_x_sorted [P, L] are written.
 bool chain_applies(int L, int F);
+// pad_offsets [E + 1] (first padded row of every expert) lets the launcher pair up tiles of the same expert on CTA
+// pairs (chain_pair.cuh); NULL: one CTA per tile.
 int launch_chain(int mode, long long P, int E, int L, int F, const void* a, const void* w_gate_up, const void* w_down,
-                 const int* tile_expert, const int* n_tiles, void* h1, void* mid, void* out, int* status,
-                 cudaStream_t stream);
+                 const int* tile_expert, const int* n_tiles, const int* pad_offsets, void* h1, void* mid, void* out,
+                 int* status, cudaStream_t stream);
 
 // True when dense GEMMs of this size run on CTA pairs (256 x 256 tiles over two SMs) rather than one CTA per 128 x 256 tile.
 bool pair_gemm_applies(int M, int N);

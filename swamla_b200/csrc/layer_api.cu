@@ -168,14 +168,15 @@ static int apply_gather(GemmCall& c, const GatherA* g) {
 }
 
 static int grouped_fwd_impl(int64_t P, int E, int L, int F, const void* x_sorted, const GatherA* g, const void* w_gate_up,
-                            const void* w_down, const int32_t* tile_expert, const int32_t* n_tiles, void* h1,
+                            const void* w_down, const int32_t* tile_expert, const int32_t* n_tiles,
+                            const int32_t* pad_offsets, void* h1,
                             void* hidden, void* y_sorted, int32_t* status, void* stream) {
   if (!x_sorted || !w_gate_up || !w_down || !tile_expert || !n_tiles || !h1 || !hidden || !y_sorted) return LMOE_ERR_ARG;
   if (P <= 0 || (P % LMOE_ROW_PAD) != 0 || E <= 0 || (L % 64) != 0 || (F % 64) != 0) return LMOE_ERR_SHAPE;
   // one kernel for gate_up -> SwiGLU -> down per 128-row tile when the latent width fits the second accumulator
   if (!g && chain_applies(L, F))
-    return launch_chain(CHAIN_FWD, P, E, L, F, x_sorted, w_gate_up, w_down, tile_expert, n_tiles, h1, hidden, y_sorted,
-                        status, static_cast<cudaStream_t>(stream));
+    return launch_chain(CHAIN_FWD, P, E, L, F, x_sorted, w_gate_up, w_down, tile_expert, n_tiles, pad_offsets, h1, hidden,
+                        y_sorted, status, static_cast<cudaStream_t>(stream));
   // h1 = x_sorted * Wgu[e]  (Wgu stacked [E*L, 2F], N contiguous), hidden = silu(gate) * up
   GemmCall a;
   a.a_mn = 0;
@@ -219,10 +220,11 @@ static int grouped_fwd_impl(int64_t P, int E, int L, int F, const void* x_sorted
 }
 
 extern "C" int lmoe_grouped_fwd(int64_t P, int E, int L, int F, const void* x_sorted, const void* w_gate_up,
-                                const void* w_down, const int32_t* tile_expert, const int32_t* n_tiles, void* h1,
-                                void* hidden, void* y_sorted, int32_t* status, void* stream) {
-  return grouped_fwd_impl(P, E, L, F, x_sorted, nullptr, w_gate_up, w_down, tile_expert, n_tiles, h1, hidden, y_sorted,
-                          status, stream);
+                                const void* w_down, const int32_t* tile_expert, const int32_t* n_tiles,
+                                const int32_t* pad_offsets, void* h1, void* hidden, void* y_sorted, int32_t* status,
+                                void* stream) {
+  return grouped_fwd_impl(P, E, L, F, x_sorted, nullptr, w_gate_up, w_down, tile_expert, n_tiles, pad_offsets, h1, hidden,
+                          y_sorted, status, stream);
 }
 
 extern "C" int lmoe_grouped_fwd_gather(int64_t P, int E, int L, int F, const void* src_rows, int64_t n_src_rows,
@@ -236,8 +238,8 @@ extern "C" int lmoe_grouped_fwd_gather(int64_t P, int E, int L, int F, const voi
   g.index_div = index_div;
   g.n_src_rows = n_src_rows;
   g.zero_row = zero_row;
-  return grouped_fwd_impl(P, E, L, F, src_rows, &g, w_gate_up, w_down, tile_expert, n_tiles, h1, hidden, y_sorted, status,
-                          stream);
+  return grouped_fwd_impl(P, E, L, F, src_rows, &g, w_gate_up, w_down, tile_expert, n_tiles, nullptr, h1, hidden, y_sorted,
+                          status, stream);
 }
 
 extern "C" int lmoe_experts_fwd(const lmoe_shape* s, const void* x_latent, const void* w_gate_up, const void* w_down,
@@ -247,7 +249,7 @@ extern "C" int lmoe_experts_fwd(const lmoe_shape* s, const void* x_latent, const
   if (!x_latent || !w_gate_up || !w_down || !r || !x_sorted || !h1 || !hidden || !y_sorted) return LMOE_ERR_ARG;
   const long long P = lmoe_padded_rows(s);
   if (int rc = gather_rows(x_latent, r, s->K, s->L, P, x_sorted, static_cast<cudaStream_t>(stream))) return rc;
-  return lmoe_grouped_fwd(P, s->E, s->L, s->F, x_sorted, w_gate_up, w_down, r->tile_expert, r->n_tiles, h1, hidden,
+  return lmoe_grouped_fwd(P, s->E, s->L, s->F, x_sorted, w_gate_up, w_down, r->tile_expert, r->n_tiles, r->pad_offsets, h1, hidden,
                           y_sorted, status, stream);
 }
 
@@ -374,15 +376,16 @@ extern "C" int lmoe_grouped_wgrad_bf16(int64_t P, int E, int M, int N, const voi
 
 extern "C" int lmoe_grouped_bwd_dgrad(int64_t P, int E, int L, int F, const void* d_y_sorted, const void* h1,
                                       const void* w_gate_up, const void* w_down, const int32_t* tile_expert,
-                                      const int32_t* n_tiles, void* d_hidden, void* d_h1, void* d_x_sorted,
+                                      const int32_t* n_tiles, const int32_t* pad_offsets, void* d_hidden, void* d_h1,
+                                      void* d_x_sorted,
                                       int32_t* status, void* stream) {
   if (!d_y_sorted || !h1 || !w_gate_up || !w_down || !tile_expert || !n_tiles || !d_h1 || !d_x_sorted)
     return LMOE_ERR_ARG;
   if (P <= 0 || (P % LMOE_ROW_PAD) != 0 || E <= 0 || (L % 64) != 0 || (F % 64) != 0) return LMOE_ERR_SHAPE;
   // one kernel for d_hidden -> SwiGLU adjoint -> d_x_sorted per 128-row tile (d_hidden is not written then)
   if (chain_applies(L, F))
-    return launch_chain(CHAIN_BWD, P, E, L, F, d_y_sorted, w_gate_up, w_down, tile_expert, n_tiles, const_cast<void*>(h1),
-                        d_h1, d_x_sorted, status, static_cast<cudaStream_t>(stream));
+    return launch_chain(CHAIN_BWD, P, E, L, F, d_y_sorted, w_gate_up, w_down, tile_expert, n_tiles, pad_offsets,
+                        const_cast<void*>(h1), d_h1, d_x_sorted, status, static_cast<cudaStream_t>(stream));
   // d_hidden[P,F] = d_y_sorted[P,L] * Wd[e]^T : Wd[e] is [F,L] = [N,K] row-major -> K-major B
   GemmCall a;
   a.a_mn = 0;
@@ -438,7 +441,7 @@ extern "C" int lmoe_experts_bwd_dgrad(const lmoe_shape* s, const void* d_y_sorte
   if (int rc = check_dims(s)) return rc;
   if (!r) return LMOE_ERR_ARG;
   return lmoe_grouped_bwd_dgrad(lmoe_padded_rows(s), s->E, s->L, s->F, d_y_sorted, h1, w_gate_up, w_down,
-                                r->tile_expert, r->n_tiles, d_hidden, d_h1, d_x_sorted, status, stream);
+                                r->tile_expert, r->n_tiles, r->pad_offsets, d_hidden, d_h1, d_x_sorted, status, stream);
 }
 
 static int grouped_bwd_wgrad_impl(int64_t P, int E, int L, int F, const void* x_sorted, const GatherA* g,

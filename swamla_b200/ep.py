@@ -167,7 +167,7 @@ class ExpertParallelLatentMoE(torch.autograd.Function):
         y_recv = torch.empty(n_recv, L, **bf)
         if n_recv > 0:
             _cabi.call("lmoe_gather_rows", ptr(recv_rows), ptr(row_src), 1, P, L, ptr(n_tiles), ptr(x_sorted), st)
-            _cabi.call("lmoe_grouped_fwd", P, El, L, F, ptr(x_sorted), ptr(wgu), ptr(wde), ptr(tile_expert), ptr(n_tiles),
+            _cabi.call("lmoe_grouped_fwd", P, El, L, F, ptr(x_sorted), ptr(wgu), ptr(wde), ptr(tile_expert), ptr(n_tiles), ptr(pad_offsets),
                        ptr(h1), ptr(hidden), ptr(y_sorted), ptr(status), st)
             _cabi.call("lmoe_gather_rows", ptr(y_sorted), ptr(recv_pos), 1, n_recv, L, None, ptr(y_recv), st)
         y_back = _a2a(y_recv, n_send, recv_splits, send_splits, group)          # combine
@@ -243,7 +243,7 @@ class ExpertParallelLatentMoE(torch.autograd.Function):
             d_x_sorted = torch.empty(P, L, **bf)
             d_hidden = d_hidden_scratch(lib, P, L, F, **bf)
             _cabi.call("lmoe_grouped_bwd_dgrad", P, El, L, F, ptr(d_y_sorted), ptr(h1), ptr(wgu), ptr(wde),
-                       ptr(tile_expert), ptr(n_tiles), ptr(d_hidden), ptr(d_h1), ptr(d_x_sorted), ptr(status), st)
+                       ptr(tile_expert), ptr(n_tiles), ptr(pad_offsets), ptr(d_hidden), ptr(d_h1), ptr(d_x_sorted), ptr(status), st)
             _cabi.call("lmoe_grouped_bwd_wgrad", P, El, L, F, ptr(x_sorted), ptr(d_h1), ptr(hidden), ptr(d_y_sorted),
                        ptr(pad_offsets), ptr(d_w_gate_up), ptr(d_w_down_e), ptr(status), st)
             _cabi.call("lmoe_gather_rows", ptr(d_x_sorted), ptr(recv_pos), 1, n_recv, L, None, ptr(d_x_recv), st)
@@ -394,7 +394,7 @@ class ExpertParallelP2P(torch.autograd.Function):
         h1 = torch.empty(P, 2 * F, **bf)
         hidden = torch.empty(P, F, **bf)
         y_sorted = torch.empty(P, L, **bf)
-        _cabi.call("lmoe_grouped_fwd", P, El, L, F, ptr(bufs.x_in), ptr(wgu), ptr(wde), ptr(tile_expert), ptr(n_tiles),
+        _cabi.call("lmoe_grouped_fwd", P, El, L, F, ptr(bufs.x_in), ptr(wgu), ptr(wde), ptr(tile_expert), ptr(n_tiles), ptr(pad_offsets),
                    ptr(h1), ptr(hidden), ptr(y_sorted), ptr(status), st)
         _cabi.call("lmoe_ep_return", ptr(y_sorted), ptr(tile_expert), ptr(n_tiles), ptr(pad_offsets), ptr(seg_cum),
                    ptr(src_off), ptr(counts_all), G, E, rank, L, P, ptr(bufs.peer_y_ret), st)
@@ -471,7 +471,7 @@ class ExpertParallelP2P(torch.autograd.Function):
         d_x_sorted = torch.empty(P, L, **bf)
         d_hidden = d_hidden_scratch(lib, P, L, F, **bf)
         _cabi.call("lmoe_grouped_bwd_dgrad", P, El, L, F, ptr(bufs.dy_in), ptr(h1), ptr(wgu), ptr(wde), ptr(tile_expert),
-                   ptr(n_tiles), ptr(d_hidden), ptr(d_h1), ptr(d_x_sorted), ptr(status), st)
+                   ptr(n_tiles), ptr(pad_offsets), ptr(d_hidden), ptr(d_h1), ptr(d_x_sorted), ptr(status), st)
         ready2 = torch.cuda.Event()
         ready2.record(main)
         side.wait_event(ready2)
@@ -642,7 +642,7 @@ class ExpertParallelDedup(torch.autograd.Function):
         h1 = torch.empty(P, 2 * F, **bf)
         hidden = torch.empty(P, F, **bf)
         y_sorted = torch.empty(P, L, **bf)
-        _cabi.call("lmoe_grouped_fwd", P, El, L, F, ptr(x_in), ptr(wgu), ptr(wde), ptr(tile_expert), ptr(n_tiles),
+        _cabi.call("lmoe_grouped_fwd", P, El, L, F, ptr(x_in), ptr(wgu), ptr(wde), ptr(tile_expert), ptr(n_tiles), ptr(pad_offsets),
                    ptr(h1), ptr(hidden), ptr(y_sorted), ptr(status), st)
         _cabi.call("lmoe_epd_reduce_return", ptr(y_sorted), ptr(bufs.meta), ptr(bufs.mask), ptr(bufs.slots), None,
                    ptr(src_off), ptr(counts_all), G, E, rank, K, L, stride, P, ptr(bufs.peer_ret_y), None, st)
@@ -718,7 +718,7 @@ class ExpertParallelDedup(torch.autograd.Function):
         d_x_sorted = torch.empty(P, L, **bf)
         d_hidden = d_hidden_scratch(lib, P, L, F, **bf)
         _cabi.call("lmoe_grouped_bwd_dgrad", P, El, L, F, ptr(dy_in), ptr(h1), ptr(wgu), ptr(wde), ptr(tile_expert),
-                   ptr(n_tiles), ptr(d_hidden), ptr(d_h1), ptr(d_x_sorted), ptr(status), st)
+                   ptr(n_tiles), ptr(pad_offsets), ptr(d_hidden), ptr(d_h1), ptr(d_x_sorted), ptr(status), st)
         ready2 = torch.cuda.Event()
         ready2.record(main)
         side.wait_event(ready2)

@@ -181,7 +181,7 @@ class LatentMoEFunction(torch.autograd.Function):
                            ptr(y_sorted), ptr(status), st)
             else:
                 _cabi.call("lmoe_grouped_fwd", P, E, L, F, ptr(x_sorted), ptr(wgu), ptr(wde), ptr(route.tile_expert),
-                           ptr(route.n_tiles), ptr(h1), ptr(hidden), ptr(y_sorted), ptr(status), st)
+                           ptr(route.n_tiles), ptr(route.pad_offsets), ptr(h1), ptr(hidden), ptr(y_sorted), ptr(status), st)
 
         # weighted combine, up-projection, shared down-projection, add
         y = torch.empty(T, D, **bf)
@@ -278,7 +278,7 @@ class LatentMoEFunction(torch.autograd.Function):
             te, nt = ptr(route.tile_expert), ptr(route.n_tiles)
             # d_h1 = swiglu'(h1, d_y_sorted * Wd[e]^T), d_x_sorted = d_h1 * Wgu[e]^T: one chained kernel
             d_hidden = d_hidden_scratch(lib, P, L, F, **bf)
-            _cabi.call("lmoe_grouped_bwd_dgrad", P, E, L, F, ptr(d_y_sorted), ptr(h1), ptr(wgu), ptr(wde), te, nt,
+            _cabi.call("lmoe_grouped_bwd_dgrad", P, E, L, F, ptr(d_y_sorted), ptr(h1), ptr(wgu), ptr(wde), te, nt, ptr(route.pad_offsets),
                        ptr(d_hidden), ptr(d_h1), ptr(d_x_sorted), ptr(status), st)
             # [gather adjoint + router adjoint] beside [routed weight gradients]
             fork.to_side()

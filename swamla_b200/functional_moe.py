@@ -79,7 +79,7 @@ class MoEFunction(torch.autograd.Function):
         hidden = torch.empty(P, F, **bf)
         y_sorted = torch.empty(P, D, **bf)
         _cabi.call("lmoe_grouped_fwd", P, E, D, F, ptr(x_sorted), ptr(wgu), ptr(wde), ptr(route.tile_expert),
-                   ptr(route.n_tiles), ptr(h1), ptr(hidden), ptr(y_sorted), ptr(status), st)
+                   ptr(route.n_tiles), ptr(route.pad_offsets), ptr(h1), ptr(hidden), ptr(y_sorted), ptr(status), st)
         # shared expert                                                              (moe.py:351-354, 63-69)
         h1_s = torch.empty(T, 2 * Fs, **bf)
         hidden_s = torch.empty(T, Fs, **bf)
@@ -139,7 +139,7 @@ class MoEFunction(torch.autograd.Function):
         d_h1 = torch.empty(P, 2 * F, **bf)
         d_x_sorted = torch.empty(P, D, **bf)
         _cabi.call("lmoe_grouped_bwd_dgrad", P, E, D, F, ptr(d_y_sorted), ptr(h1), ptr(wgu), ptr(wde),
-                   ptr(route.tile_expert), ptr(route.n_tiles), ptr(d_hidden), ptr(d_h1), ptr(d_x_sorted), ptr(status), st)
+                   ptr(route.tile_expert), ptr(route.n_tiles), ptr(route.pad_offsets), ptr(d_hidden), ptr(d_h1), ptr(d_x_sorted), ptr(status), st)
         d_w_gate_up = torch.empty(E, D, 2 * F, **bf)
         d_w_down_e = torch.empty(E, F, D, **bf)
         _cabi.call("lmoe_grouped_bwd_wgrad", P, E, D, F, ptr(x_sorted), ptr(d_h1), ptr(hidden), ptr(d_y_sorted),

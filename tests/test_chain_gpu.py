@@ -22,7 +22,9 @@ def _layout(counts, capacity_tiles, dev):
         valid[t0 * 128:t0 * 128 + c] = True
         row_expert[t0 * 128:(t0 + nt) * 128] = e
         t0 += nt
-    return P, tile_expert.to(dev), torch.tensor([n_tiles], dtype=torch.int32, device=dev), valid, row_expert, n_tiles
+    pad_offsets = torch.tensor([0] + [128 * sum(tiles[:e + 1]) for e in range(len(counts))], dtype=torch.int32, device=dev)
+    return (P, tile_expert.to(dev), torch.tensor([n_tiles], dtype=torch.int32, device=dev), pad_offsets, valid, row_expert,
+            n_tiles)
 
 
 CASES = [
@@ -42,8 +44,10 @@ def test_chain_forward_and_backward_match_the_separate_kernels(E, L, F, counts, 
     lib = _cabi.load()
     dev = torch.device("cuda:0")
     st = torch.cuda.current_stream().cuda_stream
+    prev = lib.lmoe_chain_enable(1)
     assert lib.lmoe_chain_applies(L, F) == 1
-    P, tile_expert, n_tiles, valid, row_expert, nt = _layout(counts, cap, dev)
+    lib.lmoe_chain_enable(prev)
+    P, tile_expert, n_tiles, pad_offsets, valid, row_expert, nt = _layout(counts, cap, dev)
     used = nt * 128
     g = torch.Generator().manual_seed(E * 1000 + L + F)
     x = torch.randn(P, L, generator=g)
@@ -55,7 +59,9 @@ def test_chain_forward_and_backward_match_the_separate_kernels(E, L, F, counts, 
     x, dy = x.to(BF).to(dev), dy.to(BF).to(dev)
     status = torch.zeros(1, dtype=torch.int32, device=dev)
 
-    def run(chain):
+    def run(chain, pairs=True):
+        # pairs: the pad_offsets table lets the launcher put two tiles of an expert on a CTA pair (L a multiple of 128)
+        po = pad_offsets.data_ptr() if pairs else None
         prev = lib.lmoe_chain_enable(1 if chain else 0)
         try:
             o = dict(h1=torch.full((P, 2 * F), 3.0, dtype=BF, device=dev), hidden=torch.full((P, F), 3.0, dtype=BF, device=dev),
@@ -63,9 +69,9 @@ def test_chain_forward_and_backward_match_the_separate_kernels(E, L, F, counts, 
                      d_x=torch.full((P, L), 3.0, dtype=BF, device=dev))
             d_hidden = None if chain else torch.empty(P, F, dtype=BF, device=dev)
             _cabi.call("lmoe_grouped_fwd", P, E, L, F, x.data_ptr(), wgu.data_ptr(), wd.data_ptr(), tile_expert.data_ptr(),
-                       n_tiles.data_ptr(), o["h1"].data_ptr(), o["hidden"].data_ptr(), o["y"].data_ptr(), status.data_ptr(), st)
+                       n_tiles.data_ptr(), po, o["h1"].data_ptr(), o["hidden"].data_ptr(), o["y"].data_ptr(), status.data_ptr(), st)
             _cabi.call("lmoe_grouped_bwd_dgrad", P, E, L, F, dy.data_ptr(), o["h1"].data_ptr(), wgu.data_ptr(), wd.data_ptr(),
-                       tile_expert.data_ptr(), n_tiles.data_ptr(), _cabi.ptr(d_hidden), o["d_h1"].data_ptr(),
+                       tile_expert.data_ptr(), n_tiles.data_ptr(), po, _cabi.ptr(d_hidden), o["d_h1"].data_ptr(),
                        o["d_x"].data_ptr(), status.data_ptr(), st)
             torch.cuda.synchronize()
             assert status.item() == 0
@@ -73,9 +79,11 @@ def test_chain_forward_and_backward_match_the_separate_kernels(E, L, F, counts, 
         finally:
             lib.lmoe_chain_enable(prev)
 
-    a, b = run(True), run(False)
+    a, b, single = run(True), run(False), run(True, pairs=False)
     for k in ("h1", "hidden", "y"):                      # same MMAs in the same order: identical bits
         assert torch.equal(a[k][:used], b[k][:used]), k
+    for k in a:                                          # one CTA per tile or CTA pairs: the same arithmetic
+        assert torch.equal(a[k], single[k]), k
     for k in ("d_h1", "d_x"):                            # d_x sums its 2F products in another order
         ta, tb = a[k][:used].float(), b[k][:used].float()
         rel = ((ta - tb).norm() / tb.norm().clamp_min(1e-30)).item()

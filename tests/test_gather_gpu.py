@@ -49,7 +49,7 @@ def test_gathered_gate_up_forward_equals_materialised(T, E, K, L, F, skew):
             _cabi.call("lmoe_grouped_fwd_gather", P, E, L, F, x_ext.data_ptr(), T + 1, route.row_src.data_ptr(), 1, K, T,
                        *tail)
         else:
-            _cabi.call("lmoe_grouped_fwd", P, E, L, F, x_sorted.data_ptr(), *tail)
+            _cabi.call("lmoe_grouped_fwd", P, E, L, F, x_sorted.data_ptr(), *tail[:4], route.pad_offsets.data_ptr(), *tail[4:])
         outs.append((h1, hidden, y))
     torch.cuda.synchronize()
     assert status.item() == 0
