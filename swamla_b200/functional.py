@@ -74,18 +74,28 @@ class _Fork:
         self.main.wait_event(ev)
 
 
-class RouteTables:
-    """Device buffers behind an ``lmoe_route`` struct."""
+def padded_rows_of(T: int, K: int, E: int) -> int:
+    """Static row count of the padded expert layout (what ``lmoe_padded_rows`` returns)."""
+    return (T * K + 127) // 128 * 128 + E * 128
 
-    def __init__(self, shape: Shape, device):
+
+class RouteTables:
+    """Device buffers behind an ``lmoe_route`` struct: one int32 allocation (``storage``), sliced."""
+
+    @staticmethod
+    def storage_numel(T: int, K: int, E: int) -> int:
+        P = padded_rows_of(T, K, E)
+        return sum((n + 3) // 4 * 4 for n in (E, E + 1, E + 1, 1, P // 128, T * K, T * K, P))
+
+    def __init__(self, shape: Shape, device, storage: Optional[torch.Tensor] = None):
         T, K, E = shape.T, shape.K, shape.E
-        self.padded_rows = int(_cabi.load().lmoe_padded_rows(shape))
+        self.padded_rows = padded_rows_of(T, K, E)
         i32 = dict(dtype=torch.int32, device=device)
         # one allocation, sliced; every slice starts 16-byte aligned
         sizes = dict(counts=E, offsets=E + 1, pad_offsets=E + 1, n_tiles=1, tile_expert=self.padded_rows // 128,
                      perm=T * K, pos=T * K, row_src=self.padded_rows)
         total = sum((n + 3) // 4 * 4 for n in sizes.values())
-        self.storage = torch.empty(total, **i32)
+        self.storage = torch.empty(total, **i32) if storage is None else storage   # given: tables of an earlier forward
         off = 0
         for name, n in sizes.items():
             setattr(self, name, self.storage[off:off + n])

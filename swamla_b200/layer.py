@@ -12,6 +12,7 @@ import torch.nn as nn
 
 from . import _cabi, status as status_monitor
 from .functional import latent_moe, make_shape, _stream
+from .compiled_ops import latent_moe_compiled
 
 
 def _ep_size(group) -> int:
@@ -217,7 +218,9 @@ class LatentMoELayer(nn.Module):
             raise ValueError("kernel constraints: at most 256 routed experts and top-32")
 
     def forward(self, x: torch.Tensor) -> torch.Tensor:
-        status_monitor.poll()            # raises if an earlier step's kernels reported a failure (no synchronisation)
+        compiling = torch.compiler.is_compiling()
+        if not compiling:
+            status_monitor.poll()        # raises if an earlier step's kernels reported a failure (no synchronisation)
         batch_size, seq_len, d_model = x.shape
         x_flat = x.reshape(-1, d_model)
         shared = self.shared_experts[0]
@@ -244,6 +247,10 @@ class LatentMoELayer(nn.Module):
         elif self.ep_size > 1:
             from .ep import latent_moe_ep
             y, z_loss, sel, counts = latent_moe_ep(*args, self.ep_group)   # counts: load summed over all ranks
+        elif compiling and not self.fp8_experts:
+            # torch.compile (the reference's default, train.py:936-942): custom operators with fake implementations
+            # keep one graph across the layer; they run the same kernels as the eager call below
+            y, z_loss, sel, counts = latent_moe_compiled(*args)
         else:
             y, z_loss, sel, counts = latent_moe(*args, fp8=self.fp8_experts)
         self.aux_loss = z_loss                                            # moe.py:719
