@@ -39,7 +39,7 @@ static bool chain_pair_enabled() {
 template <int MODE>
 static int launch_chain_pair_inst(const ChainPairParams& p, int total_tiles, cudaStream_t stream) {
   auto kfn = chain_pair_kernel<MODE>;
-  constexpr int smem = ChainSmem<MODE>::kTotal;
+  constexpr int smem = ChainPairSmem<MODE>::kTotal;
   static PerDeviceOnce once;
   static int max_pairs_dev[kMaxDevices] = {};
   const int dev = current_device();
@@ -49,7 +49,7 @@ static int launch_chain_pair_inst(const ChainPairParams& p, int total_tiles, cud
         cudaFuncSetAttribute(kfn, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
         cudaLaunchConfig_t cfg = {};
         cfg.gridDim = dim3(2 * (num_sms() / 2), 1, 1);
-        cfg.blockDim = dim3(kGemmThreads, 1, 1);
+        cfg.blockDim = dim3(kChainPairThreads, 1, 1);
         cfg.dynamicSmemBytes = smem;
         cudaLaunchAttribute attr;
         attr.id = cudaLaunchAttributeClusterDimension;
@@ -71,7 +71,7 @@ static int launch_chain_pair_inst(const ChainPairParams& p, int total_tiles, cud
   long long want = (static_cast<long long>(total_tiles) + 1) / 2 + p.E;
   if (want > max_pairs_dev[dev]) want = max_pairs_dev[dev];
   if (want < 1) want = 1;
-  kfn<<<2 * static_cast<int>(want), kGemmThreads, smem, stream>>>(p);
+  kfn<<<2 * static_cast<int>(want), kChainPairThreads, smem, stream>>>(p);
   count_launch();
   cudaError_t e = cudaGetLastError();
   return e == cudaSuccess ? 0 : static_cast<int>(e);
@@ -109,7 +109,7 @@ static int launch_chain_pair(int mode, long long P, int E, int L, int F, const v
     if ((rc = encode_2d(&p.tmMid, mid, F, P, F, kBM, 2))) return rc;
   } else {
     if ((rc = encode_2d(&p.tmB1, w_down, L, wd_rows, L, 32, 2))) return rc;               // 32 of the chunk's 64 rows
-    if ((rc = encode_2d(&p.tmB2, w_gate_up, 2ll * F, wgu_rows, 2ll * F, L / 2, 2))) return rc;  // half of d_x's columns
+    if ((rc = encode_2d(&p.tmB2, w_gate_up, 2ll * F, wgu_rows, 2ll * F, 64, 2))) return rc;     // 64 of d_x's columns
     if ((rc = encode_2d(&p.tmMid, mid, 2ll * F, P, 2ll * F, kBM, 2))) return rc;
   }
   if ((rc = encode_out(&p.tmAux, h1, false, 2ll * F, P, 1, 2ll * F, 0))) return rc;

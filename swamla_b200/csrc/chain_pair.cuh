@@ -12,7 +12,10 @@
 // of 128, fewer than 2^23 tiles) gives the runs; the pair index -> (expert, tile) map comes from a small per-expert table
 // in shared memory.
 //
-// Roles per CTA as in chain.cuh.  Differences (as in gemm_pair.cuh):
+// Roles per CTA (384 threads): warp 0 producer of the A operand and the first GEMM's weights, warp 10 producer of the
+// second GEMM's weights, warp 1 / warp 11 MMA issuers of the first / second GEMM (separate threads and separate rings, so
+// the first GEMM runs ahead by its two accumulators and never queues behind the second GEMM's wait for the epilogue),
+// warps 2-9 epilogue as in chain.cuh.  As in gemm_pair.cuh:
 //   * rank 0's "full" barriers collect the bytes of BOTH CTAs' loads (the loads name rank 0's barrier through its
 //     shared::cluster address; no multicast load anywhere);
 //   * only rank 0 issues MMAs; its tcgen05.commit arrives at the barriers of both CTAs (ring / A / A2 "empty",
@@ -73,11 +76,31 @@ __device__ __forceinline__ bool mbar_wait_cluster(uint64_t* bar, uint32_t parity
   return true;
 }
 
+constexpr int kChainPairThreads = 384;  // 12 warps: two producers, two MMA issuers, eight epilogue warps
+
+// Shared memory of one CTA of a pair.  Two weight rings, one per GEMM, each fed by its own producer thread and drained
+// by its own MMA-issuing thread: the first GEMM runs ahead of the epilogue warps by as many chunks as its two
+// accumulators allow and never waits behind the second GEMM's dependence on them.
 template <int MODE>
-__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads, 1)
+struct ChainPairSmem {
+  static constexpr bool kFwd = (MODE == CHAIN_FWD);
+  static constexpr int kA2Bytes = kFwd ? 16384 : 32768;   // hidden chunk | d_gate + d_up chunk (backward: also the
+                                                          // staging slabs of the tile epilogue, which runs when both are free)
+  static constexpr int kAuxBytes = kFwd ? 32768 : 65536;  // FWD: gate/up slabs on their way to h1; BWD: saved gate/up, two chunks
+  static constexpr int kOutBytes = kFwd ? 16384 : 0;      // tile-epilogue slabs (backward uses the A2 buffer)
+  static constexpr int kR1Stages = kFwd ? 4 : 2, kR1Bytes = 16384;         // first GEMM: two chunks ahead
+  static constexpr int kR2Stages = kFwd ? 2 : 4, kR2Bytes = kFwd ? 16384 : 8192;  // second GEMM: two chunks | one chunk
+  static constexpr int kBarrierBytes = 2048;
+  static constexpr int kFixed = kChainA1Bytes + kA2Bytes + kAuxBytes + kOutBytes;
+  static constexpr int kTotal = 1024 + kFixed + kR1Stages * kR1Bytes + kR2Stages * kR2Bytes + kBarrierBytes;
+  static_assert(kTotal <= 232448, "shared memory");
+};
+
+template <int MODE>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kChainPairThreads, 1)
 chain_pair_kernel(const __grid_constant__ ChainPairParams p) {
-  using S = ChainSmem<MODE>;
-  constexpr int STAGES = S::kStages;
+  using S = ChainPairSmem<MODE>;
+  constexpr int R1 = S::kR1Stages, R2 = S::kR2Stages;
   constexpr bool FWD = (MODE == CHAIN_FWD);
   constexpr uint32_t TMEM_COLS = 512;
   constexpr uint32_t ACC2_COL = 256;
@@ -87,12 +110,15 @@ chain_pair_kernel(const __grid_constant__ ChainPairParams p) {
   uint8_t* const a1 = smem;
   uint8_t* const a2 = a1 + kChainA1Bytes;
   uint8_t* const aux = a2 + S::kA2Bytes;
-  uint8_t* const outb = aux + S::kAuxBytes;
-  uint8_t* const ring = outb + S::kOutBytes;
-  uint64_t* const bars = reinterpret_cast<uint64_t*>(ring + STAGES * kChainStageBytes);
-  uint64_t* const ring_full = bars;                      // rank 0's: bytes of both CTAs
-  uint64_t* const ring_empty = ring_full + STAGES;       // local: one commit arrival
-  uint64_t* const a1_full = ring_empty + STAGES;         // [4] rank 0's
+  uint8_t* const outb = FWD ? aux + S::kAuxBytes : a2;
+  uint8_t* const ring1 = aux + S::kAuxBytes + S::kOutBytes;
+  uint8_t* const ring2 = ring1 + R1 * S::kR1Bytes;
+  uint64_t* const bars = reinterpret_cast<uint64_t*>(ring2 + R2 * S::kR2Bytes);
+  uint64_t* const r1_full = bars;                        // rank 0's: bytes of both CTAs
+  uint64_t* const r1_empty = r1_full + R1;               // local: one commit arrival
+  uint64_t* const r2_full = r1_empty + R1;               // rank 0's
+  uint64_t* const r2_empty = r2_full + R2;               // local
+  uint64_t* const a1_full = r2_empty + R2;               // [4] rank 0's
   uint64_t* const a1_empty = a1_full + 4;                // [4] local
   uint64_t* const acc1_full = a1_empty + 4;              // [2] local
   uint64_t* const acc1_empty = acc1_full + 2;            // [2] rank 0's: 16 arrivals
@@ -110,9 +136,13 @@ chain_pair_kernel(const __grid_constant__ ChainPairParams p) {
   const uint32_t rank = cluster_ctarank();
 
   if (threadIdx.x == 0) {
-    for (int i = 0; i < STAGES; ++i) {
-      mbar_init(&ring_full[i], 1);
-      mbar_init(&ring_empty[i], 1);
+    for (int i = 0; i < R1; ++i) {
+      mbar_init(&r1_full[i], 1);
+      mbar_init(&r1_empty[i], 1);
+    }
+    for (int i = 0; i < R2; ++i) {
+      mbar_init(&r2_full[i], 1);
+      mbar_init(&r2_empty[i], 1);
     }
     for (int i = 0; i < 4; ++i) {
       mbar_init(&a1_full[i], 1);
@@ -225,35 +255,32 @@ chain_pair_kernel(const __grid_constant__ ChainPairParams p) {
     return locate(k.pid + n_clusters, 0);
   };
 
+  // A ring as seen by one thread: producers wait on "empty" and arm rank 0's "full"; MMA issuers wait on "full" and
+  // release with a commit to both CTAs.
+  struct Ring {
+    uint8_t* base;
+    uint64_t *full, *empty;
+    int stages, stage_bytes;
+    int stage = 0;
+    uint32_t phase = 0;
+    __device__ __forceinline__ void advance() {
+      if (++stage == stages) {
+        stage = 0;
+        phase ^= 1;
+      }
+    }
+  };
+
   if (warp == 0) {
-    // ======================================= TMA producer (both CTAs) =======================================
+    // =========== producer 1 (both CTAs): the tile's A operand and the first GEMM's weight slices ===========
     if (lane == 0) {
-      int stage = 0;
-      uint32_t phase = 0;
+      Ring rg{ring1, r1_full, r1_empty, R1, S::kR1Bytes};
       bool ok = true;
-      // next ring stage; rank 0 arms its "full" barrier for the bytes of BOTH CTAs; returns this CTA's stage buffer
-      // and leaves the shared::cluster address of rank 0's barrier in `full0`
-      uint32_t full0 = 0;
-      auto acquire = [&](uint32_t bytes_per_cta) -> uint8_t* {
-        if (!mbar_wait(&ring_empty[stage], phase ^ 1, abort_flag, p.status, kStatusProducerTimeout)) {
-          ok = false;
-          return nullptr;
-        }
-        if (rank == 0) mbar_expect_tx(&ring_full[stage], 2 * bytes_per_cta);
-        full0 = mapa_shared(smem_u32(&ring_full[stage]), 0);
-        return ring + stage * kChainStageBytes;
-      };
-      auto advance = [&]() {
-        if (++stage == STAGES) {
-          stage = 0;
-          phase ^= 1;
-        }
-      };
       int tiles_loaded = 0;
-      auto emit_g1 = [&](const Cur& k) {
+      for (Cur k = locate(cluster_id, 0); ok && valid(k); k = next(k)) {
         const int m0 = k.tile * kBM;
         if (k.c == 0) {  // this CTA's A operand, k-block by k-block as the previous tile's last chunk releases them
-          for (int kb = 0; kb < KB1 && ok; ++kb) {
+          for (int kb = 0; kb < KB1; ++kb) {
             if (!mbar_wait(&a1_empty[kb], (tiles_loaded & 1) ^ 1, abort_flag, p.status, kStatusProducerTimeout)) {
               ok = false;
               break;
@@ -261,6 +288,7 @@ chain_pair_kernel(const __grid_constant__ ChainPairParams p) {
             if (rank == 0) mbar_expect_tx(&a1_full[kb], 2 * 16384);
             tma_load_2d_pair(a1 + kb * 16384, &p.tmA, mapa_shared(smem_u32(&a1_full[kb]), 0), kb * 64, m0);
           }
+          if (!ok) break;
           ++tiles_loaded;
           if (p.prefetch_a) {  // the A operand of this CTA's next tile: into L2 a whole tile period ahead
             const Cur nx = locate(k.pid + n_clusters, 0);
@@ -268,189 +296,171 @@ chain_pair_kernel(const __grid_constant__ ChainPairParams p) {
               for (int kb = 0; kb < KB1; ++kb) tma_prefetch_2d(&p.tmA, kb * 64, nx.tile * kBM);
           }
         }
-        if (!ok) return;
-        if (FWD) {
-          // this CTA's half of the chunk's B: rank 0 the 64 gate columns, rank 1 the 64 up columns of Wgu[e];
-          // two k-blocks (8 KB each) per stage
-          const int col = static_cast<int>(rank) * F + k.c * 64;
-          for (int kb = 0; kb < KB1; kb += 2) {
-            const int nkb = min(2, KB1 - kb);
-            uint8_t* st = acquire(nkb * 8192);
-            if (!st) return;
-            for (int h = 0; h < nkb; ++h) tma_load_2d_pair(st + h * 8192, &p.tmB1, full0, col, k.e * L + (kb + h) * 64);
-            advance();
+        // FWD: this CTA's half of the chunk's B: rank 0 the 64 gate columns, rank 1 the 64 up columns of Wgu[e], two
+        //      k-blocks (8 KB each) per stage.
+        // BWD: rows [c*64 + rank*32, +32) of Wd[e] (its half of the chunk's d_hidden columns), 4 KB per k-block, all
+        //      k-blocks of the chunk in one stage.
+        const int n_stage = FWD ? (KB1 + 1) / 2 : 1;
+        for (int s = 0; s < n_stage && ok; ++s) {
+          if (!mbar_wait(&rg.empty[rg.stage], rg.phase ^ 1, abort_flag, p.status, kStatusProducerTimeout)) {
+            ok = false;
+            break;
           }
-        } else {
-          // rows [c*64 + rank*32, +32) of Wd[e] (this CTA's half of the chunk's d_hidden columns): 4 KB per k-block,
-          // all k-blocks of the chunk in one stage
-          uint8_t* st = acquire(KB1 * 4096);
-          if (!st) return;
-          for (int kb = 0; kb < KB1; ++kb)
-            tma_load_2d_pair(st + kb * 4096, &p.tmB1, full0, kb * 64, k.e * F + k.c * 64 + static_cast<int>(rank) * 32);
-          advance();
-        }
-      };
-      auto emit_g2 = [&](const Cur& k) {
-        const int half = L / 2;  // this CTA's share of the second GEMM's N extent
-        if (FWD) {
-          // rows [c*64, +64) of Wd[e], columns [rank*L/2, +L/2): L/128 MN-major chunks of 8 KB
-          uint8_t* st = acquire(half * 128);
-          if (!st) return;
-          for (int j = 0; j < half / 64; ++j)
-            tma_load_2d_pair(st + j * 8192, &p.tmB2, full0, static_cast<int>(rank) * half + j * 64, k.e * F + k.c * 64);
-          advance();
-        } else {
-          // Wgu[e] rows [rank*L/2, +L/2) (output columns of d_x), k columns [c*64, +64) (gate part), then the up part
-          for (int part = 0; part < 2; ++part) {
-            uint8_t* st = acquire(half * 128);
-            if (!st) return;
-            tma_load_2d_pair(st, &p.tmB2, full0, part * F + k.c * 64, k.e * L + static_cast<int>(rank) * half);
-            advance();
+          uint8_t* st = rg.base + rg.stage * rg.stage_bytes;
+          const uint32_t full0 = mapa_shared(smem_u32(&rg.full[rg.stage]), 0);
+          if (FWD) {
+            const int nkb = min(2, KB1 - 2 * s);
+            if (rank == 0) mbar_expect_tx(&rg.full[rg.stage], 2 * nkb * 8192);
+            for (int h = 0; h < nkb; ++h)
+              tma_load_2d_pair(st + h * 8192, &p.tmB1, full0, static_cast<int>(rank) * F + k.c * 64, k.e * L + (2 * s + h) * 64);
+          } else {
+            if (rank == 0) mbar_expect_tx(&rg.full[rg.stage], 2 * KB1 * 4096);
+            for (int kb = 0; kb < KB1; ++kb)
+              tma_load_2d_pair(st + kb * 4096, &p.tmB1, full0, kb * 64, k.e * F + k.c * 64 + static_cast<int>(rank) * 32);
           }
+          rg.advance();
         }
-      };
-      Cur cur = locate(cluster_id, 0);
-      if (valid(cur)) emit_g1(cur);
-      while (ok && valid(cur)) {
-        const Cur nx = next(cur);
-        if (valid(nx)) emit_g1(nx);
-        if (!ok) break;
-        emit_g2(cur);
-        cur = nx;
+      }
+    }
+  } else if (warp == 10) {
+    // =========== producer 2 (both CTAs): the second GEMM's weight slices ===========
+    if (lane == 0) {
+      Ring rg{ring2, r2_full, r2_empty, R2, S::kR2Bytes};
+      bool ok = true;
+      const int half = L / 2;  // this CTA's share of the second GEMM's N extent
+      for (Cur k = locate(cluster_id, 0); ok && valid(k); k = next(k)) {
+        // FWD: rows [c*64, +64) of Wd[e], columns [rank*L/2, +L/2): L/128 MN-major chunks of 8 KB, one stage.
+        // BWD: per part (gate columns, up columns of Wgu[e]) and per 128-column slice s of d_x: rows
+        //      [s*128 + rank*64, +64) x k columns [part*F + c*64, +64), one 8 KB stage each.
+        const int n_stage = FWD ? 1 : 2 * (L / 128);
+        for (int s = 0; s < n_stage && ok; ++s) {
+          if (!mbar_wait(&rg.empty[rg.stage], rg.phase ^ 1, abort_flag, p.status, kStatusProducerTimeout)) {
+            ok = false;
+            break;
+          }
+          uint8_t* st = rg.base + rg.stage * rg.stage_bytes;
+          const uint32_t full0 = mapa_shared(smem_u32(&rg.full[rg.stage]), 0);
+          if (FWD) {
+            if (rank == 0) mbar_expect_tx(&rg.full[rg.stage], 2 * half * 128);
+            for (int j = 0; j < half / 64; ++j)
+              tma_load_2d_pair(st + j * 8192, &p.tmB2, full0, static_cast<int>(rank) * half + j * 64, k.e * F + k.c * 64);
+          } else {
+            const int part = s / (L / 128), sl = s % (L / 128);
+            if (rank == 0) mbar_expect_tx(&rg.full[rg.stage], 2 * 8192);
+            tma_load_2d_pair(st, &p.tmB2, full0, part * F + k.c * 64, k.e * L + sl * 128 + static_cast<int>(rank) * 64);
+          }
+          rg.advance();
+        }
       }
     }
   } else if (warp == 1) {
-    // ==================================== MMA issuer (rank 0 only) ====================================
+    // =========== MMA issuer 1 (rank 0 only): the first GEMM of every chunk ===========
     if (lane == 0 && rank == 0) {
-      int stage = 0;
-      uint32_t phase = 0;
+      Ring rg{ring1, r1_full, r1_empty, R1, S::kR1Bytes};
       bool ok = true;
-      auto wait_stage = [&]() -> uint32_t {
-        if (!mbar_wait(&ring_full[stage], phase, abort_flag, p.status, kStatusMmaTimeout)) {
-          ok = false;
-          return 0u;
-        }
-        tc_fence_after();
-        return smem_u32(ring + stage * kChainStageBytes);
-      };
-      auto release_stage = [&]() {
-        umma_commit_pair(&ring_empty[stage], 0x3);
-        if (++stage == STAGES) {
-          stage = 0;
-          phase ^= 1;
-        }
-      };
-      const uint32_t a1_addr = smem_u32(a1), a2_addr = smem_u32(a2);
-      int tiles_g1 = 0, tiles_g2 = 0;
-      auto issue_g1 = [&](const Cur& k, int gi) {
+      const uint32_t a1_addr = smem_u32(a1);
+      int tiles_g1 = 0, gi = 0;
+      for (Cur k = locate(cluster_id, 0); ok && valid(k); k = next(k), ++gi) {
         const int b = gi & 1;
-        if (!mbar_wait_cluster(&acc1_empty[b], ((gi >> 1) & 1) ^ 1, abort_flag, p.status, kStatusMmaTimeout)) {
-          ok = false;
-          return;
-        }
+        if (!mbar_wait_cluster(&acc1_empty[b], ((gi >> 1) & 1) ^ 1, abort_flag, p.status, kStatusMmaTimeout)) break;
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + b * 128;
         const uint32_t a_par = tiles_g1 & 1;
-        if (FWD) {
-          constexpr uint32_t idesc = make_idesc(1u, 1u, false, true, 256, 128);
-          for (int kb = 0; kb < KB1; kb += 2) {
-            const uint32_t sb = wait_stage();
-            if (!ok) return;
-            const int nkb = min(2, KB1 - kb);
-            for (int h = 0; h < nkb; ++h) {
-              if (k.c == 0) {
-                if (!mbar_wait(&a1_full[kb + h], a_par, abort_flag, p.status, kStatusMmaTimeout)) {
-                  ok = false;
-                  return;
-                }
-                tc_fence_after();
-              }
-#pragma unroll
-              for (int kk = 0; kk < 4; ++kk) {
-                const uint64_t da = make_smem_desc_sw128(a1_addr + (kb + h) * 16384 + kk * 32, 0, 1024);
-                const uint64_t db = make_smem_desc_sw128(sb + h * 8192 + kk * 2048, 8192, 1024);
-                umma_f16_pair(d_tmem, da, db, idesc, (kb + h > 0 || kk > 0) ? 1u : 0u);
-              }
-              if (k.c == NC - 1) umma_commit_pair(&a1_empty[kb + h], 0x3);
-            }
-            release_stage();
+        CHAIN_TRACE(1, 1);
+        const int n_stage = FWD ? (KB1 + 1) / 2 : 1;
+        for (int s = 0; s < n_stage && ok; ++s) {
+          if (!mbar_wait(&rg.full[rg.stage], rg.phase, abort_flag, p.status, kStatusMmaTimeout)) {
+            ok = false;
+            break;
           }
-        } else {
-          constexpr uint32_t idesc = make_idesc(1u, 1u, false, false, 256, 64);
-          const uint32_t sb = wait_stage();
-          if (!ok) return;
-          for (int kb = 0; kb < KB1; ++kb) {
+          tc_fence_after();
+          const uint32_t sb = smem_u32(rg.base + rg.stage * rg.stage_bytes);
+          const int kb0 = FWD ? 2 * s : 0;
+          const int nkb = FWD ? min(2, KB1 - 2 * s) : KB1;
+          for (int h = 0; h < nkb && ok; ++h) {
+            const int kb = kb0 + h;
             if (k.c == 0) {
               if (!mbar_wait(&a1_full[kb], a_par, abort_flag, p.status, kStatusMmaTimeout)) {
                 ok = false;
-                return;
+                break;
               }
               tc_fence_after();
             }
 #pragma unroll
             for (int kk = 0; kk < 4; ++kk) {
               const uint64_t da = make_smem_desc_sw128(a1_addr + kb * 16384 + kk * 32, 0, 1024);
-              const uint64_t db = make_smem_desc_sw128(sb + kb * 4096 + kk * 32, 0, 1024);
-              umma_f16_pair(d_tmem, da, db, idesc, (kb > 0 || kk > 0) ? 1u : 0u);
+              if (FWD) {
+                constexpr uint32_t idesc = make_idesc(1u, 1u, false, true, 256, 128);
+                const uint64_t db = make_smem_desc_sw128(sb + h * 8192 + kk * 2048, 8192, 1024);
+                umma_f16_pair(d_tmem, da, db, idesc, (kb > 0 || kk > 0) ? 1u : 0u);
+              } else {
+                constexpr uint32_t idesc = make_idesc(1u, 1u, false, false, 256, 64);
+                const uint64_t db = make_smem_desc_sw128(sb + kb * 4096 + kk * 32, 0, 1024);
+                umma_f16_pair(d_tmem, da, db, idesc, (kb > 0 || kk > 0) ? 1u : 0u);
+              }
             }
-            if (k.c == NC - 1) umma_commit_pair(&a1_empty[kb], 0x3);
+            if (k.c == NC - 1) umma_commit_pair(&a1_empty[kb], 0x3);  // last reader of this k-block of the A operand
           }
-          release_stage();
+          if (!ok) break;
+          umma_commit_pair(&rg.empty[rg.stage], 0x3);
+          rg.advance();
         }
+        if (!ok) break;
         if (k.c == 0) ++tiles_g1;
         umma_commit_pair(&acc1_full[b], 0x3);
-      };
-      auto issue_g2 = [&](const Cur& k, int gi) {
+        CHAIN_TRACE(1, 2);
+      }
+    }
+  } else if (warp == 11) {
+    // =========== MMA issuer 2 (rank 0 only): the second GEMM of every chunk ===========
+    if (lane == 0 && rank == 0) {
+      Ring rg{ring2, r2_full, r2_empty, R2, S::kR2Bytes};
+      bool ok = true;
+      const uint32_t a2_addr = smem_u32(a2);
+      int tiles_g2 = 0, gi = 0;
+      for (Cur k = locate(cluster_id, 0); ok && valid(k); k = next(k), ++gi) {
         if (k.c == 0) {
-          if (!mbar_wait_cluster(acc2_empty, (tiles_g2 & 1) ^ 1, abort_flag, p.status, kStatusMmaTimeout)) {
-            ok = false;
-            return;
-          }
+          if (!mbar_wait_cluster(acc2_empty, (tiles_g2 & 1) ^ 1, abort_flag, p.status, kStatusMmaTimeout)) break;
           ++tiles_g2;
         }
         // both CTAs' epilogue warps have written their A2 buffers (cluster-scope acquire: one of them is remote)
-        if (!mbar_wait_cluster(a2_full, gi & 1, abort_flag, p.status, kStatusMmaTimeout)) {
-          ok = false;
-          return;
-        }
+        CHAIN_TRACE(0, 3);
+        if (!mbar_wait_cluster(a2_full, gi & 1, abort_flag, p.status, kStatusMmaTimeout)) break;
         tc_fence_after();
-        const uint32_t idesc = make_idesc(1u, 1u, false, FWD, 256, static_cast<uint32_t>(L));
-        if (FWD) {
-          const uint32_t sb = wait_stage();
-          if (!ok) return;
-#pragma unroll
-          for (int kk = 0; kk < 4; ++kk) {
-            const uint64_t da = make_smem_desc_sw128(a2_addr + kk * 32, 0, 1024);
-            const uint64_t db = make_smem_desc_sw128(sb + kk * 2048, 8192, 1024);
-            umma_f16_pair(tmem_base + ACC2_COL, da, db, idesc, (k.c > 0 || kk > 0) ? 1u : 0u);
+        CHAIN_TRACE(0, 4);
+        const int n_stage = FWD ? 1 : 2 * (L / 128);
+        for (int s = 0; s < n_stage && ok; ++s) {
+          if (!mbar_wait(&rg.full[rg.stage], rg.phase, abort_flag, p.status, kStatusMmaTimeout)) {
+            ok = false;
+            break;
           }
-          release_stage();
-        } else {
-          for (int part = 0; part < 2; ++part) {
-            const uint32_t sb = wait_stage();
-            if (!ok) return;
+          tc_fence_after();
+          const uint32_t sb = smem_u32(rg.base + rg.stage * rg.stage_bytes);
+          if (FWD) {
+            const uint32_t idesc = make_idesc(1u, 1u, false, true, 256, static_cast<uint32_t>(L));
+#pragma unroll
+            for (int kk = 0; kk < 4; ++kk) {
+              const uint64_t da = make_smem_desc_sw128(a2_addr + kk * 32, 0, 1024);
+              const uint64_t db = make_smem_desc_sw128(sb + kk * 2048, 8192, 1024);
+              umma_f16_pair(tmem_base + ACC2_COL, da, db, idesc, (k.c > 0 || kk > 0) ? 1u : 0u);
+            }
+          } else {
+            constexpr uint32_t idesc = make_idesc(1u, 1u, false, false, 256, 128);
+            const int part = s / (L / 128), sl = s % (L / 128);
 #pragma unroll
             for (int kk = 0; kk < 4; ++kk) {
               const uint64_t da = make_smem_desc_sw128(a2_addr + part * 16384 + kk * 32, 0, 1024);
               const uint64_t db = make_smem_desc_sw128(sb + kk * 32, 0, 1024);
-              umma_f16_pair(tmem_base + ACC2_COL, da, db, idesc, (k.c > 0 || part > 0 || kk > 0) ? 1u : 0u);
+              umma_f16_pair(tmem_base + ACC2_COL + sl * 128, da, db, idesc, (k.c > 0 || part > 0 || kk > 0) ? 1u : 0u);
             }
-            release_stage();
           }
+          umma_commit_pair(&rg.empty[rg.stage], 0x3);
+          rg.advance();
         }
-        umma_commit_pair(a2_empty, 0x3);
-        if (k.c == NC - 1) umma_commit_pair(acc2_full, 0x3);
-      };
-      Cur cur = locate(cluster_id, 0);
-      int gi = 0;
-      if (valid(cur)) issue_g1(cur, 0);
-      while (ok && valid(cur)) {
-        const Cur nx = next(cur);
-        if (valid(nx)) issue_g1(nx, gi + 1);
         if (!ok) break;
-        issue_g2(cur, gi);
-        cur = nx;
-        ++gi;
+        CHAIN_TRACE(0, 5);
+        umma_commit_pair(a2_empty, 0x3);                       // the A2 buffers may be rewritten once these MMAs have read them
+        if (k.c == NC - 1) umma_commit_pair(acc2_full, 0x3);   // the tile's result is complete in both CTAs
       }
     }
   } else {
@@ -489,7 +499,9 @@ chain_pair_kernel(const __grid_constant__ ChainPairParams p) {
       const int b = gi & 1;
       const int m0 = cur.tile * kBM;
       // ---------------- chunk epilogue ----------------
+      if (chunk_issuer) CHAIN_TRACE(2, 10);
       if (!mbar_wait(&acc1_full[b], (gi >> 1) & 1, abort_flag, p.status, kStatusEpilogueTimeout)) ok = false;
+      if (chunk_issuer) CHAIN_TRACE(2, 11);
       if (!FWD && ok && !mbar_wait(&gu_full[b], (gi >> 1) & 1, abort_flag, p.status, kStatusEpilogueTimeout)) ok = false;
       tc_fence_after();
       uint32_t pa[16], pb[16], pc[16];
@@ -539,8 +551,13 @@ chain_pair_kernel(const __grid_constant__ ChainPairParams p) {
           }
         }
       }
+      if (chunk_issuer) CHAIN_TRACE(2, 12);
       if (ok && !mbar_wait(a2_empty, (gi & 1) ^ 1, abort_flag, p.status, kStatusEpilogueTimeout)) ok = false;
-      if (chunk_issuer) tma_store_wait_read_all();
+      if (chunk_issuer) CHAIN_TRACE(2, 13);
+      // stores issued from the buffers about to be rewritten have read their source (backward: the tile epilogue's slabs
+      // share the A2 buffer, and each group's issuer committed its own)
+      if (FWD ? chunk_issuer : group_issuer) tma_store_wait_read_all();
+      if (chunk_issuer) CHAIN_TRACE(2, 14);
       ok = epi_all_and(ok);
       if (!ok) break;
       if (!FWD && chunk_issuer) {  // every thread holds its gate / up rows in registers: refill the buffer (chunk gi + 2)
@@ -556,9 +573,12 @@ chain_pair_kernel(const __grid_constant__ ChainPairParams p) {
         a2_write_half(a2, r, group, pa);
         a2_write_half(a2 + 16384, r, group, pb);
       }
+      if (chunk_issuer) CHAIN_TRACE(2, 15);
       fence_proxy_async_smem();
+      if (chunk_issuer) CHAIN_TRACE(2, 17);
       epi_all_sync();
       if (chunk_issuer) {
+        CHAIN_TRACE(2, 16);
         mbar_arrive_cluster(a2_full0);  // release at cluster scope: the MMAs issued by rank 0 read this CTA's A2 buffer
         if (cur.live) {
           if (FWD) {
@@ -576,8 +596,11 @@ chain_pair_kernel(const __grid_constant__ ChainPairParams p) {
       }
       if (cur.c != NC - 1) continue;
       // ---------------- tile epilogue ----------------
+      if (chunk_issuer) CHAIN_TRACE(2, 20);
       if (!mbar_wait(acc2_full, tiles_done & 1, abort_flag, p.status, kStatusEpilogueTimeout)) ok = false;
+      if (chunk_issuer) CHAIN_TRACE(2, 21);
       tc_fence_after();
+      if (!FWD && chunk_issuer) tma_store_wait_read_all();  // the last chunk's stores have read the A2 buffer (slabs go there)
       ok = epi_all_and(ok);
       if (!ok) break;
       const int slabs = L / kSlabCols;
@@ -612,6 +635,7 @@ chain_pair_kernel(const __grid_constant__ ChainPairParams p) {
         }
       }
       ++tiles_done;
+      if (chunk_issuer) CHAIN_TRACE(2, 22);
     }
     if (group_issuer) tma_store_wait0();
   }
