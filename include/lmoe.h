@@ -153,7 +153,7 @@ int lmoe_route_permute(const lmoe_shape* s, const int32_t* sel, const lmoe_route
  * library image on every GPU that loads it (held until the process exits).
  *   - Nothing is allocated or freed, here or in any library routine this calls.
  *   - Limit: lmoe_route_workspace_bytes(s) must not exceed LMOE_STATIC_ROUTE_SCRATCH_BYTES, i.e.
- *     ceil(T*K/512) * E <= 1,048,576 (for E = 128: T*K up to 4,194,304); beyond that the call launches
+ *     ceil(T*K/256) * E <= 1,048,576 (for E = 128: T*K up to 2,097,152); beyond that the call launches
  *     nothing and returns LMOE_ERR_TOO_LARGE.
  *   - The first call on each device looks up the array's device address (with that device current);
  *     make that first call before any stream capture begins.

@@ -112,7 +112,7 @@ static int launch_chain_pair(int mode, long long P, int E, int L, int F, const v
     if ((rc = encode_2d(&p.tmB2, w_gate_up, 2ll * F, wgu_rows, 2ll * F, 64, 2))) return rc;     // 64 of d_x's columns
     if ((rc = encode_2d(&p.tmMid, mid, 2ll * F, P, 2ll * F, kBM, 2))) return rc;
   }
-  if ((rc = encode_out(&p.tmAux, h1, false, 2ll * F, P, 1, 2ll * F, 0))) return rc;
+  if ((rc = encode_out(&p.tmAux, h1, false, 2ll * F, P, 1, 2ll * F, 0, mode == CHAIN_BWD))) return rc;
   if ((rc = encode_out(&p.tmOut, out, false, L, P, 1, L, 0))) return rc;
   p.L = L;
   p.F = F;
@@ -149,7 +149,7 @@ int launch_chain(int mode, long long P, int E, int L, int F, const void* a, cons
     if ((rc = encode_2d(&p.tmB2, w_gate_up, 2ll * F, wgu_rows, 2ll * F, L < 128 ? L : 128, 2))) return rc;
     if ((rc = encode_2d(&p.tmMid, mid, 2ll * F, P, 2ll * F, kBM, 2))) return rc;  // d_h1 [P, 2F]
   }
-  if ((rc = encode_out(&p.tmAux, h1, false, 2ll * F, P, 1, 2ll * F, 0))) return rc;
+  if ((rc = encode_out(&p.tmAux, h1, false, 2ll * F, P, 1, 2ll * F, 0, mode == CHAIN_BWD))) return rc;
   if ((rc = encode_out(&p.tmOut, out, false, L, P, 1, L, 0))) return rc;
   p.L = L;
   p.F = F;

@@ -562,7 +562,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1) chain_kernel(const __grid_con
             float dg[2], du[2];
 #pragma unroll
             for (int t = 0; t < 2; ++t) {
-              const float s = 1.0f / (1.0f + __expf(-g[t]));
+              const float s = sigmoid_fast(g[t]);
               du[t] = dh[t] * g[t] * s;
               dg[t] = dh[t] * uu[t] * s * (1.0f + g[t] * (1.0f - s));
             }

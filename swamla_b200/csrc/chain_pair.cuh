@@ -542,7 +542,7 @@ chain_pair_kernel(const __grid_constant__ ChainPairParams p) {
             float dg[2], du[2];
 #pragma unroll
             for (int t = 0; t < 2; ++t) {
-              const float s = 1.0f / (1.0f + __expf(-g[t]));
+              const float s = sigmoid_fast(g[t]);
               du[t] = dh[t] * g[t] * s;
               dg[t] = dh[t] * uu[t] * s * (1.0f + g[t] * (1.0f - s));
             }

@@ -71,7 +71,7 @@ int encode_2d(CUtensorMap* map, const void* base, long long inner, long long out
 // Output map: 3-D {cols, rows, planes}; one 128 x 32 slab per store.  bf16: 64-byte rows in shared
 // memory (SWIZZLE_64B); fp32: 128-byte rows (SWIZZLE_128B).
 int encode_out(CUtensorMap* map, void* base, bool f32, long long cols, long long rows, long long planes,
-                      long long ld_elems, long long plane_elems) {
+               long long ld_elems, long long plane_elems, bool as_source) {
   EncodeTiledFn fn = encode_fn();
   if (!fn) return LMOE_ERR_DRIVER;
   const int es = f32 ? 4 : 2;
@@ -88,7 +88,10 @@ int encode_out(CUtensorMap* map, void* base, bool f32, long long cols, long long
   cuuint32_t estr[3] = {1, 1, 1};
   CUresult r = fn(map, f32 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, base, dims, strides,
                   box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, f32 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_64B,
-                  CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+                  // a slab row is 64 bytes: as a load source, let L2 fetch whole 256-byte pieces from HBM once, so that the
+                  // neighbouring slabs (read by the other epilogue group a moment later) hit L2
+                  as_source ? CU_TENSOR_MAP_L2_PROMOTION_L2_256B : CU_TENSOR_MAP_L2_PROMOTION_NONE,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   return r == CUDA_SUCCESS ? 0 : LMOE_ERR_DRIVER;
 }
 
@@ -155,8 +158,8 @@ static int dispatch(const GemmCall& c, int bn, const GemmParams& p, int grid, cu
     // grouped over the contraction (routed wgrads)
     LMOE_CASE_BN(1, 1, EPI_BF16, GRP_K, 2)
     // dgrad with the SwiGLU adjoint in the epilogue (routed and shared)
-    LMOE_CASE_BN(0, 0, EPI_SWIGLU_BWD, GRP_M, 2)
-    LMOE_CASE_BN(0, 1, EPI_SWIGLU_BWD, GRP_NONE, 2)
+    LMOE_CASE(0, 0, 128, EPI_SWIGLU_BWD, GRP_M, 2)
+    LMOE_CASE(0, 1, 128, EPI_SWIGLU_BWD, GRP_NONE, 2)
     // ---- e4m3 ----
     LMOE_CASE_MAJORS(EPI_BF16, GRP_NONE, 1)
     LMOE_CASE(0, 1, 256, EPI_SWIGLU, GRP_M, 1)
@@ -339,6 +342,7 @@ int launch_gemm(const GemmCall& c) {
     // per-expert weight gradients contract over thousands of rows: wide tiles even when they do not fill a wave
     // (128-wide tiles measured 2.5x slower for 32 experts per GPU)
     if (c.grp == GRP_K && n_eff >= 256) bn = 256;
+    if (swiglu_bwd) bn = 128;  // the staged gate / up slabs take 64 KB of shared memory: 32 KB stages
   }
   if (bn != 128 && bn != 256) return LMOE_ERR_ARG;
   const int n_per_tile = swiglu ? bn / 2 : bn;
@@ -407,6 +411,10 @@ int launch_gemm(const GemmCall& c) {
     if (rc) return rc;
     if (swiglu) {
       rc = encode_out(&p.tmC2, c.C2, false, c.N, rows_total, 1, c.ldc2, 0);
+      if (rc) return rc;
+    }
+    if (swiglu_bwd) {  // the saved gate / up as a slab source; rows past the end read as zeros
+      rc = encode_out(&p.tmAux, const_cast<void*>(c.aux), false, 2ll * c.N, rows_total, 1, c.ld_aux, 0, true);
       if (rc) return rc;
     }
   }

@@ -70,6 +70,7 @@ struct alignas(64) GemmParams {
   const float* deq_b;
   const void* aux;         // EPI_SWIGLU_BWD: h1 [rows, 2*N] bf16 (gate | up), row stride ld_aux elements
   long long ld_aux;
+  CUtensorMap tmAux;       // EPI_SWIGLU_BWD: the same tensor as 128 x 32 slabs (64-byte swizzle), staged by TMA
   // Gathered A operand (bf16, one K segment): row i of the padded routed layout is row
   // a_rows[i * a_rows_stride] / a_rows_div of the tensor behind tmA[0] (negative entry: a_zero_row, a row of zeros).  GRP_M with K-major A gathers the tile's M rows,
   // GRP_K (MN-major A) gathers the contraction rows.  NULL: A is read in place.
@@ -92,16 +93,27 @@ struct GemmSmem {
   // read latency of the previous TMA store would otherwise be exposed on every slab), one for the others
   static constexpr int kBufsPerGroup = (EPI == EPI_BF16) ? 2 : 1;
   static constexpr int kStagingBytes = 2 * kBufsPerGroup * kStreams * kSlabBytes;
+  // EPI_SWIGLU_BWD: the saved gate / up slabs of the next two slabs of each epilogue group, staged by TMA
+  // (2 groups x 2 buffers x (gate 8 KB + up 8 KB))
+  static constexpr int kAuxBytes = (EPI == EPI_SWIGLU_BWD) ? 65536 : 0;
   static constexpr int kBarrierBytes = 256;
-  static constexpr int kBudget = 232448 - 1024 - kBarrierBytes - kStagingBytes;
+  static constexpr int kBudget = 232448 - 1024 - kBarrierBytes - kStagingBytes - kAuxBytes;
   static constexpr int kStagesMax = kBudget / kStageBytes;
   static constexpr int kStages = kStagesMax > 6 ? 6 : kStagesMax;
-  static constexpr int kTotal = kStages * kStageBytes + kStagingBytes + kBarrierBytes + 1024;  // +1024: alignment
+  static constexpr int kTotal = kStages * kStageBytes + kStagingBytes + kAuxBytes + kBarrierBytes + 1024;  // +1024: alignment
   static_assert(kStages >= 3, "pipeline too shallow");
 };
 
-// silu(g) = g * sigmoid(g) with the approximate exp2 / reciprocal units (error far below bf16 rounding).
-__device__ __forceinline__ float silu_f(float g) { return __fdividef(g, 1.0f + __expf(-g)); }
+// sigmoid(g) = 0.5 + 0.5 * tanh(g / 2) on the hardware tanh unit: ONE special-function instruction per value
+// (exp2 + reciprocal take two, and a full-precision division many more; the SwiGLU epilogues are bound by instruction
+// issue, not by memory).  tanh.approx.f32 has a relative error of 2^-11, an eighth of a bf16 ulp.
+__device__ __forceinline__ float sigmoid_fast(float g) {
+  float t;
+  asm("tanh.approx.f32 %0, %1;" : "=f"(t) : "f"(0.5f * g));
+  return fmaf(0.5f, t, 0.5f);
+}
+// silu(g) = g * sigmoid(g)
+__device__ __forceinline__ float silu_f(float g) { return g * sigmoid_fast(g); }
 
 // Named barrier over the 128 threads of one epilogue group (barrier id 1 or 2).
 __device__ __forceinline__ void epi_bar_sync(int id) { asm volatile("bar.sync %0, 128;" ::"r"(id) : "memory"); }
@@ -127,6 +139,13 @@ __device__ __forceinline__ void tma_store_3d(const CUtensorMap* map, const void*
                    reinterpret_cast<uint64_t>(map)),
                "r"(smem_u32(smem_src)), "r"(c0), "r"(c1), "r"(c2)
                : "memory");
+}
+// 3-D tiled load (an output-style map used as a source).
+__device__ __forceinline__ void tma_load_3d_g(void* smem_dst, const CUtensorMap* map, uint64_t* bar, int c0, int c1, int c2) {
+  asm volatile(
+      "cp.async.bulk.tensor.3d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];"
+      ::"r"(smem_u32(smem_dst)), "l"(reinterpret_cast<uint64_t>(map)), "r"(smem_u32(bar)), "r"(c0), "r"(c1), "r"(c2)
+      : "memory");
 }
 __device__ __forceinline__ void tma_store_wait_read_all() { asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory"); }
 __device__ __forceinline__ void tma_store_wait_read_1() { asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory"); }
@@ -167,11 +186,13 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_kernel(const __grid_cons
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint8_t* staging = smem + STAGES * S::kStageBytes;  // 1024-aligned: stage sizes are multiples of 1024
-  uint64_t* bar_full = reinterpret_cast<uint64_t*>(staging + S::kStagingBytes);
+  uint8_t* aux_stage = staging + S::kStagingBytes;       // EPI_SWIGLU_BWD only (kAuxBytes == 0 otherwise)
+  uint64_t* bar_full = reinterpret_cast<uint64_t*>(aux_stage + S::kAuxBytes);
   uint64_t* bar_empty = bar_full + STAGES;
   uint64_t* bar_tfull = bar_empty + STAGES;
   uint64_t* bar_tempty = bar_tfull + 2;
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bar_tempty + 2);
+  uint64_t* bar_aux = bar_tempty + 2;                    // [2 groups][2 buffers]
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bar_aux + 4);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5;
@@ -186,6 +207,8 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_kernel(const __grid_cons
       mbar_init(&bar_tfull[i], 1);
       mbar_init(&bar_tempty[i], 8);
     }
+    for (int i = 0; i < 4; ++i) mbar_init(&bar_aux[i], 1);
+    if (EPI == EPI_SWIGLU_BWD) tma_prefetch_desc(&p.tmAux);
     *abort_flag = 0;
     fence_mbar_init();
     for (int i = 0; i < p.nseg; ++i) {
@@ -427,6 +450,39 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_kernel(const __grid_cons
     int acc = 0;
     uint32_t acc_phase = 0;
     bool ok = true;
+    // EPI_SWIGLU_BWD: this group's slabs form one sequence over all its tiles (slab c of a tile, c = group, group + 2,
+    // ...); the group's issuer stages the saved gate / up of the slab TWO places ahead in that sequence by TMA, so the
+    // rows are in shared memory when the accumulator is ready.  Buffer = place in the sequence & 1.
+    const int n_per_tile_e = (EPI == EPI_SWIGLU) ? BN / 2 : BN;
+    auto slabs_of = [&](const Tile& tt) {
+      const int n0_ = tt.nt * n_per_tile_e;
+      int sl = (p.N - n0_ + kSlabCols - 1) / kSlabCols;
+      return sl > n_per_tile_e / kSlabCols ? n_per_tile_e / kSlabCols : sl;
+    };
+    int aux_seq = 0;        // slabs this group has consumed
+    int pre_id = blockIdx.x, pre_c = group, pre_seq = 0;   // next slab to stage (issuer only)
+    auto stage_next = [&]() {   // issues the TMA loads of the next unstaged slab of the sequence, if there is one
+      while (pre_id < total_tiles) {
+        const Tile tt = decode(pre_id);
+        if (pre_c < slabs_of(tt)) {
+          const int b = pre_seq & 1;
+          uint8_t* dst = aux_stage + (group * 2 + b) * 16384;
+          const int col = tt.nt * BN + pre_c * kSlabCols;
+          mbar_expect_tx(&bar_aux[group * 2 + b], 16384);
+          tma_load_3d_g(dst, &p.tmAux, &bar_aux[group * 2 + b], col, tt.m0, 0);
+          tma_load_3d_g(dst + 8192, &p.tmAux, &bar_aux[group * 2 + b], p.N + col, tt.m0, 0);
+          ++pre_seq;
+          pre_c += 2;
+          return;
+        }
+        pre_id += gridDim.x;
+        pre_c = group;
+      }
+    };
+    if (EPI == EPI_SWIGLU_BWD && issuer) {
+      stage_next();
+      stage_next();
+    }
     for (int id = blockIdx.x; id < total_tiles && ok; id += gridDim.x) {
       const Tile t = decode(id);
       const int nk = tile_kiters(t);
@@ -457,21 +513,22 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_kernel(const __grid_cons
         float v[32], u[32];
         uint4 hg[4], hu[4];  // EPI_SWIGLU_BWD: saved gate / up of this row, 32 columns each
         if (EPI == EPI_SWIGLU_BWD) {
-          const long long grow = static_cast<long long>(t.m0) + r;
-          if (GRP == GRP_M || grow < p.M) {
-            const uint4* gp = reinterpret_cast<const uint4*>(static_cast<const __nv_bfloat16*>(p.aux) + grow * p.ld_aux +
-                                                             n0 + c * kSlabCols);
-            const uint4* up = reinterpret_cast<const uint4*>(static_cast<const __nv_bfloat16*>(p.aux) + grow * p.ld_aux +
-                                                             p.N + n0 + c * kSlabCols);
+          const int b = aux_seq & 1;
+          // staged two slabs ago by this group's issuer; rows beyond the tensor arrive as zeros (TMA bounds fill)
+          if (!mbar_wait(&bar_aux[group * 2 + b], (aux_seq >> 1) & 1, abort_flag, p.status, kStatusEpilogueTimeout))
+            ok = false;
+          const uint8_t* src = aux_stage + (group * 2 + b) * 16384;
+          const int sw = (r >> 1) & 3;
 #pragma unroll
-            for (int j = 0; j < 4; ++j) {
-              hg[j] = __ldg(gp + j);
-              hu[j] = __ldg(up + j);
-            }
-          } else {
-#pragma unroll
-            for (int j = 0; j < 4; ++j) hg[j] = hu[j] = make_uint4(0, 0, 0, 0);
+          for (int j = 0; j < 4; ++j) {
+            hg[j] = *reinterpret_cast<const uint4*>(src + r * 64 + ((j ^ sw) << 4));
+            hu[j] = *reinterpret_cast<const uint4*>(src + 8192 + r * 64 + ((j ^ sw) << 4));
           }
+          ++aux_seq;
+          // every thread of the group must agree before the (unbounded) named barriers below
+          ok = epi_bar_all(bar_id, ok);
+          if (!ok) break;
+          if (issuer) stage_next();  // the buffer just read is free: all threads of the group hold their rows
         }
         if (nk > 0) {
           tmem_ld32(taddr + c * 32, v);
@@ -512,7 +569,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_kernel(const __grid_cons
             float dg[2], du[2];
 #pragma unroll
             for (int k = 0; k < 2; ++k) {
-              const float sg = __fdividef(1.0f, 1.0f + __expf(-g[k]));
+              const float sg = sigmoid_fast(g[k]);
               du[k] = dh[k] * g[k] * sg;
               dg[k] = dh[k] * uu[k] * sg * (1.0f + g[k] * (1.0f - sg));
             }

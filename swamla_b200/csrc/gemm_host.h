@@ -64,7 +64,7 @@ int num_sms();
 int encode_2d(CUtensorMap* map, const void* base, long long inner, long long outer, long long ld_elems, int box_outer,
               int esz);
 int encode_out(CUtensorMap* map, void* base, bool f32, long long cols, long long rows, long long planes,
-               long long ld_elems, long long plane_elems);
+               long long ld_elems, long long plane_elems, bool as_source = false);
 
 // The routed expert chain (chain.cuh) in one launch.  mode 0 (forward): a = x_sorted [P, L], h1 [P, 2F] and
 // mid = hidden [P, F] and out = y_sorted [P, L] are written.  mode 1 (backward): a = d_y_sorted, h1 is read,

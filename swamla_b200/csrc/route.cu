@@ -216,7 +216,7 @@ __global__ void __launch_bounds__(256) zloss_finalize_kernel(const float* __rest
 
 // ----------------------------------------------------------------------------- routing tables
 // The flat (token, slot) list is cut into chunks of kChunk entries, one warp per chunk.
-constexpr int kChunk = 512;
+constexpr int kChunk = 256;
 constexpr int kRouteWarps = 8;
 
 // Pass 1: per-chunk histogram -> chunk_hist[chunk][E].

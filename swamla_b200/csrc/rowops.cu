@@ -31,19 +31,39 @@ __device__ __forceinline__ uint4 pack8(const float (&f)[8]) {
   return v;
 }
 
+// The three gather-type kernels below keep several independent 16-byte loads per lane in flight (rows are taken four
+// or two at a time, the K rows of a token four at a time): with one row per warp at a time the bytes in flight per SM
+// were too few for the HBM latency and the kernels ran at half the copy bandwidth.
+constexpr int kGatherUnroll = 4;
+
 // x_sorted[row] = x_latent[row_src[row] / K]  (zeros for pad rows); rows < 128 * n_tiles[0].
 __global__ void __launch_bounds__(kRowWarps * 32)
 gather_rows_kernel(const uint4* __restrict__ src, const int* __restrict__ row_src, const int* __restrict__ n_tiles, int K,
                    int vec_per_row, uint4* __restrict__ dst, long long max_rows) {
   const int lane = threadIdx.x & 31;
   const long long rows = n_tiles ? min(static_cast<long long>(n_tiles[0]) * LMOE_ROW_PAD, max_rows) : max_rows;
-  for (long long row = static_cast<long long>(blockIdx.x) * kRowWarps + (threadIdx.x >> 5); row < rows;
-       row += static_cast<long long>(gridDim.x) * kRowWarps) {
-    const int flat = row_src[row];
-    const uint4 zero = make_uint4(0, 0, 0, 0);
-    const uint4* s = (flat >= 0) ? src + static_cast<long long>(flat / K) * vec_per_row : nullptr;
-    uint4* d = dst + row * vec_per_row;
-    for (int v = lane; v < vec_per_row; v += 32) d[v] = s ? s[v] : zero;
+  const long long warps_total = static_cast<long long>(gridDim.x) * kRowWarps;
+  for (long long row0 = (static_cast<long long>(blockIdx.x) * kRowWarps + (threadIdx.x >> 5)) * kGatherUnroll; row0 < rows;
+       row0 += warps_total * kGatherUnroll) {
+    long long from[kGatherUnroll];  // source row, -1: pad row (zeros), -2: beyond the rows in use
+#pragma unroll
+    for (int u = 0; u < kGatherUnroll; ++u) {
+      const long long row = row0 + u;
+      from[u] = -2;
+      if (row < rows) {
+        const int flat = row_src[row];
+        from[u] = flat >= 0 ? flat / K : -1;
+      }
+    }
+    for (int v = lane; v < vec_per_row; v += 32) {
+      uint4 x[kGatherUnroll];
+#pragma unroll
+      for (int u = 0; u < kGatherUnroll; ++u)
+        x[u] = from[u] >= 0 ? src[from[u] * vec_per_row + v] : make_uint4(0, 0, 0, 0);
+#pragma unroll
+      for (int u = 0; u < kGatherUnroll; ++u)
+        if (from[u] != -2) dst[(row0 + u) * vec_per_row + v] = x[u];
+    }
   }
 }
 
@@ -58,13 +78,24 @@ combine_kernel(const uint4* __restrict__ y, const int* __restrict__ pos, const f
     for (int v = lane; v < vec_per_row; v += 32) {
       float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
       if (addend) unpack8(addend[t * addend_ld_vec + v], acc);
-      for (int k = 0; k < K; ++k) {
-        const long long i = t * K + k;
-        const float wk = w ? w[i] : 1.0f;
-        float f[8];
-        unpack8(y[static_cast<long long>(pos[i]) * vec_per_row + v], f);
+      for (int k0 = 0; k0 < K; k0 += kGatherUnroll) {
+        uint4 rows[kGatherUnroll];
+        float wk[kGatherUnroll];
 #pragma unroll
-        for (int j = 0; j < 8; ++j) acc[j] = fmaf(wk, f[j], acc[j]);
+        for (int u = 0; u < kGatherUnroll; ++u) {
+          const long long i = t * K + min(k0 + u, K - 1);
+          wk[u] = w ? w[i] : 1.0f;
+          rows[u] = y[static_cast<long long>(pos[i]) * vec_per_row + v];
+        }
+#pragma unroll
+        for (int u = 0; u < kGatherUnroll; ++u) {
+          if (k0 + u < K) {  // slot order is kept: the sum has the same bits as a one-row-at-a-time loop
+            float f[8];
+            unpack8(rows[u], f);
+#pragma unroll
+            for (int j = 0; j < 8; ++j) acc[j] = fmaf(wk[u], f[j], acc[j]);
+          }
+        }
       }
       out[t * out_ld_vec + v] = pack8(acc);
     }
@@ -77,33 +108,47 @@ __global__ void __launch_bounds__(kRowWarps * 32)
 combine_bwd_kernel(const uint4* __restrict__ d_routed, const uint4* __restrict__ y, const float* __restrict__ w,
                    const int* __restrict__ row_src, const int* __restrict__ n_tiles, int K, int vec_per_row,
                    uint4* __restrict__ d_y, float* __restrict__ d_w, long long max_rows) {
+  constexpr int U = 2;  // rows per warp iteration
   const int lane = threadIdx.x & 31;
   const long long rows = n_tiles ? min(static_cast<long long>(n_tiles[0]) * LMOE_ROW_PAD, max_rows) : max_rows;
-  for (long long row = static_cast<long long>(blockIdx.x) * kRowWarps + (threadIdx.x >> 5); row < rows;
-       row += static_cast<long long>(gridDim.x) * kRowWarps) {
-    const int flat = row_src[row];
-    uint4* d = d_y + row * vec_per_row;
-    if (flat < 0) {
-      for (int v = lane; v < vec_per_row; v += 32) d[v] = make_uint4(0, 0, 0, 0);
-      continue;
+  const long long warps_total = static_cast<long long>(gridDim.x) * kRowWarps;
+  for (long long row0 = (static_cast<long long>(blockIdx.x) * kRowWarps + (threadIdx.x >> 5)) * U; row0 < rows;
+       row0 += warps_total * U) {
+    int flat[U];
+    float wk[U], dot[U];
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      flat[u] = (row0 + u < rows) ? row_src[row0 + u] : -2;  // -1: pad row, -2: beyond the rows in use
+      wk[u] = flat[u] >= 0 ? w[flat[u]] : 0.f;
+      dot[u] = 0.f;
     }
-    const long long t = flat / K;
-    const float wk = w[flat];
-    float dot = 0.f;
     for (int v = lane; v < vec_per_row; v += 32) {
-      float g[8], yy[8], o[8];
-      unpack8(d_routed[t * vec_per_row + v], g);
-      unpack8(y[row * vec_per_row + v], yy);
+      uint4 g4[U], y4[U];
 #pragma unroll
-      for (int j = 0; j < 8; ++j) {
-        dot = fmaf(g[j], yy[j], dot);
-        o[j] = wk * g[j];
+      for (int u = 0; u < U; ++u) {
+        g4[u] = flat[u] >= 0 ? d_routed[static_cast<long long>(flat[u] / K) * vec_per_row + v] : make_uint4(0, 0, 0, 0);
+        y4[u] = flat[u] >= 0 ? y[(row0 + u) * vec_per_row + v] : make_uint4(0, 0, 0, 0);
       }
-      d[v] = pack8(o);
+#pragma unroll
+      for (int u = 0; u < U; ++u) {
+        if (flat[u] == -2) continue;
+        float g[8], yy[8], o[8];
+        unpack8(g4[u], g);
+        unpack8(y4[u], yy);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          dot[u] = fmaf(g[j], yy[j], dot[u]);
+          o[j] = wk[u] * g[j];
+        }
+        d_y[(row0 + u) * vec_per_row + v] = pack8(o);  // pad rows: w = 0 and g = 0 -> zeros
+      }
     }
 #pragma unroll
-    for (int o = 16; o > 0; o >>= 1) dot += __shfl_xor_sync(0xffffffffu, dot, o);
-    if (lane == 0) d_w[flat] = dot;
+    for (int u = 0; u < U; ++u) {
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) dot[u] += __shfl_xor_sync(0xffffffffu, dot[u], o);
+      if (lane == 0 && flat[u] >= 0) d_w[flat[u]] = dot[u];
+    }
   }
 }
 

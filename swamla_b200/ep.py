@@ -216,9 +216,8 @@ class ExpertParallelLatentMoE(torch.autograd.Function):
         # output stage (local)
         d_routed = torch.empty(T, L, **bf)
         dgrad_cat = torch.empty(T, 2 * Fs + L + E, **bf)
-        d_hidden_s = torch.empty(T, Fs, **bf)
         _cabi.call("lmoe_combine_out_bwd_dgrad", shape, ptr(dyb), ptr(wup), ptr(wds), ptr(h1_s), ptr(d_routed),
-                   ptr(d_hidden_s), ptr(dgrad_cat), ptr(status), st)
+                   None, ptr(dgrad_cat), ptr(status), st)
         # adjoint of the combine in send order, then back to the expert ranks
         d_y_send = torch.empty(n_send, L, **bf)
         d_weights = torch.empty(T, K, **f32)
@@ -442,9 +441,8 @@ class ExpertParallelP2P(torch.autograd.Function):
 
         d_routed = torch.empty(T, L, **bf)
         dgrad_cat = torch.empty(T, 2 * Fs + L + E, **bf)
-        d_hidden_s = torch.empty(T, Fs, **bf)
         _cabi.call("lmoe_combine_out_bwd_dgrad", shape, ptr(dyb), ptr(wup), ptr(wds), ptr(h1_s), ptr(d_routed),
-                   ptr(d_hidden_s), ptr(dgrad_cat), ptr(status), st)
+                   None, ptr(dgrad_cat), ptr(status), st)
         # adjoint of the combine fused into the dispatch: rows w * d_routed go to the expert ranks, the gating
         # gradients <d_routed, y> are formed from the returned rows kept in y_ret
         d_weights = torch.empty(T, K, **f32)
@@ -688,9 +686,8 @@ class ExpertParallelDedup(torch.autograd.Function):
 
         d_routed = torch.empty(T, L, **bf)
         dgrad_cat = torch.empty(T, 2 * Fs + L + E, **bf)
-        d_hidden_s = torch.empty(T, Fs, **bf)
         _cabi.call("lmoe_combine_out_bwd_dgrad", shape, ptr(dyb), ptr(wup), ptr(wds), ptr(h1_s), ptr(d_routed),
-                   ptr(d_hidden_s), ptr(dgrad_cat), ptr(status), st)
+                   None, ptr(dgrad_cat), ptr(status), st)
         main, side = torch.cuda.current_stream(), bufs.side
         ready = torch.cuda.Event()
         ready.record(main)

@@ -24,9 +24,9 @@ TMA_GATHER = _os.environ.get("LMOE_TMA_GATHER", "0") == "1"
 
 
 def d_hidden_scratch(lib, P, L, F, **kw):
-    """The [P, F] scratch of the routed dgrad stage, or None when the chain kernel (which never writes d_hidden)
-    serves this shape."""
-    return None if lib.lmoe_chain_applies(L, F) else torch.empty(P, F, **kw)
+    """The routed dgrad stage needs no [P, F] scratch: the SwiGLU adjoint runs in the epilogue of the d_hidden GEMM
+    (saved gate / up staged by TMA), or inside the chain kernel; d_hidden never reaches memory."""
+    return None
 
 
 def _stream() -> int:
@@ -263,9 +263,9 @@ class LatentMoEFunction(torch.autograd.Function):
         ld_cat = 2 * Fs + L + E
 
         # output stage dgrads, then: [adjoint of the combine] beside [output-stage weight gradients]
-        d_hidden_s = torch.empty(T, Fs, **bf)
+        # d_hidden_s = NULL: the shared expert's SwiGLU adjoint runs in the epilogue of the d_hidden_s GEMM
         _cabi.call("lmoe_combine_out_bwd_dgrad", shape, ptr(dyb), ptr(wup), ptr(wds), ptr(h1_s), ptr(d_routed),
-                   ptr(d_hidden_s), ptr(dgrad_cat), ptr(status), st)
+                   None, ptr(dgrad_cat), ptr(status), st)
         fork.to_side()
         _cabi.call("lmoe_combine_bwd", shape, ptr(d_routed), ptr(y_sorted), ptr(weights), route.struct, ptr(d_y_sorted),
                    ptr(d_weights), fork.s)

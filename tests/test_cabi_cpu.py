@@ -37,6 +37,6 @@ def test_host_side_shape_helpers():
     lib = _cabi.load()
     s = _cabi.Shape(T=1024, D=1024, L=256, E=128, K=12, F=256, Fs=1024, n_shared=1)
     assert lib.lmoe_padded_rows(s) == 1024 * 12 + 128 * 128
-    assert lib.lmoe_route_workspace_bytes(s) == ((1024 * 12 + 511) // 512) * 128 * 4
+    assert lib.lmoe_route_workspace_bytes(s) == ((1024 * 12 + 255) // 256) * 128 * 4
     bad = _cabi.Shape(T=1024, D=1024, L=256, E=512, K=12, F=256, Fs=1024, n_shared=1)
     assert lib.lmoe_padded_rows(bad) == 0

@@ -59,7 +59,7 @@ def test_chain_forward_and_backward_match_the_separate_kernels(E, L, F, counts, 
     x, dy = x.to(BF).to(dev), dy.to(BF).to(dev)
     status = torch.zeros(1, dtype=torch.int32, device=dev)
 
-    def run(chain, pairs=True):
+    def run(chain, pairs=True, fused_adjoint=False):
         # pairs: the pad_offsets table lets the launcher put two tiles of an expert on a CTA pair (L a multiple of 128)
         po = pad_offsets.data_ptr() if pairs else None
         prev = lib.lmoe_chain_enable(1 if chain else 0)
@@ -67,7 +67,8 @@ def test_chain_forward_and_backward_match_the_separate_kernels(E, L, F, counts, 
             o = dict(h1=torch.full((P, 2 * F), 3.0, dtype=BF, device=dev), hidden=torch.full((P, F), 3.0, dtype=BF, device=dev),
                      y=torch.full((P, L), 3.0, dtype=BF, device=dev), d_h1=torch.full((P, 2 * F), 3.0, dtype=BF, device=dev),
                      d_x=torch.full((P, L), 3.0, dtype=BF, device=dev))
-            d_hidden = None if chain else torch.empty(P, F, dtype=BF, device=dev)
+            # no d_hidden scratch: the SwiGLU adjoint runs in the epilogue of the d_hidden GEMM (gate / up staged by TMA)
+            d_hidden = None if (chain or fused_adjoint) else torch.empty(P, F, dtype=BF, device=dev)
             _cabi.call("lmoe_grouped_fwd", P, E, L, F, x.data_ptr(), wgu.data_ptr(), wd.data_ptr(), tile_expert.data_ptr(),
                        n_tiles.data_ptr(), po, o["h1"].data_ptr(), o["hidden"].data_ptr(), o["y"].data_ptr(), status.data_ptr(), st)
             _cabi.call("lmoe_grouped_bwd_dgrad", P, E, L, F, dy.data_ptr(), o["h1"].data_ptr(), wgu.data_ptr(), wd.data_ptr(),
@@ -79,7 +80,13 @@ def test_chain_forward_and_backward_match_the_separate_kernels(E, L, F, counts, 
         finally:
             lib.lmoe_chain_enable(prev)
 
-    a, b, single = run(True), run(False), run(True, pairs=False)
+    a, b, single, fused = run(True), run(False), run(True, pairs=False), run(False, fused_adjoint=True)
+    for k in ("d_h1", "d_x"):      # the same arithmetic on the same d_hidden, then the very same second GEMM: at most a
+        ta, tb = fused[k][:used].float(), b[k][:used].float()          # last-bit difference where the compiler fuses
+        assert ((ta - tb).norm() / tb.norm().clamp_min(1e-30)).item() <= 1e-3, k   # multiplies and adds differently
+        assert ((ta - tb).abs() <= 2.0 ** -7 * (tb.abs() + tb.pow(2).mean().sqrt())).all(), k
+    for k, t in fused.items():
+        assert (t[used:].float() == 3.0).all(), k
     for k in ("h1", "hidden", "y"):                      # same MMAs in the same order: identical bits
         assert torch.equal(a[k][:used], b[k][:used]), k
     for k in a:                                          # one CTA per tile or CTA pairs: the same arithmetic

@@ -61,7 +61,7 @@ def test_static_scratch_variant_refuses_problems_beyond_its_capacity():
     from swamla_b200 import _cabi
     lib = _cabi.load()
     dev = torch.device("cuda:0")
-    # ceil(T*K/512) * E * 4 bytes > 4 MiB: 2**20 tokens x top-32 over 256 experts
+    # ceil(T*K/256) * E * 4 bytes > 4 MiB: 2**20 tokens x top-32 over 256 experts
     big = _cabi.Shape(T=1 << 20, D=1024, L=256, E=256, K=32, F=256, Fs=1024, n_shared=1)
     assert lib.lmoe_route_workspace_bytes(big) > (4 << 20)
     dummy = torch.zeros(64, dtype=torch.int32, device=dev)
