@@ -184,9 +184,9 @@ static bool pair_gemm_enabled() {
 
 bool pair_gemm_applies(int M, int N) { return pair_gemm_enabled() && M >= 256 && N >= 256; }
 
-template <bool A_MN, bool B_MN, int EPI>
+template <bool A_MN, bool B_MN, int EPI, int GRP = GRP_NONE>
 static int launch_pair_inst(const GemmParams& p, long long total_tiles, cudaStream_t stream) {
-  auto kfn = gemm_pair_kernel<A_MN, B_MN, EPI>;
+  auto kfn = gemm_pair_kernel<A_MN, B_MN, EPI, GRP>;
   constexpr int smem = PairSmem<EPI>::kTotal;
   static PerDeviceOnce once;  // one per template instantiation
   static int max_pairs_dev[kMaxDevices] = {};
@@ -298,6 +298,65 @@ static int launch_gemm_pair(const GemmCall& c) {
   }
 }
 
+// Grouped-over-rows GEMM on CTA pairs: two tiles of the same expert share the expert's B loads (gemm_pair.cuh, GRP_M).
+// Needs the per-expert padded offsets; K-major A, one K segment, plain bf16 or SwiGLU epilogue.
+// Off unless the environment has LMOE_PAIR_GROUPED=1: with the 256-element contractions of the routed experts a tile's
+// main loop is four k-blocks long and the pair's cross-CTA hand-offs cost more than the halved weight traffic saves
+// (measured at E = 128, L = F = 256, 1,664 tiles: gate_up + down 202 us on pairs against 142 us with one CTA per tile).
+static bool pair_grouped_enabled() {
+  static int v = -1;
+  if (v < 0) {
+    const char* e = getenv("LMOE_PAIR_GROUPED");
+    v = (e && e[0] == '1') ? 1 : 0;
+  }
+  return v == 1;
+}
+static bool pair_grouped_applies(const GemmCall& c) {
+  const bool swiglu = (c.epi == EPI_SWIGLU);
+  return c.grp == GRP_M && c.pad_offsets && pair_gemm_enabled() && pair_grouped_enabled() && c.esz == 2 && !c.a_rows && !c.a_mn && c.nseg == 1 &&
+         c.bn == 0 && (c.epi == EPI_BF16 || (swiglu && c.b_mn)) && c.groups > 0 && c.groups <= LMOE_MAX_EXPERTS &&
+         c.padded_rows / kBM < (1 << 23) && (c.N % (swiglu ? 128 : 32)) == 0 && (c.Kseg[0] % 64) == 0;
+}
+
+static int launch_gemm_pair_grouped(const GemmCall& c) {
+  const bool swiglu = (c.epi == EPI_SWIGLU);
+  GemmParams p;
+  memset(&p, 0, sizeof(p));
+  const int K = c.Kseg[0];
+  const int n_per_tile = swiglu ? 128 : 256;
+  const int n_tiles = (c.N + n_per_tile - 1) / n_per_tile;
+  const int n_b_total = swiglu ? 2 * c.N : c.N;
+  const long long b_outer = static_cast<long long>(c.groups) * c.b_group_rows;
+  p.seg_kiters[0] = K / 64;
+  int rc = encode_2d(&p.tmA[0], c.A[0], K, c.padded_rows, c.lda[0], kBM, 2);
+  if (rc) return rc;
+  rc = !c.b_mn ? encode_2d(&p.tmB[0], c.B[0], K, b_outer, c.ldb[0], 128, 2)       // this CTA's 128 rows of B[e]
+               : encode_2d(&p.tmB[0], c.B[0], n_b_total, b_outer, c.ldb[0], 64, 2);
+  if (rc) return rc;
+  rc = encode_out(&p.tmC, c.C, false, swiglu ? 2ll * c.N : c.N, c.padded_rows, 1, c.ldc, 0);
+  if (rc) return rc;
+  if (swiglu) {
+    rc = encode_out(&p.tmC2, c.C2, false, c.N, c.padded_rows, 1, c.ldc2, 0);
+    if (rc) return rc;
+  }
+  p.nseg = 1;
+  p.M = static_cast<int>(c.padded_rows);
+  p.N = c.N;
+  p.m_tiles = static_cast<int>(c.padded_rows / kBM);
+  p.n_tiles = n_tiles;
+  p.groups = c.groups;
+  p.split_k = 1;
+  p.half = c.N;
+  p.b_group_rows = c.b_group_rows;
+  p.pad_offsets = c.pad_offsets;
+  p.status = c.status;
+  // pairs are counted on the device; at most one per two tiles plus one per expert
+  const long long total = (static_cast<long long>(p.m_tiles + 1) / 2 + c.groups) * n_tiles;
+  if (swiglu) return launch_pair_inst<false, true, EPI_SWIGLU, GRP_M>(p, total, c.stream);
+  if (c.b_mn) return launch_pair_inst<false, true, EPI_BF16, GRP_M>(p, total, c.stream);
+  return launch_pair_inst<false, false, EPI_BF16, GRP_M>(p, total, c.stream);
+}
+
 int launch_gemm(const GemmCall& c) {
   if (c.nseg < 1 || c.nseg > 3 || !c.C || c.M <= 0 || c.N <= 0) return LMOE_ERR_ARG;
   if (c.split_k > 1 && (c.epi != EPI_F32 || c.nseg != 1 || c.grp != GRP_NONE)) return LMOE_ERR_ARG;
@@ -314,6 +373,7 @@ int launch_gemm(const GemmCall& c) {
     return LMOE_ERR_SHAPE;
 
   const bool gather = c.a_rows != nullptr;
+  if (pair_grouped_applies(c)) return launch_gemm_pair_grouped(c);
   if (c.grp == GRP_NONE && esz == 2 && !gather && c.bn != 128 && pair_gemm_applies(c.M, swiglu ? 2 * c.N : c.N) &&
       (c.epi == EPI_BF16 || c.epi == EPI_F32 || (swiglu && !c.a_mn && !c.b_mn)))
     return launch_gemm_pair(c);

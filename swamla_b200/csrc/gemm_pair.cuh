@@ -28,7 +28,7 @@ struct PairSmem {
   static constexpr int kStreams = (EPI == EPI_SWIGLU) ? 3 : 1;
   static constexpr int kBufsPerGroup = (EPI == EPI_BF16) ? 2 : 1;
   static constexpr int kStagingBytes = 2 * kBufsPerGroup * kStreams * kSlabBytes;
-  static constexpr int kBarrierBytes = 256;
+  static constexpr int kBarrierBytes = 1536;  // barriers + the per-expert table of the grouped form (<= 257 ints)
   static constexpr int kBudget = 232448 - 1024 - kBarrierBytes - kStagingBytes;
   static constexpr int kStagesMax = kBudget / kStageBytes;
   static constexpr int kStages = kStagesMax > 6 ? 6 : kStagesMax;
@@ -36,9 +36,14 @@ struct PairSmem {
   static_assert(kStages >= 4, "pipeline too shallow");
 };
 
-template <bool A_MN, bool B_MN, int EPI>
+// GRP == GRP_M (grouped over rows, K-major A): the rows are the padded routed layout; the two CTAs of a pair take two
+// consecutive 128-row tiles of the SAME expert (tiles 2j, 2j+1 of its run, from pad_offsets) and share that expert's
+// slice of the stacked B tensor.  An expert with an odd number of tiles ends with a pair whose second CTA recomputes
+// the first tile and stores nothing.
+template <bool A_MN, bool B_MN, int EPI, int GRP = GRP_NONE>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads, 1)
 gemm_pair_kernel(const __grid_constant__ GemmParams p) {
+  static_assert(GRP == GRP_NONE || (GRP == GRP_M && !A_MN), "grouped form: rows of a K-major A");
   using S = PairSmem<EPI>;
   constexpr int BN = 256;
   constexpr int STAGES = S::kStages;
@@ -58,10 +63,41 @@ gemm_pair_kernel(const __grid_constant__ GemmParams p) {
   uint64_t* bar_tempty = bar_tfull + 2;
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bar_tempty + 2);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+  int* etab = reinterpret_cast<int*>(tmem_slot + 2);  // GRP_M: first tile of expert e | experts before e with an odd tile count << 23
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
   const uint32_t rank = cluster_ctarank();   // 0: issues the MMAs and owns the pair's "full" / "accumulator empty" barriers
+  if (GRP == GRP_M) {
+    const int E = p.groups;
+    const int cap_rows = p.m_tiles * kBM;   // m_tiles: capacity of the padded layout in 128-row tiles
+    if (static_cast<int>(threadIdx.x) <= E) etab[threadIdx.x] = min(p.pad_offsets[threadIdx.x], cap_rows) / kBM;
+    __syncthreads();
+    if (warp == 0) {  // lane l scans experts 8l .. 8l+7, a shuffle scan joins the lanes
+      int odd[8], sum = 0;
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        const int e = lane * 8 + i;
+        odd[i] = (e < E) ? ((etab[e + 1] - etab[e]) & 1) : 0;
+        sum += odd[i];
+      }
+      int incl = sum;
+#pragma unroll
+      for (int o = 1; o < 32; o <<= 1) {
+        const int t = __shfl_up_sync(0xffffffffu, incl, o);
+        if (lane >= o) incl += t;
+      }
+      __syncwarp();
+      int run = incl - sum;
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        const int e = lane * 8 + i;
+        if (e < E) etab[e] |= run << 23;
+        run += odd[i];
+        if (e + 1 == E) etab[E] |= run << 23;
+      }
+    }
+  }
 
   if (threadIdx.x == 0) {
     for (int i = 0; i < STAGES; ++i) {
@@ -94,14 +130,40 @@ gemm_pair_kernel(const __grid_constant__ GemmParams p) {
   // ---- tile schedule over pairs (identical arithmetic in every role of both CTAs) ----
   const int pair_id = blockIdx.x >> 1;
   const int n_pairs = gridDim.x >> 1;
-  const int tiles_mn = p.m_tiles * p.n_tiles;  // m_tiles counts 256-row tiles here
+  auto first_tile = [&](int e) { return etab[e] & 0x7fffff; };
+  auto pairs_before = [&](int e) { return ((etab[e] & 0x7fffff) - (etab[0] & 0x7fffff) + (etab[e] >> 23)) >> 1; };
+  // m_tiles counts 256-row tiles (dense) or is the layout's capacity in 128-row tiles (grouped: pairs come from etab)
+  const int tiles_mn = (GRP == GRP_M ? pairs_before(p.groups) : p.m_tiles) * p.n_tiles;
   const int total_tiles = tiles_mn * p.split_k;
 
   struct Tile {
     int m0, nt, plane, kb, ke;
+    int grp;   // GRP_M: expert of the pair
+    int live;  // GRP_M: 0 for the tile-less second CTA of an odd run (loads the first tile, stores nothing)
   };
   auto decode = [&](int id) {
     Tile t;
+    t.grp = 0;
+    t.live = 1;
+    if (GRP == GRP_M) {
+      const int pid = id / p.n_tiles;
+      t.nt = id - pid * p.n_tiles;
+      int lo = 0, hi = p.groups - 1;  // largest e with pairs_before(e) <= pid
+      while (lo < hi) {
+        const int mid = (lo + hi + 1) >> 1;
+        if (pairs_before(mid) <= pid) lo = mid;
+        else hi = mid - 1;
+      }
+      const int first = first_tile(lo) + 2 * (pid - pairs_before(lo));
+      const int own = first + static_cast<int>(rank);
+      t.grp = lo;
+      t.live = own < first_tile(lo + 1) ? 1 : 0;
+      t.m0 = (t.live ? own : first) * kBM;
+      t.plane = 0;
+      t.kb = 0;
+      t.ke = p.seg_kiters[0];
+      return t;
+    }
     const int outer = id / tiles_mn;
     const int rem = id - outer * tiles_mn;
     t.m0 = (rem / p.n_tiles) * 256 + static_cast<int>(rank) * kBM;  // this CTA's 128 rows
@@ -156,11 +218,13 @@ gemm_pair_kernel(const __grid_constant__ GemmParams p) {
 #pragma unroll
               for (int j = 0; j < kBM / CH; ++j) tma_load_2d_pair(sa + j * CH_BYTES, &p.tmA[s], full0, t.m0 + j * CH, kcoord);
             }
+            const int grp_rows = (GRP == GRP_M) ? t.grp * p.b_group_rows : 0;  // this expert's slice of the stacked B
             if (!B_MN) {
-              tma_load_2d_pair(sb, &p.tmB[s], full0, kcoord, b0);
+              tma_load_2d_pair(sb, &p.tmB[s], full0, kcoord, grp_rows + b0);
             } else {
 #pragma unroll
-              for (int j = 0; j < 128 / CH; ++j) tma_load_2d_pair(sb + j * CH_BYTES, &p.tmB[s], full0, b0 + j * CH, kcoord);
+              for (int j = 0; j < 128 / CH; ++j)
+                tma_load_2d_pair(sb + j * CH_BYTES, &p.tmB[s], full0, b0 + j * CH, grp_rows + kcoord);
             }
             if (++stage == STAGES) {
               stage = 0;
@@ -300,7 +364,7 @@ gemm_pair_kernel(const __grid_constant__ GemmParams p) {
         }
         fence_proxy_async_smem();
         epi_bar_sync(bar_id);
-        if (issuer && t.m0 < p.M) {  // the second half of a ragged last tile may lie entirely outside the output
+        if (issuer && t.live && (GRP == GRP_M || t.m0 < p.M)) {  // dense: the second half of a ragged last tile may lie outside
           const int col = n0 + c * kSlabCols;
           if (kSwiglu) {
             tma_store_3d(&p.tmC, sbuf, col, t.m0, 0);

@@ -199,6 +199,7 @@ static int grouped_fwd_impl(int64_t P, int E, int L, int F, const void* x_sorted
   a.b_group_rows = L;
   a.tile_expert = tile_expert;
   a.n_m_tiles = n_tiles;
+  a.pad_offsets = pad_offsets;  // lets both GEMMs run on CTA pairs that share an expert's weight loads
   a.status = status;
   a.stream = static_cast<cudaStream_t>(stream);
   GemmCall b = a;
@@ -423,6 +424,7 @@ extern "C" int lmoe_grouped_bwd_dgrad(int64_t P, int E, int L, int F, const void
   }
   // d_x_sorted[P,L] = d_h1[P,2F] * Wgu[e]^T : Wgu[e] is [L,2F] = [N,K] row-major -> K-major B
   GemmCall b = a;
+  b.pad_offsets = pad_offsets;  // CTA pairs that share an expert's weight loads
   b.A[0] = d_h1;
   b.lda[0] = 2ll * F;
   b.B[0] = w_gate_up;

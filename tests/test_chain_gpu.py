@@ -81,6 +81,13 @@ def test_chain_forward_and_backward_match_the_separate_kernels(E, L, F, counts, 
             lib.lmoe_chain_enable(prev)
 
     a, b, single, fused = run(True), run(False), run(True, pairs=False), run(False, fused_adjoint=True)
+    # with the per-expert offsets the separate grouped GEMMs run on CTA pairs too (gemm_pair.cuh, grouped form); without
+    # them, one CTA per tile: the same products summed in the same order
+    # (the grouped form of the pair kernel is opt-in, LMOE_PAIR_GROUPED=1, read once per process: without it both runs
+    #  use one CTA per tile and the comparison is trivially true)
+    plain = run(False, pairs=False)
+    for k in b:
+        assert torch.equal(b[k][:used], plain[k][:used]), k
     for k in ("d_h1", "d_x"):      # the same arithmetic on the same d_hidden, then the very same second GEMM: at most a
         ta, tb = fused[k][:used].float(), b[k][:used].float()          # last-bit difference where the compiler fuses
         assert ((ta - tb).norm() / tb.norm().clamp_min(1e-30)).item() <= 1e-3, k   # multiplies and adds differently
