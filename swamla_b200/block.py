@@ -32,7 +32,9 @@ class _NormAndPass(torch.autograd.Function):
         _cabi.call("lmoe_rmsnorm_fwd", ptr(xb), ptr(w32), float(eps), T, D, ptr(xn), ptr(rstd), _stream())
         ctx.save_for_backward(xb, w32, rstd)
         ctx.dtypes = (x2d.dtype, weight.dtype)
-        return (xn if x2d.dtype == BF else xn.to(x2d.dtype)), xb
+        # the residual branch keeps the input's dtype: under the reference's autocast training the residual stream
+        # is fp32 (train.py:1195, normalization.py:25-39) and must not be rounded to bf16 at every block
+        return (xn if x2d.dtype == BF else xn.to(x2d.dtype)), (xb if x2d.dtype == BF else x2d)
 
     @staticmethod
     def backward(ctx, d_xn, d_pass):
@@ -43,21 +45,30 @@ class _NormAndPass(torch.autograd.Function):
         if d_xn is None:
             d_xn = torch.zeros(T, D, dtype=BF, device=dev)
         g = _as_bf16(d_xn)
-        r = None if d_pass is None else _as_bf16(d_pass)
+        x_dtype, w_dtype = ctx.dtypes
+        # bf16 stream: the residual gradient is added inside the kernel; wider stream: added afterwards in that dtype
+        r = None if (d_pass is None or x_dtype != BF) else _as_bf16(d_pass)
         dx = torch.empty(T, D, dtype=BF, device=dev)
         d_w = torch.empty(D, dtype=torch.float32, device=dev)
         ws = torch.empty(lib.lmoe_rmsnorm_workspace_bytes(D), dtype=torch.uint8, device=dev)
         _cabi.call("lmoe_rmsnorm_bwd", ptr(xb), ptr(w32), ptr(rstd), ptr(g), ptr(r), T, D, ptr(dx), ptr(d_w), ptr(ws),
                    ws.numel(), _stream())
-        x_dtype, w_dtype = ctx.dtypes
-        return (dx if x_dtype == BF else dx.to(x_dtype)), (d_w if w_dtype == torch.float32 else d_w.to(w_dtype)), None
+        if x_dtype != BF:
+            dx = dx.to(x_dtype)
+            if d_pass is not None:
+                dx = dx + d_pass.to(x_dtype)
+        return dx, (d_w if w_dtype == torch.float32 else d_w.to(w_dtype)), None
 
 
 class _Add(torch.autograd.Function):
-    """out = a + b (bf16 rows); both inputs receive the output's gradient as it is."""
+    """out = a + b (fused kernel for bf16 rows; a wider residual stream is added in its own dtype); both inputs receive
+    the output's gradient as it is."""
 
     @staticmethod
     def forward(ctx, a, b):
+        ctx.dtypes = (a.dtype, b.dtype)
+        if a.dtype != BF:                     # fp32 residual stream: the add stays in that dtype
+            return a + b.to(a.dtype)
         ab, bb = _as_bf16(a), _as_bf16(b)
         out = torch.empty_like(ab)
         _cabi.call("lmoe_add_bf16", ptr(ab), ptr(bb), ptr(out), ab.numel(), _stream())
