@@ -153,30 +153,27 @@ def test_block_with_moe_layer_matches_oracle(name):
 
 def test_fp32_residual_stream_is_not_rounded_to_bf16():
     """Under the reference's autocast training the residual stream is fp32 (train.py:1195): the block must add the
-    feed-forward output to x in fp32 and hand the residual branch's gradient back unrounded."""
+    feed-forward output to x in fp32 and hand the residual branch's gradient back unrounded.  With a feed-forward
+    branch a thousand times smaller than x, any bf16 rounding of the residual (2^-9 relative) would dwarf the error of
+    the branch itself."""
     from swamla_b200.block import NormedResidualFFN
 
     class Scale(torch.nn.Module):            # a stand-in feed-forward so that only the block's own arithmetic is seen
         def forward(self, t):
-            return t * 0.25
+            return t * 1e-3
 
     dev = torch.device("cuda:0")
     g = torch.Generator().manual_seed(4)
-    x = (torch.randn(2, 33, 256, generator=g) * (1 + 2.0 ** -12)).to(dev)      # not representable in bf16
+    x = torch.randn(2, 33, 256, generator=g) * 3.0
+    dy = torch.randn(2, 33, 256, generator=g) * 3.0
     block = NormedResidualFFN(Scale(), 256).to(dev)
-    xg = x.clone().requires_grad_(True)
+    xg = x.to(dev).requires_grad_(True)
     out = block(xg)
     assert out.dtype == torch.float32
-    ffn_out = block.ffn(block_ref.rmsnorm(x.cpu().to(torch.bfloat16).float(), torch.ones(256), 1e-6).to(dev))
-    # out - x is the (bf16-precision) feed-forward branch; x itself must survive to fp32 accuracy
-    resid = (out.detach().double() - x.double())
-    assert (resid - ffn_out.double()).abs().max().item() <= 2e-2 * ffn_out.abs().max().item()
-    back = out.detach() - resid.float()
-    assert (back - x).abs().max().item() <= 1e-6 * x.abs().max().item()
-    assert (out.detach() - (x.to(torch.bfloat16).float() + resid.float())).abs().max().item() > 1e-4   # bf16 x would differ
-    dy = torch.randn(2, 33, 256, generator=g).to(dev) * (1 + 2.0 ** -12)
-    out.backward(dy)
-    norm_part = (xg.grad.double() - dy.double())           # gradient through the norm branch, bf16 precision
-    assert norm_part.abs().max().item() < 2.0
-    # the residual branch's share of dx is dy itself, unrounded: removing the norm branch leaves dy to fp32 accuracy
-    assert ((xg.grad.double() - norm_part).float() - dy).abs().max().item() <= 1e-6 * dy.abs().max().item()
+    out.backward(dy.to(dev))
+    xr = x.clone().requires_grad_(True)
+    ref = xr + 1e-3 * block_ref.rmsnorm(xr, torch.ones(256), 1e-6)
+    ref.backward(dy)
+    assert (out.detach().cpu() - ref.detach()).abs().max().item() <= 2e-5          # bf16 rounding of x would be ~2e-2
+    assert (xg.grad.cpu() - xr.grad).abs().max().item() <= 2e-5
+    assert (x.to(torch.bfloat16).float() - x).abs().max().item() > 1e-3            # (what a bf16 residual would lose)
