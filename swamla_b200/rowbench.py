@@ -1,7 +1,11 @@
 """Achieved HBM bandwidth of the library's memory-bound kernels (routing, gather, combine, SwiGLU adjoint, e4m3
 quantisation, casts) at a benchmark workload's shapes.
 
-    python -m swamla_b200.rowbench [--workload cfg2] [--reps 20]
+    python -m swamla_b200.rowbench [--workload cfg2] [--reps 20] [--experts]
+
+``--experts`` times the routed expert stage instead (forward: gate_up -> SwiGLU -> down; backward: d_hidden -> SwiGLU
+adjoint -> d_x) in its kernel variants: the separate grouped GEMMs (default path), the chain kernel on one CTA per tile
+and on CTA pairs.  With ``LMOE_PAIR_GROUPED=1`` in the environment the "separate" rows run the grouped GEMMs on CTA pairs.
 
 Each kernel is called through the C ABI on synthetic tensors of the workload's sizes, timed with CUDA events on the
 launching stream (median of ``--reps`` launches after warm-up), with the L2 flushed by a 256 MB write between
@@ -35,6 +39,7 @@ def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--workload", default="cfg2")
     ap.add_argument("--reps", type=int, default=20)
+    ap.add_argument("--experts", action="store_true", help="time the routed expert stage in its kernel variants")
     args = ap.parse_args()
     w = workloads.WORKLOADS[args.workload]
     lib = _cabi.load()
@@ -111,11 +116,8 @@ def main():
          lambda: call("lmoe_cast_f32_to_bf16", p(w32), p(w16), w32.numel(), st)),
     ]
     peak, src = _hbm_peak()
-    print(f"# HBM-bound kernels at {w.name}: T={T} E={E} K={K} L={L} F={F} Fs={Fs}, padded rows in use {used}; "
-          f"HBM peak {peak:.0f} GB/s ({src} copy bandwidth)\n")
-    print("| kernel | algorithmic bytes | us (median) | GB/s | frac of peak |")
-    print("|---|---|---|---|---|")
-    for name, nbytes, fn in kernels:
+
+    def median_us(fn):
         for _ in range(3):
             fn()
         ts = []
@@ -128,7 +130,58 @@ def main():
             torch.cuda.synchronize()
             ts.append(e0.elapsed_time(e1) * 1e3)
         ts.sort()
-        us = ts[len(ts) // 2]
+        return ts[len(ts) // 2]
+
+    if args.experts:
+        wgu = (torch.randn(E, L, 2 * F, generator=g, **f32) * 0.05).to(BF)
+        wd = (torch.randn(E, F, L, generator=g, **f32) * 0.05).to(BF)
+        call("lmoe_gather_rows", p(x_latent), p(route.row_src), K, P, L, p(route.n_tiles), p(x_sorted), st)
+        hidden = torch.empty(P, F, **bf)
+        d_x = torch.empty(P, L, **bf)
+        call("lmoe_combine_bwd", shape, p(d_routed), p(y_sorted), p(weights), route.struct, p(d_y_sorted), p(d_weights), st)
+        te, nt, po = p(route.tile_expert), p(route.n_tiles), p(route.pad_offsets)
+
+        def fwd(pairs):
+            call("lmoe_grouped_fwd", P, E, L, F, p(x_sorted), p(wgu), p(wd), te, nt, po if pairs else None, p(h1), p(hidden),
+                 p(y_sorted), p(status), st)
+
+        def bwd(pairs, scratch):
+            call("lmoe_grouped_bwd_dgrad", P, E, L, F, p(d_y_sorted), p(h1), p(wgu), p(wd), te, nt, po if pairs else None,
+                 p(d_hidden) if scratch else None, p(d_h1), p(d_x), p(status), st)
+
+        status = torch.zeros(1, dtype=torch.int32, device=dev)
+        fb = used * (L * 2 + 2 * F * 2 + F * 2 + L * 2)          # x_sorted in; h1, hidden, y_sorted out
+        bb = used * (L * 2 + 2 * F * 2 + 2 * F * 2 + L * 2)      # d_y_sorted, h1 in; d_h1, d_x_sorted out
+        flops_f, flops_b = used * 6 * L * F, used * 6 * L * F
+        print(f"# Routed expert stage at {w.name}: {used} padded rows ({used // 128} tiles), E={E} L={L} F={F}; algorithmic "
+              f"bytes forward {fb / 1e6:.0f} MB, backward (data gradients) {bb / 1e6:.0f} MB; {flops_f / 1e9:.1f} GFLOP each\n")
+        print("| variant | forward us | GB/s | TFLOP/s | backward us | GB/s | TFLOP/s |")
+        print("|---|---|---|---|---|---|---|")
+        variants = [("separate grouped GEMMs, SwiGLU adjoint as a streaming kernel", 0, True, True),
+                    ("separate grouped GEMMs, SwiGLU adjoint in the d_hidden GEMM's epilogue (default)", 0, True, False),
+                    ("chain kernel, one CTA per tile", 1, False, False),
+                    ("chain kernel, CTA pairs of one expert", 1, True, False)]
+        for name, chain, pairs, scratch in variants:
+            prev = lib.lmoe_chain_enable(chain)
+            try:
+                if chain and not lib.lmoe_chain_applies(L, F):
+                    continue
+                tf = median_us(lambda: fwd(pairs))
+                tb = median_us(lambda: bwd(pairs, scratch))
+            finally:
+                lib.lmoe_chain_enable(prev)
+            print(f"| {name} | {tf:.1f} | {fb / tf / 1e3:.0f} | {flops_f / tf / 1e6:.0f} | {tb:.1f} | {bb / tb / 1e3:.0f} | "
+                  f"{flops_b / tb / 1e6:.0f} |")
+        torch.cuda.synchronize()
+        assert status.item() == 0
+        return
+
+    print(f"# HBM-bound kernels at {w.name}: T={T} E={E} K={K} L={L} F={F} Fs={Fs}, padded rows in use {used}; "
+          f"HBM peak {peak:.0f} GB/s ({src} copy bandwidth)\n")
+    print("| kernel | algorithmic bytes | us (median) | GB/s | frac of peak |")
+    print("|---|---|---|---|---|")
+    for name, nbytes, fn in kernels:
+        us = median_us(fn)
         gbs = nbytes / us / 1e3
         print(f"| {name} | {nbytes / 1e6:.1f} MB | {us:.1f} | {gbs:.0f} | {gbs / peak:.2f} |")
 
