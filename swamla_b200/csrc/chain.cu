@@ -133,7 +133,7 @@ int launch_chain(int mode, long long P, int E, int L, int F, const void* a, cons
                  int* status, cudaStream_t stream) {
   if (!a || !w_gate_up || !w_down || !tile_expert || !n_tiles || !h1 || !mid || !out) return LMOE_ERR_ARG;
   if (P <= 0 || (P % kBM) != 0 || E <= 0 || !chain_applies(L, F)) return LMOE_ERR_SHAPE;
-  if (pad_offsets && chain_pair_enabled() && (L % 128) == 0 && E <= LMOE_MAX_EXPERTS && P / kBM < (1 << 23))
+  if (pad_offsets && chain_pair_enabled() && (L % 128) == 0 && (F % 128) == 0 && E <= LMOE_MAX_EXPERTS && P / kBM < (1 << 23))
     return launch_chain_pair(mode, P, E, L, F, a, w_gate_up, w_down, pad_offsets, h1, mid, out, status, stream);
   ChainParams p;
   memset(&p, 0, sizeof(p));
@@ -182,9 +182,9 @@ extern "C" int lmoe_chain_applies(int L, int F) { return lmoe::chain_applies(L, 
 // Development aid: copies CTA 0's event trace of the last chain launch to the host and clears it.
 extern "C" int lmoe_chain_trace_read(long long* host, int* counts) {
   cudaDeviceSynchronize();
-  cudaMemcpyFromSymbol(host, lmoe::g_chain_trace, sizeof(long long) * 3 * lmoe::kTraceSlots * 2);
-  cudaMemcpyFromSymbol(counts, lmoe::g_chain_trace_n, sizeof(int) * 3);
-  int zero[3] = {0, 0, 0};
+  cudaMemcpyFromSymbol(host, lmoe::g_chain_trace, sizeof(long long) * lmoe::kTraceRoles * lmoe::kTraceSlots * 2);
+  cudaMemcpyFromSymbol(counts, lmoe::g_chain_trace_n, sizeof(int) * lmoe::kTraceRoles);
+  int zero[lmoe::kTraceRoles] = {};
   cudaMemcpyToSymbol(lmoe::g_chain_trace_n, zero, sizeof(zero));
   return 0;
 }

@@ -59,21 +59,23 @@ struct alignas(64) ChainParams {
 // Development aid (compiled only with -DLMOE_CHAIN_TRACE): CTA 0 records (tag, globaltimer) pairs per role.
 #ifdef LMOE_CHAIN_TRACE
 constexpr int kTraceSlots = 4096;
-__device__ long long g_chain_trace[3][kTraceSlots][2];
-__device__ int g_chain_trace_n[3];
-__device__ __forceinline__ void chain_trace(int role, int tag) {
-  if (blockIdx.x != 0) return;
-  const int i = g_chain_trace_n[role];
-  if (i >= kTraceSlots) return;
+constexpr int kTraceRoles = 5;
+__device__ long long g_chain_trace[kTraceRoles][kTraceSlots][2];
+__device__ int g_chain_trace_n[kTraceRoles];
+// The slot counter lives in a register of the (single) thread that records for a role: no load on the recording path.
+__device__ __forceinline__ void chain_trace(int role, int tag, int& i) {
+  if (blockIdx.x != 0 || i >= kTraceSlots) return;
   long long t;
   asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
   g_chain_trace[role][i][0] = tag;
   g_chain_trace[role][i][1] = t;
-  g_chain_trace_n[role] = i + 1;
+  g_chain_trace_n[role] = ++i;
 }
-#define CHAIN_TRACE(role, tag) chain_trace(role, tag)
+#define CHAIN_TRACE(role, tag) chain_trace(role, tag, trace_i)
+#define CHAIN_TRACE_DECL int trace_i = 0;
 #else
 #define CHAIN_TRACE(role, tag)
+#define CHAIN_TRACE_DECL
 #endif
 
 template <int MODE>
@@ -148,6 +150,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1) chain_kernel(const __grid_con
   constexpr uint32_t TMEM_COLS = 512;
   constexpr uint32_t ACC2_COL = 256;
 
+  CHAIN_TRACE_DECL
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint8_t* const a1 = smem;                              // [KB1][128 x 64] K-major, 128-byte swizzle

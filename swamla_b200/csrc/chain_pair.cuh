@@ -43,39 +43,6 @@ struct alignas(64) ChainPairParams {
   int* status;
 };
 
-__device__ __forceinline__ bool mbar_try_wait_cluster(uint64_t* bar, uint32_t parity) {
-  uint32_t ok;
-  asm volatile(
-      "{\n"
-      ".reg .pred p;\n"
-      "mbarrier.try_wait.parity.acquire.cluster.shared::cta.b64 p, [%1], %2;\n"
-      "selp.u32 %0, 1, 0, p;\n"
-      "}\n"
-      : "=r"(ok)
-      : "r"(smem_u32(bar)), "r"(parity)
-      : "memory");
-  return ok != 0;
-}
-// Bounded wait with cluster-scope acquire: for barriers that threads of the OTHER CTA arrive on after writing memory
-// this CTA's tensor-core operations will read.
-__device__ __forceinline__ bool mbar_wait_cluster(uint64_t* bar, uint32_t parity, volatile int* abort_flag, int* status,
-                                                  int code) {
-  if (mbar_try_wait_cluster(bar, parity)) return true;
-  const long long t0 = clock64();
-  uint32_t spins = 0;
-  while (!mbar_try_wait_cluster(bar, parity)) {
-    if ((++spins & 63u) == 0u) {
-      if (*abort_flag) return false;
-      if (clock64() - t0 > kWaitBudgetCycles) {
-        *abort_flag = 1;
-        if (status) atomicCAS(status, 0, code);
-        return false;
-      }
-    }
-  }
-  return true;
-}
-
 constexpr int kChainPairThreads = 384;  // 12 warps: two producers, two MMA issuers, eight epilogue warps
 
 // Shared memory of one CTA of a pair.  Two weight rings, one per GEMM, each fed by its own producer thread and drained
@@ -84,10 +51,13 @@ constexpr int kChainPairThreads = 384;  // 12 warps: two producers, two MMA issu
 template <int MODE>
 struct ChainPairSmem {
   static constexpr bool kFwd = (MODE == CHAIN_FWD);
-  static constexpr int kA2Bytes = kFwd ? 16384 : 32768;   // hidden chunk | d_gate + d_up chunk (backward: also the
-                                                          // staging slabs of the tile epilogue, which runs when both are free)
-  static constexpr int kAuxBytes = kFwd ? 32768 : 65536;  // FWD: gate/up slabs on their way to h1; BWD: saved gate/up, two chunks
-  static constexpr int kOutBytes = kFwd ? 16384 : 0;      // tile-epilogue slabs (backward uses the A2 buffer)
+  // FWD: two hidden chunks (one per epilogue group); BWD: d_gate + d_up chunk (also the staging slabs of the tile
+  // epilogue, which runs when both are free)
+  static constexpr int kA2Bytes = 32768;
+  // FWD: per epilogue group a gate slab and an up slab on their way to h1 (the tile epilogue's slab reuses the first);
+  // BWD: saved gate/up, two chunks
+  static constexpr int kAuxBytes = kFwd ? 32768 : 65536;
+  static constexpr int kOutBytes = 0;
   static constexpr int kR1Stages = kFwd ? 4 : 2, kR1Bytes = 16384;         // first GEMM: two chunks ahead
   static constexpr int kR2Stages = kFwd ? 2 : 4, kR2Bytes = kFwd ? 16384 : 8192;  // second GEMM: two chunks | one chunk
   static constexpr int kBarrierBytes = 2048;
@@ -105,12 +75,13 @@ chain_pair_kernel(const __grid_constant__ ChainPairParams p) {
   constexpr uint32_t TMEM_COLS = 512;
   constexpr uint32_t ACC2_COL = 256;
 
+  CHAIN_TRACE_DECL
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint8_t* const a1 = smem;
   uint8_t* const a2 = a1 + kChainA1Bytes;
   uint8_t* const aux = a2 + S::kA2Bytes;
-  uint8_t* const outb = FWD ? aux + S::kAuxBytes : a2;
+  uint8_t* const outb = a2;  // backward: tile-epilogue slabs
   uint8_t* const ring1 = aux + S::kAuxBytes + S::kOutBytes;
   uint8_t* const ring2 = ring1 + R1 * S::kR1Bytes;
   uint64_t* const bars = reinterpret_cast<uint64_t*>(ring2 + R2 * S::kR2Bytes);
@@ -122,9 +93,9 @@ chain_pair_kernel(const __grid_constant__ ChainPairParams p) {
   uint64_t* const a1_empty = a1_full + 4;                // [4] local
   uint64_t* const acc1_full = a1_empty + 4;              // [2] local
   uint64_t* const acc1_empty = acc1_full + 2;            // [2] rank 0's: 16 arrivals
-  uint64_t* const a2_full = acc1_empty + 2;              // [1] rank 0's: 2 arrivals
-  uint64_t* const a2_empty = a2_full + 1;                // [1] local
-  uint64_t* const acc2_full = a2_empty + 1;              // [1] local
+  uint64_t* const a2_full = acc1_empty + 2;              // [2] rank 0's: 2 arrivals (forward: one per epilogue group)
+  uint64_t* const a2_empty = a2_full + 2;                // [2] local
+  uint64_t* const acc2_full = a2_empty + 2;              // [1] local
   uint64_t* const acc2_empty = acc2_full + 1;            // [1] rank 0's: 16 arrivals
   uint64_t* const gu_full = acc2_empty + 1;              // [2] local (BWD)
   uint32_t* const tmem_slot = reinterpret_cast<uint32_t*>(gu_full + 2);
@@ -150,11 +121,11 @@ chain_pair_kernel(const __grid_constant__ ChainPairParams p) {
     }
     for (int i = 0; i < 2; ++i) {
       mbar_init(&acc1_full[i], 1);
-      mbar_init(&acc1_empty[i], 16);
+      mbar_init(&acc1_empty[i], FWD ? 8 : 16);  // forward: one epilogue group (four warps) per CTA reads a buffer
       mbar_init(&gu_full[i], 1);
+      mbar_init(&a2_full[i], 2);
+      mbar_init(&a2_empty[i], 1);
     }
-    mbar_init(a2_full, 2);
-    mbar_init(a2_empty, 1);
     mbar_init(acc2_full, 1);
     mbar_init(acc2_empty, 16);
     *abort_flag = 0;
@@ -272,35 +243,19 @@ chain_pair_kernel(const __grid_constant__ ChainPairParams p) {
   };
 
   if (warp == 0) {
-    // =========== producer 1 (both CTAs): the tile's A operand and the first GEMM's weight slices ===========
+    // =========== producer 1 (both CTAs): the first GEMM's weight slices ===========
+    // (the tile's A operand comes from producer 2: this thread never blocks on the A buffer, so the weight ring stays
+    //  two chunks ahead across tile boundaries)
     if (lane == 0) {
       Ring rg{ring1, r1_full, r1_empty, R1, S::kR1Bytes};
       bool ok = true;
-      int tiles_loaded = 0;
       for (Cur k = locate(cluster_id, 0); ok && valid(k); k = next(k)) {
-        const int m0 = k.tile * kBM;
-        if (k.c == 0) {  // this CTA's A operand, k-block by k-block as the previous tile's last chunk releases them
-          for (int kb = 0; kb < KB1; ++kb) {
-            if (!mbar_wait(&a1_empty[kb], (tiles_loaded & 1) ^ 1, abort_flag, p.status, kStatusProducerTimeout)) {
-              ok = false;
-              break;
-            }
-            if (rank == 0) mbar_expect_tx(&a1_full[kb], 2 * 16384);
-            tma_load_2d_pair(a1 + kb * 16384, &p.tmA, mapa_shared(smem_u32(&a1_full[kb]), 0), kb * 64, m0);
-          }
-          if (!ok) break;
-          ++tiles_loaded;
-          if (p.prefetch_a) {  // the A operand of this CTA's next tile: into L2 a whole tile period ahead
-            const Cur nx = locate(k.pid + n_clusters, 0);
-            if (valid(nx))
-              for (int kb = 0; kb < KB1; ++kb) tma_prefetch_2d(&p.tmA, kb * 64, nx.tile * kBM);
-          }
-        }
         // FWD: this CTA's half of the chunk's B: rank 0 the 64 gate columns, rank 1 the 64 up columns of Wgu[e], two
         //      k-blocks (8 KB each) per stage.
         // BWD: rows [c*64 + rank*32, +32) of Wd[e] (its half of the chunk's d_hidden columns), 4 KB per k-block, all
         //      k-blocks of the chunk in one stage.
         const int n_stage = FWD ? (KB1 + 1) / 2 : 1;
+        CHAIN_TRACE(4, 30);
         for (int s = 0; s < n_stage && ok; ++s) {
           if (!mbar_wait(&rg.empty[rg.stage], rg.phase ^ 1, abort_flag, p.status, kStatusProducerTimeout)) {
             ok = false;
@@ -328,7 +283,40 @@ chain_pair_kernel(const __grid_constant__ ChainPairParams p) {
       Ring rg{ring2, r2_full, r2_empty, R2, S::kR2Bytes};
       bool ok = true;
       const int half = L / 2;  // this CTA's share of the second GEMM's N extent
+      int tiles_loaded = 0;
+      // this CTA's A operand of tile `t`, k-block by k-block as the previous tile's last chunk releases the buffers
+      auto load_a = [&](const Cur& t) {
+        for (int kb = 0; kb < KB1; ++kb) {
+          if (!mbar_wait(&a1_empty[kb], (tiles_loaded & 1) ^ 1, abort_flag, p.status, kStatusProducerTimeout)) {
+            ok = false;
+            return;
+          }
+          if (rank == 0) mbar_expect_tx(&a1_full[kb], 2 * 16384);
+          tma_load_2d_pair(a1 + kb * 16384, &p.tmA, mapa_shared(smem_u32(&a1_full[kb]), 0), kb * 64, t.tile * kBM);
+        }
+        ++tiles_loaded;
+      };
+      // The next tile's A operand is requested in front of the weights of chunk NC - 2: the buffers come free when the
+      // first GEMM of the tile's LAST chunk completes, which is about when the epilogue warps start on chunk NC - 3, well
+      // before the second GEMM of chunk NC - 2 needs its weights.
+      const int a_slot = NC >= 2 ? NC - 2 : 0;
+      {
+        const Cur k0 = locate(cluster_id, 0);
+        if (valid(k0)) load_a(k0);
+      }
       for (Cur k = locate(cluster_id, 0); ok && valid(k); k = next(k)) {
+        if (k.c == a_slot) {
+          const Cur nx = locate(k.pid + n_clusters, 0);
+          if (valid(nx)) {
+            load_a(nx);
+            if (!ok) break;
+            if (p.prefetch_a) {  // and the one after it into L2
+              const Cur nx2 = locate(nx.pid + n_clusters, 0);
+              if (valid(nx2))
+                for (int kb = 0; kb < KB1; ++kb) tma_prefetch_2d(&p.tmA, kb * 64, nx2.tile * kBM);
+            }
+          }
+        }
         // FWD: rows [c*64, +64) of Wd[e], columns [rank*L/2, +L/2): L/128 MN-major chunks of 8 KB, one stage.
         // BWD: per part (gate columns, up columns of Wgu[e]) and per 128-column slice s of d_x: rows
         //      [s*128 + rank*64, +64) x k columns [part*F + c*64, +64), one 8 KB stage each.
@@ -362,7 +350,7 @@ chain_pair_kernel(const __grid_constant__ ChainPairParams p) {
       int tiles_g1 = 0, gi = 0;
       for (Cur k = locate(cluster_id, 0); ok && valid(k); k = next(k), ++gi) {
         const int b = gi & 1;
-        if (!mbar_wait_cluster(&acc1_empty[b], ((gi >> 1) & 1) ^ 1, abort_flag, p.status, kStatusMmaTimeout)) break;
+        if (!mbar_wait(&acc1_empty[b], ((gi >> 1) & 1) ^ 1, abort_flag, p.status, kStatusMmaTimeout)) break;
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + b * 128;
         const uint32_t a_par = tiles_g1 & 1;
@@ -420,12 +408,14 @@ chain_pair_kernel(const __grid_constant__ ChainPairParams p) {
       int tiles_g2 = 0, gi = 0;
       for (Cur k = locate(cluster_id, 0); ok && valid(k); k = next(k), ++gi) {
         if (k.c == 0) {
-          if (!mbar_wait_cluster(acc2_empty, (tiles_g2 & 1) ^ 1, abort_flag, p.status, kStatusMmaTimeout)) break;
+          if (!mbar_wait(acc2_empty, (tiles_g2 & 1) ^ 1, abort_flag, p.status, kStatusMmaTimeout)) break;
           ++tiles_g2;
         }
-        // both CTAs' epilogue warps have written their A2 buffers (cluster-scope acquire: one of them is remote)
+        // both CTAs' epilogue warps have written their A2 buffers and handed them to the async proxy
         CHAIN_TRACE(0, 3);
-        if (!mbar_wait_cluster(a2_full, gi & 1, abort_flag, p.status, kStatusMmaTimeout)) break;
+        const int b2 = FWD ? (gi & 1) : 0;                          // forward: the A2 buffer of the chunk's epilogue group
+        const uint32_t par2 = FWD ? ((gi >> 1) & 1) : (gi & 1);
+        if (!mbar_wait(&a2_full[b2], par2, abort_flag, p.status, kStatusMmaTimeout)) break;
         tc_fence_after();
         CHAIN_TRACE(0, 4);
         const int n_stage = FWD ? 1 : 2 * (L / 128);
@@ -440,7 +430,7 @@ chain_pair_kernel(const __grid_constant__ ChainPairParams p) {
             const uint32_t idesc = make_idesc(1u, 1u, false, true, 256, static_cast<uint32_t>(L));
 #pragma unroll
             for (int kk = 0; kk < 4; ++kk) {
-              const uint64_t da = make_smem_desc_sw128(a2_addr + kk * 32, 0, 1024);
+              const uint64_t da = make_smem_desc_sw128(a2_addr + b2 * 16384 + kk * 32, 0, 1024);
               const uint64_t db = make_smem_desc_sw128(sb + kk * 2048, 8192, 1024);
               umma_f16_pair(tmem_base + ACC2_COL, da, db, idesc, (k.c > 0 || kk > 0) ? 1u : 0u);
             }
@@ -459,12 +449,151 @@ chain_pair_kernel(const __grid_constant__ ChainPairParams p) {
         }
         if (!ok) break;
         CHAIN_TRACE(0, 5);
-        umma_commit_pair(a2_empty, 0x3);                       // the A2 buffers may be rewritten once these MMAs have read them
+        umma_commit_pair(&a2_empty[b2], 0x3);                  // the A2 buffers may be rewritten once these MMAs have read them
         if (k.c == NC - 1) umma_commit_pair(acc2_full, 0x3);   // the tile's result is complete in both CTAs
       }
     }
+  } else if constexpr (FWD) {
+    // ================= epilogue, forward (both CTAs, own 128 rows): two groups on ALTERNATING chunks =================
+    // Group s (four warps, one per tensor-memory lane quadrant) owns the chunks whose running index has parity s, the
+    // first GEMM's accumulator s and the hidden buffer s: while one group turns its chunk into the second GEMM's
+    // operand, the other is one chunk ahead or behind, the second GEMM of either never waits for a CTA-wide barrier, and
+    // a buffer is rewritten two chunks after the MMAs that read it were issued.  A chunk is done in two 32-column
+    // halves through one pair of 8 KB slabs (gate, up on their way to h1).  The tile's result (eight 32-column slabs at
+    // L = 256) is drained half by each group: the group of the last chunk right after it, the other after its first
+    // chunk of the NEXT tile, so that neither idles while the last chunk's second GEMM completes.
+    const int q = warp & 3;
+    const int gs = (warp - 2) >> 2;
+    const int bar_id = 1 + gs;
+    const int r = q * 32 + lane;
+    const bool issuer = (((warp - 2) & 3) == 0) && lane == 0;
+    const uint32_t lane_addr = tmem_base + (static_cast<uint32_t>(q * 32) << 16);
+    uint8_t* const slabs = aux + gs * 16384;
+    uint8_t* const a2g = a2 + gs * 16384;
+    const uint32_t acc1_empty0 = mapa_shared(smem_u32(&acc1_empty[gs]), 0);
+    const uint32_t acc2_empty0 = mapa_shared(smem_u32(acc2_empty), 0);
+    const uint32_t a2_full0 = mapa_shared(smem_u32(&a2_full[gs]), 0);
+    const int nsl = L / kSlabCols;
+    int tiles_done = 0;
+    bool ok = true;
+    // the second GEMM's accumulator of tile `t` -> bf16 -> y_sorted: slabs gs, gs + 2, ...
+    auto tile_epilogue = [&](const Cur& t) {
+      if (issuer) CHAIN_TRACE(2 + gs, 20);
+      if (!mbar_wait(acc2_full, tiles_done & 1, abort_flag, p.status, kStatusEpilogueTimeout)) ok = false;
+      if (issuer) CHAIN_TRACE(2 + gs, 21);
+      tc_fence_after();
+      ok = epi_bar_all(bar_id, ok);
+      if (!ok) return;
+      const int m0 = t.tile * kBM;
+#pragma unroll 1
+      for (int c = gs; c < nsl; c += 2) {
+        float v[32];
+        tmem_ld32(lane_addr + ACC2_COL + c * 32, v);
+        tmem_ld_wait();
+        if (c + 2 >= nsl) {  // this warp's last slab is in registers: hand the accumulator back
+          tc_fence_before();
+          __syncwarp();
+          if (lane == 0) mbar_arrive_cluster(acc2_empty0);
+        }
+        if (!t.live) continue;  // uniform over the CTA: a tile-less second CTA only drains its accumulator
+        uint32_t pk[16];
+#pragma unroll
+        for (int j = 0; j < 16; ++j) pk[j] = pack_bf16x2(v[2 * j], v[2 * j + 1]);
+        if (issuer) tma_store_wait_read_all();
+        epi_bar_sync(bar_id);
+        stage_row_bf16(slabs, r, pk);
+        fence_proxy_async_smem();
+        epi_bar_sync(bar_id);
+        if (issuer) {
+          tma_store_3d(&p.tmOut, slabs, c * kSlabCols, m0, 0);
+          tma_store_commit();
+        }
+      }
+      ++tiles_done;
+      if (issuer) CHAIN_TRACE(2 + gs, 22);
+    };
+    Cur cur = locate(cluster_id, 0);
+    if (gs == 1 && valid(cur)) cur = next(cur);
+    Cur pend = cur;
+    bool pending = false;  // group 0: a tile whose result slabs are still to be drained
+    for (int n = 0; valid(cur); ++n) {
+      const int m0 = cur.tile * kBM;
+      if (issuer) CHAIN_TRACE(2 + gs, 10);
+      if (!mbar_wait(&acc1_full[gs], n & 1, abort_flag, p.status, kStatusEpilogueTimeout)) ok = false;
+      if (issuer) CHAIN_TRACE(2 + gs, 11);
+      tc_fence_after();
+#pragma unroll 1
+      for (int h = 0; h < 2; ++h) {
+        uint32_t pa[16], pb[16], pc[16];
+        if (ok) {
+          float v[32], u[32];
+          tmem_ld32(lane_addr + gs * 128 + h * 32, v);        // gate
+          tmem_ld32(lane_addr + gs * 128 + 64 + h * 32, u);   // up
+          tmem_ld_wait();
+          if (issuer) CHAIN_TRACE(2 + gs, 18);
+          if (h == 1) {
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive_cluster(acc1_empty0);
+          }
+#pragma unroll
+          for (int j = 0; j < 16; ++j) {
+            // gate/up are saved as bf16; hidden is formed from the rounded values
+            pa[j] = pack_bf16x2(v[2 * j], v[2 * j + 1]);
+            pb[j] = pack_bf16x2(u[2 * j], u[2 * j + 1]);
+            const float g0 = __uint_as_float(pa[j] << 16), g1 = __uint_as_float(pa[j] & 0xffff0000u);
+            const float u0 = __uint_as_float(pb[j] << 16), u1 = __uint_as_float(pb[j] & 0xffff0000u);
+            pc[j] = pack_bf16x2(silu_f(g0) * u0, silu_f(g1) * u1);
+          }
+        }
+        // the hidden buffer: the second GEMM of this group's previous chunk has read it; the slabs (and, first half, the
+        // hidden buffer): the stores issued from them have read their source
+        if (issuer) CHAIN_TRACE(2 + gs, 12);
+        if (h == 0 && ok && !mbar_wait(&a2_empty[gs], (n & 1) ^ 1, abort_flag, p.status, kStatusEpilogueTimeout)) ok = false;
+        if (issuer) CHAIN_TRACE(2 + gs, 13);
+        if (issuer) tma_store_wait_read_all();
+        if (issuer) CHAIN_TRACE(2 + gs, 14);
+        ok = epi_bar_all(bar_id, ok);
+        if (!ok) break;
+        stage_row_bf16(slabs, r, pa);
+        stage_row_bf16(slabs + 8192, r, pb);
+        a2_write_half(a2g, r, h, pc);
+        fence_proxy_async_smem();
+        if (issuer) CHAIN_TRACE(2 + gs, 15);
+        epi_bar_sync(bar_id);
+        if (issuer) {
+          if (h == 1) {
+            CHAIN_TRACE(2 + gs, 16);
+            mbar_arrive_cluster(a2_full0);  // the MMAs issued by rank 0 read this CTA's buffer
+          }
+          if (cur.live) {
+            tma_store_3d(&p.tmAux, slabs, cur.c * 64 + h * 32, m0, 0);             // gate -> h1
+            tma_store_3d(&p.tmAux, slabs + 8192, F + cur.c * 64 + h * 32, m0, 0);  // up   -> h1
+            if (h == 1) tma_store_2d(&p.tmMid, a2g, cur.c * 64, m0);               // hidden
+          }
+          tma_store_commit();
+        }
+      }
+      if (!ok) break;
+      if (cur.c == 0 && pending) {
+        tile_epilogue(pend);
+        pending = false;
+        if (!ok) break;
+      }
+      if (cur.c == NC - 1) {
+        tile_epilogue(cur);
+        if (!ok) break;
+      } else if (cur.c == NC - 2) {
+        pend = cur;
+        pending = true;
+      }
+      cur = next(cur);
+      if (valid(cur)) cur = next(cur);
+    }
+    if (ok && pending) tile_epilogue(pend);
+    if (issuer) tma_store_wait0();
   } else {
-    // ============================= epilogue (both CTAs, own 128 rows) =============================
+    // ============================= epilogue, backward (both CTAs, own 128 rows) =============================
     const int q = warp & 3;
     const int group = (warp - 2) >> 2;
     const int bar_id = 1 + group;
@@ -579,7 +708,7 @@ chain_pair_kernel(const __grid_constant__ ChainPairParams p) {
       epi_all_sync();
       if (chunk_issuer) {
         CHAIN_TRACE(2, 16);
-        mbar_arrive_cluster(a2_full0);  // release at cluster scope: the MMAs issued by rank 0 read this CTA's A2 buffer
+        mbar_arrive_cluster(a2_full0);  // the MMAs issued by rank 0 read this CTA's A2 buffer
         if (cur.live) {
           if (FWD) {
             for (int gr = 0; gr < 2; ++gr) {
