@@ -2,6 +2,7 @@
 #include <cuda.h>
 #include <cuda_runtime.h>
 
+#include <cstdlib>
 #include <cstring>
 #include <mutex>
 #include <utility>
@@ -473,8 +474,8 @@ int launch_gemm(const GemmCall& c) {
       rc = encode_out(&p.tmC2, c.C2, false, c.N, rows_total, 1, c.ldc2, 0);
       if (rc) return rc;
     }
-    if (swiglu_bwd) {  // the saved gate / up as a slab source; rows past the end read as zeros
-      rc = encode_out(&p.tmAux, const_cast<void*>(c.aux), false, 2ll * c.N, rows_total, 1, c.ld_aux, 0, true);
+    if (swiglu_bwd) {  // the saved gate / up as a source of 128-row x 64-column boxes; rows past the end read as zeros
+      rc = encode_2d(&p.tmAux, c.aux, 2ll * c.N, rows_total, c.ld_aux, kBM, 2);
       if (rc) return rc;
     }
   }

@@ -70,7 +70,7 @@ struct alignas(64) GemmParams {
   const float* deq_b;
   const void* aux;         // EPI_SWIGLU_BWD: h1 [rows, 2*N] bf16 (gate | up), row stride ld_aux elements
   long long ld_aux;
-  CUtensorMap tmAux;       // EPI_SWIGLU_BWD: the same tensor as 128 x 32 slabs (64-byte swizzle), staged by TMA
+  CUtensorMap tmAux;       // EPI_SWIGLU_BWD: the same tensor as 128-row boxes of 64 columns (128-byte swizzle), staged by TMA
   // Gathered A operand (bf16, one K segment): row i of the padded routed layout is row
   // a_rows[i * a_rows_stride] / a_rows_div of the tensor behind tmA[0] (negative entry: a_zero_row, a row of zeros).  GRP_M with K-major A gathers the tile's M rows,
   // GRP_K (MN-major A) gathers the contraction rows.  NULL: A is read in place.
@@ -91,9 +91,10 @@ struct GemmSmem {
   static constexpr int kStreams = (EPI == EPI_SWIGLU) ? 3 : (EPI == EPI_SWIGLU_BWD ? 2 : 1);  // gate, up, hidden
   // staging buffers per epilogue group: two for the plain bf16 epilogue (its slabs are cheap to produce, so the
   // read latency of the previous TMA store would otherwise be exposed on every slab), one for the others
-  static constexpr int kBufsPerGroup = (EPI == EPI_BF16) ? 2 : 1;
+  static constexpr int kBufsPerGroup =
+      (EPI == EPI_BF16 || EPI == EPI_SWIGLU_BWD || (EPI == EPI_SWIGLU && BN == 128)) ? 2 : 1;
   static constexpr int kStagingBytes = 2 * kBufsPerGroup * kStreams * kSlabBytes;
-  // EPI_SWIGLU_BWD: the saved gate / up slabs of the next two slabs of each epilogue group, staged by TMA
+  // EPI_SWIGLU_BWD: per epilogue group the saved gate / up of its 64 columns of the next tile (two 16 KB boxes)
   // (2 groups x 2 buffers x (gate 8 KB + up 8 KB))
   static constexpr int kAuxBytes = (EPI == EPI_SWIGLU_BWD) ? 65536 : 0;
   static constexpr int kBarrierBytes = 256;
@@ -140,13 +141,6 @@ __device__ __forceinline__ void tma_store_3d(const CUtensorMap* map, const void*
                "r"(smem_u32(smem_src)), "r"(c0), "r"(c1), "r"(c2)
                : "memory");
 }
-// 3-D tiled load (an output-style map used as a source).
-__device__ __forceinline__ void tma_load_3d_g(void* smem_dst, const CUtensorMap* map, uint64_t* bar, int c0, int c1, int c2) {
-  asm volatile(
-      "cp.async.bulk.tensor.3d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];"
-      ::"r"(smem_u32(smem_dst)), "l"(reinterpret_cast<uint64_t>(map)), "r"(smem_u32(bar)), "r"(c0), "r"(c1), "r"(c2)
-      : "memory");
-}
 __device__ __forceinline__ void tma_store_wait_read_all() { asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory"); }
 __device__ __forceinline__ void tma_store_wait_read_1() { asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory"); }
 
@@ -191,7 +185,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_kernel(const __grid_cons
   uint64_t* bar_empty = bar_full + STAGES;
   uint64_t* bar_tfull = bar_empty + STAGES;
   uint64_t* bar_tempty = bar_tfull + 2;
-  uint64_t* bar_aux = bar_tempty + 2;                    // [2 groups][2 buffers]
+  uint64_t* bar_aux = bar_tempty + 2;                    // [4]: one per epilogue group in use
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bar_aux + 4);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
@@ -450,39 +444,36 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_kernel(const __grid_cons
     int acc = 0;
     uint32_t acc_phase = 0;
     bool ok = true;
-    // EPI_SWIGLU_BWD: this group's slabs form one sequence over all its tiles (slab c of a tile, c = group, group + 2,
-    // ...); the group's issuer stages the saved gate / up of the slab TWO places ahead in that sequence by TMA, so the
-    // rows are in shared memory when the accumulator is ready.  Buffer = place in the sequence & 1.
+    // EPI_SWIGLU_BWD (BN = 128): group g owns the tile's columns [64 g, 64 g + 64), i.e. slabs 2g and 2g + 1, and the
+    // saved gate / up of those columns arrive as TWO 128-row boxes of 64 columns (128-byte rows, 128-byte swizzle: a
+    // TMA load costs the SM one request slot per box row whatever the row's width, so 64-column boxes halve what the
+    // 32-column slabs cost).  One 32 KB buffer per group: every thread takes its two rows (gate, up: 128 bytes each)
+    // into registers at the start of the tile, which frees the buffer for the group's NEXT tile a whole tile's
+    // epilogue ahead of its use.
+    constexpr bool kAdj = (EPI == EPI_SWIGLU_BWD);
     const int n_per_tile_e = (EPI == EPI_SWIGLU) ? BN / 2 : BN;
     auto slabs_of = [&](const Tile& tt) {
       const int n0_ = tt.nt * n_per_tile_e;
       int sl = (p.N - n0_ + kSlabCols - 1) / kSlabCols;
       return sl > n_per_tile_e / kSlabCols ? n_per_tile_e / kSlabCols : sl;
     };
-    int aux_seq = 0;        // slabs this group has consumed
-    int pre_id = blockIdx.x, pre_c = group, pre_seq = 0;   // next slab to stage (issuer only)
-    auto stage_next = [&]() {   // issues the TMA loads of the next unstaged slab of the sequence, if there is one
+    int aux_seq = 0;             // tiles whose rows this group has taken from its buffer
+    int pre_id = blockIdx.x;     // next tile to stage (issuer only)
+    auto stage_next = [&]() {    // issues the loads of the group's next tile that has columns for it, if there is one
       while (pre_id < total_tiles) {
         const Tile tt = decode(pre_id);
-        if (pre_c < slabs_of(tt)) {
-          const int b = pre_seq & 1;
-          uint8_t* dst = aux_stage + (group * 2 + b) * 16384;
-          const int col = tt.nt * BN + pre_c * kSlabCols;
-          mbar_expect_tx(&bar_aux[group * 2 + b], 16384);
-          tma_load_3d_g(dst, &p.tmAux, &bar_aux[group * 2 + b], col, tt.m0, 0);
-          tma_load_3d_g(dst + 8192, &p.tmAux, &bar_aux[group * 2 + b], p.N + col, tt.m0, 0);
-          ++pre_seq;
-          pre_c += 2;
+        pre_id += gridDim.x;
+        if (2 * group < slabs_of(tt)) {
+          uint8_t* dst = aux_stage + group * 32768;
+          const int col = tt.nt * BN + group * 64;
+          mbar_expect_tx(&bar_aux[group], 32768);
+          tma_load_2d(dst, &p.tmAux, &bar_aux[group], col, tt.m0);                 // gate; rows / columns beyond the
+          tma_load_2d(dst + 16384, &p.tmAux, &bar_aux[group], p.N + col, tt.m0);   // up      tensor arrive as zeros
           return;
         }
-        pre_id += gridDim.x;
-        pre_c = group;
       }
     };
-    if (EPI == EPI_SWIGLU_BWD && issuer) {
-      stage_next();
-      stage_next();
-    }
+    if (kAdj && issuer) stage_next();
     for (int id = blockIdx.x; id < total_tiles && ok; id += gridDim.x) {
       const Tile t = decode(id);
       const int nk = tile_kiters(t);
@@ -500,35 +491,43 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_kernel(const __grid_cons
       const int n_lim = kSwiglu ? p.half : p.N;
       int slabs = (n_lim - n0 + kSlabCols - 1) / kSlabCols;
       if (slabs > n_per_tile / kSlabCols) slabs = n_per_tile / kSlabCols;
-      // this group's slabs: group, group + 2, ...; the accumulator is released after the last one is loaded
-      const int last = ((slabs - 1 - group) >= 0) ? group + ((slabs - 1 - group) & ~1) : -1;
+      // this group's slabs: group, group + 2, ... (adjoint epilogue: 2 group, 2 group + 1); the accumulator is released
+      // after the last one is loaded
+      const int c_begin = kAdj ? 2 * group : group;
+      const int c_step = kAdj ? 1 : 2;
+      const int c_end = kAdj ? min(slabs, 2 * group + 2) : slabs;
+      const int last = (c_end > c_begin) ? c_begin + ((c_end - 1 - c_begin) / c_step) * c_step : -1;
       if (nk > 0 && last < 0) {
         tc_fence_before();
         __syncwarp();
         if (lane == 0) mbar_arrive(&bar_tempty[acc]);
       }
 
+      uint4 hg8[kAdj ? 8 : 1], hu8[kAdj ? 8 : 1];  // adjoint epilogue: saved gate / up of this row, 64 columns each
+      if (kAdj && c_end > c_begin) {
+        if (!mbar_wait(&bar_aux[group], aux_seq & 1, abort_flag, p.status, kStatusEpilogueTimeout)) ok = false;
+        const uint8_t* src = aux_stage + group * 32768 + r * 128;
+        const int sw = r & 7;
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          hg8[j] = *reinterpret_cast<const uint4*>(src + ((j ^ sw) << 4));
+          hu8[j] = *reinterpret_cast<const uint4*>(src + 16384 + ((j ^ sw) << 4));
+        }
+        ++aux_seq;
+        ok = epi_bar_all(bar_id, ok);  // every thread of the group holds its rows: the buffer is free
+        if (!ok) break;
+        if (issuer) stage_next();
+      }
 #pragma unroll 1
-      for (int c = group; c < slabs; c += 2) {
+      for (int c = c_begin; c < c_end; c += c_step) {
         float v[32], u[32];
-        uint4 hg[4], hu[4];  // EPI_SWIGLU_BWD: saved gate / up of this row, 32 columns each
-        if (EPI == EPI_SWIGLU_BWD) {
-          const int b = aux_seq & 1;
-          // staged two slabs ago by this group's issuer; rows beyond the tensor arrive as zeros (TMA bounds fill)
-          if (!mbar_wait(&bar_aux[group * 2 + b], (aux_seq >> 1) & 1, abort_flag, p.status, kStatusEpilogueTimeout))
-            ok = false;
-          const uint8_t* src = aux_stage + (group * 2 + b) * 16384;
-          const int sw = (r >> 1) & 3;
+        uint4 hg[4], hu[4];  // adjoint epilogue: the 32 columns of this slab
+        if (kAdj) {
 #pragma unroll
           for (int j = 0; j < 4; ++j) {
-            hg[j] = *reinterpret_cast<const uint4*>(src + r * 64 + ((j ^ sw) << 4));
-            hu[j] = *reinterpret_cast<const uint4*>(src + 8192 + r * 64 + ((j ^ sw) << 4));
+            hg[j] = (c == c_begin) ? hg8[j] : hg8[(kAdj ? 4 : 0) + j];   // (index 0 when the arrays are dummies)
+            hu[j] = (c == c_begin) ? hu8[j] : hu8[(kAdj ? 4 : 0) + j];
           }
-          ++aux_seq;
-          // every thread of the group must agree before the (unbounded) named barriers below
-          ok = epi_bar_all(bar_id, ok);
-          if (!ok) break;
-          if (issuer) stage_next();  // the buffer just read is free: all threads of the group hold their rows
         }
         if (nk > 0) {
           tmem_ld32(taddr + c * 32, v);
