@@ -515,16 +515,34 @@ int launch_gemm(const GemmCall& c) {
 // ---------------------------------------------------------------- split-K reduction
 // out[r, c] = sum_s ws[s, r, c] for a row range of the workspace, written as fp32 or bf16 with its own
 // leading dimension.  Fixed summation order: deterministic.
+// Up to three row/column ranges of the workspace per launch, each with its own output: the ranges of one weight-gradient
+// GEMM are reduced by one kernel.
+struct SplitKRange {
+  int row0, col0, rows, cols;
+  void* out;
+  long long out_ld;
+  long long vec_begin;  // first float4 of this range in the launch's linear index space
+};
+struct SplitKRanges {
+  SplitKRange r[3];
+  int n;
+  long long total;
+};
+
 __global__ void __launch_bounds__(256)
-splitk_reduce_kernel(const float* __restrict__ ws, int planes, long long plane_elems, int ws_ld, int row0, int col0,
-                     int rows, int cols, void* __restrict__ out, long long out_ld, int out_f32) {
-  const int vec_per_row = cols / 4;
-  const long long total = static_cast<long long>(rows) * vec_per_row;
-  for (long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; i < total;
+splitk_reduce_kernel(const float* __restrict__ ws, int planes, long long plane_elems, int ws_ld, const SplitKRanges rg,
+                     int out_f32) {
+  for (long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; i < rg.total;
        i += static_cast<long long>(gridDim.x) * blockDim.x) {
-    const int r = static_cast<int>(i / vec_per_row);
-    const int c = static_cast<int>(i - static_cast<long long>(r) * vec_per_row) * 4;
-    const float* src = ws + static_cast<long long>(row0 + r) * ws_ld + col0 + c;
+    int k = 0;
+    if (rg.n > 1 && i >= rg.r[1].vec_begin) k = 1;
+    if (rg.n > 2 && i >= rg.r[2].vec_begin) k = 2;
+    const SplitKRange& q = rg.r[k];
+    const long long li = i - q.vec_begin;
+    const int vec_per_row = q.cols / 4;
+    const int r = static_cast<int>(li / vec_per_row);
+    const int c = static_cast<int>(li - static_cast<long long>(r) * vec_per_row) * 4;
+    const float* src = ws + static_cast<long long>(q.row0 + r) * ws_ld + q.col0 + c;
     float4 acc = *reinterpret_cast<const float4*>(src);
     for (int s = 1; s < planes; ++s) {
       const float4 v = *reinterpret_cast<const float4*>(src + s * plane_elems);
@@ -534,26 +552,46 @@ splitk_reduce_kernel(const float* __restrict__ ws, int planes, long long plane_e
       acc.w += v.w;
     }
     if (out_f32) {
-      *reinterpret_cast<float4*>(static_cast<float*>(out) + r * out_ld + c) = acc;
+      *reinterpret_cast<float4*>(static_cast<float*>(q.out) + r * q.out_ld + c) = acc;
     } else {
       __nv_bfloat162 a = __floats2bfloat162_rn(acc.x, acc.y), b = __floats2bfloat162_rn(acc.z, acc.w);
-      *reinterpret_cast<uint2*>(static_cast<__nv_bfloat16*>(out) + r * out_ld + c) =
+      *reinterpret_cast<uint2*>(static_cast<__nv_bfloat16*>(q.out) + r * q.out_ld + c) =
           make_uint2(*reinterpret_cast<uint32_t*>(&a), *reinterpret_cast<uint32_t*>(&b));
     }
   }
 }
 
-int splitk_reduce(const float* ws, int planes, long long plane_elems, int ws_ld, int row0, int col0, int rows, int cols,
-                  void* out, long long out_ld, int out_f32, cudaStream_t stream) {
-  if ((cols & 3) != 0 || (col0 & 3) != 0 || (ws_ld & 3) != 0 || (out_ld & 3) != 0) return LMOE_ERR_SHAPE;
-  const long long total = static_cast<long long>(rows) * (cols / 4);
+int splitk_reduce_multi(const float* ws, int planes, long long plane_elems, int ws_ld, int n_ranges, const int* row0,
+                        const int* col0, const int* rows, const int* cols, void* const* out, const long long* out_ld,
+                        int out_f32, cudaStream_t stream) {
+  if (n_ranges < 1 || n_ranges > 3 || (ws_ld & 3) != 0) return LMOE_ERR_SHAPE;
+  SplitKRanges rg;
+  memset(&rg, 0, sizeof(rg));
+  rg.n = n_ranges;
+  long long total = 0;
+  for (int k = 0; k < n_ranges; ++k) {
+    if ((cols[k] & 3) != 0 || (col0[k] & 3) != 0 || (out_ld[k] & 3) != 0 || rows[k] <= 0 || cols[k] <= 0) return LMOE_ERR_SHAPE;
+    rg.r[k].row0 = row0[k];
+    rg.r[k].col0 = col0[k];
+    rg.r[k].rows = rows[k];
+    rg.r[k].cols = cols[k];
+    rg.r[k].out = out[k];
+    rg.r[k].out_ld = out_ld[k];
+    rg.r[k].vec_begin = total;
+    total += static_cast<long long>(rows[k]) * (cols[k] / 4);
+  }
+  rg.total = total;
   long long blocks = (total + 255) / 256;
   if (blocks > 148 * 8) blocks = 148 * 8;
-  splitk_reduce_kernel<<<static_cast<int>(blocks), 256, 0, stream>>>(ws, planes, plane_elems, ws_ld, row0, col0, rows,
-                                                                    cols, out, out_ld, out_f32);
+  splitk_reduce_kernel<<<static_cast<int>(blocks), 256, 0, stream>>>(ws, planes, plane_elems, ws_ld, rg, out_f32);
   count_launch();
   cudaError_t e = cudaGetLastError();
   return e == cudaSuccess ? 0 : static_cast<int>(e);
+}
+
+int splitk_reduce(const float* ws, int planes, long long plane_elems, int ws_ld, int row0, int col0, int rows, int cols,
+                  void* out, long long out_ld, int out_f32, cudaStream_t stream) {
+  return splitk_reduce_multi(ws, planes, plane_elems, ws_ld, 1, &row0, &col0, &rows, &cols, &out, &out_ld, out_f32, stream);
 }
 
 }  // namespace lmoe

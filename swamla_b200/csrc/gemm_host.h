@@ -82,5 +82,9 @@ bool pair_gemm_applies(int M, int N);
 // out[rows, cols] = sum over `planes` of ws[plane][row0 + r][col0 + c]; fp32 or bf16 output.
 int splitk_reduce(const float* ws, int planes, long long plane_elems, int ws_ld, int row0, int col0, int rows, int cols,
                   void* out, long long out_ld, int out_f32, cudaStream_t stream);
+// The same for up to three ranges of one workspace in ONE launch (fixed summation order per element all the same).
+int splitk_reduce_multi(const float* ws, int planes, long long plane_elems, int ws_ld, int n_ranges, const int* row0,
+                        const int* col0, const int* rows, const int* cols, void* const* out, const long long* out_ld,
+                        int out_f32, cudaStream_t stream);
 
 }  // namespace lmoe

@@ -314,8 +314,10 @@ extern "C" int lmoe_combine_out_bwd_wgrad(const lmoe_shape* s, const void* dy, c
   float* ws = static_cast<float*>(workspace);
   if (int rc = wgrad_gemm(dy, s->D, s->D, act_cat, N, N, s->T, ws, split, status, stream)) return rc;
   const long long plane = static_cast<long long>(s->D) * N;
-  if (int rc = splitk_reduce(ws, split, plane, N, 0, 0, s->D, s->L, d_w_up, s->L, grad_type == LMOE_F32, st)) return rc;
-  return splitk_reduce(ws, split, plane, N, 0, s->L, s->D, s->Fs, d_w_down_s, s->Fs, grad_type == LMOE_F32, st);
+  const int row0[2] = {0, 0}, col0[2] = {0, s->L}, rows[2] = {s->D, s->D}, cols[2] = {s->L, s->Fs};
+  void* const outs[2] = {d_w_up, d_w_down_s};
+  const long long lds[2] = {s->L, s->Fs};
+  return splitk_reduce_multi(ws, split, plane, N, 2, row0, col0, rows, cols, outs, lds, grad_type == LMOE_F32, st);
 }
 
 // Generic grouped-by-rows bf16 GEMM: out[P,N] = a[P,K] * B[e], B stacked [E,K,N] (b_mn = 1) or [E,N,K] (b_mn = 0).
@@ -556,7 +558,8 @@ extern "C" int lmoe_xside_bwd(const lmoe_shape* s, const void* dgrad_cat, const 
   if (int rc = wgrad_gemm(dgrad_cat, ld, M, x, s->D, s->D, s->T, ws, split, status, stream)) return rc;
   const long long plane = static_cast<long long>(M) * s->D;
   const int f32 = grad_type == LMOE_F32;
-  if (int rc = splitk_reduce(ws, split, plane, s->D, 0, 0, Fs2, s->D, d_w_gate_up_s, s->D, f32, st)) return rc;
-  if (int rc = splitk_reduce(ws, split, plane, s->D, Fs2, 0, s->L, s->D, d_w_down, s->D, f32, st)) return rc;
-  return splitk_reduce(ws, split, plane, s->D, Fs2 + s->L, 0, s->E, s->D, d_w_gate, s->D, f32, st);
+  const int row0[3] = {0, Fs2, Fs2 + s->L}, col0[3] = {0, 0, 0}, rows[3] = {Fs2, s->L, s->E}, cols[3] = {s->D, s->D, s->D};
+  void* const outs[3] = {d_w_gate_up_s, d_w_down, d_w_gate};
+  const long long lds[3] = {s->D, s->D, s->D};
+  return splitk_reduce_multi(ws, split, plane, s->D, 3, row0, col0, rows, cols, outs, lds, f32, st);
 }
