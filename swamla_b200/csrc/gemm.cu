@@ -107,7 +107,7 @@ static std::vector<std::pair<cudaEvent_t, cudaEvent_t>> g_prof_events;
 template <bool A_MN, bool B_MN, int BN, int EPI, int GRP, int ESZ>
 static int launch_inst(const GemmParams& p, int grid, cudaStream_t stream) {
   auto kfn = gemm_kernel<A_MN, B_MN, BN, EPI, GRP, ESZ>;
-  constexpr int smem = GemmSmem<BN, EPI>::kTotal;
+  constexpr int smem = GemmSmem<BN, EPI, GRP>::kTotal;
   static PerDeviceOnce once;  // one per template instantiation
   if (int rc = once.run([&] {
         cudaError_t e = cudaFuncSetAttribute(kfn, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);

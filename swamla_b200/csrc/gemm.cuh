@@ -81,7 +81,7 @@ struct alignas(64) GemmParams {
   int* status;
 };
 
-template <int BN, int EPI>
+template <int BN, int EPI, int GRP = 0>
 struct GemmSmem {
   static constexpr int kABytes = kBM * kBKBytes;
   static constexpr int kBBytes = BN * kBKBytes;
@@ -90,9 +90,11 @@ struct GemmSmem {
   static constexpr int kSlabBytes = (EPI == EPI_F32) ? 16384 : 8192;
   static constexpr int kStreams = (EPI == EPI_SWIGLU) ? 3 : (EPI == EPI_SWIGLU_BWD ? 2 : 1);  // gate, up, hidden
   // staging buffers per epilogue group: two for the plain bf16 epilogue (its slabs are cheap to produce, so the
-  // read latency of the previous TMA store would otherwise be exposed on every slab), one for the others
+  // read latency of the previous TMA store would otherwise be exposed on every slab) and for the adjoint epilogue of
+  // the grouped GEMM (four k-blocks per tile: three stages are enough, the second buffer gains 3 %); one for the
+  // others, whose long contractions need the shared memory for a fourth stage
   static constexpr int kBufsPerGroup =
-      (EPI == EPI_BF16 || EPI == EPI_SWIGLU_BWD || (EPI == EPI_SWIGLU && BN == 128)) ? 2 : 1;
+      (EPI == EPI_BF16 || (EPI == EPI_SWIGLU_BWD && GRP == 1) || (EPI == EPI_SWIGLU && BN == 128)) ? 2 : 1;
   static constexpr int kStagingBytes = 2 * kBufsPerGroup * kStreams * kSlabBytes;
   // EPI_SWIGLU_BWD: per epilogue group the saved gate / up of its 64 columns of the next tile (two 16 KB boxes)
   // (2 groups x 2 buffers x (gate 8 KB + up 8 KB))
@@ -165,7 +167,7 @@ __device__ __forceinline__ void stage_row_f32(uint8_t* buf, int r, const float (
 // ESZ = operand element size in bytes: 2 (bf16) or 1 (e4m3).
 template <bool A_MN, bool B_MN, int BN, int EPI, int GRP, int ESZ = 2>
 __global__ void __launch_bounds__(kGemmThreads, 1) gemm_kernel(const __grid_constant__ GemmParams p) {
-  using S = GemmSmem<BN, EPI>;
+  using S = GemmSmem<BN, EPI, GRP>;
   constexpr int STAGES = S::kStages;
   constexpr uint32_t TMEM_COLS = 2 * BN;
   static_assert(BN == 128 || BN == 256, "BN");
