@@ -26,9 +26,9 @@ import torch  # noqa: E402
 from swamla_b200 import workloads as inputs  # noqa: E402
 
 METRIC = "LatentMoE fwd+bwd tokens/s"
-# dram__bytes_read.sum + dram__bytes_write.sum of ALL tcgen05 GEMM launches of one step (ncu, one capture per kernel
-# change, scaled from the 4,096-token case to the workload's token count); None: no capture of the current kernels
-TRAFFIC_BYTES_PER_STEP = {"cfg2": 4 * 656417536, "cfg2_4k": 656417536}
+# dram__bytes_read.sum + dram__bytes_write.sum of ALL tcgen05 GEMM launches of one step (ncu, one three-counter capture
+# of an eager step at the workload's full size); a workload without a capture of the current kernels reports null
+TRAFFIC_BYTES_PER_STEP = {"cfg2": 2592600832}
 SUSTAINED_SECONDS = 2.0
 CPU_SAMPLE_TOKENS = 1024
 
