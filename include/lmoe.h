@@ -52,8 +52,8 @@ extern "C" {
 #define LMOE_E4M3 2
 
 typedef struct lmoe_shape {
-  int32_t T, D, L, E, K, F, Fs;
-  int32_t n_shared;
+  int32_t T, D, L, E, K, F, Fs;   /* Fs: width of the shared expert; n shared experts = one of n times the width */
+  int32_t n_shared;               /* informational, 1 */
 } lmoe_shape;
 
 /* Routing tables produced by lmoe_route_permute, all int32, caller-allocated.

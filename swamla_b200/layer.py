@@ -140,6 +140,20 @@ class AuxLossFreeRouter(nn.Module):
         }
 
 
+def _merged_shared_weights(shared_experts):
+    """The shared experts as ONE SwiGLU expert of width ``n * expert_dim`` (``models/moe.py:713-715`` sums their outputs:
+    ``sum_i down_i(silu(gate_i x) * up_i x)`` is a single expert whose gate/up rows and whose down columns are the
+    experts' stacked).  Returns ``(gate_up [2nFs, D] = [gate_0 .. gate_n-1 | up_0 .. up_n-1], down [D, nFs])``; with
+    one expert its own parameters, otherwise concatenations that autograd splits back onto the experts' parameters."""
+    if len(shared_experts) == 1:
+        return shared_experts[0].gate_up_proj.weight, shared_experts[0].down_proj.weight
+    gu = [e.gate_up_proj.weight for e in shared_experts]
+    fs = gu[0].shape[0] // 2
+    gate_up = torch.cat([w[:fs] for w in gu] + [w[fs:] for w in gu], dim=0)
+    down = torch.cat([e.down_proj.weight for e in shared_experts], dim=1)
+    return gate_up, down
+
+
 class LatentMoELayer(nn.Module):
     """LatentMoE feed-forward layer; see the module docstring.  ``models/moe.py:603-866``."""
 
@@ -164,8 +178,8 @@ class LatentMoELayer(nn.Module):
         z_loss_coef = getattr(config, "router_z_loss_coef", 0.001)
         if bias:
             raise NotImplementedError("config.bias=True is not supported on this path (no preset uses it)")
-        if n_shared != 1:
-            raise NotImplementedError("this path implements n_shared_experts == 1 (every preset uses 1)")
+        if n_shared < 1:
+            raise NotImplementedError("at least one shared expert is required (every preset uses 1)")
 
         self.n_experts = n_experts
         self.n_shared = n_shared
@@ -223,9 +237,9 @@ class LatentMoELayer(nn.Module):
             status_monitor.poll()        # raises if an earlier step's kernels reported a failure (no synchronisation)
         batch_size, seq_len, d_model = x.shape
         x_flat = x.reshape(-1, d_model)
-        shared = self.shared_experts[0]
+        w_gate_up_s, w_down_s = _merged_shared_weights(self.shared_experts)
         args = (x_flat, self.router.gate.weight, self.down_proj.weight, self.up_proj.weight,
-                shared.gate_up_proj.weight, shared.down_proj.weight,
+                w_gate_up_s, w_down_s,
                 self.experts.gate_up_weight, self.experts.down_weight,
                 self.router.expert_bias, self.n_activated, self.router.z_loss_coef)
         if self.ep_size > 1 and self.ep_mode == "p2p_dedup":
@@ -307,8 +321,8 @@ class MoELayer(nn.Module):
         z_loss_coef = getattr(config, "router_z_loss_coef", 0.001)
         if bias:
             raise NotImplementedError("config.bias=True is not supported on this path (no preset uses it)")
-        if n_shared != 1:
-            raise NotImplementedError("this path implements n_shared_experts == 1 (every preset uses 1)")
+        if n_shared < 1:
+            raise NotImplementedError("at least one shared expert is required (every preset uses 1)")
         if getattr(config, "ep_group", None) is not None or getattr(config, "moe_fp8", False):
             raise NotImplementedError("expert parallelism and FP8 are provided for the latent layer only")
         self.n_experts, self.n_shared, self.n_activated = n_experts, n_shared, n_activated
@@ -332,9 +346,9 @@ class MoELayer(nn.Module):
         status_monitor.poll()
         batch_size, seq_len, d_model = x.shape
         x_flat = x.reshape(-1, d_model)
-        shared = self.shared_experts[0]
-        y, z_loss, sel, counts = moe(x_flat, self.router.gate.weight, shared.gate_up_proj.weight,
-                                     shared.down_proj.weight, self.experts.gate_up_weight, self.experts.down_weight,
+        w_gate_up_s, w_down_s = _merged_shared_weights(self.shared_experts)
+        y, z_loss, sel, counts = moe(x_flat, self.router.gate.weight, w_gate_up_s,
+                                     w_down_s, self.experts.gate_up_weight, self.experts.down_weight,
                                      self.router.expert_bias, self.n_activated, self.router.z_loss_coef)
         self.aux_loss = z_loss                                            # moe.py:358
         if self.training:                                                 # moe.py:237-240

@@ -81,6 +81,9 @@ WORKLOADS: Dict[str, Workload] = {
     # small shapes for exhaustive parity (all dims are multiples of 64 so they fit the kernels)
     "tiny": Workload("tiny", n_embd=256, n_experts=4, n_activated=1, expert_dim=256, batch=2, seq=96),
     "tiny_ragged": Workload("tiny_ragged", n_embd=256, n_experts=8, n_activated=2, expert_dim=256, batch=1, seq=131),
+    # two shared experts (models/moe.py:671-674, 713-715)
+    "tiny_shared2": Workload("tiny_shared2", n_embd=256, n_experts=4, n_activated=1, n_shared_experts=2, expert_dim=256,
+                             batch=2, seq=80),
     # e4m3 GEMMs contract over multiples of 128: latent 128, routed hidden 128
     "tiny_fp8": Workload("tiny_fp8", n_embd=512, n_experts=4, n_activated=1, expert_dim=512, batch=2, seq=160, dtype="fp8"),
     # the five benchmark configurations
@@ -101,6 +104,8 @@ WORKLOADS: Dict[str, Workload] = {
     "tiny_moe": Workload("tiny_moe", n_embd=256, n_experts=8, n_activated=2, expert_dim=128, batch=2, seq=96, latent=False),
     "tiny_moe_ragged": Workload("tiny_moe_ragged", n_embd=256, n_experts=16, n_activated=3, expert_dim=128, batch=1, seq=131,
                                 latent=False),
+    "tiny_moe_shared2": Workload("tiny_moe_shared2", n_embd=256, n_experts=8, n_activated=2, n_shared_experts=2, expert_dim=128,
+                                 batch=2, seq=96, latent=False),
     "moe_1b": Workload("moe_1b", n_embd=1024, n_experts=32, n_activated=3, expert_dim=1024, batch=2, seq=2048,
                        dtype="bf16", latent=False),
 }

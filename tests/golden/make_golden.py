@@ -81,6 +81,7 @@ if __name__ == "__main__":
         sys.exit("reference tree not found; fixtures can only be regenerated where it is present")
     make("tiny", True)
     make("tiny_ragged", True)
+    make("tiny_shared2", True)       # two shared experts
     make("cfg1", False)
     make("tiny_moe", True)           # the non-latent MoELayer (models/moe.py:294-559)
     make("tiny_moe_ragged", True)

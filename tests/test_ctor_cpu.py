@@ -14,6 +14,7 @@ CONFIGS = [
     dict(n_embd=512, latent_ratio=4, latent_dim=256, n_experts=4, n_activated=1, expert_dim=512),            # explicit latent_dim
     dict(n_embd=512, latent_ratio=4, n_experts=4, n_activated=2, expert_dim=256, latent_preserve_expert_dim=True),
     dict(n_embd=256),                                                                                         # all defaults
+    dict(n_embd=256, n_experts=4, n_activated=1, n_shared_experts=2, latent_ratio=4, expert_dim=256),         # two shared experts
 ]
 
 
@@ -40,7 +41,8 @@ def test_latent_layer_ctor_matches_reference(cfg):
 
 @pytest.mark.skipif(not ref_shim.available(), reason="reference source tree not present")
 @pytest.mark.parametrize("cfg", [dict(n_embd=256, n_experts=8, n_activated=2, expert_dim=128),
-                                 dict(n_embd=1024, n_experts=32, n_activated=3, expert_dim=1024), dict(n_embd=512)])
+                                 dict(n_embd=1024, n_experts=32, n_activated=3, expert_dim=1024), dict(n_embd=512),
+                                 dict(n_embd=256, n_experts=8, n_activated=2, expert_dim=128, n_shared_experts=3)])
 def test_moe_layer_ctor_matches_reference(cfg):
     from swamla_b200.layer import MoELayer, create_moe_layer
     moe = ref_shim.load_reference_moe()
@@ -58,7 +60,7 @@ def test_ctor_refuses_what_the_kernels_do_not_cover():
     with pytest.raises(NotImplementedError):
         LatentMoELayer(SimpleNamespace(**base, bias=True))
     with pytest.raises(NotImplementedError):
-        LatentMoELayer(SimpleNamespace(**base, n_shared_experts=2))
+        LatentMoELayer(SimpleNamespace(**base, n_shared_experts=0))
     with pytest.raises(ValueError):
         LatentMoELayer(SimpleNamespace(**{**base, "n_experts": 128}))            # 512 routed experts > 256
     with pytest.raises(ValueError):

@@ -124,6 +124,37 @@ def test_layer_fwd_bwd_matches_oracle(name, aux_grad):
         assert_matches_bf16_model(f"grad {k}", named[k].grad, model_grads[k])
 
 
+@pytest.mark.parametrize("aux_grad", [0.0, 2.0])
+def test_layer_with_two_shared_experts_matches_oracle(aux_grad):
+    """``models/moe.py:671-674, 713-715``: the outputs of all shared experts are summed.  The layer runs them as one
+    expert of twice the width; output and every gradient (each shared expert's own parameters included) against the fp32
+    oracle on the rounded inputs (the oracle itself is pinned on ``tests/golden/tiny_shared2.pt``, frozen from the
+    reference module)."""
+    w = inputs.WORKLOADS["tiny_shared2"]
+    params, buffers, x, dy = inputs.make_inputs(w)
+    layer = build_layer(w, params, buffers, torch.bfloat16)
+    assert len(layer.shared_experts) == 2
+    layer.train()
+    xg = x.to("cuda:0").to(torch.bfloat16).requires_grad_(True)
+    y = layer(xg)
+    loss = (y.float() * dy.to("cuda:0").to(torch.bfloat16).float()).sum() + aux_grad * layer.get_aux_loss()
+    loss.backward()
+    layer.check_status()
+    sel = layer.router._last_selected_experts.cpu().long()
+    out, grads = oracle_on_rounded(w, params, buffers, x, dy, aux_grad, sel_override=sel)
+    assert (sel != oracle_on_rounded(w, params, buffers, x, dy, aux_grad)[0]["sel"]).any(dim=1).float().mean().item() < 0.01
+    assert_close("y", y, out["y"])
+    assert_close("grad x", xg.grad, grads["x"])
+    named = dict(layer.named_parameters())
+    for k, ref in grads.items():
+        if k == "x":
+            continue
+        assert named[k].grad is not None, k
+        assert_close(f"grad {k}", named[k].grad, ref)
+    assert {k for k in grads if k.startswith("shared_experts.1.")} == {"shared_experts.1.gate_up_proj.weight",
+                                                                        "shared_experts.1.down_proj.weight"}
+
+
 def test_layer_state_dict_and_attributes_match_reference_contract():
     fx = torch.load(golden_path("tiny"), weights_only=False)
     w = inputs.WORKLOADS["tiny"]

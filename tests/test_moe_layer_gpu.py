@@ -35,7 +35,7 @@ def near_ties_only(sel, ref_sel, scores, limit):
     return rows.float().mean().item()
 
 
-@pytest.mark.parametrize("name", ["tiny_moe", "tiny_moe_ragged", "moe_1b"])
+@pytest.mark.parametrize("name", ["tiny_moe", "tiny_moe_ragged", "tiny_moe_shared2", "moe_1b"])
 @pytest.mark.parametrize("aux_grad", [0.0, 3.0])
 def test_moe_layer_fwd_bwd_matches_oracle(name, aux_grad):
     if name == "moe_1b" and aux_grad != 0.0:

@@ -13,7 +13,7 @@ def _check_digest(t: torch.Tensor, d: dict, rtol=1e-5, atol=1e-6):
     assert abs(flat.double().pow(2).sum().sqrt().item() - d["l2"]) <= rtol * max(d["l2"], 1e-12) + atol
 
 
-@pytest.mark.parametrize("name", ["tiny", "tiny_ragged", "cfg1", "tiny_moe", "tiny_moe_ragged"])
+@pytest.mark.parametrize("name", ["tiny", "tiny_ragged", "tiny_shared2", "cfg1", "tiny_moe", "tiny_moe_ragged"])
 def test_oracle_matches_reference_fixture(name):
     fx = torch.load(golden_path(name), weights_only=False)
     w = inputs.WORKLOADS[name]
