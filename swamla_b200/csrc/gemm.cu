@@ -301,20 +301,23 @@ static int launch_gemm_pair(const GemmCall& c) {
 
 // Grouped-over-rows GEMM on CTA pairs: two tiles of the same expert share the expert's B loads (gemm_pair.cuh, GRP_M).
 // Needs the per-expert padded offsets; K-major A, one K segment, plain bf16 or SwiGLU epilogue.
-// Off unless the environment has LMOE_PAIR_GROUPED=1: with the 256-element contractions of the routed experts a tile's
-// main loop is four k-blocks long and the pair's cross-CTA hand-offs cost more than the halved weight traffic saves
-// (measured at E = 128, L = F = 256, 1,664 tiles: gate_up + down 202 us on pairs against 142 us with one CTA per tile).
-static bool pair_grouped_enabled() {
+// Off unless the environment has LMOE_PAIR_GROUPED=1 (2: only the SwiGLU GEMM, 3: only the plain ones): with the
+// 256-element contractions of the routed experts a tile's main loop is four k-blocks long, an expert with an odd tile
+// count wastes half a pair and the last round of pairs is mostly empty (measured at E = 128, L = F = 256, 1,594 tiles:
+// gate_up + down 140 us on pairs against 134 us with one CTA per tile).
+static int pair_grouped_mode() {
   static int v = -1;
   if (v < 0) {
     const char* e = getenv("LMOE_PAIR_GROUPED");
-    v = (e && e[0] == '1') ? 1 : 0;
+    v = (e && e[0] >= '1' && e[0] <= '3') ? e[0] - '0' : 0;
   }
-  return v == 1;
+  return v;
 }
 static bool pair_grouped_applies(const GemmCall& c) {
   const bool swiglu = (c.epi == EPI_SWIGLU);
-  return c.grp == GRP_M && c.pad_offsets && pair_gemm_enabled() && pair_grouped_enabled() && c.esz == 2 && !c.a_rows && !c.a_mn && c.nseg == 1 &&
+  const int mode = pair_grouped_mode();
+  if (mode == 0 || (mode == 2 && !swiglu) || (mode == 3 && swiglu)) return false;
+  return c.grp == GRP_M && c.pad_offsets && pair_gemm_enabled() && c.esz == 2 && !c.a_rows && !c.a_mn && c.nseg == 1 &&
          c.bn == 0 && (c.epi == EPI_BF16 || (swiglu && c.b_mn)) && c.groups > 0 && c.groups <= LMOE_MAX_EXPERTS &&
          c.padded_rows / kBM < (1 << 23) && (c.N % (swiglu ? 128 : 32)) == 0 && (c.Kseg[0] % 64) == 0;
 }
