@@ -375,6 +375,13 @@ int lmoe_epd_reduce_return(const void* rows, const void* meta, const void* mask,
 int lmoe_epd_sum(const void* ret, const int32_t* sel, int64_t T, int K, int E, int G, int L, int64_t stride, void* out,
                  int64_t ld_out, void* stream);
 
+/* Barrier across the G ranks of an expert-parallel group without a collective library call: peer_flags[g] points at rank
+ * g's int32 flags[G] in symmetric memory (zeroed once, before the first barrier), epoch counts the barriers (same
+ * sequence on every rank, starting at 1).  Stream-ordered like any kernel.  A rank that waits longer than about two
+ * seconds records status 202 and carries on.  Replaces the one-word all-reduce the exchange used as a barrier (the
+ * reference has no counterpart: its expert parallelism is pseudo-code, aidocs/moe.md:940-997). */
+int lmoe_ep_flag_barrier(void* const* peer_flags, int rank, int G, int epoch, int32_t* status, void* stream);
+
 /* ---- FP8 (e4m3) expert path ----
  * Per-tensor dynamic scaling, the "tensorwise" recipe named by optimization/fp8_native.py:103-110 (torchao
  * Float8Linear; the reference applies it to nn.Linear modules only, fp8_native.py:38-66,112-116, never to the

@@ -410,3 +410,37 @@ extern "C" int lmoe_epd_sum(const void* ret, const int32_t* sel, int64_t T, int 
       static_cast<uint4*>(out), ld_out / 8);
   return epd_last_err();
 }
+
+// ---------------------------------------------------------------- barrier across the ranks on flag words
+// Every rank owns int32 flags[G] in symmetric memory; word s is written by rank s only.  One warp: thread j stores this
+// step's epoch into rank j's word for this rank (system-scope release), then waits until rank j's epoch has arrived in
+// this rank's word j (system-scope acquire).  Stream order puts the exchange kernels queued before it in front of the
+// stores, and what is queued after it behind the loads.  The wait is bounded (about two seconds): on expiry the
+// kernel records status 202 and returns, so a rank that never arrives ends a step with an error instead of a hang.
+constexpr long long kEpdBarrierBudgetCycles = 4000000000LL;
+__global__ void __launch_bounds__(32) epd_flag_barrier_kernel(int* const* peer_flags, int rank, int G, int epoch,
+                                                              int* status) {
+  const int j = threadIdx.x;
+  if (j >= G) return;
+  __threadfence_system();
+  asm volatile("st.release.sys.global.s32 [%0], %1;" ::"l"(peer_flags[j] + rank), "r"(epoch) : "memory");
+  const int* mine = peer_flags[rank] + j;
+  const long long t0 = clock64();
+  for (;;) {
+    int v;
+    asm volatile("ld.acquire.sys.global.s32 %0, [%1];" : "=r"(v) : "l"(mine) : "memory");
+    if (v - epoch >= 0) break;
+    if (clock64() - t0 > kEpdBarrierBudgetCycles) {
+      if (status) atomicCAS(status, 0, 202);
+      break;
+    }
+  }
+}
+
+extern "C" int lmoe_ep_flag_barrier(void* const* peer_flags, int rank, int G, int epoch, int32_t* status, void* stream) {
+  if (!peer_flags || G < 1 || G > 32 || rank < 0 || rank >= G) return LMOE_ERR_ARG;
+  epd_flag_barrier_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>(reinterpret_cast<int* const*>(peer_flags), rank,
+                                                                           G, epoch, status);
+  return epd_last_err();
+}
+

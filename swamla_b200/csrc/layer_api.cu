@@ -100,6 +100,7 @@ extern "C" const char* lmoe_status_string(int code) {
     case kStatusEpilogueTimeout: return "device: epilogue wait timed out";
     case 201: return "device: an expert-parallel shard received more rows than its buffers hold (raise ep_capacity_factor); "
                      "the excess rows were dropped and the results of that step are wrong";
+    case 202: return "device: a rank of the expert-parallel group did not reach a barrier within two seconds";
     default: return code > 0 ? cudaGetErrorString(static_cast<cudaError_t>(code)) : "unknown error";
   }
 }

@@ -17,6 +17,7 @@ wrapper's job, as in the reference); gradients of the expert shard are complete 
 """
 from __future__ import annotations
 
+import os
 from typing import List, Tuple
 
 import torch
@@ -284,6 +285,39 @@ def latent_moe_ep(x2d, w_gate, w_down, w_up, w_gate_up_s, w_down_s, w_gate_up_lo
 # layout through peer pointers of symmetric buffers (csrc/ep_p2p.cu).  No send buffer, no all-to-all, no
 # regroup copy and no host synchronisation: sizes stay on the device, capacities are static.
 # ======================================================================================================
+class _FlagBarrier:
+    """Barrier across the ranks on flag words in symmetric memory (``lmoe_ep_flag_barrier``): one small kernel per rank
+    instead of a one-word all-reduce.  ``LMOE_EP_FLAG_BARRIER=0`` keeps the collective.  A rank that waits longer than
+    about two seconds records device status 202 in ``status`` (read by the status monitor like any other)."""
+
+    def __init__(self, group, device):
+        import torch.distributed._symmetric_memory as symm_mem
+        self.group = group
+        self.G = dist.get_world_size(group)
+        self.rank = dist.get_rank(group)
+        self.use_flags = os.environ.get("LMOE_EP_FLAG_BARRIER", "1") != "0"
+        self.sync_word = torch.zeros(1, dtype=torch.int32, device=device)
+        self.epoch = 0
+        if self.use_flags:
+            self.flags = symm_mem.empty(32, dtype=torch.int32, device=device)
+            self.flags.zero_()
+            self.handle = symm_mem.rendezvous(self.flags, group)
+            self.peer_flags = torch.tensor(list(self.handle.buffer_ptrs), dtype=torch.int64, device=device)
+            self.status = torch.zeros(1, dtype=torch.int32, device=device)
+            torch.cuda.synchronize(device)
+            dist.all_reduce(self.sync_word, group=group)     # every rank's flags are zero before anyone's first barrier
+            torch.cuda.synchronize(device)
+
+    def __call__(self, status=None):
+        if not self.use_flags:
+            dist.all_reduce(self.sync_word, group=self.group)
+            return
+        self.epoch += 1
+        st = status if status is not None else self.status
+        _cabi.call("lmoe_ep_flag_barrier", self.peer_flags.data_ptr(), self.rank, self.G, self.epoch, st.data_ptr(),
+                   _stream())
+
+
 class SymmetricBuffers:
     """Per-layer symmetric buffers and their peer pointer tables.
 
@@ -306,13 +340,13 @@ class SymmetricBuffers:
         self.handles = [symm_mem.rendezvous(b, group) for b in (self.x_in, self.dy_in, self.y_ret, self.dx_ret)]
         ptrs = lambda h: torch.tensor(list(h.buffer_ptrs), dtype=torch.int64, device=device)
         self.peer_x_in, self.peer_dy_in, self.peer_y_ret, self.peer_dx_ret = (ptrs(h) for h in self.handles)
-        self.sync_word = torch.zeros(1, dtype=torch.int32, device=device)
+        self._barrier = _FlagBarrier(group, device)
         self.side = torch.cuda.Stream(device=device)   # the exchange kernels run here, beside independent GEMMs
 
-    def barrier(self, group):
-        """Stream-ordered barrier across the ranks: a collective on one word.  Every kernel queued before it on any
-        rank has completed (its peer stores included) before any kernel queued after it starts."""
-        dist.all_reduce(self.sync_word, group=group)
+    def barrier(self, group, status=None):
+        """Stream-ordered barrier across the ranks.  Every kernel queued before it on any rank has completed (its peer
+        stores included) before any kernel queued after it starts."""
+        self._barrier(status)
 
 
 class ExpertParallelP2P(torch.autograd.Function):
@@ -388,7 +422,7 @@ class ExpertParallelP2P(torch.autograd.Function):
         act_cat = torch.empty(T, L + Fs, **bf)
         _cabi.call("lmoe_shared_gateup_fwd", shape, ptr(xb), ptr(wgus), ptr(h1_s), ptr(act_cat), ptr(status), st)
         main.wait_event(sent)
-        bufs.barrier(group)                                   # all rows have landed in x_in
+        bufs.barrier(group, status)                                   # all rows have landed in x_in
 
         h1 = torch.empty(P, 2 * F, **bf)
         hidden = torch.empty(P, F, **bf)
@@ -397,7 +431,7 @@ class ExpertParallelP2P(torch.autograd.Function):
                    ptr(h1), ptr(hidden), ptr(y_sorted), ptr(status), st)
         _cabi.call("lmoe_ep_return", ptr(y_sorted), ptr(tile_expert), ptr(n_tiles), ptr(pad_offsets), ptr(seg_cum),
                    ptr(src_off), ptr(counts_all), G, E, rank, L, P, ptr(bufs.peer_y_ret), st)
-        bufs.barrier(group)                                   # all results have landed in y_ret
+        bufs.barrier(group, status)                                   # all results have landed in y_ret
 
         y = torch.empty(T, D, **bf)
         back_route = Route(counts=ptr(route.counts), offsets=ptr(route.offsets), perm=ptr(route.perm),
@@ -463,7 +497,7 @@ class ExpertParallelP2P(torch.autograd.Function):
         _cabi.call("lmoe_combine_out_bwd_wgrad", shape, ptr(dyb), ptr(act_cat), ptr(d_w_up), ptr(d_w_down_s), gtype,
                    ptr(ws), ws.numel(), ptr(status), st)
         main.wait_event(sent)
-        bufs.barrier(group)                                   # all gradient rows have landed in dy_in
+        bufs.barrier(group, status)                                   # all gradient rows have landed in dy_in
 
         d_h1 = torch.empty(P, 2 * F, **bf)
         d_x_sorted = torch.empty(P, L, **bf)
@@ -483,7 +517,7 @@ class ExpertParallelP2P(torch.autograd.Function):
         _cabi.call("lmoe_grouped_bwd_wgrad", P, El, L, F, ptr(bufs.x_in), ptr(d_h1), ptr(hidden), ptr(bufs.dy_in),
                    ptr(pad_offsets), ptr(d_w_gate_up), ptr(d_w_down_e), ptr(status), st)
         main.wait_event(returned)
-        bufs.barrier(group)                                   # all rows have landed in dx_ret
+        bufs.barrier(group, status)                                   # all rows have landed in dx_ret
 
         d_x_latent = dgrad_cat[:, 2 * Fs:]
         _cabi.call("lmoe_combine_rows", ptr(bufs.dx_ret), ptr(inv), None, T, K, L, ptr(d_x_latent), 2 * Fs + L + E, st)
@@ -548,12 +582,12 @@ class DedupBuffers:
         ptrs = lambda h: torch.tensor(list(h.buffer_ptrs), dtype=torch.int64, device=device)
         (self.peer_stage_x, self.peer_stage_dy, self.peer_ret_y, self.peer_ret_dx, self.peer_meta, self.peer_mask,
          self.peer_slots, self.peer_dw) = (ptrs(h) for h in self.handles)
-        self.sync_word = torch.zeros(1, dtype=torch.int32, device=device)
+        self._barrier = _FlagBarrier(group, device)
         self.side = torch.cuda.Stream(device=device)
 
-    def barrier(self, group):
-        """Stream-ordered barrier across the ranks (a collective on one word)."""
-        dist.all_reduce(self.sync_word, group=group)
+    def barrier(self, group, status=None):
+        """Stream-ordered barrier across the ranks (flag words in symmetric memory, ``_FlagBarrier``)."""
+        self._barrier(status)
 
 
 class ExpertParallelDedup(torch.autograd.Function):
@@ -632,7 +666,7 @@ class ExpertParallelDedup(torch.autograd.Function):
         sent = torch.cuda.Event()
         sent.record(side)
         main.wait_event(sent)
-        bufs.barrier(group)                                   # all rows and routing words have landed
+        bufs.barrier(group, status)                                   # all rows and routing words have landed
 
         x_in = torch.empty(P, L, **bf)
         _cabi.call("lmoe_epd_gather", ptr(bufs.stage_x), ptr(bufs.meta), ptr(tile_expert), ptr(n_tiles), ptr(pad_offsets),
@@ -644,7 +678,7 @@ class ExpertParallelDedup(torch.autograd.Function):
                    ptr(h1), ptr(hidden), ptr(y_sorted), ptr(status), st)
         _cabi.call("lmoe_epd_reduce_return", ptr(y_sorted), ptr(bufs.meta), ptr(bufs.mask), ptr(bufs.slots), None,
                    ptr(src_off), ptr(counts_all), G, E, rank, K, L, stride, P, ptr(bufs.peer_ret_y), None, st)
-        bufs.barrier(group)                                   # all partial sums have landed in ret_y
+        bufs.barrier(group, status)                                   # all partial sums have landed in ret_y
 
         _cabi.call("lmoe_epd_sum", ptr(bufs.ret_y), ptr(sel), T, K, E, G, L, stride, ptr(act_cat), L + Fs, st)
         y = torch.empty(T, D, **bf)
@@ -703,7 +737,7 @@ class ExpertParallelDedup(torch.autograd.Function):
         _cabi.call("lmoe_combine_out_bwd_wgrad", shape, ptr(dyb), ptr(act_cat), ptr(d_w_up), ptr(d_w_down_s), gtype,
                    ptr(ws), ws.numel(), ptr(status), st)
         main.wait_event(sent)
-        bufs.barrier(group)                                   # all gradient rows have landed in stage_dy
+        bufs.barrier(group, status)                                   # all gradient rows have landed in stage_dy
 
         # adjoint of the weighted combine on the owner: d_y rows and the gating gradients of its rows
         dy_in = torch.empty(P, L, **bf)
@@ -730,7 +764,7 @@ class ExpertParallelDedup(torch.autograd.Function):
         _cabi.call("lmoe_grouped_bwd_wgrad", P, El, L, F, ptr(x_in), ptr(d_h1), ptr(hidden), ptr(dy_in),
                    ptr(pad_offsets), ptr(d_w_gate_up), ptr(d_w_down_e), ptr(status), st)
         main.wait_event(returned)
-        bufs.barrier(group)                                   # partial sums in ret_dx, gating gradients in dw
+        bufs.barrier(group, status)                                   # partial sums in ret_dx, gating gradients in dw
 
         d_x_latent = dgrad_cat[:, 2 * Fs:]
         _cabi.call("lmoe_epd_sum", ptr(bufs.ret_dx), ptr(sel), T, K, E, G, L, stride, ptr(d_x_latent), 2 * Fs + L + E, st)

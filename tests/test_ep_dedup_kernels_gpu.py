@@ -237,3 +237,31 @@ def test_shard_overflow_raises_status_201_and_drops_rows_without_faulting():
     with pytest.raises(_cabi.LmoeError, match="201"):
         status_monitor.poll(block=True)
     assert status_monitor.pending() == 0
+
+
+@pytest.mark.gpu
+def test_flag_barrier_passes_when_every_peer_has_arrived_and_reports_a_missing_one():
+    """``lmoe_ep_flag_barrier`` with two ranks whose flag words live on this one GPU.  Only rank 0's kernel ever runs (two
+    kernels that wait for each other must not be separate launches on one GPU): first with rank 1's arrival written
+    by hand, which must pass at once and leave rank 0's own arrival in rank 1's word; then with an epoch nobody
+    announces, where the bounded wait must give up with status 202 and leave the context usable."""
+    import time
+    from swamla_b200 import _cabi
+    dev = torch.device("cuda:0")
+    st = torch.cuda.current_stream().cuda_stream
+    flags = [torch.zeros(32, dtype=torch.int32, device=dev) for _ in range(2)]
+    peers = torch.tensor([f.data_ptr() for f in flags], dtype=torch.int64, device=dev)
+    status = torch.zeros(1, dtype=torch.int32, device=dev)
+    flags[0][1] = 1                                            # "rank 1 has reached barrier 1"
+    _cabi.call("lmoe_ep_flag_barrier", peers.data_ptr(), 0, 2, 1, status.data_ptr(), st)
+    torch.cuda.synchronize()
+    assert status.item() == 0
+    assert flags[1][0].item() == 1 and flags[0][0].item() == 1  # rank 0 told rank 1 and itself
+    t0 = time.time()
+    _cabi.call("lmoe_ep_flag_barrier", peers.data_ptr(), 0, 2, 2, status.data_ptr(), st)   # rank 1 never arrives
+    torch.cuda.synchronize()
+    assert status.item() == 202
+    assert time.time() - t0 < 10.0
+    assert flags[1][0].item() == 2
+    # the context is intact: an ordinary kernel still runs
+    assert torch.ones(8, device=dev).sum().item() == 8.0
