@@ -376,11 +376,12 @@ int lmoe_epd_sum(const void* ret, const int32_t* sel, int64_t T, int K, int E, i
                  int64_t ld_out, void* stream);
 
 /* Barrier across the G ranks of an expert-parallel group without a collective library call: peer_flags[g] points at rank
- * g's int32 flags[G] in symmetric memory (zeroed once, before the first barrier), epoch counts the barriers (same
- * sequence on every rank, starting at 1).  Stream-ordered like any kernel.  A rank that waits longer than about two
- * seconds records status 202 and carries on.  Replaces the one-word all-reduce the exchange used as a barrier (the
- * reference has no counterpart: its expert parallelism is pseudo-code, aidocs/moe.md:940-997). */
-int lmoe_ep_flag_barrier(void* const* peer_flags, int rank, int G, int epoch, int32_t* status, void* stream);
+ * g's int32 flags[G] in symmetric memory, epoch_counter at an int32 in this rank's own memory (both zeroed once, before
+ * the first barrier; the kernel increments the counter, so the call may sit in a replayed CUDA graph; every rank must run
+ * the same sequence of barriers).  Stream-ordered like any kernel.  A rank that waits longer than about two seconds
+ * records status 202 and carries on.  Replaces the one-word all-reduce the exchange used as a barrier (the reference has
+ * no counterpart: its expert parallelism is pseudo-code, aidocs/moe.md:940-997). */
+int lmoe_ep_flag_barrier(void* const* peer_flags, int32_t* epoch_counter, int rank, int G, int32_t* status, void* stream);
 
 /* ---- FP8 (e4m3) expert path ----
  * Per-tensor dynamic scaling, the "tensorwise" recipe named by optimization/fp8_native.py:103-110 (torchao

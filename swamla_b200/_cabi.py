@@ -93,7 +93,7 @@ SIGNATURES = {
     "lmoe_epd_reduce_return": (c_int, [P, P, P, P, P, P, P, c_int, c_int, c_int, c_int, c_int, c_int64, c_int64, P, P,
                                         P]),
     "lmoe_epd_sum": (c_int, [P, P, c_int64, c_int, c_int, c_int, c_int, c_int64, P, c_int64, P]),
-    "lmoe_ep_flag_barrier": (c_int, [P, c_int, c_int, c_int, P, P]),
+    "lmoe_ep_flag_barrier": (c_int, [P, P, c_int, c_int, P, P]),
     "lmoe_fp8_quantize": (c_int, [P, c_int64, c_int, P, P, P, P, P]),
     "lmoe_gemm_fp8": (c_int, [c_int, c_int, c_int, P, c_int64, c_int, P, c_int64, c_int, P, P, P, c_int64, P, P]),
     "lmoe_grouped_gateup_fp8": (c_int, [c_int64, c_int, c_int, c_int, P, P, P, P, P, P, P, P, P, P]),

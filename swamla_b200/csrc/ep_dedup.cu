@@ -412,15 +412,24 @@ extern "C" int lmoe_epd_sum(const void* ret, const int32_t* sel, int64_t T, int 
 }
 
 // ---------------------------------------------------------------- barrier across the ranks on flag words
-// Every rank owns int32 flags[G] in symmetric memory; word s is written by rank s only.  One warp: thread j stores this
-// step's epoch into rank j's word for this rank (system-scope release), then waits until rank j's epoch has arrived in
-// this rank's word j (system-scope acquire).  Stream order puts the exchange kernels queued before it in front of the
-// stores, and what is queued after it behind the loads.  The wait is bounded (about two seconds): on expiry the
-// kernel records status 202 and returns, so a rank that never arrives ends a step with an error instead of a hang.
+// Every rank owns int32 flags[G] in symmetric memory; word s is written by rank s only.  The barrier's number comes from
+// a counter in this rank's own memory that the kernel increments (every rank runs the same sequence of barriers, so
+// the counters agree; a counter on the device keeps the kernel valid inside a replayed CUDA graph).  One warp: thread j
+// stores the number into rank j's word for this rank (system-scope release), then waits until rank j's number has
+// arrived in this rank's word j (system-scope acquire).  Stream order puts the exchange kernels queued before it in
+// front of the stores, and what is queued after it behind the loads.  The wait is bounded (about two seconds): on
+// expiry the kernel records status 202 and returns, so a rank that never arrives ends a step with an error instead of a
+// hang.
 constexpr long long kEpdBarrierBudgetCycles = 4000000000LL;
-__global__ void __launch_bounds__(32) epd_flag_barrier_kernel(int* const* peer_flags, int rank, int G, int epoch,
+__global__ void __launch_bounds__(32) epd_flag_barrier_kernel(int* const* peer_flags, int* epoch_counter, int rank, int G,
                                                               int* status) {
   const int j = threadIdx.x;
+  int epoch = 0;
+  if (j == 0) {
+    epoch = *epoch_counter + 1;
+    *epoch_counter = epoch;
+  }
+  epoch = __shfl_sync(0xffffffffu, epoch, 0);
   if (j >= G) return;
   __threadfence_system();
   asm volatile("st.release.sys.global.s32 [%0], %1;" ::"l"(peer_flags[j] + rank), "r"(epoch) : "memory");
@@ -437,10 +446,10 @@ __global__ void __launch_bounds__(32) epd_flag_barrier_kernel(int* const* peer_f
   }
 }
 
-extern "C" int lmoe_ep_flag_barrier(void* const* peer_flags, int rank, int G, int epoch, int32_t* status, void* stream) {
-  if (!peer_flags || G < 1 || G > 32 || rank < 0 || rank >= G) return LMOE_ERR_ARG;
-  epd_flag_barrier_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>(reinterpret_cast<int* const*>(peer_flags), rank,
-                                                                           G, epoch, status);
+extern "C" int lmoe_ep_flag_barrier(void* const* peer_flags, int32_t* epoch_counter, int rank, int G, int32_t* status,
+                                    void* stream) {
+  if (!peer_flags || !epoch_counter || G < 1 || G > 32 || rank < 0 || rank >= G) return LMOE_ERR_ARG;
+  epd_flag_barrier_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>(reinterpret_cast<int* const*>(peer_flags),
+                                                                           epoch_counter, rank, G, status);
   return epd_last_err();
 }
-

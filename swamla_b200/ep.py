@@ -297,13 +297,13 @@ class _FlagBarrier:
         self.rank = dist.get_rank(group)
         self.use_flags = os.environ.get("LMOE_EP_FLAG_BARRIER", "1") != "0"
         self.sync_word = torch.zeros(1, dtype=torch.int32, device=device)
-        self.epoch = 0
         if self.use_flags:
             self.flags = symm_mem.empty(32, dtype=torch.int32, device=device)
             self.flags.zero_()
             self.handle = symm_mem.rendezvous(self.flags, group)
             self.peer_flags = torch.tensor(list(self.handle.buffer_ptrs), dtype=torch.int64, device=device)
             self.status = torch.zeros(1, dtype=torch.int32, device=device)
+            self.epoch = torch.zeros(1, dtype=torch.int32, device=device)   # barriers so far; the kernel counts
             torch.cuda.synchronize(device)
             dist.all_reduce(self.sync_word, group=group)     # every rank's flags are zero before anyone's first barrier
             torch.cuda.synchronize(device)
@@ -312,10 +312,9 @@ class _FlagBarrier:
         if not self.use_flags:
             dist.all_reduce(self.sync_word, group=self.group)
             return
-        self.epoch += 1
         st = status if status is not None else self.status
-        _cabi.call("lmoe_ep_flag_barrier", self.peer_flags.data_ptr(), self.rank, self.G, self.epoch, st.data_ptr(),
-                   _stream())
+        _cabi.call("lmoe_ep_flag_barrier", self.peer_flags.data_ptr(), self.epoch.data_ptr(), self.rank, self.G,
+                   st.data_ptr(), _stream())
 
 
 class SymmetricBuffers:

@@ -252,16 +252,17 @@ def test_flag_barrier_passes_when_every_peer_has_arrived_and_reports_a_missing_o
     flags = [torch.zeros(32, dtype=torch.int32, device=dev) for _ in range(2)]
     peers = torch.tensor([f.data_ptr() for f in flags], dtype=torch.int64, device=dev)
     status = torch.zeros(1, dtype=torch.int32, device=dev)
+    epoch = torch.zeros(1, dtype=torch.int32, device=dev)      # rank 0's barrier counter
     flags[0][1] = 1                                            # "rank 1 has reached barrier 1"
-    _cabi.call("lmoe_ep_flag_barrier", peers.data_ptr(), 0, 2, 1, status.data_ptr(), st)
+    _cabi.call("lmoe_ep_flag_barrier", peers.data_ptr(), epoch.data_ptr(), 0, 2, status.data_ptr(), st)
     torch.cuda.synchronize()
     assert status.item() == 0
     assert flags[1][0].item() == 1 and flags[0][0].item() == 1  # rank 0 told rank 1 and itself
     t0 = time.time()
-    _cabi.call("lmoe_ep_flag_barrier", peers.data_ptr(), 0, 2, 2, status.data_ptr(), st)   # rank 1 never arrives
+    _cabi.call("lmoe_ep_flag_barrier", peers.data_ptr(), epoch.data_ptr(), 0, 2, status.data_ptr(), st)   # rank 1 never arrives
     torch.cuda.synchronize()
     assert status.item() == 202
     assert time.time() - t0 < 10.0
-    assert flags[1][0].item() == 2
+    assert flags[1][0].item() == 2 and epoch.item() == 2
     # the context is intact: an ordinary kernel still runs
     assert torch.ones(8, device=dev).sum().item() == 8.0
