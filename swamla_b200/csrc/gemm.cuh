@@ -88,7 +88,11 @@ struct GemmSmem {
   static constexpr int kStageBytes = kABytes + kBBytes;
   // one slab = 128 rows x 32 columns: 8 KB in bf16 (64-byte rows), 16 KB in fp32 (128-byte rows)
   static constexpr int kSlabBytes = (EPI == EPI_F32) ? 16384 : 8192;
-  static constexpr int kStreams = (EPI == EPI_SWIGLU) ? 3 : (EPI == EPI_SWIGLU_BWD ? 2 : 1);  // gate, up, hidden
+  // SwiGLU with 256-wide tiles: the hidden slab is staged in the gate slab's buffer once the gate store has read it, so
+  // that two slabs per group are enough and the operand ring gets a fourth 48 KB stage (bytes in flight are what
+  // these kernels are short of; measured 5 us per GEMM and stage)
+  static constexpr bool kHiddenReusesGate = (EPI == EPI_SWIGLU && BN == 256);
+  static constexpr int kStreams = (EPI == EPI_SWIGLU) ? (kHiddenReusesGate ? 2 : 3) : (EPI == EPI_SWIGLU_BWD ? 2 : 1);
   // staging buffers per epilogue group: two for the plain bf16 epilogue (its slabs are cheap to produce, so the
   // read latency of the previous TMA store would otherwise be exposed on every slab) and for the adjoint epilogue of
   // the grouped GEMM (four k-blocks per tile: three stages are enough, the second buffer gains 3 %); one for the
@@ -608,11 +612,28 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_kernel(const __grid_cons
         } else {
           stage_row_bf16(sbuf, r, pk);
           stage_row_bf16(sbuf + S::kSlabBytes, r, pu);
-          stage_row_bf16(sbuf + 2 * S::kSlabBytes, r, ph);
+          if (!S::kHiddenReusesGate) stage_row_bf16(sbuf + 2 * S::kSlabBytes, r, ph);
         }
         fence_proxy_async_smem();
         epi_bar_sync(bar_id);
-        if (issuer) {
+        if (kSwiglu && S::kHiddenReusesGate) {
+          const int col = n0 + c * kSlabCols;
+          if (issuer) {
+            tma_store_3d(&p.tmC, sbuf, col, t.m0, 0);
+            tma_store_commit();
+            tma_store_3d(&p.tmC, sbuf + S::kSlabBytes, p.half + col, t.m0, 0);
+            tma_store_commit();
+            tma_store_wait_read_1();   // the gate store (all but the latest group) has read its slab
+          }
+          epi_bar_sync(bar_id);
+          stage_row_bf16(sbuf, r, ph);
+          fence_proxy_async_smem();
+          epi_bar_sync(bar_id);
+          if (issuer) {
+            tma_store_3d(&p.tmC2, sbuf, col, t.m0, 0);
+            tma_store_commit();
+          }
+        } else if (issuer) {
           const int col = n0 + c * kSlabCols;
           if (kSwiglu) {
             tma_store_3d(&p.tmC, sbuf, col, t.m0, 0);
