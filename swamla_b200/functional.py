@@ -144,9 +144,12 @@ class LatentMoEFunction(torch.autograd.Function):
 
         # router + latent down-projection
         logits = torch.empty(T, E, **f32)
-        # one extra row of zeros after the T latent rows: the pad rows of the routed layout gather it
+        # one extra row after the T latent rows: zeros that the pad rows of the routed layout read when the gather runs
+        # inside the GEMM's TMA producer
         x_latent_ext = torch.empty(T + 1, L, **bf)
-        x_latent_ext[T].zero_()
+        gather = TMA_GATHER and not fp8 and L % 128 == 0   # whole 128-column tiles of the weight gradient
+        if gather:
+            x_latent_ext[T].zero_()     # (the gather kernel of the default path writes the pad rows' zeros itself)
         x_latent = x_latent_ext[:T]
         _cabi.call("lmoe_xproj_fwd", shape, ptr(xb), ptr(wg), ptr(wdn), ptr(logits), ptr(x_latent), ptr(status), st)
         sel = torch.empty(T, top_k, dtype=torch.int32, device=dev)
@@ -157,7 +160,6 @@ class LatentMoEFunction(torch.autograd.Function):
         route = RouteTables(shape, dev)
         P = route.padded_rows
         ws = torch.empty(max(16, lib.lmoe_route_workspace_bytes(shape)), dtype=torch.uint8, device=dev)
-        gather = TMA_GATHER and not fp8 and L % 128 == 0   # whole 128-column tiles of the weight gradient
         x_sorted = None if (gather and not _testing.capturing()) else torch.empty(P, L, **bf)
         h1_s = torch.empty(T, 2 * Fs, **bf)
         act_cat = torch.empty(T, L + Fs, **bf)
